@@ -1,0 +1,105 @@
+// Fused residual add + RMSNorm.
+//
+// For each output row r (source row s = rows ? rows[r] : r):
+//     x   = resid[s, :] + sum_k delta[k, s, :]      (32-bit, k ascending)
+//     if write_resid: resid[s, :] = x
+//     out[r, :] = (x * (1 / sqrt(mean(x^2) + eps))) * gain
+// The residual stream is always 32-bit; `delta` is the previous part's output
+// in the activation type (or 32-bit split-K partial sums, delta_splits > 1);
+// `out` is in the activation type. The formula and its order are the
+// reference's (backends/cpu/src/backend.rs:172-193: mean square :185-186,
+// inverse :187, scale :189; the residual add is crates/quantinfer-runtime/src/linear.rs:129-142).
+#include "common.cuh"
+
+namespace {
+
+template <typename TD, typename TO>
+__global__ void add_rmsnorm_kernel(float* __restrict__ resid, const TD* __restrict__ delta,
+                                   int delta_splits, size_t delta_split_stride,
+                                   const float* __restrict__ gain, float eps,
+                                   TO* __restrict__ out, const int* __restrict__ rows, int hidden,
+                                   int write_resid) {
+    __shared__ float scratch[32];
+    const int r = blockIdx.x;
+    const int s = rows ? rows[r] : r;
+    float* xr = resid + (size_t)s * hidden;
+    const TD* dr = delta ? delta + (size_t)s * hidden : nullptr;
+
+    float sumsq = 0.f;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+        float x = xr[i];
+        if (dr) {
+            for (int k = 0; k < delta_splits; ++k) x += qi::to_f32<TD>(dr[k * delta_split_stride + i]);
+        }
+        if (write_resid) xr[i] = x;
+        sumsq += x * x;
+    }
+    const float total = qi::block_sum(sumsq, scratch);
+    const float inv = 1.0f / sqrtf(total / (float)hidden + eps);
+    TO* orow = out + (size_t)r * hidden;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+        float x = xr[i];  // same thread wrote it in the first pass when write_resid
+        if (dr && !write_resid) {
+            for (int k = 0; k < delta_splits; ++k) x += qi::to_f32<TD>(dr[k * delta_split_stride + i]);
+        }
+        orow[i] = qi::from_f32<TO>(x * inv * gain[i]);
+    }
+}
+
+// Plain RMSNorm over the last dimension of a [rows, width] matrix of type T,
+// used by tests of the norm alone and by parts that normalise activations.
+template <typename T>
+__global__ void rmsnorm_kernel(const T* __restrict__ x, const float* __restrict__ gain, float eps,
+                               T* __restrict__ out, int width) {
+    __shared__ float scratch[32];
+    const T* xr = x + (size_t)blockIdx.x * width;
+    float sumsq = 0.f;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) {
+        const float v = qi::to_f32<T>(xr[i]);
+        sumsq += v * v;
+    }
+    const float total = qi::block_sum(sumsq, scratch);
+    const float inv = 1.0f / sqrtf(total / (float)width + eps);
+    T* orow = out + (size_t)blockIdx.x * width;
+    for (int i = threadIdx.x; i < width; i += blockDim.x)
+        orow[i] = qi::from_f32<T>(qi::to_f32<T>(xr[i]) * inv * gain[i]);
+}
+
+int pick_threads(int hidden) { return hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : (hidden >= 128 ? 128 : 32)); }
+
+}  // namespace
+
+// delta may be null (no add). rows may be null (identity; n_rows rows).
+// With rows given, write_resid must be 0 (the gather variant feeds the head).
+extern "C" int qi_add_rmsnorm(float* resid, const void* delta, int delta_dtype, int delta_splits,
+                              long long delta_split_stride, const float* gain, float eps,
+                              void* out, int out_dtype, const int* rows, int n_rows, int hidden,
+                              int write_resid, cudaStream_t stream) {
+    QI_REQUIRE(n_rows >= 0 && hidden > 0, "add_rmsnorm: bad sizes rows=%d hidden=%d", n_rows, hidden);
+    QI_REQUIRE(!(rows && write_resid), "add_rmsnorm: the row-gather form does not write the residual");
+    QI_REQUIRE(delta_splits >= 1, "add_rmsnorm: delta_splits must be >= 1");
+    QI_REQUIRE(eps > 0.f, "add_rmsnorm: eps must be positive");
+    if (n_rows == 0) return 0;
+    const int threads = pick_threads(hidden);
+    const int dd = delta ? delta_dtype : qi::kF32;
+    QI_DISPATCH_DTYPE(dd, TD, {
+        QI_DISPATCH_DTYPE(out_dtype, TO, {
+            add_rmsnorm_kernel<TD, TO><<<n_rows, threads, 0, stream>>>(
+                resid, (const TD*)delta, delta_splits, (size_t)delta_split_stride, gain, eps,
+                (TO*)out, rows, hidden, write_resid);
+        });
+    });
+    return qi::check_launch("add_rmsnorm");
+}
+
+extern "C" int qi_rmsnorm(const void* x, const float* gain, float eps, void* out, int dtype,
+                          int n_rows, int width, cudaStream_t stream) {
+    QI_REQUIRE(n_rows >= 0 && width > 0, "rmsnorm: bad sizes rows=%d width=%d", n_rows, width);
+    QI_REQUIRE(eps > 0.f, "rmsnorm: eps must be positive");
+    if (n_rows == 0) return 0;
+    const int threads = pick_threads(width);
+    QI_DISPATCH_DTYPE(dtype, T, {
+        rmsnorm_kernel<T><<<n_rows, threads, 0, stream>>>((const T*)x, gain, eps, (T*)out, width);
+    });
+    return qi::check_launch("rmsnorm");
+}

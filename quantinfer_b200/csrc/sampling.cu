@@ -1,0 +1,317 @@
+// Token selection from 32-bit logits [rows, vocab], one block per row.
+//
+// temperature == 0: the first maximum (strict >, lowest index wins ties), as
+// the reference's argmax (crates/quantinfer-runtime/src/generation.rs:58-77).
+// Otherwise the reference's candidate rule (generation.rs:104-154): scale by
+// 1/temperature, keep the top_k largest (ties: lowest index first, which is
+// what its stable descending sort keeps), then the shortest prefix of the
+// descending order whose mass reaches top_p of the kept mass, then draw from
+// what is left. Two things differ from the reference on purpose. Its draw is a
+// hash of the logits that never advances with the seed (generation.rs:219-230);
+// here the uniform comes from Philox-4x32-10 keyed by the request's seed with
+// the number of tokens already emitted as counter, so a request's samples do
+// not depend on the batch it is in. And the inverse CDF runs over the kept
+// candidates in index order, which needs no sort.
+//
+// Arithmetic: y = logit / temperature and w = exp(y - max y) in 32-bit; every
+// sum of weights in 64-bit, warp by warp in index order.
+#include "common.cuh"
+
+#include <math.h>
+
+namespace {
+
+constexpr int kThreads = 1024;
+constexpr int kNumWarps = kThreads / 32;
+
+__device__ __forceinline__ uint32_t order_key(float v) {
+    const uint32_t b = __float_as_uint(v);
+    return (b & 0x80000000u) ? ~b : (b | 0x80000000u);
+}
+
+// Inverse of order_key.
+__device__ __forceinline__ float key_value(uint32_t key) {
+    return __uint_as_float((key & 0x80000000u) ? (key & 0x7fffffffu) : ~key);
+}
+
+__device__ __forceinline__ uint4 philox4x32_10(uint4 c, uint2 k) {
+    const uint32_t M0 = 0xD2511F53u, M1 = 0xCD9E8D57u, W0 = 0x9E3779B9u, W1 = 0xBB67AE85u;
+#pragma unroll
+    for (int round = 0; round < 10; ++round) {
+        if (round > 0) {
+            k.x += W0;
+            k.y += W1;
+        }
+        const uint32_t hi0 = __umulhi(M0, c.x), lo0 = M0 * c.x;
+        const uint32_t hi1 = __umulhi(M1, c.z), lo1 = M1 * c.z;
+        c = make_uint4(hi1 ^ c.y ^ k.x, lo1, hi0 ^ c.w ^ k.y, lo0);
+    }
+    return c;
+}
+
+__device__ __forceinline__ double warp_sum_d(double v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+// Block sums in a fixed order; every thread gets the result.
+__device__ double block_sum_d(double v, double* scratch) {
+    v = warp_sum_d(v);
+    __syncthreads();
+    if ((threadIdx.x & 31) == 0) scratch[threadIdx.x >> 5] = v;
+    __syncthreads();
+    double t = 0.0;
+    for (int w = 0; w < kNumWarps; ++w) t += scratch[w];
+    return t;
+}
+
+__device__ long long block_sum_ll(long long v, long long* scratch) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    __syncthreads();
+    if ((threadIdx.x & 31) == 0) scratch[threadIdx.x >> 5] = v;
+    __syncthreads();
+    long long t = 0;
+    for (int w = 0; w < kNumWarps; ++w) t += scratch[w];
+    return t;
+}
+
+__global__ void __launch_bounds__(kThreads)
+sample_kernel(const float* __restrict__ logits, int vocab, const float* __restrict__ temperature,
+              const int* __restrict__ top_k, const float* __restrict__ top_p,
+              const long long* __restrict__ seed, const int* __restrict__ counter,
+              int* __restrict__ out_token, int* __restrict__ status) {
+    __shared__ double sd[kNumWarps];
+    __shared__ long long sl[kNumWarps];
+    __shared__ float sbest_v[kNumWarps];
+    __shared__ int sbest_i[kNumWarps];
+    __shared__ double warp_mass[kNumWarps];
+    __shared__ long long warp_eq[kNumWarps];
+    __shared__ int result;
+
+    const int row = blockIdx.x;
+    const float* x = logits + (size_t)row * vocab;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+
+    // Pass 0: first maximum and a finiteness check.
+    float bv = -INFINITY;
+    int bi = 0x7fffffff;
+    bool nonfinite = false;
+    for (int i = tid; i < vocab; i += kThreads) {
+        const float v = x[i];
+        if (!isfinite(v)) nonfinite = true;
+        if (v > bv || bi == 0x7fffffff) { bv = v; bi = i; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+    }
+    if (lane == 0) { sbest_v[warp] = bv; sbest_i[warp] = bi; }
+    if (nonfinite && status) atomicOr(status, qi::kStatusNonFinite);
+    __syncthreads();
+    float max_v = sbest_v[0];
+    int max_i = sbest_i[0];
+    for (int w = 1; w < kNumWarps; ++w) {
+        if (sbest_v[w] > max_v || (sbest_v[w] == max_v && sbest_i[w] < max_i)) {
+            max_v = sbest_v[w];
+            max_i = sbest_i[w];
+        }
+    }
+    const float temp = temperature ? temperature[row] : 0.f;
+    if (!(temp > 0.f)) {
+        if (tid == 0) out_token[row] = max_i;
+        return;
+    }
+
+    const float max_y = max_v / temp;
+    int k = top_k ? top_k[row] : 0;
+    if (k <= 0 || k > vocab) k = 0;  // 0: keep all
+    float p_keep = top_p ? top_p[row] : 0.f;
+    if (!(p_keep > 0.f) || p_keep >= 1.f) p_keep = 0.f;  // 0: keep all
+
+    // Threshold of the kept set: every y > thr_key is kept, and the first
+    // n_eq (by index) of those equal to it. thr_key = 0 keeps everything.
+    uint32_t thr_key = 0;
+    long long n_eq = (long long)vocab + 1;
+
+    if (k > 0) {
+        uint32_t t = 0;
+        for (int bit = 31; bit >= 0; --bit) {
+            const uint32_t cand = t | (1u << bit);
+            long long c = 0;
+            for (int i = tid; i < vocab; i += kThreads) c += order_key(x[i] / temp) >= cand;
+            if (block_sum_ll(c, sl) >= k) t = cand;
+        }
+        long long gt = 0;
+        for (int i = tid; i < vocab; i += kThreads) gt += order_key(x[i] / temp) > t;
+        gt = block_sum_ll(gt, sl);
+        thr_key = t;
+        n_eq = k - gt;
+    }
+
+    // Mass of the kept set after top-k: everything above the threshold, plus
+    // n_eq times the weight of the threshold value itself.
+    double total;
+    {
+        double s = 0.0;
+        for (int i = tid; i < vocab; i += kThreads) {
+            const float y = x[i] / temp;
+            if (order_key(y) > thr_key) s += (double)expf(y - max_y);
+        }
+        total = block_sum_d(s, sd);
+        if (thr_key != 0) total += (double)n_eq * (double)expf(key_value(thr_key) - max_y);
+    }
+
+    if (p_keep > 0.f) {
+        const double need = (double)p_keep * total;
+        // Largest t with mass(kept, key >= t) >= need.
+        uint32_t t = 0;
+        for (int bit = 31; bit >= 0; --bit) {
+            const uint32_t cand = t | (1u << bit);
+            double mass;
+            if (cand <= thr_key) {
+                mass = total;  // everything kept by top-k lies at or above the candidate
+            } else {
+                double s = 0.0;
+                for (int i = tid; i < vocab; i += kThreads) {
+                    const float y = x[i] / temp;
+                    if (order_key(y) >= cand) s += (double)expf(y - max_y);
+                }
+                mass = block_sum_d(s, sd);
+            }
+            if (mass >= need) t = cand;
+        }
+        // Mass strictly above t and the number of equals available.
+        double sgt = 0.0;
+        long long ceq = 0;
+        for (int i = tid; i < vocab; i += kThreads) {
+            const float y = x[i] / temp;
+            const uint32_t key = order_key(y);
+            if (key > t) sgt += (double)expf(y - max_y);
+            ceq += key == t;
+        }
+        sgt = block_sum_d(sgt, sd);
+        ceq = block_sum_ll(ceq, sl);
+        const long long avail = (t == thr_key) ? n_eq : ceq;
+        const double wt = (double)expf(key_value(t) - max_y);
+        long long want = 1;
+        if (wt > 0.0) {
+            const double rest = need - sgt;
+            want = (long long)ceil(rest / wt);
+            if (want < 1) want = 1;
+        }
+        if (want > avail) want = avail;
+        thr_key = t;
+        n_eq = want;
+        total = sgt + (double)want * wt;
+    }
+
+    // Draw.
+    const unsigned long long sd64 = seed ? (unsigned long long)seed[row] : 0ull;
+    const uint32_t ctr = counter ? (uint32_t)counter[row] : 0u;
+    const uint4 rnd = philox4x32_10(make_uint4(ctr, 0u, 0u, 0u),
+                                    make_uint2((uint32_t)sd64, (uint32_t)(sd64 >> 32)));
+    const double target = (double)((float)(rnd.x >> 8) * (1.0f / 16777216.0f)) * total;
+
+    // Ordered passes: each warp owns a contiguous range of indices.
+    int per = (vocab + kNumWarps - 1) / kNumWarps;
+    per = (per + 31) / 32 * 32;
+    const int w_begin = min(vocab, warp * per), w_end = min(vocab, w_begin + per);
+
+    // (1) equals to the threshold per warp -> how many equals precede each warp.
+    {
+        long long c = 0;
+        for (int i = w_begin + lane; i < w_end; i += 32) c += order_key(x[i] / temp) == thr_key;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) c += __shfl_xor_sync(0xffffffffu, c, o);
+        if (lane == 0) warp_eq[warp] = c;
+    }
+    __syncthreads();
+    long long eq_base = 0;
+    for (int w = 0; w < warp; ++w) eq_base += warp_eq[w];
+
+    // (2) kept mass per warp, in index order.
+    double my_mass = 0.0;
+    {
+        long long eq_seen = eq_base;
+        for (int base = w_begin; base < w_end; base += 32) {
+            const int i = base + lane;
+            float y = 0.f;
+            uint32_t key = 0;
+            const bool in = i < w_end;
+            if (in) { y = x[i] / temp; key = order_key(y); }
+            const bool is_eq = in && key == thr_key;
+            const unsigned eq_mask = __ballot_sync(0xffffffffu, is_eq);
+            const long long rank = eq_seen + __popc(eq_mask & ((1u << lane) - 1u));
+            const bool kept = in && (key > thr_key || (is_eq && rank < n_eq));
+            if (kept) my_mass += (double)expf(y - max_y);
+            eq_seen += __popc(eq_mask);
+        }
+        my_mass = warp_sum_d(my_mass);
+        if (lane == 0) warp_mass[warp] = my_mass;
+    }
+    if (tid == 0) result = -1;
+    __syncthreads();
+
+    // (3) the warp whose range holds the target walks it.
+    double mass_before = 0.0;
+    for (int w = 0; w < warp; ++w) mass_before += warp_mass[w];
+    int last_nonempty = -1;
+    for (int w = 0; w < kNumWarps; ++w) if (warp_mass[w] > 0.0) last_nonempty = w;
+    const bool holds = (warp_mass[warp] > 0.0) &&
+                       ((target <= mass_before + warp_mass[warp] && target > mass_before) ||
+                        (target <= mass_before && mass_before == 0.0 && target == 0.0) ||
+                        (warp == last_nonempty && target > mass_before));
+    // More than one warp can satisfy the first test only through rounding; the
+    // lowest index wins below (atomicMin-like selection via ordered check).
+    if (holds) {
+        double cum = mass_before;
+        long long eq_seen = eq_base;
+        int found = -1, last_kept = -1;
+        for (int base = w_begin; base < w_end && found < 0; base += 32) {
+            const int i = base + lane;
+            float y = 0.f;
+            uint32_t key = 0;
+            const bool in = i < w_end;
+            if (in) { y = x[i] / temp; key = order_key(y); }
+            const bool is_eq = in && key == thr_key;
+            const unsigned eq_mask = __ballot_sync(0xffffffffu, is_eq);
+            const long long rank = eq_seen + __popc(eq_mask & ((1u << lane) - 1u));
+            const bool kept = in && (key > thr_key || (is_eq && rank < n_eq));
+            double wv = kept ? (double)expf(y - max_y) : 0.0;
+            // inclusive scan over lanes
+            double inc = wv;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const double n = __shfl_up_sync(0xffffffffu, inc, o);
+                if (lane >= o) inc += n;
+            }
+            const bool hit = kept && (cum + inc >= target);
+            const unsigned hit_mask = __ballot_sync(0xffffffffu, hit);
+            const unsigned kept_mask = __ballot_sync(0xffffffffu, kept);
+            if (kept_mask) last_kept = base + 31 - __clz(kept_mask);
+            if (hit_mask) found = base + __ffs(hit_mask) - 1;
+            cum += __shfl_sync(0xffffffffu, inc, 31);
+            eq_seen += __popc(eq_mask);
+        }
+        if (found < 0) found = last_kept;
+        if (lane == 0 && found >= 0) atomicCAS(&result, -1, found);
+    }
+    __syncthreads();
+    if (tid == 0) out_token[row] = result >= 0 ? result : max_i;
+}
+
+}  // namespace
+
+extern "C" int qi_sample(const float* logits, int rows, int vocab, const float* temperature,
+                         const int* top_k, const float* top_p, const long long* seed,
+                         const int* counter, int* out_token, int* status, cudaStream_t stream) {
+    QI_REQUIRE(rows >= 0 && vocab > 0, "sample: bad sizes rows=%d vocab=%d", rows, vocab);
+    if (rows == 0) return 0;
+    sample_kernel<<<rows, kThreads, 0, stream>>>(logits, vocab, temperature, top_k, top_p, seed,
+                                                 counter, out_token, status);
+    return qi::check_launch("sample");
+}

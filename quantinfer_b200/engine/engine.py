@@ -1,0 +1,190 @@
+"""The engine: a model, its cache manager, and the one step function.
+
+`step(entries)` runs exactly the tokens it is given, as one batch, from the
+cache that earlier steps left, and returns 32-bit logits at the wanted places.
+Everything above it (trace replay, the scheduler, generation) goes through it.
+
+Failure rules follow the reference's mixed batch
+(crates/quantinfer-runtime/src/batch.rs:133-169 per-item checks: empty tokens,
+id outside the vocabulary, over capacity; :223-242 a failed shared pass rolls
+every cache back to where the step began): entries are checked on the host
+before anything is launched, pages are taken for all entries or for none, and
+a device status word that a kernel set (bad page, bad token) turns the step
+into an error after which no request has advanced.
+"""
+
+from __future__ import annotations
+
+from pathlib import Path
+from typing import Sequence
+
+import torch
+
+from .. import kernels
+from ..cache import CacheManager
+from ..config import load_config
+from ..config.spec import ModelSpec
+from ..errors import CacheError, KernelError, QuantInferError
+from ..parts import Runtime
+from ..weights.loader import load_folder
+from .batch import StepBatch, StepEntry, batch_from_packed, pack_batch
+from .model import Model
+
+_DTYPES = {"float32": torch.float32, "fp32": torch.float32, "bfloat16": torch.bfloat16, "bf16": torch.bfloat16,
+           torch.float32: torch.float32, torch.bfloat16: torch.bfloat16}
+
+DEFAULT_PAGE_SIZE = 64
+
+
+def parse_dtype(name) -> torch.dtype:
+    try:
+        return _DTYPES[name]
+    except KeyError:
+        raise QuantInferError(f"unknown dtype {name!r}; use bfloat16 or float32") from None
+
+
+class Engine:
+    def __init__(self, spec: ModelSpec, tensors: dict, *, dtype="bfloat16", device="cuda:0",
+                 page_size: int = DEFAULT_PAGE_SIZE, max_tokens: int | None = None,
+                 num_pages: int | None = None, max_requests: int = 64, max_seq_len: int | None = None,
+                 config=None):
+        """`tensors` are the model's weights by file name (CPU or device tensors).
+
+        The page pool holds `num_pages` pages per layer group, or enough for
+        `max_tokens` cached tokens when each request's count is rounded up to a
+        multiple of 64 (or of the page size, if that is larger)."""
+        if not torch.cuda.is_available():
+            raise KernelError("no CUDA device is visible: the engine runs only on the GPU (there is no CPU path)")
+        kernels.library()  # fail now, loudly, if the kernels cannot be built or loaded
+        self.spec = spec
+        self.config = config
+        self.dtype = parse_dtype(dtype)
+        self.device = torch.device(device)
+        torch.cuda.set_device(self.device)
+        self.runtime = Runtime(self.dtype, self.device)
+        self.model = Model(spec, self.runtime)
+        self.model.load(tensors)
+        self.max_seq_len = min(max_seq_len or spec.max_positions, spec.max_positions)
+        self.page_size = page_size
+        if num_pages is None:
+            if max_tokens is None:
+                max_tokens = self.max_seq_len * min(max_requests, 4)
+            unit = max(64, page_size)
+            num_pages = -(-max_tokens // page_size)
+            if unit % page_size:
+                num_pages += max_requests  # pages that do not divide the rounding unit need slack
+        self.cache = CacheManager(self.model.cache_needs, page_size, num_pages, max_requests,
+                                  self.max_seq_len, self.dtype, self.device)
+        self._views = [self.cache.view(call.cache, call.writes_cache) for call in self.model.order]
+        self._staging = [None, None]
+        self._staging_event = [None, None]
+        self._staging_turn = 0
+        self.steps_run = 0
+
+    # ---- construction ------------------------------------------------------
+
+    @classmethod
+    def from_folder(cls, folder, **kw) -> "Engine":
+        folder = Path(folder)
+        config = load_config(folder)
+        spec = config.to_model_spec()
+        from .model import tensor_needs_of_spec
+
+        tensors = load_folder(folder, tensor_needs_of_spec(spec))
+        return cls(spec, tensors, config=config, **kw)
+
+    # ---- requests ------------------------------------------------------------
+
+    def open(self, request_id):
+        return self.cache.open(request_id)
+
+    def close(self, request_id) -> None:
+        self.cache.close(request_id)
+
+    def length(self, request_id) -> int:
+        return self.cache.get(request_id).length
+
+    # ---- the step --------------------------------------------------------------
+
+    def _check_entries(self, entries: Sequence[StepEntry]) -> None:
+        seen = set()
+        vocab = self.spec.vocab_size
+        for e in entries:
+            if e.request_id in seen:
+                raise QuantInferError(f"request {e.request_id!r} appears twice in one step")
+            seen.add(e.request_id)
+            rc = self.cache.get(e.request_id)
+            n = len(e.tokens)
+            if n == 0:
+                raise QuantInferError(f"request {e.request_id!r}: a step entry needs at least one token")
+            for t in e.tokens:
+                if not 0 <= t < vocab:
+                    raise QuantInferError(f"request {e.request_id!r}: token id {t} is outside the vocabulary of {vocab}")
+            if rc.length + n > self.max_seq_len:
+                raise QuantInferError(
+                    f"request {e.request_id!r}: {rc.length} cached + {n} new tokens exceed the limit of {self.max_seq_len} positions")
+            for w in e.want:
+                if not 0 <= w < n:
+                    raise QuantInferError(f"request {e.request_id!r}: wanted place {w} is outside its {n} tokens")
+
+    def _to_device(self, buf) -> torch.Tensor:
+        turn = self._staging_turn
+        self._staging_turn ^= 1
+        host = self._staging[turn]
+        if host is None or host.numel() < buf.size:
+            host = torch.empty(max(buf.size * 2, 4096), dtype=torch.int32, pin_memory=True)
+            self._staging[turn] = host
+            self._staging_event[turn] = torch.cuda.Event()
+        else:
+            self._staging_event[turn].synchronize()  # the copy that last used this buffer is done
+        host[:buf.size].numpy()[:] = buf
+        dev = host[:buf.size].to(self.device, non_blocking=True)
+        self._staging_event[turn].record()
+        return dev
+
+    def make_batch(self, entries: Sequence[StepEntry]) -> StepBatch:
+        reqs = [self.cache.get(e.request_id) for e in entries]
+        starts = [rc.length for rc in reqs]
+        slots = [rc.slot for rc in reqs]
+        tables = [[rc.tables[g] for rc in reqs] for g in range(len(self.cache.groups))]
+        buf, layout, q_start, lens = pack_batch(entries, starts, slots, tables, self.cache.max_blocks)
+        dev = self._to_device(buf)
+        return batch_from_packed(dev, layout, entries, starts, slots, q_start, lens,
+                                 len(self.cache.groups), self.cache.max_blocks)
+
+    def step(self, entries: Sequence[StepEntry], check_status: bool = True) -> torch.Tensor:
+        """Runs one batch; returns float32 logits [wanted places, vocab] on the device,
+        in the order of the entries and of each entry's `want`."""
+        entries = [e if isinstance(e, StepEntry) else StepEntry(*e) for e in entries]
+        if not entries:
+            return torch.empty((0, self.spec.vocab_size), dtype=torch.float32, device=self.device)
+        self._check_entries(entries)
+        prepared = []
+        try:
+            for e in entries:
+                self.cache.prepare(e.request_id, len(e.tokens))
+                prepared.append(e.request_id)
+            batch = self.make_batch(entries)
+            logits = self.model.forward(batch, self._views)
+            if check_status:
+                self.raise_on_status()
+        except Exception:
+            for rid in prepared:
+                self.cache.rollback(rid)
+            raise
+        for e in entries:
+            self.cache.commit(e.request_id)
+        self.steps_run += 1
+        return logits
+
+    def raise_on_status(self) -> None:
+        """Reads the device status word (this waits for the step) and raises if a kernel set a bit."""
+        code = int(self.runtime.status.item())
+        if code:
+            self.runtime.status.zero_()
+            what = [name for bit, name in ((kernels.STATUS_BAD_TOKEN, "a token id outside the vocabulary"),
+                                           (kernels.STATUS_BAD_PAGE, "a position without a cache page"),
+                                           (kernels.STATUS_NON_FINITE, "non-finite logits"),
+                                           (kernels.STATUS_WAIT_TIMEOUT, "a bounded wait inside a kernel ran out"))
+                    if code & bit]
+            raise QuantInferError("the step failed on the device: " + "; ".join(what))

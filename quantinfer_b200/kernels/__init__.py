@@ -1,0 +1,324 @@
+"""Python face of the hand-written sm_100a kernels.
+
+Each function checks its tensors (device, type, layout, sizes), passes raw
+pointers and the current CUDA stream to the C entry point of the same name and
+raises :class:`KernelError` with the library's message when the entry point
+refuses. There is no fallback: without a CUDA device or without the compiled
+library every call raises.
+"""
+
+from __future__ import annotations
+
+import ctypes as C
+import threading
+
+import torch
+
+from ..errors import KernelError
+
+F32, BF16 = 0, 1
+_DTYPE_CODE = {torch.float32: F32, torch.bfloat16: BF16}
+
+STATUS_BAD_TOKEN = 1
+STATUS_BAD_PAGE = 2
+STATUS_NON_FINITE = 4
+STATUS_WAIT_TIMEOUT = 8
+
+ABI_VERSION = 1
+
+_lib = None
+_lib_lock = threading.Lock()
+
+
+def library() -> C.CDLL:
+    """The compiled kernel library; built at the first call if needed."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    with _lib_lock:
+        if _lib is not None:
+            return _lib
+        if not torch.cuda.is_available():
+            raise KernelError(
+                "no CUDA device is visible: the engine runs only on the GPU (there is no CPU path)"
+            )
+        from ..csrc.build import library_path
+
+        try:
+            path = library_path()
+        except Exception as exc:  # the build failed or nvcc is missing
+            raise KernelError(f"the sm_100a kernel library could not be built: {exc}") from exc
+        lib = C.CDLL(str(path))
+        lib.qi_last_error.restype = C.c_char_p
+        lib.qi_abi_version.restype = C.c_int
+        if lib.qi_abi_version() != ABI_VERSION:
+            raise KernelError(
+                f"{path} has ABI version {lib.qi_abi_version()}, expected {ABI_VERSION}; rebuild it"
+            )
+        _lib = lib
+    return _lib
+
+
+def library_file() -> str:
+    return library()._name
+
+
+def _stream() -> C.c_void_p:
+    return C.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _check(rc: int, name: str) -> None:
+    if rc != 0:
+        raise KernelError(f"{name}: {library().qi_last_error().decode()}")
+
+
+def _code(t: torch.Tensor) -> int:
+    try:
+        return _DTYPE_CODE[t.dtype]
+    except KeyError:
+        raise KernelError(f"element type {t.dtype} is not supported (float32 or bfloat16)") from None
+
+
+def _req(t: torch.Tensor, name: str, dtype=None, ndim=None) -> None:
+    if not isinstance(t, torch.Tensor) or not t.is_cuda:
+        raise KernelError(f"{name} must be a CUDA tensor")
+    if not t.is_contiguous():
+        raise KernelError(f"{name} must be contiguous")
+    if dtype is not None and t.dtype != dtype:
+        raise KernelError(f"{name} must be {dtype}, got {t.dtype}")
+    if ndim is not None and t.dim() != ndim:
+        raise KernelError(f"{name} must have {ndim} dimensions, got shape {tuple(t.shape)}")
+
+
+def _ptr(t) -> C.c_void_p:
+    return C.c_void_p(0 if t is None else t.data_ptr())
+
+
+# --------------------------------------------------------------------------
+# embedding
+
+
+def embedding(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor, status: torch.Tensor) -> None:
+    """out[t, :] = table[ids[t], :] as float32. ids int32 [n]; out float32 [n, hidden]."""
+    _req(table, "table", ndim=2)
+    _req(ids, "ids", torch.int32, 1)
+    _req(out, "out", torch.float32, 2)
+    _req(status, "status", torch.int32)
+    n, hidden = out.shape
+    if ids.numel() != n or table.shape[1] != hidden:
+        raise KernelError(f"embedding: shapes do not agree: table {tuple(table.shape)}, ids {tuple(ids.shape)}, out {tuple(out.shape)}")
+    rc = library().qi_embedding(_ptr(table), _code(table), _ptr(ids), _ptr(out), n, hidden,
+                                table.shape[0], _ptr(status), _stream())
+    _check(rc, "embedding")
+
+
+# --------------------------------------------------------------------------
+# norms
+
+
+def add_rmsnorm(resid: torch.Tensor, delta, gain: torch.Tensor, eps: float, out: torch.Tensor,
+                rows=None, write_resid: bool = True) -> None:
+    """Fused residual add and RMSNorm.
+
+    resid float32 [n, h] (updated in place when write_resid); delta None, [n, h]
+    or [splits, n, h] (partial sums added in order); gain float32 [h]; out
+    [n, h], or [len(rows), h] when `rows` (int32) selects source rows.
+    """
+    _req(resid, "resid", torch.float32, 2)
+    _req(gain, "gain", torch.float32, 1)
+    _req(out, "out", ndim=2)
+    n, h = resid.shape
+    splits, stride = 1, 0
+    if delta is not None:
+        _req(delta, "delta")
+        if delta.dim() == 3:
+            splits, stride = delta.shape[0], delta.shape[1] * delta.shape[2]
+            if tuple(delta.shape[1:]) != (n, h):
+                raise KernelError(f"add_rmsnorm: delta {tuple(delta.shape)} does not match resid {tuple(resid.shape)}")
+        elif tuple(delta.shape) != (n, h):
+            raise KernelError(f"add_rmsnorm: delta {tuple(delta.shape)} does not match resid {tuple(resid.shape)}")
+    if gain.numel() != h:
+        raise KernelError(f"add_rmsnorm: gain has {gain.numel()} elements, rows have {h}")
+    n_out = n
+    if rows is not None:
+        _req(rows, "rows", torch.int32, 1)
+        n_out = rows.numel()
+        write_resid = False
+    if tuple(out.shape) != (n_out, h):
+        raise KernelError(f"add_rmsnorm: out is {tuple(out.shape)}, expected {(n_out, h)}")
+    rc = library().qi_add_rmsnorm(
+        _ptr(resid), _ptr(delta), _code(delta) if delta is not None else F32, splits,
+        C.c_longlong(stride), _ptr(gain), C.c_float(eps), _ptr(out), _code(out), _ptr(rows), n_out, h,
+        int(bool(write_resid)), _stream())
+    _check(rc, "add_rmsnorm")
+
+
+def rmsnorm(x: torch.Tensor, gain: torch.Tensor, eps: float, out: torch.Tensor) -> None:
+    """out = rmsnorm(x) * gain over the last dimension; x and out of one type."""
+    _req(x, "x")
+    _req(out, "out", x.dtype)
+    _req(gain, "gain", torch.float32, 1)
+    width = x.shape[-1]
+    if gain.numel() != width or out.shape != x.shape:
+        raise KernelError("rmsnorm: shapes do not agree")
+    rc = library().qi_rmsnorm(_ptr(x), _ptr(gain), C.c_float(eps), _ptr(out), _code(x),
+                              x.numel() // width, width, _stream())
+    _check(rc, "rmsnorm")
+
+
+# --------------------------------------------------------------------------
+# matrix products
+
+
+def gemm_simt(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
+    """out[M, N] = x[M, K] @ w[N, K]^T with 32-bit products and sums (no tensor cores)."""
+    _req(x, "x", ndim=2)
+    _req(w, "w", ndim=2)
+    _req(out, "out", ndim=2)
+    M, K = x.shape
+    N = w.shape[0]
+    if w.shape[1] != K or tuple(out.shape) != (M, N):
+        raise KernelError(f"gemm: shapes do not agree: x {tuple(x.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}")
+    rc = library().qi_gemm_simt(_ptr(x), _code(x), _ptr(w), _code(w), _ptr(out), _code(out), M, N, K,
+                                C.c_longlong(K), C.c_longlong(K), C.c_longlong(N), _stream())
+    _check(rc, "gemm_simt")
+
+
+# --------------------------------------------------------------------------
+# position encoding, q/k norm, cache write
+
+
+def rope_table(inv_freq: torch.Tensor, max_positions: int):
+    """cos and sin tables [max_positions, len(inv_freq)] in float32 from 32-bit angles."""
+    _req(inv_freq, "inv_freq", torch.float32, 1)
+    half = inv_freq.numel()
+    cos = torch.empty((max_positions, half), dtype=torch.float32, device=inv_freq.device)
+    sin = torch.empty_like(cos)
+    rc = library().qi_rope_table(_ptr(inv_freq), _ptr(cos), _ptr(sin), max_positions, half, _stream())
+    _check(rc, "rope_table")
+    return cos, sin
+
+
+def qk_norm_rope_kv(qkv, q_out, q_gain, k_gain, eps, cos, sin, rotary_dim, positions, token_req,
+                    block_table, page_size, k_pages, v_pages, nq, nkv, d, status) -> None:
+    """Per-head q/k RMSNorm, rotation, and the write of k and v into cache pages.
+
+    qkv [n, (nq + 2 nkv) d]; q_out [n, nq d]; gains float32 [d] or None; cos/sin
+    float32 [positions, rotary_dim / 2] or None; k_pages/v_pages
+    [num_pages, nkv, page_size, d] or None (no write); block_table int32
+    [requests, max_blocks].
+    """
+    _req(qkv, "qkv", ndim=2)
+    _req(q_out, "q_out", qkv.dtype, 2)
+    n = qkv.shape[0]
+    if qkv.shape[1] != (nq + 2 * nkv) * d or tuple(q_out.shape) != (n, nq * d):
+        raise KernelError(f"qk_norm_rope_kv: qkv {tuple(qkv.shape)} / q_out {tuple(q_out.shape)} do not match heads {nq}+2*{nkv} of {d}")
+    for g, name in ((q_gain, "q_gain"), (k_gain, "k_gain")):
+        if g is not None:
+            _req(g, name, torch.float32, 1)
+            if g.numel() != d:
+                raise KernelError(f"{name} has {g.numel()} elements, head_dim is {d}")
+    table_positions = 0
+    if cos is not None:
+        _req(cos, "cos", torch.float32, 2)
+        _req(sin, "sin", torch.float32, 2)
+        if cos.shape != sin.shape or cos.shape[1] * 2 != rotary_dim:
+            raise KernelError("qk_norm_rope_kv: rotation tables do not match rotary_dim")
+        table_positions = cos.shape[0]
+    _req(positions, "positions", torch.int32, 1)
+    _req(token_req, "token_req", torch.int32, 1)
+    num_pages, max_blocks = 0, 0
+    if k_pages is not None:
+        _req(k_pages, "k_pages", qkv.dtype, 4)
+        _req(v_pages, "v_pages", qkv.dtype, 4)
+        _req(block_table, "block_table", torch.int32, 2)
+        if tuple(k_pages.shape[1:]) != (nkv, page_size, d) or k_pages.shape != v_pages.shape:
+            raise KernelError(f"qk_norm_rope_kv: pages {tuple(k_pages.shape)} do not match (pages, {nkv}, {page_size}, {d})")
+        num_pages, max_blocks = k_pages.shape[0], block_table.shape[1]
+    rc = library().qi_qk_norm_rope_kv(
+        _ptr(qkv), _ptr(q_out), _code(qkv), _ptr(q_gain), _ptr(k_gain), C.c_float(eps), _ptr(cos),
+        _ptr(sin), rotary_dim, table_positions, _ptr(positions), _ptr(token_req), _ptr(block_table),
+        max_blocks, page_size, num_pages, _ptr(k_pages), _ptr(v_pages), n, nq, nkv, d, _ptr(status),
+        _stream())
+    _check(rc, "qk_norm_rope_kv")
+
+
+# --------------------------------------------------------------------------
+# attention
+
+
+def attention_generic(q, out, k_pages, v_pages, block_table, positions, token_req, nq, nkv, d,
+                      scale: float, window: int, status) -> None:
+    """Causal paged GQA attention, 32-bit arithmetic, any span length and page size."""
+    _req(q, "q", ndim=2)
+    _req(out, "out", q.dtype, 2)
+    _req(k_pages, "k_pages", q.dtype, 4)
+    _req(v_pages, "v_pages", q.dtype, 4)
+    _req(block_table, "block_table", torch.int32, 2)
+    _req(positions, "positions", torch.int32, 1)
+    _req(token_req, "token_req", torch.int32, 1)
+    n = q.shape[0]
+    if q.shape[1] != nq * d or out.shape != q.shape:
+        raise KernelError(f"attention: q {tuple(q.shape)} does not match {nq} heads of {d}")
+    if k_pages.shape[1] != nkv or k_pages.shape[3] != d or k_pages.shape != v_pages.shape:
+        raise KernelError(f"attention: pages {tuple(k_pages.shape)} do not match {nkv} kv heads of {d}")
+    rc = library().qi_attention_generic(
+        _ptr(q), _ptr(out), _code(q), _ptr(k_pages), _ptr(v_pages), _ptr(block_table),
+        block_table.shape[1], k_pages.shape[2], k_pages.shape[0], _ptr(positions), _ptr(token_req), n,
+        nq, nkv, d, C.c_float(scale), int(window or 0), _ptr(status), _stream())
+    _check(rc, "attention_generic")
+
+
+# --------------------------------------------------------------------------
+# feed-forward
+
+
+def silu_mul(gate_up: torch.Tensor, out: torch.Tensor) -> None:
+    """out[t, i] = silu(gate_up[t, i]) * gate_up[t, I + i]."""
+    _req(gate_up, "gate_up", ndim=2)
+    _req(out, "out", gate_up.dtype, 2)
+    n, two_i = gate_up.shape
+    if two_i % 2 or tuple(out.shape) != (n, two_i // 2):
+        raise KernelError(f"silu_mul: gate_up {tuple(gate_up.shape)} / out {tuple(out.shape)} do not agree")
+    rc = library().qi_silu_mul(_ptr(gate_up), _ptr(out), _code(out), n, two_i // 2, _stream())
+    _check(rc, "silu_mul")
+
+
+# --------------------------------------------------------------------------
+# sampling
+
+
+def sample(logits, temperature, top_k, top_p, seed, counter, out_token, status) -> None:
+    """Token per row of float32 logits [rows, vocab]; temperature 0 = first maximum.
+
+    temperature/top_p float32 [rows], top_k/counter int32 [rows], seed int64
+    [rows]; any of them may be None (greedy / no truncation / seed 0 / counter 0).
+    """
+    _req(logits, "logits", torch.float32, 2)
+    _req(out_token, "out_token", torch.int32, 1)
+    rows, vocab = logits.shape
+    for t, name, dt in ((temperature, "temperature", torch.float32), (top_k, "top_k", torch.int32),
+                        (top_p, "top_p", torch.float32), (seed, "seed", torch.int64),
+                        (counter, "counter", torch.int32)):
+        if t is not None:
+            _req(t, name, dt, 1)
+            if t.numel() < rows:
+                raise KernelError(f"sample: {name} has {t.numel()} entries for {rows} rows")
+    if out_token.numel() < rows:
+        raise KernelError("sample: out_token is too short")
+    rc = library().qi_sample(_ptr(logits), rows, vocab, _ptr(temperature), _ptr(top_k), _ptr(top_p),
+                             _ptr(seed), _ptr(counter), _ptr(out_token), _ptr(status), _stream())
+    _check(rc, "sample")
+
+
+# --------------------------------------------------------------------------
+# tensor-core matrix product (bfloat16 operands, 32-bit accumulation)
+
+
+def gemm_bf16_supported(M: int, N: int, K: int, out_dtype) -> bool:
+    """Whether `gemm_bf16` takes this problem; callers use `gemm_simt` otherwise."""
+    return False
+
+
+def gemm_bf16(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
+    raise KernelError("gemm_bf16 is not available in this build")

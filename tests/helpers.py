@@ -1,0 +1,63 @@
+"""Shared by the tests: the tiny configurations and small utilities.
+
+The two configurations differ in every size and option: layers, width, head
+counts and grouping (GQA 2:1 against MQA 8:1), head size (hidden / heads
+against a decoupled one), intermediate size, vocabulary (neither a power of two
+in B), rope base, eps, tied against untied head, position limit, and the seed.
+"""
+
+from __future__ import annotations
+
+import json
+import random
+from pathlib import Path
+
+import torch
+
+TINY_CONFIGS = {
+    "A": dict(
+        architectures=["Qwen3ForCausalLM"], model_type="qwen3",
+        vocab_size=256, hidden_size=64, intermediate_size=128, num_hidden_layers=2,
+        num_attention_heads=4, num_key_value_heads=2, head_dim=16,
+        max_position_embeddings=128, rms_norm_eps=1e-6, rope_theta=10000.0,
+        tie_word_embeddings=True,
+    ),
+    "B": dict(
+        architectures=["Qwen3ForCausalLM"], model_type="qwen3",
+        vocab_size=384, hidden_size=96, intermediate_size=224, num_hidden_layers=3,
+        num_attention_heads=8, num_key_value_heads=1, head_dim=32,
+        max_position_embeddings=256, rms_norm_eps=1e-5, rope_theta=1000000.0,
+        tie_word_embeddings=False,
+    ),
+    # sizes that are no power of two anywhere, head size 48, 3 kv heads
+    "C": dict(
+        architectures=["Qwen3ForCausalLM"], model_type="qwen3",
+        vocab_size=517, hidden_size=168, intermediate_size=328, num_hidden_layers=2,
+        num_attention_heads=6, num_key_value_heads=3, head_dim=48,
+        max_position_embeddings=320, rms_norm_eps=3e-6, rope_theta=50000.0,
+        tie_word_embeddings=False,
+    ),
+}
+SEEDS = {"A": 0, "B": 1, "C": 2}
+PAGE_SIZES = {"A": 16, "B": 8, "C": 32}
+
+
+def make_folder(path, name: str, dtype=torch.bfloat16) -> Path:
+    from quantinfer_b200.config import config_from_dict
+    from quantinfer_b200.weights import write_model_folder
+
+    cfg = config_from_dict(TINY_CONFIGS[name])
+    return write_model_folder(path, cfg, SEEDS[name], dtype)
+
+
+def random_tokens(n: int, vocab: int, seed: int) -> list:
+    rng = random.Random(seed)
+    return [rng.randrange(vocab) for _ in range(n)]
+
+
+def vocab_of(folder) -> int:
+    return json.loads((Path(folder) / "config.json").read_text())["vocab_size"]
+
+
+def max_abs_diff(a: torch.Tensor, b: torch.Tensor) -> float:
+    return float((a.double().cpu() - b.double().cpu()).abs().max())
