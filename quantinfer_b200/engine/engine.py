@@ -47,7 +47,7 @@ class Engine:
     def __init__(self, spec: ModelSpec, tensors: dict, *, dtype="bfloat16", device="cuda:0",
                  page_size: int = DEFAULT_PAGE_SIZE, max_tokens: int | None = None,
                  num_pages: int | None = None, max_requests: int = 64, max_seq_len: int | None = None,
-                 config=None):
+                 config=None, use_graphs: bool = True):
         """`tensors` are the model's weights by file name (CPU or device tensors).
 
         The page pool holds `num_pages` pages per layer group, or enough for
@@ -80,6 +80,7 @@ class Engine:
         self._staging_event = [None, None]
         self._staging_turn = 0
         self.steps_run = 0
+        self.use_graphs = use_graphs
 
     # ---- construction ------------------------------------------------------
 
