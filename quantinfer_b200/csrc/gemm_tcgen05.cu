@@ -1,0 +1,465 @@
+// bfloat16 matrix product on the 5th-generation tensor cores:
+//     y[M, N] = x[M, K] . w[N, K]^T        (32-bit accumulation)
+// Both operands are read along K ("K-major"), which is the checkpoint's
+// [out, in] layout for w, so nothing is transposed at load.
+//
+// One CTA computes one 128 x BN tile of  D = A . B^T  where A and B are the two
+// row-major operands. For many tokens A = x and B = w. For few tokens (decode)
+// the operands are swapped: A = w, so the 128 rows of the MMA ride the weight's
+// output dimension and the small token count rides the MMA's N (16..256); the
+// epilogue then stores the tile transposed. A skinny product is bound by the
+// weight stream from HBM, so the K dimension can be split over blockIdx.z to
+// put enough CTAs in flight; partial sums go to a 32-bit workspace
+// [splits, M, N] and are added in split order by a second kernel (or by the
+// consumer: add_rmsnorm takes the partials directly).
+//
+// Roles inside a CTA (192 threads):
+//   warp 0     one lane issues TMA loads (cp.async.bulk.tensor, 128-byte swizzle)
+//              into a ring of STAGES shared-memory buffers, each guarded by a
+//              "full" mbarrier (expect-tx) and an "empty" mbarrier
+//   warp 1     allocates tensor memory; one lane issues tcgen05.mma (kind::f16,
+//              M = 128, N = BN, K = 16 per instruction, 4 per 64-wide k block) and
+//              tcgen05.commit, which frees the stage and finally signals the
+//              accumulator
+//   warps 2-5  read the accumulator from tensor memory (tcgen05.ld, 32 lanes x
+//              32 columns per warp) and store it
+// No load uses cluster multicast. Every mbarrier wait is bounded: when a bound
+// runs out the thread sets kStatusWaitTimeout in the status word and an abort
+// flag in shared memory, all roles leave their loops, the producer waits (with
+// a bound) for the copies it still has in flight, tensor memory is freed and
+// the kernel returns.
+//
+// K must be a multiple of 8 (TMA wants row strides of whole 16 bytes); rows of
+// A, B and K beyond the tensors are zero-filled by TMA and masked at the store.
+#include "common.cuh"
+
+#include <cuda.h>
+
+namespace {
+
+constexpr int BM = 128;       // rows of A per tile = MMA M
+constexpr int BK = 64;        // bf16 elements per k block = 128 bytes = one swizzle row
+constexpr int UMMA_K = 16;
+constexpr int kThreads = 192;
+constexpr uint32_t kSpinLimit = 1u << 24;   // polls of try_wait before giving up (a second or so)
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+    return (uint32_t)__cvta_generic_to_shared(p);
+}
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+
+// Waits for the phase with the given parity to complete; false when the bound ran out
+// or another role already gave up.
+// A timeout that any CTA recorded in the global status word ends the waits of all others early.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                          const volatile int* status) {
+    for (uint32_t i = 0; i < kSpinLimit; ++i) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((i & 1023u) == 1023u && *abort_flag) return false;
+        if ((i & 65535u) == 65535u && status && (*status & qi::kStatusWaitTimeout)) return false;
+    }
+    return false;
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y) : "memory");
+}
+
+__device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t cols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() {
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t addr, uint32_t cols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %6, %7, %8}, p;\n\t}"
+        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(0), "r"(0), "r"(0), "r"(0) : "memory");
+}
+
+// Arrives on the mbarrier when every MMA issued so far by this thread has completed.
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+__device__ __forceinline__ void tmem_ld32(uint32_t addr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(addr));
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t addr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(addr));
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor of a K-major tile stored as rows of 128 bytes
+// with the 128-byte swizzle (what TMA writes with CU_TENSOR_MAP_SWIZZLE_128B):
+// start address >> 4 in bits 0-13, leading byte offset (unused for swizzled
+// K-major, 1) in 16-29, stride byte offset = 8 rows x 128 B = 1024 >> 4 in
+// 32-45, descriptor version 1 in 46-47, layout type 2 (128-byte swizzle) in 61-63.
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr & 0x3FFFFu) >> 4);
+    d |= (uint64_t)1 << 16;
+    d |= (uint64_t)(1024 >> 4) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)2 << 61;
+    return d;
+}
+
+// Instruction descriptor of kind::f16: D format F32 (1) in bits 4-5, A and B
+// format BF16 (1) in 7-9 and 10-12, both K-major (0) in 15 and 16, N >> 3 in
+// 17-22, M >> 4 in 24-28.
+__host__ __device__ constexpr uint32_t make_idesc(int m, int n) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+
+template <typename TOut> __device__ __forceinline__ void store1(TOut* p, float v);
+template <> __device__ __forceinline__ void store1<float>(float* p, float v) { *p = v; }
+template <> __device__ __forceinline__ void store1<qi::bf16>(qi::bf16* p, float v) { *p = __float2bfloat16_rn(v); }
+
+template <int BN, int STAGES>
+struct Smem {
+    static constexpr int kABytes = BM * BK * 2;
+    static constexpr int kBBytes = BN * BK * 2;
+    static constexpr int kStageBytes = kABytes + kBBytes;
+    static constexpr int kBarrierBytes = 8 * (2 * STAGES + 1) + 16;
+    static constexpr int kTotal = STAGES * kStageBytes + kBarrierBytes + 1024;  // + alignment slack
+};
+
+template <int BN, int STAGES, bool SWAP, typename TOut>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                    TOut* __restrict__ out, int rows_a, int rows_b, int K, long long ld_out,
+                    int kb_per_split, long long split_stride, int* __restrict__ status) {
+    extern __shared__ uint8_t smem_raw[];
+    using L = Smem<BN, STAGES>;
+    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t* aligned = smem_raw + (base - smem_u32(smem_raw));
+    const uint32_t bars = base + STAGES * L::kStageBytes;       // full[STAGES], empty[STAGES], accum
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(aligned + STAGES * L::kStageBytes + 8 * (2 * STAGES + 1));
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    auto full_bar = [&](int s) { return bars + 8u * s; };
+    auto empty_bar = [&](int s) { return bars + 8u * (STAGES + s); };
+    const uint32_t accum_bar = bars + 8u * (2 * STAGES);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int tile_a = blockIdx.x, tile_b = blockIdx.y, split = blockIdx.z;
+    const int kb_total = (K + BK - 1) / BK;
+    const int kb_begin = split * kb_per_split;
+    const int kb_end = min(kb_total, kb_begin + kb_per_split);
+    const int n_kb = max(kb_end - kb_begin, 0);
+    constexpr uint32_t kTmemCols = BN < 32 ? 32 : BN;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(full_bar(s), 1);
+            mbar_init(empty_bar(s), 1);
+        }
+        mbar_init(accum_bar, 1);
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        tmem_alloc(smem_u32(tmem_slot), kTmemCols);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ---------------- TMA producer ----------------
+        if (lane == 0) {
+            int issued = 0;
+            for (int i = 0; i < n_kb; ++i) {
+                const int s = i % STAGES;
+                const uint32_t round = (uint32_t)(i / STAGES);
+                if (!mbar_wait(empty_bar(s), (round & 1u) ^ 1u, abort_flag, status)) {
+                    if (!*abort_flag) { *abort_flag = 1; if (status) atomicOr(status, qi::kStatusWaitTimeout); }
+                    break;
+                }
+                mbar_expect_tx(full_bar(s), L::kStageBytes);
+                const uint32_t a_dst = base + s * L::kStageBytes;
+                const uint32_t b_dst = a_dst + L::kABytes;
+                const int k0 = (kb_begin + i) * BK;
+                tma_load_2d(a_dst, &map_a, full_bar(s), k0, tile_a * BM);
+                tma_load_2d(b_dst, &map_b, full_bar(s), k0, tile_b * BN);
+                issued = i + 1;
+            }
+            if (*abort_flag) {
+                // Copies still in flight write into this CTA's shared memory: wait for the
+                // stages armed last (at most STAGES of them) before the CTA may exit.
+                for (int i = max(issued - STAGES, 0); i < issued; ++i) {
+                    const int s = i % STAGES;
+                    const uint32_t round = (uint32_t)(i / STAGES);
+                    for (uint32_t t = 0; t < (1u << 20); ++t)
+                        if (mbar_try_wait(full_bar(s), round & 1u)) break;
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer ----------------
+        if (lane == 0) {
+            constexpr uint32_t idesc = make_idesc(BM, BN);
+            bool ok = true;
+            for (int i = 0; i < n_kb && ok; ++i) {
+                const int s = i % STAGES;
+                const uint32_t round = (uint32_t)(i / STAGES);
+                if (!mbar_wait(full_bar(s), round & 1u, abort_flag, status)) {
+                    if (!*abort_flag) { *abort_flag = 1; if (status) atomicOr(status, qi::kStatusWaitTimeout); }
+                    ok = false;
+                    break;
+                }
+                tc_fence_after();
+                const uint32_t a_addr = base + s * L::kStageBytes;
+                const uint64_t adesc = make_smem_desc(a_addr);
+                const uint64_t bdesc = make_smem_desc(a_addr + L::kABytes);
+#pragma unroll
+                for (int k = 0; k < BK / UMMA_K; ++k) {
+                    // 16 bf16 = 32 bytes further along the swizzled row: +2 in units of 16 bytes
+                    umma_bf16(tmem_base, adesc + 2u * k, bdesc + 2u * k, idesc, (i > 0 || k > 0) ? 1u : 0u);
+                }
+                umma_commit(empty_bar(s));   // the stage is free once these MMAs have read it
+            }
+            if (ok) umma_commit(accum_bar);  // the accumulator is complete
+        }
+    } else {
+        // ---------------- epilogue (warps 2..5) ----------------
+        const int quarter = warp & 3;   // the 32 TMEM lanes this warp may read
+        bool ok = true;
+        if (n_kb > 0) {
+            ok = mbar_wait(accum_bar, 0, abort_flag, status);
+            if (!ok && !*abort_flag) { *abort_flag = 1; if (status && lane == 0) atomicOr(status, qi::kStatusWaitTimeout); }
+        }
+        tc_fence_after();
+        const int a_row = tile_a * BM + quarter * 32 + lane;
+        TOut* obase = out + (size_t)split * split_stride;
+        constexpr int kChunk = BN >= 32 ? 32 : 16;
+#pragma unroll 1
+        for (int c0 = 0; c0 < BN; c0 += kChunk) {
+            uint32_t r[32];
+            if (n_kb > 0 && ok) {
+                const uint32_t addr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c0;
+                if (kChunk == 32) tmem_ld32(addr, r); else tmem_ld16(addr, r);
+                tmem_ld_wait();
+            } else {
+#pragma unroll
+                for (int j = 0; j < 32; ++j) r[j] = 0u;   // an empty K range contributes zeros
+            }
+            if (!ok) continue;
+            const int b0 = tile_b * BN + c0;
+            if (SWAP) {
+                // out[b, a]: for a fixed column the warp's lanes write consecutive addresses
+                if (a_row < rows_a) {
+#pragma unroll
+                    for (int j = 0; j < kChunk; ++j)
+                        if (b0 + j < rows_b) store1<TOut>(obase + (size_t)(b0 + j) * ld_out + a_row, __uint_as_float(r[j]));
+                }
+            } else {
+                if (a_row < rows_a) {
+                    TOut* orow = obase + (size_t)a_row * ld_out + b0;
+                    const bool full = b0 + kChunk <= rows_b;
+                    const bool aligned16 = ((reinterpret_cast<uintptr_t>(orow) & 15u) == 0);
+                    if (full && aligned16 && sizeof(TOut) == 2) {
+#pragma unroll
+                        for (int j = 0; j < kChunk; j += 8) {
+                            uint4 v;
+                            __nv_bfloat162 p0 = __floats2bfloat162_rn(__uint_as_float(r[j + 0]), __uint_as_float(r[j + 1]));
+                            __nv_bfloat162 p1 = __floats2bfloat162_rn(__uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
+                            __nv_bfloat162 p2 = __floats2bfloat162_rn(__uint_as_float(r[j + 4]), __uint_as_float(r[j + 5]));
+                            __nv_bfloat162 p3 = __floats2bfloat162_rn(__uint_as_float(r[j + 6]), __uint_as_float(r[j + 7]));
+                            v.x = *reinterpret_cast<uint32_t*>(&p0);
+                            v.y = *reinterpret_cast<uint32_t*>(&p1);
+                            v.z = *reinterpret_cast<uint32_t*>(&p2);
+                            v.w = *reinterpret_cast<uint32_t*>(&p3);
+                            *reinterpret_cast<uint4*>(reinterpret_cast<qi::bf16*>(orow) + j) = v;
+                        }
+                    } else if (full && aligned16 && sizeof(TOut) == 4) {
+#pragma unroll
+                        for (int j = 0; j < kChunk; j += 4) {
+                            uint4 v = make_uint4(r[j], r[j + 1], r[j + 2], r[j + 3]);
+                            *reinterpret_cast<uint4*>(reinterpret_cast<float*>(orow) + j) = v;
+                        }
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < kChunk; ++j)
+                            if (b0 + j < rows_b) store1<TOut>(orow + j, __uint_as_float(r[j]));
+                    }
+                }
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) tmem_dealloc(tmem_base, kTmemCols);
+}
+
+// Adds split-K partial sums in split order: out[i] = sum_s partial[s, i].
+template <typename TOut>
+__global__ void splitk_reduce_kernel(const float* __restrict__ partial, TOut* __restrict__ out, size_t n, int splits) {
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+        float s = 0.f;
+        for (int k = 0; k < splits; ++k) s += partial[(size_t)k * n + i];
+        store1<TOut>(out + i, s);
+    }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encode() {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+    }
+    return fn;
+}
+
+// Map of a row-major bf16 matrix [rows, K] with boxes of [box_rows, 64] and the 128-byte swizzle.
+int make_map(CUtensorMap* map, const void* ptr, int rows, int K, int box_rows) {
+    EncodeTiledFn enc = get_encode();
+    if (!enc) return qi::fail("gemm_bf16: cuTensorMapEncodeTiled is not available from the driver");
+    cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)K * 2};
+    cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return qi::fail("gemm_bf16: cuTensorMapEncodeTiled failed with code %d (rows=%d K=%d box=%d)", (int)r, rows, K, box_rows);
+    return 0;
+}
+
+template <int BN, int STAGES, bool SWAP, typename TOut>
+int launch(const CUtensorMap& ma, const CUtensorMap& mb, TOut* out, int rows_a, int rows_b, int K, long long ld,
+           int splits, int kb_per_split, long long split_stride, int* status, cudaStream_t stream) {
+    auto kern = gemm_tcgen05_kernel<BN, STAGES, SWAP, TOut>;
+    constexpr int smem = Smem<BN, STAGES>::kTotal;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (e != cudaSuccess) return qi::fail("gemm_bf16: cannot reserve %d bytes of shared memory: %s", smem, cudaGetErrorString(e));
+        configured = true;
+    }
+    dim3 grid((rows_a + BM - 1) / BM, (rows_b + BN - 1) / BN, splits);
+    kern<<<grid, kThreads, smem, stream>>>(ma, mb, out, rows_a, rows_b, K, ld, kb_per_split, split_stride, status);
+    return qi::check_launch("gemm_bf16");
+}
+
+template <bool SWAP, typename TOut>
+int launch_bn(int bn, const CUtensorMap& ma, const CUtensorMap& mb, TOut* out, int rows_a, int rows_b, int K,
+              long long ld, int splits, int kb_per_split, long long split_stride, int* status, cudaStream_t stream) {
+    switch (bn) {
+        case 16: return launch<16, 8, SWAP, TOut>(ma, mb, out, rows_a, rows_b, K, ld, splits, kb_per_split, split_stride, status, stream);
+        case 32: return launch<32, 8, SWAP, TOut>(ma, mb, out, rows_a, rows_b, K, ld, splits, kb_per_split, split_stride, status, stream);
+        case 64: return launch<64, 8, SWAP, TOut>(ma, mb, out, rows_a, rows_b, K, ld, splits, kb_per_split, split_stride, status, stream);
+        case 128: return launch<128, 6, SWAP, TOut>(ma, mb, out, rows_a, rows_b, K, ld, splits, kb_per_split, split_stride, status, stream);
+        case 256: return launch<256, 4, SWAP, TOut>(ma, mb, out, rows_a, rows_b, K, ld, splits, kb_per_split, split_stride, status, stream);
+    }
+    return qi::fail("gemm_bf16: no kernel for a tile width of %d", bn);
+}
+
+}  // namespace
+
+// Workspace bytes `qi_gemm_bf16` needs for the split count it would choose (0: none).
+extern "C" int qi_gemm_bf16_plan(int M, int N, int K, int* swap, int* bn, int* splits) {
+    const int kb_total = (K + BK - 1) / BK;
+    int sw = M <= 256 ? 1 : 0, b, sp = 1;
+    if (sw) {
+        b = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : 256;
+        const int tiles = (N + BM - 1) / BM;
+        // enough CTAs to keep the weight stream busy on 148 SMs, at least 8 k blocks per split
+        while (tiles * sp < 148 && sp * 2 <= 16 && kb_total / (sp * 2) >= 8) sp *= 2;
+    } else {
+        b = N >= 256 ? 256 : N > 64 ? 128 : N > 32 ? 64 : N > 16 ? 32 : 16;
+    }
+    *swap = sw; *bn = b; *splits = sp;
+    return 0;
+}
+
+// y[M, N] = x[M, K] . w[N, K]^T, bf16 operands, out bf16 or float32 (out_dtype).
+// With splits > 1, `workspace` must hold splits * M * N floats.
+extern "C" int qi_gemm_bf16(const void* x, const void* w, void* out, int out_dtype, int M, int N, int K,
+                            int swap, int bn, int splits, void* workspace, int* status, cudaStream_t stream) {
+    QI_REQUIRE(M > 0 && N > 0 && K > 0, "gemm_bf16: bad sizes M=%d N=%d K=%d", M, N, K);
+    QI_REQUIRE(K % 8 == 0, "gemm_bf16: K=%d must be a multiple of 8 (16-byte rows for TMA)", K);
+    QI_REQUIRE(((uintptr_t)x & 15) == 0 && ((uintptr_t)w & 15) == 0, "gemm_bf16: operands must be 16-byte aligned");
+    QI_REQUIRE(splits >= 1 && (splits == 1 || workspace), "gemm_bf16: split-K needs a workspace");
+    QI_REQUIRE(out_dtype == qi::kF32 || out_dtype == qi::kBF16, "gemm_bf16: output type must be float32 or bfloat16");
+    const int kb_total = (K + BK - 1) / BK;
+    const int kb_per_split = (kb_total + splits - 1) / splits;
+    QI_REQUIRE((splits - 1) * kb_per_split < kb_total, "gemm_bf16: %d splits leave one without work (K=%d)", splits, K);
+    const void* a = swap ? w : x;
+    const void* b = swap ? x : w;
+    const int rows_a = swap ? N : M, rows_b = swap ? M : N;
+    QI_REQUIRE((rows_a + BM - 1) / BM <= 2147483647 && (rows_b + bn - 1) / bn <= 65535 && splits <= 65535, "gemm_bf16: grid too large");
+    CUtensorMap ma, mb;
+    if (make_map(&ma, a, rows_a, K, BM)) return 1;
+    if (make_map(&mb, b, rows_b, K, bn)) return 1;
+    const long long split_stride = (long long)M * N;
+    int rc;
+    if (splits > 1) {
+        float* ws = (float*)workspace;
+        rc = swap ? launch_bn<true, float>(bn, ma, mb, ws, rows_a, rows_b, K, N, splits, kb_per_split, split_stride, status, stream)
+                  : launch_bn<false, float>(bn, ma, mb, ws, rows_a, rows_b, K, N, splits, kb_per_split, split_stride, status, stream);
+        if (rc) return rc;
+        if (out) {
+            const size_t n = (size_t)M * N;
+            unsigned blocks = (unsigned)((n + 255) / 256 < 148 * 8 ? (n + 255) / 256 : 148 * 8);
+            if (out_dtype == qi::kF32) splitk_reduce_kernel<float><<<blocks, 256, 0, stream>>>(ws, (float*)out, n, splits);
+            else splitk_reduce_kernel<qi::bf16><<<blocks, 256, 0, stream>>>(ws, (qi::bf16*)out, n, splits);
+            return qi::check_launch("splitk_reduce");
+        }
+        return 0;
+    }
+    if (out_dtype == qi::kF32)
+        return swap ? launch_bn<true, float>(bn, ma, mb, (float*)out, rows_a, rows_b, K, N, 1, kb_per_split, 0, status, stream)
+                    : launch_bn<false, float>(bn, ma, mb, (float*)out, rows_a, rows_b, K, N, 1, kb_per_split, 0, status, stream);
+    return swap ? launch_bn<true, qi::bf16>(bn, ma, mb, (qi::bf16*)out, rows_a, rows_b, K, N, 1, kb_per_split, 0, status, stream)
+                : launch_bn<false, qi::bf16>(bn, ma, mb, (qi::bf16*)out, rows_a, rows_b, K, N, 1, kb_per_split, 0, status, stream);
+}

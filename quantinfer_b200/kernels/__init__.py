@@ -314,11 +314,37 @@ def sample(logits, temperature, top_k, top_p, seed, counter, out_token, status) 
 # --------------------------------------------------------------------------
 # tensor-core matrix product (bfloat16 operands, 32-bit accumulation)
 
+_gemm_status = {}
+
 
 def gemm_bf16_supported(M: int, N: int, K: int, out_dtype) -> bool:
     """Whether `gemm_bf16` takes this problem; callers use `gemm_simt` otherwise."""
-    return False
+    return M > 0 and K % 8 == 0 and out_dtype in (torch.bfloat16, torch.float32)
 
 
-def gemm_bf16(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
-    raise KernelError("gemm_bf16 is not available in this build")
+def gemm_bf16_plan(M: int, N: int, K: int):
+    """(swap operands, tile width, K splits) the library would choose."""
+    swap, bn, splits = C.c_int(), C.c_int(), C.c_int()
+    library().qi_gemm_bf16_plan(M, N, K, C.byref(swap), C.byref(bn), C.byref(splits))
+    return bool(swap.value), bn.value, splits.value
+
+
+def gemm_bf16(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, plan=None, status=None) -> None:
+    """out[M, N] = x[M, K] @ w[N, K]^T on the tcgen05 tensor cores; x, w bfloat16;
+    out bfloat16 or float32. `plan` = (swap, tile width, splits) overrides the choice."""
+    _req(x, "x", torch.bfloat16, 2)
+    _req(w, "w", torch.bfloat16, 2)
+    _req(out, "out", ndim=2)
+    M, K = x.shape
+    N = w.shape[0]
+    if w.shape[1] != K or tuple(out.shape) != (M, N):
+        raise KernelError(f"gemm: shapes do not agree: x {tuple(x.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}")
+    swap, bn, splits = plan if plan is not None else gemm_bf16_plan(M, N, K)
+    ws = torch.empty((splits, M, N), dtype=torch.float32, device=x.device) if splits > 1 else None
+    if status is None:
+        status = _gemm_status.get(x.device)
+        if status is None:
+            status = _gemm_status[x.device] = torch.zeros(1, dtype=torch.int32, device=x.device)
+    rc = library().qi_gemm_bf16(_ptr(x), _ptr(w), _ptr(out), _code(out), M, N, K, int(swap), bn, splits,
+                                _ptr(ws), _ptr(status), _stream())
+    _check(rc, "gemm_bf16")
