@@ -47,6 +47,18 @@ class Model:
         self._chunk_size = chunk_size
         self._open = True
 
+    @classmethod
+    def from_engine(cls, engine, *, max_batch_tokens=2048, chunk_size=None) -> "Model":
+        """A Model over an engine that already exists (random weights made on the device, tests)."""
+        self = cls.__new__(cls)
+        self._lock = RLock()
+        self._engine = engine
+        self._sampler = Sampler(engine.device, engine.runtime.status)
+        self._max_batch_tokens = max_batch_tokens
+        self._chunk_size = chunk_size
+        self._open = True
+        return self
+
     # ---- lifetime -------------------------------------------------------------
 
     def close(self):

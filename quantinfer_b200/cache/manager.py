@@ -28,6 +28,7 @@ from __future__ import annotations
 from dataclasses import dataclass, field
 from typing import Optional
 
+import numpy as np
 import torch
 
 from ..errors import CacheError, OutOfPages
@@ -134,6 +135,8 @@ class CacheManager:
                 g.v = torch.zeros(shape, dtype=dtype, device=self.device)
         self._free_slots = list(range(max_requests - 1, -1, -1))
         self.requests: dict[object, RequestCache] = {}
+        # block tables by slot, kept as arrays so that a batch's tables are one gather
+        self.host_tables = [np.full((max_requests, self.max_blocks), -1, dtype=np.int32) for _ in self.groups]
 
     # ---- sizes ---------------------------------------------------------
 
@@ -196,11 +199,13 @@ class CacheManager:
                 table = rc.tables[gi]
                 while len(table) < need_blocks:
                     page = g.allocator.alloc()
+                    self.host_tables[gi][rc.slot, len(table)] = page
                     table.append(page)
                     taken.append((gi, page))
         except OutOfPages:
             for gi, page in reversed(taken):
                 assert rc.tables[gi].pop() == page
+                self.host_tables[gi][rc.slot, len(rc.tables[gi])] = -1
                 self.groups[gi].allocator.free(page)
             raise OutOfPages(
                 f"request {request_id!r} needs {need_blocks} pages per group for {end} positions; "
@@ -223,6 +228,7 @@ class CacheManager:
                 if table[b] >= 0:
                     g.allocator.free(table[b])
                     table[b] = -1
+                    self.host_tables[gi][rc.slot, b] = -1
 
     def rollback(self, request_id) -> None:
         """Undoes `prepare`: pages beyond the committed length go back."""
@@ -232,6 +238,7 @@ class CacheManager:
             table = rc.tables[gi]
             while len(table) > keep:
                 page = table.pop()
+                self.host_tables[gi][rc.slot, len(table)] = -1
                 if page >= 0:
                     g.allocator.free(page)
         rc.pending = 0
@@ -242,6 +249,7 @@ class CacheManager:
             for page in rc.tables[gi]:
                 if page >= 0:
                     g.allocator.free(page)
+            self.host_tables[gi][rc.slot, :] = -1
         del self.requests[request_id]
         self._free_slots.append(rc.slot)
 
@@ -279,6 +287,12 @@ class CacheManager:
                 raise CacheError(f"group {gi}: a held page is also free")
             if len(held) + len(free) != g.allocator.num_pages:
                 raise CacheError(f"group {gi}: {g.allocator.num_pages - len(held) - len(free)} pages are lost")
+        for gi in range(len(self.groups)):
+            mirror = np.full_like(self.host_tables[gi], -1)
+            for rc in self.requests.values():
+                mirror[rc.slot, :len(rc.tables[gi])] = rc.tables[gi]
+            if not np.array_equal(mirror, self.host_tables[gi]):
+                raise CacheError(f"group {gi}: the table arrays differ from the requests' tables")
         slots = [rc.slot for rc in self.requests.values()]
         if len(slots) != len(set(slots)) or set(slots) & set(self._free_slots):
             raise CacheError("a slot is held twice")

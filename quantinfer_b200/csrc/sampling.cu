@@ -304,7 +304,33 @@ sample_kernel(const float* __restrict__ logits, int vocab, const float* __restri
     if (tid == 0) out_token[row] = result >= 0 ? result : max_i;
 }
 
+// After a decode step that ran wholly on the device: the sampled tokens become the
+// next step's input, every request moves one position on, and its draw counter advances.
+__global__ void advance_decode_kernel(int* __restrict__ token_ids, int* __restrict__ positions,
+                                      int* __restrict__ start_pos, int* __restrict__ kv_len,
+                                      int* __restrict__ counter, const int* __restrict__ sampled,
+                                      int* __restrict__ history, int b) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= b) return;
+    const int t = sampled[i];
+    token_ids[i] = t;
+    positions[i] += 1;
+    start_pos[i] += 1;
+    kv_len[i] += 1;
+    if (counter) counter[i] += 1;
+    if (history) history[i] = t;
+}
+
 }  // namespace
+
+extern "C" int qi_advance_decode(int* token_ids, int* positions, int* start_pos, int* kv_len, int* counter,
+                                 const int* sampled, int* history, int b, cudaStream_t stream) {
+    QI_REQUIRE(b >= 0, "advance_decode: bad batch size %d", b);
+    if (b == 0) return 0;
+    advance_decode_kernel<<<(b + 127) / 128, 128, 0, stream>>>(token_ids, positions, start_pos, kv_len, counter,
+                                                             sampled, history, b);
+    return qi::check_launch("advance_decode");
+}
 
 extern "C" int qi_sample(const float* logits, int rows, int vocab, const float* temperature,
                          const int* top_k, const float* top_p, const long long* seed,

@@ -61,11 +61,11 @@ class StepBatch:
 
 
 def pack_batch(entries: Sequence[StepEntry], starts: Sequence[int], slots: Sequence[int],
-               tables: Sequence[Sequence[Sequence[int]]], max_blocks: int) -> tuple:
+               tables: Sequence, max_blocks: int) -> tuple:
     """Host side of a batch: one int32 array and the offsets of its parts.
 
     `starts[i]` is the position of entry i's first token, `slots[i]` its slot,
-    `tables[g][i]` its block table in group g."""
+    `tables[g]` the block tables of group g by slot, an int32 array [slots, max_blocks]."""
     b = len(entries)
     lens = [len(e.tokens) for e in entries]
     n = sum(lens)
@@ -102,10 +102,7 @@ def pack_batch(entries: Sequence[StepEntry], starts: Sequence[int], slots: Seque
             rows[ri] = a + w
             ri += 1
     for g in range(n_groups):
-        t = part(f"table{g}").reshape(b, max_blocks)
-        for i in range(b):
-            row = tables[g][i]
-            t[i, :len(row)] = row
+        part(f"table{g}").reshape(b, max_blocks)[:] = tables[g][list(slots)]
     return buf, layout, q_start, lens
 
 

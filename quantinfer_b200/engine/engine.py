@@ -81,6 +81,10 @@ class Engine:
         self._staging_turn = 0
         self.steps_run = 0
         self.use_graphs = use_graphs
+        self.max_graph_batch = 64
+        self._graphs = {}
+        self._graph_pool = None
+        self.h2d_bytes = 0
 
     # ---- construction ------------------------------------------------------
 
@@ -128,7 +132,8 @@ class Engine:
                 if not 0 <= w < n:
                     raise QuantInferError(f"request {e.request_id!r}: wanted place {w} is outside its {n} tokens")
 
-    def _to_device(self, buf) -> torch.Tensor:
+    def _stage(self, buf):
+        """Copies a packed batch into pinned host memory; returns the pinned view."""
         turn = self._staging_turn
         self._staging_turn ^= 1
         host = self._staging[turn]
@@ -139,23 +144,66 @@ class Engine:
         else:
             self._staging_event[turn].synchronize()  # the copy that last used this buffer is done
         host[:buf.size].numpy()[:] = buf
-        dev = host[:buf.size].to(self.device, non_blocking=True)
-        self._staging_event[turn].record()
-        return dev
+        self.h2d_bytes = int(buf.size) * 4
+        return host[:buf.size], self._staging_event[turn]
 
-    def make_batch(self, entries: Sequence[StepEntry]) -> StepBatch:
+    def _pack(self, entries: Sequence[StepEntry]):
         reqs = [self.cache.get(e.request_id) for e in entries]
         starts = [rc.length for rc in reqs]
         slots = [rc.slot for rc in reqs]
-        tables = [[rc.tables[g] for rc in reqs] for g in range(len(self.cache.groups))]
-        buf, layout, q_start, lens = pack_batch(entries, starts, slots, tables, self.cache.max_blocks)
-        dev = self._to_device(buf)
+        return (starts, slots) + pack_batch(entries, starts, slots, self.cache.host_tables, self.cache.max_blocks)
+
+    def make_batch(self, entries: Sequence[StepEntry]) -> StepBatch:
+        starts, slots, buf, layout, q_start, lens = self._pack(entries)
+        host, event = self._stage(buf)
+        dev = host.to(self.device, non_blocking=True)
+        event.record()
         return batch_from_packed(dev, layout, entries, starts, slots, q_start, lens,
                                  len(self.cache.groups), self.cache.max_blocks)
 
+    # ---- decode steps replayed from a CUDA graph ---------------------------------
+
+    def _graph_eligible(self, entries) -> bool:
+        return (self.use_graphs and len(entries) <= self.max_graph_batch
+                and all(len(e.tokens) == 1 and list(e.want) == [0] for e in entries))
+
+    def _graph_step(self, entries) -> torch.Tensor:
+        """A batch of single decode tokens, all wanting their logits: the packed batch has a
+        fixed layout per batch size, so the forward pass is captured once per size and
+        replayed; each step only copies the batch's arrays into the graph's buffer."""
+        starts, slots, buf, layout, q_start, lens = self._pack(entries)
+        host, event = self._stage(buf)
+        b = len(entries)
+        g = self._graphs.get(b)
+        if g is None:
+            meta = torch.empty(buf.size, dtype=torch.int32, device=self.device)
+            meta.copy_(host, non_blocking=True)
+            event.record()
+            batch = batch_from_packed(meta, layout, entries, starts, slots, q_start, lens,
+                                      len(self.cache.groups), self.cache.max_blocks)
+            batch.max_kv_len = self.max_seq_len      # kernels in a graph size their grids for the limit
+            batch.extra["graph"] = True
+            logits = self.model.forward(batch, self._views)   # eager: warms up and gives this step's result
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            before = kernels.launches
+            with torch.cuda.graph(graph, pool=self._graph_pool):
+                static_logits = self.model.forward(batch, self._views)
+            if self._graph_pool is None:
+                self._graph_pool = graph.pool()
+            self._graphs[b] = g = {"graph": graph, "meta": meta, "batch": batch, "logits": static_logits,
+                                   "layout": layout, "launches": kernels.launches - before}
+            return logits
+        g["meta"].copy_(host, non_blocking=True)
+        event.record()
+        g["graph"].replay()
+        kernels.launches += g["launches"]
+        return g["logits"]
+
     def step(self, entries: Sequence[StepEntry], check_status: bool = True) -> torch.Tensor:
         """Runs one batch; returns float32 logits [wanted places, vocab] on the device,
-        in the order of the entries and of each entry's `want`."""
+        in the order of the entries and of each entry's `want`. The tensor may be
+        reused by a later step; copy what must outlive the next call."""
         entries = [e if isinstance(e, StepEntry) else StepEntry(*e) for e in entries]
         if not entries:
             return torch.empty((0, self.spec.vocab_size), dtype=torch.float32, device=self.device)
@@ -165,8 +213,11 @@ class Engine:
             for e in entries:
                 self.cache.prepare(e.request_id, len(e.tokens))
                 prepared.append(e.request_id)
-            batch = self.make_batch(entries)
-            logits = self.model.forward(batch, self._views)
+            if self._graph_eligible(entries):
+                logits = self._graph_step(entries)
+            else:
+                batch = self.make_batch(entries)
+                logits = self.model.forward(batch, self._views)
             if check_status:
                 self.raise_on_status()
         except Exception:
@@ -177,6 +228,50 @@ class Engine:
             self.cache.commit(e.request_id)
         self.steps_run += 1
         return logits
+
+    def decode_on_device(self, request_ids, first_tokens, n_steps: int, rows, sampler) -> torch.Tensor:
+        """Runs `n_steps` decode steps for the given requests without the host in the
+        loop: each step's sampled tokens feed the next step on the device. `rows[i] =
+        (GenerationConfig, tokens emitted so far)` as for `Sampler.sample`. Pages for all
+        steps are taken first. Returns the sampled tokens, int32 [n_steps, requests]."""
+        b = len(request_ids)
+        entries = [StepEntry(rid, [int(t)], [0]) for rid, t in zip(request_ids, first_tokens)]
+        self._check_entries(entries)
+        for e in entries:
+            if self.cache.get(e.request_id).length + n_steps > self.max_seq_len:
+                raise QuantInferError(f"request {e.request_id!r}: {n_steps} more tokens exceed the limit of {self.max_seq_len} positions")
+        prepared = []
+        try:
+            for e in entries:
+                self.cache.prepare(e.request_id, n_steps)
+                prepared.append(e.request_id)
+            logits = self._graph_step(entries)          # step 0 (captures the graph at first use)
+            g = self._graphs[b]
+            lay = g["layout"]
+
+            def part(name):
+                o, n = lay[name]
+                return g["meta"][o:o + n]
+
+            params = sampler.device_params(rows)
+            history = torch.empty((n_steps, b), dtype=torch.int32, device=self.device)
+            for i in range(n_steps):
+                if i:
+                    g["graph"].replay()
+                    kernels.launches += g["launches"]
+                    logits = g["logits"]
+                tokens = sampler.sample_with(logits, params)
+                kernels.advance_decode(part("token_ids"), part("positions"), part("start_pos"), part("kv_len"),
+                                       params["counter"], tokens, history[i])
+            self.raise_on_status()
+        except Exception:
+            for rid in prepared:
+                self.cache.rollback(rid)
+            raise
+        for e in entries:
+            self.cache.commit(e.request_id)
+        self.steps_run += n_steps
+        return history
 
     def raise_on_status(self) -> None:
         """Reads the device status word (this waits for the step) and raises if a kernel set a bit."""

@@ -67,7 +67,12 @@ def _stream() -> C.c_void_p:
     return C.c_void_p(torch.cuda.current_stream().cuda_stream)
 
 
+launches = 0   # entry points called so far (each launches at least one kernel)
+
+
 def _check(rc: int, name: str) -> None:
+    global launches
+    launches += 1
     if rc != 0:
         raise KernelError(f"{name}: {library().qi_last_error().decode()}")
 
@@ -309,6 +314,18 @@ def sample(logits, temperature, top_k, top_p, seed, counter, out_token, status) 
     rc = library().qi_sample(_ptr(logits), rows, vocab, _ptr(temperature), _ptr(top_k), _ptr(top_p),
                              _ptr(seed), _ptr(counter), _ptr(out_token), _ptr(status), _stream())
     _check(rc, "sample")
+
+
+def advance_decode(token_ids, positions, start_pos, kv_len, counter, sampled, history) -> None:
+    """In place, for a decode batch kept on the device: token_ids = sampled, positions,
+    start_pos and kv_len + 1, counter + 1 (may be None), history = sampled (may be None)."""
+    for t, name in ((token_ids, "token_ids"), (positions, "positions"), (start_pos, "start_pos"),
+                    (kv_len, "kv_len"), (sampled, "sampled")):
+        _req(t, name, torch.int32, 1)
+    b = token_ids.numel()
+    rc = library().qi_advance_decode(_ptr(token_ids), _ptr(positions), _ptr(start_pos), _ptr(kv_len),
+                                     _ptr(counter), _ptr(sampled), _ptr(history), b, _stream())
+    _check(rc, "advance_decode")
 
 
 # --------------------------------------------------------------------------

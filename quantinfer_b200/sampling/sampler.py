@@ -35,11 +35,19 @@ class Sampler:
 
     def sample_async(self, logits: torch.Tensor, rows: Sequence[tuple]) -> torch.Tensor:
         """As `sample`, but returns the device tensor of tokens without waiting."""
+        return self.sample_with(logits, self.device_params(rows))
+
+    def sample_with(self, logits: torch.Tensor, params: dict) -> torch.Tensor:
+        out = torch.empty(logits.shape[0], dtype=torch.int32, device=self.device)
+        kernels.sample(logits, params["temperature"], params["top_k"], params["top_p"], params["seed"],
+                       params["counter"], out, self.status)
+        return out
+
+    def device_params(self, rows: Sequence[tuple]) -> dict:
+        """The per-row options as device arrays (None where every row is greedy)."""
         n = len(rows)
-        out = torch.empty(n, dtype=torch.int32, device=self.device)
         if all(cfg.temperature == 0.0 for cfg, _ in rows):
-            kernels.sample(logits, None, None, None, None, None, out, self.status)
-            return out
+            return {"temperature": None, "top_k": None, "top_p": None, "seed": None, "counter": None}
         # one int32 block: temperature bits | top_k | top_p bits | counter | seed lo/hi pairs
         buf = np.zeros(6 * n, dtype=np.int32)
         buf[0:n] = np.asarray([cfg.temperature for cfg, _ in rows], dtype=np.float32).view(np.int32)
@@ -48,6 +56,6 @@ class Sampler:
         buf[3 * n:4 * n] = [emitted for _, emitted in rows]
         buf[4 * n:6 * n] = np.asarray([cfg.seed for cfg, _ in rows], dtype=np.uint64).view(np.int32)
         dev = torch.from_numpy(buf).to(self.device)
-        kernels.sample(logits, dev[0:n].view(torch.float32), dev[n:2 * n], dev[2 * n:3 * n].view(torch.float32),
-                       dev[4 * n:6 * n].view(torch.int64), dev[3 * n:4 * n], out, self.status)
-        return out
+        return {"temperature": dev[0:n].view(torch.float32), "top_k": dev[n:2 * n],
+                "top_p": dev[2 * n:3 * n].view(torch.float32), "seed": dev[4 * n:6 * n].view(torch.int64),
+                "counter": dev[3 * n:4 * n]}
