@@ -12,6 +12,7 @@ Device arrays (int32), all views of one buffer that crosses in one copy:
     token_ids[n]   positions[n]   token_req[n]      per token (token_req: index of its entry)
     q_start[b+1]   start_pos[b]   kv_len[b]   slot_ids[b]      per entry
     logit_rows[r]                                    rows of the flattened batch whose logits are wanted
+    tile_req[t]    tile_q0[t]                        blocks of up to 64 query rows of one entry (longest context first)
     block_tables[g][b, max_blocks]                   per layer group
 """
 
@@ -31,6 +32,9 @@ class StepEntry:
     want: Sequence[int] = ()
 
 
+QUERY_TILE = 64   # query rows per CTA of the flash attention kernel
+
+
 def _align(n: int, a: int = 4) -> int:
     return (n + a - 1) // a * a
 
@@ -48,6 +52,8 @@ class StepBatch:
     kv_len: torch.Tensor
     slot_ids: torch.Tensor
     logit_rows: torch.Tensor
+    tile_req: torch.Tensor
+    tile_q0: torch.Tensor
     block_tables: list
     # host copies, for parts that choose a kernel or a grid by them
     h_q_start: list = field(default_factory=list)
@@ -71,9 +77,18 @@ def pack_batch(entries: Sequence[StepEntry], starts: Sequence[int], slots: Seque
     n = sum(lens)
     r = sum(len(e.want) for e in entries)
     n_groups = len(tables)
+    # blocks of QUERY_TILE query rows; those that read the most keys go first
+    tiles = []
+    a = 0
+    for i, ln in enumerate(lens):
+        for t0 in range(0, ln, QUERY_TILE):
+            tiles.append((-(starts[i] + min(t0 + QUERY_TILE, ln)), i, a + t0))
+        a += ln
+    tiles.sort()
     layout, off = {}, 0
     for name, size in (("token_ids", n), ("positions", n), ("token_req", n), ("q_start", b + 1),
-                       ("start_pos", b), ("kv_len", b), ("slot_ids", b), ("logit_rows", r)):
+                       ("start_pos", b), ("kv_len", b), ("slot_ids", b), ("logit_rows", r),
+                       ("tile_req", len(tiles)), ("tile_q0", len(tiles))):
         layout[name] = (off, size)
         off = _align(off + size)
     for g in range(n_groups):
@@ -91,6 +106,8 @@ def pack_batch(entries: Sequence[StepEntry], starts: Sequence[int], slots: Seque
     part("start_pos")[:] = starts
     part("kv_len")[:] = np.asarray(starts, dtype=np.int32) + np.asarray(lens, dtype=np.int32)
     part("slot_ids")[:] = slots
+    part("tile_req")[:] = [t[1] for t in tiles]
+    part("tile_q0")[:] = [t[2] for t in tiles]
     tok, pos, req, rows = part("token_ids"), part("positions"), part("token_req"), part("logit_rows")
     ri = 0
     for i, e in enumerate(entries):
@@ -119,6 +136,7 @@ def batch_from_packed(dev: torch.Tensor, layout: dict, entries, starts, slots, q
         token_ids=part("token_ids"), positions=part("positions"), token_req=part("token_req"),
         q_start=part("q_start"), start_pos=part("start_pos"), kv_len=part("kv_len"),
         slot_ids=part("slot_ids"), logit_rows=part("logit_rows"),
+        tile_req=part("tile_req"), tile_q0=part("tile_q0"),
         block_tables=[part(f"table{g}").view(b, max_blocks) for g in range(n_groups)],
         h_q_start=[int(x) for x in q_start], h_start_pos=list(starts), h_kv_len=kv,
         h_slot_ids=list(slots), max_q_len=max(lens) if lens else 0, max_kv_len=max(kv) if kv else 0,

@@ -274,6 +274,75 @@ def attention_generic(q, out, k_pages, v_pages, block_table, positions, token_re
     _check(rc, "attention_generic")
 
 
+def attention_mma_supported(nq: int, nkv: int, d: int) -> bool:
+    """Whether the tensor-core attention kernels take this geometry (bfloat16 only)."""
+    return bool(library().qi_attention_mma_supported(nq, nkv, d))
+
+
+def attention_prefill(q, out, k_pages, v_pages, block_table, q_start, start_pos, tile_req, tile_q0,
+                      nq, nkv, d, scale: float, window: int, status) -> None:
+    """Causal paged GQA flash attention (bfloat16, head size 64 or 128) for spans of any
+    length. `tile_req[i]`, `tile_q0[i]`: request index and first flat token of the i-th
+    block of up to 64 query rows."""
+    _req(q, "q", torch.bfloat16, 2)
+    _req(out, "out", torch.bfloat16, 2)
+    _req(k_pages, "k_pages", torch.bfloat16, 4)
+    _req(v_pages, "v_pages", torch.bfloat16, 4)
+    for t, name in ((block_table, "block_table"), (q_start, "q_start"), (start_pos, "start_pos"),
+                    (tile_req, "tile_req"), (tile_q0, "tile_q0")):
+        _req(t, name, torch.int32)
+    if q.shape[1] != nq * d or out.shape != q.shape:
+        raise KernelError(f"attention_prefill: q {tuple(q.shape)} does not match {nq} heads of {d}")
+    if k_pages.shape[1] != nkv or k_pages.shape[3] != d or k_pages.shape != v_pages.shape:
+        raise KernelError(f"attention_prefill: pages {tuple(k_pages.shape)} do not match {nkv} kv heads of {d}")
+    if tile_req.numel() != tile_q0.numel():
+        raise KernelError("attention_prefill: tile lists differ in length")
+    rc = library().qi_attention_prefill(
+        _ptr(q), _ptr(out), _ptr(k_pages), _ptr(v_pages), _ptr(block_table), block_table.shape[1],
+        k_pages.shape[2], k_pages.shape[0], _ptr(q_start), _ptr(start_pos), _ptr(tile_req), _ptr(tile_q0),
+        tile_req.numel(), nq, nkv, d, C.c_float(scale), int(window or 0), _ptr(status), _stream())
+    _check(rc, "attention_prefill")
+
+
+def attention_decode_plan(batch: int, nkv: int, max_kv_len: int):
+    """(keys per CTA, number of key ranges) for a decode batch: enough CTAs for 148 SMs,
+    ranges a multiple of 64 keys, independent of the requests' actual lengths."""
+    target = max(1, -(-296 // max(batch * nkv, 1)))
+    chunk = max(64, -(-(-(-max_kv_len // target)) // 64) * 64)
+    return chunk, -(-max_kv_len // chunk)
+
+
+def attention_decode(q, out, k_pages, v_pages, block_table, kv_len, q_start, nq, nkv, d, scale: float,
+                     window: int, chunk: int, n_splits: int, status, workspace=None) -> None:
+    """Paged GQA attention for one query token per request (bfloat16, head size 64 or
+    128), keys split into `n_splits` ranges of `chunk` positions. `workspace`: float32,
+    at least batch * nq * n_splits * (d + 2) elements (allocated when None)."""
+    _req(q, "q", torch.bfloat16, 2)
+    _req(out, "out", torch.bfloat16, 2)
+    _req(k_pages, "k_pages", torch.bfloat16, 4)
+    _req(v_pages, "v_pages", torch.bfloat16, 4)
+    for t, name in ((block_table, "block_table"), (kv_len, "kv_len"), (q_start, "q_start")):
+        _req(t, name, torch.int32)
+    batch = kv_len.numel()
+    if q.shape[1] != nq * d or out.shape != q.shape or q.shape[0] < batch:
+        raise KernelError(f"attention_decode: q {tuple(q.shape)} does not match {batch} requests, {nq} heads of {d}")
+    if k_pages.shape[1] != nkv or k_pages.shape[3] != d or k_pages.shape != v_pages.shape:
+        raise KernelError(f"attention_decode: pages {tuple(k_pages.shape)} do not match {nkv} kv heads of {d}")
+    need = batch * nq * n_splits * (d + 2)
+    if workspace is None:
+        workspace = torch.empty(need, dtype=torch.float32, device=q.device)
+    _req(workspace, "workspace", torch.float32, 1)
+    if workspace.numel() < need:
+        raise KernelError(f"attention_decode: workspace has {workspace.numel()} floats, {need} are needed")
+    ws_o = workspace
+    ws_ml = workspace[batch * nq * n_splits * d:]
+    rc = library().qi_attention_decode(
+        _ptr(q), _ptr(out), _ptr(k_pages), _ptr(v_pages), _ptr(block_table), block_table.shape[1],
+        k_pages.shape[2], k_pages.shape[0], _ptr(kv_len), _ptr(q_start), batch, nq, nkv, d, C.c_float(scale),
+        int(window or 0), chunk, n_splits, _ptr(ws_o), _ptr(ws_ml), _ptr(status), _stream())
+    _check(rc, "attention_decode")
+
+
 # --------------------------------------------------------------------------
 # feed-forward
 

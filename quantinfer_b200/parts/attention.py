@@ -89,6 +89,21 @@ class Attention(Part):
         return self.o(out)
 
     def attend(self, q, out, batch, cache, table):
+        """Picks the kernel: tensor-core kernels for bfloat16 with head size 64 or 128
+        (the split-key decode kernel when every entry is one token, else the flash
+        kernel), the 32-bit kernel for everything else."""
+        rt = self.runtime
+        if q.dtype == torch.bfloat16 and kernels.attention_mma_supported(self.nq, self.nkv, self.d):
+            if batch.all_decode:
+                chunk, splits = kernels.attention_decode_plan(batch.n_requests, self.nkv, batch.max_kv_len)
+                kernels.attention_decode(q, out, cache.k_pages, cache.v_pages, table, batch.kv_len, batch.q_start,
+                                         self.nq, self.nkv, self.d, self.scale, self.spec.window or 0, chunk,
+                                         splits, rt.status)
+            else:
+                kernels.attention_prefill(q, out, cache.k_pages, cache.v_pages, table, batch.q_start,
+                                          batch.start_pos, batch.tile_req, batch.tile_q0, self.nq, self.nkv,
+                                          self.d, self.scale, self.spec.window or 0, rt.status)
+            return
         kernels.attention_generic(q, out, cache.k_pages, cache.v_pages, table, batch.positions,
                                   batch.token_req, self.nq, self.nkv, self.d, self.scale,
                                   self.spec.window or 0, self.runtime.status)

@@ -37,9 +37,17 @@ TINY_CONFIGS = {
         max_position_embeddings=320, rms_norm_eps=3e-6, rope_theta=50000.0,
         tie_word_embeddings=False,
     ),
+    # head size 64: the size at which the bfloat16 path takes the tensor-core attention kernels
+    "D": dict(
+        architectures=["Qwen3ForCausalLM"], model_type="qwen3",
+        vocab_size=300, hidden_size=136, intermediate_size=200, num_hidden_layers=2,
+        num_attention_heads=4, num_key_value_heads=2, head_dim=64,
+        max_position_embeddings=384, rms_norm_eps=2e-6, rope_theta=100000.0,
+        tie_word_embeddings=True,
+    ),
 }
-SEEDS = {"A": 0, "B": 1, "C": 2}
-PAGE_SIZES = {"A": 16, "B": 8, "C": 32}
+SEEDS = {"A": 0, "B": 1, "C": 2, "D": 3}
+PAGE_SIZES = {"A": 16, "B": 8, "C": 32, "D": 16}
 
 
 def make_folder(path, name: str, dtype=torch.bfloat16) -> Path:

@@ -13,7 +13,8 @@ from trace_tools import (mixed_trace, plain_rows, portions_trace, round64, run_t
 pytestmark = pytest.mark.gpu
 
 TOL = {"float32": 2e-5, "bfloat16": 3e-2}
-LENGTHS = {"A": [70, 45, 100, 33, 128, 64, 17], "B": [71, 40, 9, 130, 200, 65, 2], "C": [150, 64, 33, 97, 255, 12]}
+LENGTHS = {"A": [70, 45, 100, 33, 128, 64, 17], "B": [71, 40, 9, 130, 200, 65, 2], "C": [150, 64, 33, 97, 255, 12],
+           "D": [130, 64, 300, 33, 65, 191, 5]}
 
 _plain_cache = {}
 
@@ -29,7 +30,7 @@ def _expect(folder, name):
     return _plain_cache[name]
 
 
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("family", ["whole", "tail", "portions", "mixed"])
 def test_replay_family(tiny_folders, name, dtype, family):

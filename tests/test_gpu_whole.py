@@ -14,7 +14,7 @@ TOL_F32 = 2e-5
 TOL_BF16 = 3e-2
 
 
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("length", [1, 5, 33, 100])
 def test_whole_prompt_matches_plain(tiny_folders, name, dtype, length):
