@@ -116,6 +116,8 @@ def main() -> int:
     ap.add_argument("--layers", type=int, default=None, help="run fewer layers than the configuration has (named in `config`)")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--skip-points", action="store_true", help="measure only the headline batch")
+    ap.add_argument("--only", choices=["decode", "prefill"], default=None,
+                    help="run one part only (for profiler captures of a small case)")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -173,9 +175,11 @@ def main() -> int:
     def prefill_flops(T):
         return 2.0 * T * L * layer_params + 4.0 * nq * d * (T * (T + 1) / 2) * L + 2.0 * H * vocab
 
+    if args.only:
+        args.skip_points = True
     # ---- prefill: one 2,048-token prompt in one step ---------------------------
     times = []
-    for i in range(2 + 3):
+    for i in range(0 if args.only == "decode" else 2 + 3):
         engine.open("p")
         toks = prompt()
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -188,7 +192,7 @@ def main() -> int:
         engine.close("p")
         if i >= 2:
             times.append(a.elapsed_time(b))
-    pre_ms = sorted(times)[len(times) // 2]
+    pre_ms = sorted(times)[len(times) // 2] if times else float("nan")
     prefill = {"value": PROMPT_LEN / pre_ms * 1e3, "tokens": PROMPT_LEN, "ms": pre_ms,
                "frac": prefill_flops(PROMPT_LEN) / (pre_ms * 1e-3) / (tf_peak * 1e12)}
 
@@ -223,6 +227,9 @@ def main() -> int:
             engine.close(rid)
         return batch * steps / ms * 1e3, ms / steps, launches, ck, ctx
 
+    if args.only == "prefill":
+        print(json.dumps({"only": "prefill", "prefill": prefill}))
+        return 0
     value, ms_per_step, launches, clocks, ctx_end = decode_rate(args.batch, args.steps, args.warmup, True)
     ctx_mid = ctx_end - args.steps / 2.0
     step_bytes = weight_bytes + args.batch * ctx_mid * kv_bytes_per_token
@@ -233,6 +240,9 @@ def main() -> int:
             r, _, _, _, _ = decode_rate(bsz, min(args.steps, 32), 3)
             points[f"decode_b{bsz}"] = r
 
+    if args.only == "decode":
+        print(json.dumps({"only": "decode", "value": value, "ms_per_step": ms_per_step, "gpu_launches": launches}))
+        return 0
     # ---- end to end through the Python entry point -----------------------------------
     model = Model.from_engine(engine, max_batch_tokens=PROMPT_LEN)
     prompts = [prompt() for _ in range(args.batch)]
