@@ -94,9 +94,9 @@ def test_admission_waits_for_pages_then_proceeds():
     s, model, cache = _sched(num_pages=6, page_size=4)    # 24 positions in all
     a = s.submit([1] * 8, GenerationConfig(max_new_tokens=8))     # 4 pages
     b = s.submit([2] * 8, GenerationConfig(max_new_tokens=8))     # 4 pages: must wait
-    s.step()
+    events = s.step()
     assert [r.id for r in s.running] == [a] and [r.id for r in s.waiting] == [b]
-    events = s.run()
+    events += s.run()
     assert len(_tokens(events, a)) == 8 and len(_tokens(events, b)) == 8
     first_b = next(i for i, batch in enumerate(model.batches) if any(r == b for r, _, _ in batch))
     last_a = max(i for i, batch in enumerate(model.batches) if any(r == a for r, _, _ in batch))
