@@ -165,7 +165,11 @@ struct Smem {
     static constexpr int kTotal = STAGES * kStageBytes + kBarrierBytes + 1024;  // + alignment slack
 };
 
-template <int BN, int STAGES, bool SWAP, typename TOut>
+__device__ __forceinline__ float silu_mul(float g, float u) { return g / (1.0f + expf(-g)) * u; }
+
+// EPI = 0: store the product. EPI = 1: the product's columns come in pairs (gate, up) and
+// the kernel stores silu(gate) * up, half as wide (the feed-forward's activation fused in).
+template <int BN, int STAGES, bool SWAP, typename TOut, int EPI>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                     TOut* __restrict__ out, int rows_a, int rows_b, int K, long long ld_out,
@@ -288,12 +292,47 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             }
             if (!ok) continue;
             const int b0 = tile_b * BN + c0;
-            if (SWAP) {
+            if (SWAP && EPI == 1) {
+                // rows of A come in pairs (gate, up): even lanes hold gate, their neighbours up
+#pragma unroll
+                for (int j = 0; j < kChunk; ++j) {
+                    const float mine = __uint_as_float(r[j]);
+                    const float other = __shfl_xor_sync(0xffffffffu, mine, 1);
+                    if ((lane & 1) == 0 && a_row + 1 < rows_a && b0 + j < rows_b)
+                        store1<TOut>(obase + (size_t)(b0 + j) * ld_out + (a_row >> 1), silu_mul(mine, other));
+                }
+            } else if (SWAP) {
                 // out[b, a]: for a fixed column the warp's lanes write consecutive addresses
                 if (a_row < rows_a) {
 #pragma unroll
                     for (int j = 0; j < kChunk; ++j)
                         if (b0 + j < rows_b) store1<TOut>(obase + (size_t)(b0 + j) * ld_out + a_row, __uint_as_float(r[j]));
+                }
+            } else if (EPI == 1) {
+                if (a_row < rows_a) {
+                    TOut* orow = obase + (size_t)a_row * ld_out + (b0 >> 1);
+                    const bool full = b0 + kChunk <= rows_b;
+                    const bool aligned16 = ((reinterpret_cast<uintptr_t>(orow) & 15u) == 0);
+                    if (full && aligned16 && sizeof(TOut) == 2) {
+#pragma unroll
+                        for (int j = 0; j < kChunk; j += 16) {
+                            uint4 v;
+                            uint32_t* vw = reinterpret_cast<uint32_t*>(&v);
+#pragma unroll
+                            for (int q = 0; q < 4; ++q) {
+                                __nv_bfloat162 pr = __floats2bfloat162_rn(
+                                    silu_mul(__uint_as_float(r[j + 4 * q]), __uint_as_float(r[j + 4 * q + 1])),
+                                    silu_mul(__uint_as_float(r[j + 4 * q + 2]), __uint_as_float(r[j + 4 * q + 3])));
+                                vw[q] = *reinterpret_cast<uint32_t*>(&pr);
+                            }
+                            *reinterpret_cast<uint4*>(reinterpret_cast<qi::bf16*>(orow) + (j >> 1)) = v;
+                        }
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < kChunk; j += 2)
+                            if (b0 + j + 1 < rows_b)
+                                store1<TOut>(orow + (j >> 1), silu_mul(__uint_as_float(r[j]), __uint_as_float(r[j + 1])));
+                    }
                 }
             } else {
                 if (a_row < rows_a) {
@@ -375,10 +414,10 @@ int make_map(CUtensorMap* map, const void* ptr, int rows, int K, int box_rows) {
     return 0;
 }
 
-template <int BN, int STAGES, bool SWAP, typename TOut>
+template <int BN, int STAGES, bool SWAP, typename TOut, int EPI>
 int launch(const CUtensorMap& ma, const CUtensorMap& mb, TOut* out, int rows_a, int rows_b, int K, long long ld,
            int splits, int kb_per_split, long long split_stride, int* status, cudaStream_t stream) {
-    auto kern = gemm_tcgen05_kernel<BN, STAGES, SWAP, TOut>;
+    auto kern = gemm_tcgen05_kernel<BN, STAGES, SWAP, TOut, EPI>;
     constexpr int smem = Smem<BN, STAGES>::kTotal;
     static bool configured = false;
     if (!configured) {
@@ -391,15 +430,15 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, TOut* out, int rows_a, 
     return qi::check_launch("gemm_bf16");
 }
 
-template <bool SWAP, typename TOut>
+template <bool SWAP, typename TOut, int EPI = 0>
 int launch_bn(int bn, const CUtensorMap& ma, const CUtensorMap& mb, TOut* out, int rows_a, int rows_b, int K,
               long long ld, int splits, int kb_per_split, long long split_stride, int* status, cudaStream_t stream) {
     switch (bn) {
-        case 16: return launch<16, 8, SWAP, TOut>(ma, mb, out, rows_a, rows_b, K, ld, splits, kb_per_split, split_stride, status, stream);
-        case 32: return launch<32, 8, SWAP, TOut>(ma, mb, out, rows_a, rows_b, K, ld, splits, kb_per_split, split_stride, status, stream);
-        case 64: return launch<64, 8, SWAP, TOut>(ma, mb, out, rows_a, rows_b, K, ld, splits, kb_per_split, split_stride, status, stream);
-        case 128: return launch<128, 6, SWAP, TOut>(ma, mb, out, rows_a, rows_b, K, ld, splits, kb_per_split, split_stride, status, stream);
-        case 256: return launch<256, 4, SWAP, TOut>(ma, mb, out, rows_a, rows_b, K, ld, splits, kb_per_split, split_stride, status, stream);
+        case 16: return launch<16, 8, SWAP, TOut, EPI>(ma, mb, out, rows_a, rows_b, K, ld, splits, kb_per_split, split_stride, status, stream);
+        case 32: return launch<32, 8, SWAP, TOut, EPI>(ma, mb, out, rows_a, rows_b, K, ld, splits, kb_per_split, split_stride, status, stream);
+        case 64: return launch<64, 8, SWAP, TOut, EPI>(ma, mb, out, rows_a, rows_b, K, ld, splits, kb_per_split, split_stride, status, stream);
+        case 128: return launch<128, 6, SWAP, TOut, EPI>(ma, mb, out, rows_a, rows_b, K, ld, splits, kb_per_split, split_stride, status, stream);
+        case 256: return launch<256, 4, SWAP, TOut, EPI>(ma, mb, out, rows_a, rows_b, K, ld, splits, kb_per_split, split_stride, status, stream);
     }
     return qi::fail("gemm_bf16: no kernel for a tile width of %d", bn);
 }
@@ -424,13 +463,18 @@ extern "C" int qi_gemm_bf16_plan(int M, int N, int K, int* swap, int* bn, int* s
 
 // y[M, N] = x[M, K] . w[N, K]^T, bf16 operands, out bf16 or float32 (out_dtype).
 // With splits > 1, `workspace` must hold splits * M * N floats.
+// epilogue 1: w's rows come in (gate, up) pairs and out[M, N / 2] = silu(gate) * up (bf16, no split).
+// out may be null with splits > 1: the partial sums stay in the workspace for the consumer.
 extern "C" int qi_gemm_bf16(const void* x, const void* w, void* out, int out_dtype, int M, int N, int K,
-                            int swap, int bn, int splits, void* workspace, int* status, cudaStream_t stream) {
+                            int swap, int bn, int splits, int epilogue, void* workspace, int* status,
+                            cudaStream_t stream) {
     QI_REQUIRE(M > 0 && N > 0 && K > 0, "gemm_bf16: bad sizes M=%d N=%d K=%d", M, N, K);
     QI_REQUIRE(K % 8 == 0, "gemm_bf16: K=%d must be a multiple of 8 (16-byte rows for TMA)", K);
     QI_REQUIRE(((uintptr_t)x & 15) == 0 && ((uintptr_t)w & 15) == 0, "gemm_bf16: operands must be 16-byte aligned");
     QI_REQUIRE(splits >= 1 && (splits == 1 || workspace), "gemm_bf16: split-K needs a workspace");
     QI_REQUIRE(out_dtype == qi::kF32 || out_dtype == qi::kBF16, "gemm_bf16: output type must be float32 or bfloat16");
+    QI_REQUIRE(epilogue == 0 || (epilogue == 1 && splits == 1 && out_dtype == qi::kBF16 && N % 2 == 0 && out),
+               "gemm_bf16: the fused activation needs bfloat16 output, an even N and no K split");
     const int kb_total = (K + BK - 1) / BK;
     const int kb_per_split = (kb_total + splits - 1) / splits;
     QI_REQUIRE((splits - 1) * kb_per_split < kb_total, "gemm_bf16: %d splits leave one without work (K=%d)", splits, K);
@@ -457,6 +501,9 @@ extern "C" int qi_gemm_bf16(const void* x, const void* w, void* out, int out_dty
         }
         return 0;
     }
+    if (epilogue == 1)
+        return swap ? launch_bn<true, qi::bf16, 1>(bn, ma, mb, (qi::bf16*)out, rows_a, rows_b, K, N / 2, 1, kb_per_split, 0, status, stream)
+                    : launch_bn<false, qi::bf16, 1>(bn, ma, mb, (qi::bf16*)out, rows_a, rows_b, K, N / 2, 1, kb_per_split, 0, status, stream);
     if (out_dtype == qi::kF32)
         return swap ? launch_bn<true, float>(bn, ma, mb, (float*)out, rows_a, rows_b, K, N, 1, kb_per_split, 0, status, stream)
                     : launch_bn<false, float>(bn, ma, mb, (float*)out, rows_a, rows_b, K, N, 1, kb_per_split, 0, status, stream);

@@ -97,6 +97,87 @@ __global__ void qk_norm_rope_kv_kernel(
     }
 }
 
+// Two adjacent elements per access (head_dim a multiple of 4, rotation over the whole head).
+template <typename T> struct Pair;
+template <> struct Pair<float> {
+    static __device__ __forceinline__ float2 load(const float* p) { return *reinterpret_cast<const float2*>(p); }
+    static __device__ __forceinline__ void store(float* p, float a, float b) { *reinterpret_cast<float2*>(p) = make_float2(a, b); }
+};
+template <> struct Pair<qi::bf16> {
+    static __device__ __forceinline__ float2 load(const qi::bf16* p) {
+        return __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(p));
+    }
+    static __device__ __forceinline__ void store(qi::bf16* p, float a, float b) {
+        *reinterpret_cast<__nv_bfloat162*>(p) = __floats2bfloat162_rn(a, b);
+    }
+};
+
+template <typename T>
+__global__ void qk_norm_rope_kv_vec_kernel(
+    const T* __restrict__ qkv, T* __restrict__ q_out, const float* __restrict__ q_gain,
+    const float* __restrict__ k_gain, float eps, const float* __restrict__ cos_t,
+    const float* __restrict__ sin_t, const int* __restrict__ positions,
+    const int* __restrict__ token_req, const int* __restrict__ block_table, int max_blocks,
+    int page_size, int num_pages, T* __restrict__ k_pages, T* __restrict__ v_pages, int nq, int nkv,
+    int d, int* __restrict__ status) {
+    const int t = blockIdx.x;
+    const int head = blockIdx.y * kWarpsPerBlock + (threadIdx.x >> 5);
+    const int lane = threadIdx.x & 31;
+    const int total_heads = nq + 2 * nkv;
+    if (head >= total_heads) return;
+    const T* src = qkv + (size_t)t * total_heads * d + (size_t)head * d;
+    const int pos = positions[t];
+    const bool is_q = head < nq;
+    const bool is_k = !is_q && head < nq + nkv;
+    T* dst;
+    if (is_q) {
+        dst = q_out + (size_t)t * nq * d + (size_t)head * d;
+    } else {
+        if (k_pages == nullptr) return;
+        const int hk = is_k ? head - nq : head - nq - nkv;
+        const int page = block_table[(size_t)token_req[t] * max_blocks + pos / page_size];
+        if (page < 0 || page >= num_pages) {
+            if (lane == 0 && status) atomicOr(status, qi::kStatusBadPage);
+            return;
+        }
+        dst = (is_k ? k_pages : v_pages) + (((size_t)page * nkv + hk) * page_size + (pos % page_size)) * (size_t)d;
+    }
+    if (!is_q && !is_k) {
+        for (int i = 2 * lane; i < d; i += 64) {
+            const float2 v = Pair<T>::load(src + i);
+            Pair<T>::store(dst + i, v.x, v.y);
+        }
+        return;
+    }
+    const int half = d / 2;
+    const float* gain = is_q ? q_gain : k_gain;
+    float inv = 1.f;
+    if (gain) {
+        float ss = 0.f;
+        for (int i = 2 * lane; i < d; i += 64) {
+            const float2 v = Pair<T>::load(src + i);
+            ss += v.x * v.x + v.y * v.y;
+        }
+        ss = qi::warp_sum(ss);
+        inv = 1.0f / sqrtf(ss / (float)d + eps);
+    }
+    for (int p = 2 * lane; p < half; p += 64) {
+        float2 a = Pair<T>::load(src + p), b = Pair<T>::load(src + p + half);
+        if (gain) {
+            const float2 ga = *reinterpret_cast<const float2*>(gain + p), gb = *reinterpret_cast<const float2*>(gain + p + half);
+            a.x = a.x * inv * ga.x; a.y = a.y * inv * ga.y;
+            b.x = b.x * inv * gb.x; b.y = b.y * inv * gb.y;
+        }
+        float2 c = make_float2(1.f, 1.f), sn = make_float2(0.f, 0.f);
+        if (cos_t) {
+            c = *reinterpret_cast<const float2*>(cos_t + (size_t)pos * half + p);
+            sn = *reinterpret_cast<const float2*>(sin_t + (size_t)pos * half + p);
+        }
+        Pair<T>::store(dst + p, a.x * c.x - b.x * sn.x, a.y * c.y - b.y * sn.y);
+        Pair<T>::store(dst + p + half, a.x * sn.x + b.x * c.x, a.y * sn.y + b.y * c.y);
+    }
+}
+
 __global__ void rope_table_kernel(const float* __restrict__ inv_freq, float* __restrict__ cos_t,
                                   float* __restrict__ sin_t, int max_pos, int half) {
     const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -138,6 +219,15 @@ extern "C" int qi_qk_norm_rope_kv(const void* qkv, void* q_out, int dtype, const
     dim3 grid(n_tokens, (heads + kWarpsPerBlock - 1) / kWarpsPerBlock);
     QI_REQUIRE(grid.y <= 65535, "qk_norm_rope_kv: too many heads");
     if (!cos_t) rot = 0;
+    if (d % 4 == 0 && (rot == d || rot == 0) && ((uintptr_t)qkv & 7) == 0 && ((uintptr_t)q_out & 7) == 0 &&
+        ((uintptr_t)k_pages & 7) == 0 && ((uintptr_t)v_pages & 7) == 0) {
+        QI_DISPATCH_DTYPE(dtype, T, {
+            qk_norm_rope_kv_vec_kernel<T><<<grid, kWarpsPerBlock * 32, 0, stream>>>(
+                (const T*)qkv, (T*)q_out, q_gain, k_gain, eps, cos_t, sin_t, positions, token_req,
+                block_table, max_blocks, page_size, num_pages, (T*)k_pages, (T*)v_pages, nq, nkv, d, status);
+        });
+        return qi::check_launch("qk_norm_rope_kv");
+    }
     QI_DISPATCH_DTYPE(dtype, T, {
         qk_norm_rope_kv_kernel<T><<<grid, kWarpsPerBlock * 32, 0, stream>>>(
             (const T*)qkv, (T*)q_out, q_gain, k_gain, eps, cos_t, sin_t, rot, positions, token_req,

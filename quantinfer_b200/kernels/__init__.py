@@ -24,7 +24,7 @@ STATUS_BAD_PAGE = 2
 STATUS_NON_FINITE = 4
 STATUS_WAIT_TIMEOUT = 8
 
-ABI_VERSION = 1
+ABI_VERSION = 2
 
 _lib = None
 _lib_lock = threading.Lock()
@@ -347,14 +347,15 @@ def attention_decode(q, out, k_pages, v_pages, block_table, kv_len, q_start, nq,
 # feed-forward
 
 
-def silu_mul(gate_up: torch.Tensor, out: torch.Tensor) -> None:
-    """out[t, i] = silu(gate_up[t, i]) * gate_up[t, I + i]."""
+def silu_mul(gate_up: torch.Tensor, out: torch.Tensor, interleaved: bool = False) -> None:
+    """out[t, i] = silu(gate[t, i]) * up[t, i]; gate, up = gate_up[t, i], gate_up[t, I + i],
+    or gate_up[t, 2i], gate_up[t, 2i + 1] when `interleaved`."""
     _req(gate_up, "gate_up", ndim=2)
     _req(out, "out", gate_up.dtype, 2)
     n, two_i = gate_up.shape
     if two_i % 2 or tuple(out.shape) != (n, two_i // 2):
         raise KernelError(f"silu_mul: gate_up {tuple(gate_up.shape)} / out {tuple(out.shape)} do not agree")
-    rc = library().qi_silu_mul(_ptr(gate_up), _ptr(out), _code(out), n, two_i // 2, _stream())
+    rc = library().qi_silu_mul(_ptr(gate_up), _ptr(out), _code(out), n, two_i // 2, int(bool(interleaved)), _stream())
     _check(rc, "silu_mul")
 
 
@@ -415,22 +416,37 @@ def gemm_bf16_plan(M: int, N: int, K: int):
     return bool(swap.value), bn.value, splits.value
 
 
-def gemm_bf16(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, plan=None, status=None) -> None:
-    """out[M, N] = x[M, K] @ w[N, K]^T on the tcgen05 tensor cores; x, w bfloat16;
-    out bfloat16 or float32. `plan` = (swap, tile width, splits) overrides the choice."""
+def gemm_bf16(x: torch.Tensor, w: torch.Tensor, out, plan=None, status=None, epilogue: str | None = None,
+              keep_partials: bool = False):
+    """out[M, N] = x[M, K] @ w[N, K]^T on the tcgen05 tensor cores; x, w bfloat16; out
+    bfloat16 or float32. `plan` = (swap, tile width, splits) overrides the choice.
+
+    epilogue="silu_mul": w's rows are (gate, up) pairs and out is [M, N / 2] =
+    silu(gate) * up. keep_partials=True: when the plan splits K, the float32 partial sums
+    [splits, M, N] are returned unreduced (and `out` is not written); else `out` is returned."""
     _req(x, "x", torch.bfloat16, 2)
     _req(w, "w", torch.bfloat16, 2)
-    _req(out, "out", ndim=2)
     M, K = x.shape
     N = w.shape[0]
-    if w.shape[1] != K or tuple(out.shape) != (M, N):
-        raise KernelError(f"gemm: shapes do not agree: x {tuple(x.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}")
     swap, bn, splits = plan if plan is not None else gemm_bf16_plan(M, N, K)
+    epi = 0
+    if epilogue == "silu_mul":
+        epi, splits = 1, 1
+    elif epilogue is not None:
+        raise KernelError(f"gemm_bf16: unknown epilogue {epilogue!r}")
+    n_out = N // 2 if epi else N
+    partial_only = keep_partials and splits > 1
+    if not partial_only:
+        _req(out, "out", ndim=2)
+        if w.shape[1] != K or tuple(out.shape) != (M, n_out):
+            raise KernelError(f"gemm: shapes do not agree: x {tuple(x.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}")
     ws = torch.empty((splits, M, N), dtype=torch.float32, device=x.device) if splits > 1 else None
     if status is None:
         status = _gemm_status.get(x.device)
         if status is None:
             status = _gemm_status[x.device] = torch.zeros(1, dtype=torch.int32, device=x.device)
-    rc = library().qi_gemm_bf16(_ptr(x), _ptr(w), _ptr(out), _code(out), M, N, K, int(swap), bn, splits,
+    rc = library().qi_gemm_bf16(_ptr(x), _ptr(w), _ptr(None if partial_only else out),
+                                BF16 if partial_only else _code(out), M, N, K, int(swap), bn, splits, epi,
                                 _ptr(ws), _ptr(status), _stream())
     _check(rc, "gemm_bf16")
+    return ws if partial_only else out

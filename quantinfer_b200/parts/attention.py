@@ -86,7 +86,7 @@ class Attention(Part):
             self.nq, self.nkv, self.d, rt.status)
         out = torch.empty_like(q)
         self.attend(q, out, batch, cache, table)
-        return self.o(out)
+        return self.o(out, keep_partials=True)
 
     def attend(self, q, out, batch, cache, table):
         """Picks the kernel: tensor-core kernels for bfloat16 with head size 64 or 128

@@ -1,7 +1,8 @@
 """Gated feed-forward (SwiGLU): y = down(silu(gate(x)) * up(x)), no biases.
 
-gate and up are stacked into one [2I, H] weight at load so that one product
-feeds the activation kernel. The reference runs them as two products followed
+gate and up are interleaved row by row into one [2I, H] weight at load (row 2i
+gate, row 2i + 1 up), so that one product computes both and the thread that
+holds a (gate, up) pair applies the activation in the product's epilogue. The reference runs them as two products followed
 by silu(g) * u in the division form and the down projection
 (crates/quantinfer-runtime/src/qwen3/mod.rs:194-209; backends/cpu/src/backend.rs:224-238).
 """
@@ -40,14 +41,11 @@ class GatedMLP(Part):
         g, u = tensors[p + "gate_proj.weight"], tensors[p + "up_proj.weight"]
         if g.dtype != u.dtype:
             g, u = g.to(torch.float32), u.to(torch.float32)
-        self.gate_up.load(torch.cat([g, u], dim=0))
+        self.gate_up.load(torch.stack([g, u], dim=1).reshape(2 * g.shape[0], g.shape[1]))
         self.down.load(tensors[p + "down_proj.weight"])
 
     def forward(self, x):
-        gu = self.gate_up(x)
-        act = torch.empty((x.shape[0], self.spec.intermediate_size), dtype=x.dtype, device=x.device)
-        kernels.silu_mul(gu, act)
-        return self.down(act)
+        return self.down(self.gate_up.forward_silu_mul(x), keep_partials=True)
 
     __call__ = forward
 

@@ -39,17 +39,35 @@ class Linear:
             w = w.to(device=rt.device)  # bfloat16 stays bfloat16, a 32-bit tensor stays 32-bit
         self.weight = w.contiguous()
 
-    def forward(self, x: torch.Tensor, out_dtype=None, out=None) -> torch.Tensor:
+    def tensor_core(self, x: torch.Tensor, out_dtype) -> bool:
+        return (x.dtype == torch.bfloat16 and self.weight.dtype == torch.bfloat16 and x.shape[0] > 0
+                and kernels.gemm_bf16_supported(x.shape[0], self.out_features, self.in_features, out_dtype))
+
+    def forward(self, x: torch.Tensor, out_dtype=None, keep_partials: bool = False) -> torch.Tensor:
+        """y = x . W^T. With keep_partials the result may come back as float32 partial sums
+        [splits, tokens, out] of a K-split product, for a consumer that adds them itself
+        (the fused add + norm does)."""
         out_dtype = out_dtype or x.dtype
-        if out is None:
-            out = torch.empty((x.shape[0], self.out_features), dtype=out_dtype, device=x.device)
+        out = torch.empty((x.shape[0], self.out_features), dtype=out_dtype, device=x.device)
         if x.shape[0] == 0:
             return out
-        if (x.dtype == torch.bfloat16 and self.weight.dtype == torch.bfloat16
-                and kernels.gemm_bf16_supported(x.shape[0], self.out_features, self.in_features, out.dtype)):
-            kernels.gemm_bf16(x, self.weight, out)
-        else:
-            kernels.gemm_simt(x, self.weight, out)
+        if self.tensor_core(x, out_dtype):
+            return kernels.gemm_bf16(x, self.weight, out, status=self.runtime.status, keep_partials=keep_partials)
+        kernels.gemm_simt(x, self.weight, out)
         return out
+
+    def forward_silu_mul(self, x: torch.Tensor) -> torch.Tensor:
+        """silu(gate) * up of a projection whose weight rows are (gate, up) pairs: [tokens, out / 2]."""
+        half = self.out_features // 2
+        act = torch.empty((x.shape[0], half), dtype=x.dtype, device=x.device)
+        if x.shape[0] == 0:
+            return act
+        if self.tensor_core(x, x.dtype):
+            kernels.gemm_bf16(x, self.weight, act, status=self.runtime.status, epilogue="silu_mul")
+            return act
+        gu = torch.empty((x.shape[0], self.out_features), dtype=x.dtype, device=x.device)
+        kernels.gemm_simt(x, self.weight, gu)
+        kernels.silu_mul(gu, act, interleaved=True)
+        return act
 
     __call__ = forward
