@@ -2,7 +2,8 @@
 // m16n8k16, 32-bit scores, softmax and accumulation), for head sizes 64 and 128:
 //
 //  * attention_prefill: causal flash attention for spans of any length. One CTA
-//    takes 64 query rows of one request and one query head and walks the keys
+//    takes 64 query rows of one request (a part of a tile of the batch's tile
+//    list) and one query head and walks the keys
 //    0 .. position in tiles of 64, with the softmax evaluated online.
 //  * attention_decode: one query token per request. One CTA takes one request,
 //    one kv head (all query heads of its group share every key and value read)
@@ -21,16 +22,12 @@
 // Keys and values are fetched with cp.async through the request's block table
 // (page = table[position / page_size]), so any page size works; rows are kept in
 // shared memory with a 16-byte-chunk XOR swizzle and read with ldmatrix.
-#include "common.cuh"
-
-#include <math.h>
+#include "attention_frag.cuh"
 
 namespace {
 
 constexpr int kTileKeys = 64;
 constexpr int kThreads = 128;
-
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
@@ -38,29 +35,9 @@ __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
-__device__ __forceinline__ void ldmatrix_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
-    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
-                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
-}
-__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
-    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
-                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
-}
-__device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
-    asm volatile(
-        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
-        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
-}
-__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
-    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
-    return *reinterpret_cast<uint32_t*>(&v);
-}
+using namespace qi_attn;
 
-// Byte offset of 16-byte chunk `chunk` of row `row` in a [rows, D] bf16 tile.
-template <int D> __device__ __forceinline__ uint32_t swz(int row, int chunk) {
-    return (uint32_t)(row * (D * 2) + ((chunk ^ (row & 7)) << 4));
-}
+template <int D> __device__ __forceinline__ uint32_t swz(int row, int chunk) { return RowSwizzle<D>::off(row, chunk); }
 
 // Copies keys [t0, t0 + 64) of one kv head into a shared tile; rows outside [vlo, vhi) are zeroed.
 template <int D>
@@ -87,94 +64,6 @@ __device__ __forceinline__ void load_kv_tile(uint32_t dst, const qi::bf16* __res
     }
 }
 
-// One warp: scores of its 16 query rows against NT * 8 keys starting at tile row `krow0`.
-template <int D, int NT>
-__device__ __forceinline__ void qk_tile(float (&s)[NT][4], const uint32_t (&qa)[D / 16][4], uint32_t k_smem, int krow0, int lane) {
-#pragma unroll
-    for (int j = 0; j < NT; ++j)
-#pragma unroll
-        for (int e = 0; e < 4; ++e) s[j][e] = 0.f;
-#pragma unroll
-    for (int ks = 0; ks < D / 16; ++ks) {
-#pragma unroll
-        for (int jp = 0; jp < NT / 2; ++jp) {
-            uint32_t r0, r1, r2, r3;
-            const int row = krow0 + jp * 16 + (lane & 7) + (lane >> 4) * 8;
-            const int chunk = ks * 2 + ((lane >> 3) & 1);
-            ldmatrix_x4(k_smem + swz<D>(row, chunk), r0, r1, r2, r3);
-            mma_bf16(s[2 * jp], qa[ks], r0, r1);
-            mma_bf16(s[2 * jp + 1], qa[ks], r2, r3);
-        }
-    }
-}
-
-// One warp: o += p . v for its 16 rows and NT * 8 keys starting at tile row `krow0`.
-template <int D, int NT>
-__device__ __forceinline__ void pv_tile(float (&o)[D / 8][4], const float (&p)[NT][4], uint32_t v_smem, int krow0, int lane) {
-#pragma unroll
-    for (int kk = 0; kk < NT / 2; ++kk) {
-        uint32_t pa[4];
-        pa[0] = pack_bf16(p[2 * kk][0], p[2 * kk][1]);
-        pa[1] = pack_bf16(p[2 * kk][2], p[2 * kk][3]);
-        pa[2] = pack_bf16(p[2 * kk + 1][0], p[2 * kk + 1][1]);
-        pa[3] = pack_bf16(p[2 * kk + 1][2], p[2 * kk + 1][3]);
-#pragma unroll
-        for (int nd = 0; nd < D / 16; ++nd) {
-            uint32_t r0, r1, r2, r3;
-            const int row = krow0 + kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
-            const int chunk = nd * 2 + (lane >> 4);
-            ldmatrix_x4_trans(v_smem + swz<D>(row, chunk), r0, r1, r2, r3);
-            mma_bf16(o[2 * nd], pa, r0, r1);
-            mma_bf16(o[2 * nd + 1], pa, r2, r3);
-        }
-    }
-}
-
-// Online softmax over one tile of scores (already scaled by scale * log2 e, masked with
-// -inf): updates the running maximum m and sum l of the two rows this thread holds
-// (g and g + 8), rescales o, and leaves the weights in s.
-template <int D, int NT>
-__device__ __forceinline__ void softmax_tile(float (&s)[NT][4], float (&m)[2], float (&l)[2], float (&o)[D / 8][4]) {
-    float mx[2] = {-INFINITY, -INFINITY};
-#pragma unroll
-    for (int j = 0; j < NT; ++j) {
-        mx[0] = fmaxf(mx[0], fmaxf(s[j][0], s[j][1]));
-        mx[1] = fmaxf(mx[1], fmaxf(s[j][2], s[j][3]));
-    }
-#pragma unroll
-    for (int r = 0; r < 2; ++r) {
-        mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
-        mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
-    }
-    float corr[2], mn[2];
-#pragma unroll
-    for (int r = 0; r < 2; ++r) {
-        mn[r] = fmaxf(m[r], mx[r]);
-        corr[r] = (m[r] == -INFINITY) ? 0.f : exp2f(m[r] - mn[r]);   // mn is finite whenever m is
-        m[r] = mn[r];
-    }
-    float sum[2] = {0.f, 0.f};
-#pragma unroll
-    for (int j = 0; j < NT; ++j) {
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-            const int r = e >> 1;
-            const float p = (s[j][e] == -INFINITY) ? 0.f : exp2f(s[j][e] - mn[r]);
-            s[j][e] = p;
-            sum[r] += p;
-        }
-    }
-#pragma unroll
-    for (int r = 0; r < 2; ++r) l[r] = l[r] * corr[r] + sum[r];
-#pragma unroll
-    for (int n = 0; n < D / 8; ++n) {
-        o[n][0] *= corr[0];
-        o[n][1] *= corr[0];
-        o[n][2] *= corr[1];
-        o[n][3] *= corr[1];
-    }
-}
-
 // ------------------------------------------------------------------ prefill
 
 template <int D>
@@ -194,7 +83,8 @@ attention_prefill_kernel(const qi::bf16* __restrict__ q, qi::bf16* __restrict__ 
     const int tile = blockIdx.x, h = blockIdx.y;
     const int hk = h / (nq / nkv);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int r = tile_req[tile], q0 = tile_q0[tile];
+    const int r = tile_req[tile], q0 = tile_q0[tile] + blockIdx.z * kTileKeys;   // blockIdx.z: 64-row part of the tile
+    if (q0 >= q_start[r + 1]) return;
     const int rows_valid = min(kTileKeys, q_start[r + 1] - q0);
     const int pos0 = start_pos[r] + (q0 - q_start[r]);
     const int* table = block_table + (size_t)r * max_blocks;
@@ -251,7 +141,7 @@ attention_prefill_kernel(const qi::bf16* __restrict__ q, qi::bf16* __restrict__ 
         if (t0 <= warp_max_pos) {   // this warp's rows see at least one key of the tile
             const uint32_t k_s = kv_s + buf * 2 * kTileBytes, v_s = k_s + kTileBytes;
             float s[8][4];
-            qk_tile<D, 8>(s, qa, k_s, 0, lane);
+            qk_tile<D, 8, RowSwizzle<D>>(s, qa, k_s, 0, lane);
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
 #pragma unroll
@@ -263,7 +153,7 @@ attention_prefill_kernel(const qi::bf16* __restrict__ q, qi::bf16* __restrict__ 
                 }
             }
             softmax_tile<D, 8>(s, m, l, o);
-            pv_tile<D, 8>(o, s, v_s, 0, lane);
+            pv_tile<D, 8, RowSwizzle<D>>(o, s, v_s, 0, lane);
         }
         __syncthreads();
     }
@@ -374,7 +264,7 @@ attention_decode_kernel(const qi::bf16* __restrict__ q, const qi::bf16* __restri
         if (wkey0 < k1 && wkey0 + 16 > k0) {
             const uint32_t k_s = kv_s + buf * 2 * kTileBytes, v_s = k_s + kTileBytes;
             float s[2][4];
-            qk_tile<D, 2>(s, qa, k_s, warp * 16, lane);
+            qk_tile<D, 2, RowSwizzle<D>>(s, qa, k_s, warp * 16, lane);
 #pragma unroll
             for (int j = 0; j < 2; ++j) {
 #pragma unroll
@@ -384,7 +274,7 @@ attention_decode_kernel(const qi::bf16* __restrict__ q, const qi::bf16* __restri
                 }
             }
             softmax_tile<D, 2>(s, m, l, o);
-            pv_tile<D, 2>(o, s, v_s, warp * 16, lane);
+            pv_tile<D, 2, RowSwizzle<D>>(o, s, v_s, warp * 16, lane);
         }
         __syncthreads();
     }
@@ -467,8 +357,8 @@ template <int D> int decode_smem() {
 template <int D>
 int launch_prefill(const void* q, void* out, const void* k_pages, const void* v_pages, const int* block_table,
                    int max_blocks, int page_size, int num_pages, const int* q_start, const int* start_pos,
-                   const int* tile_req, const int* tile_q0, int n_tiles, int nq, int nkv, float scale, int window,
-                   int* status, cudaStream_t stream) {
+                   const int* tile_req, const int* tile_q0, int n_tiles, int tile_rows, int nq, int nkv, float scale,
+                   int window, int* status, cudaStream_t stream) {
     auto kern = attention_prefill_kernel<D>;
     static bool configured = false;
     if (!configured) {
@@ -476,7 +366,7 @@ int launch_prefill(const void* q, void* out, const void* k_pages, const void* v_
         if (e != cudaSuccess) return qi::fail("attention_prefill: cannot reserve shared memory: %s", cudaGetErrorString(e));
         configured = true;
     }
-    dim3 grid(n_tiles, nq);
+    dim3 grid(n_tiles, nq, tile_rows / kTileKeys);
     kern<<<grid, kThreads, prefill_smem<D>(), stream>>>(
         (const qi::bf16*)q, (qi::bf16*)out, (const qi::bf16*)k_pages, (const qi::bf16*)v_pages, block_table, max_blocks,
         page_size, num_pages, q_start, start_pos, tile_req, tile_q0, nq, nkv, scale * 1.4426950408889634f, window, status);
@@ -515,17 +405,19 @@ extern "C" int qi_attention_mma_supported(int nq, int nkv, int d) {
 extern "C" int qi_attention_prefill(const void* q, void* out, const void* k_pages, const void* v_pages,
                                     const int* block_table, int max_blocks, int page_size, int num_pages,
                                     const int* q_start, const int* start_pos, const int* tile_req,
-                                    const int* tile_q0, int n_tiles, int nq, int nkv, int d, float scale,
-                                    int window, int* status, cudaStream_t stream) {
+                                    const int* tile_q0, int n_tiles, int tile_rows, int nq, int nkv, int d,
+                                    float scale, int window, int* status, cudaStream_t stream) {
     QI_REQUIRE(qi_attention_mma_supported(nq, nkv, d), "attention_prefill: heads %d/%d of size %d are not covered (head size 64 or 128, group <= 16)", nq, nkv, d);
     QI_REQUIRE(page_size > 0 && max_blocks > 0 && num_pages > 0 && window >= 0, "attention_prefill: bad page geometry");
     QI_REQUIRE(n_tiles >= 0 && nq <= 65535, "attention_prefill: grid too large");
+    QI_REQUIRE(tile_rows > 0 && tile_rows % kTileKeys == 0 && tile_rows / kTileKeys <= 64,
+               "attention_prefill: the tile lists must be cut to a multiple of %d query rows", kTileKeys);
     if (n_tiles == 0) return 0;
     if (d == 64)
         return launch_prefill<64>(q, out, k_pages, v_pages, block_table, max_blocks, page_size, num_pages, q_start,
-                                  start_pos, tile_req, tile_q0, n_tiles, nq, nkv, scale, window, status, stream);
+                                  start_pos, tile_req, tile_q0, n_tiles, tile_rows, nq, nkv, scale, window, status, stream);
     return launch_prefill<128>(q, out, k_pages, v_pages, block_table, max_blocks, page_size, num_pages, q_start,
-                               start_pos, tile_req, tile_q0, n_tiles, nq, nkv, scale, window, status, stream);
+                               start_pos, tile_req, tile_q0, n_tiles, tile_rows, nq, nkv, scale, window, status, stream);
 }
 
 // Workspace floats: ws_o = batch * nq * n_splits * d, ws_ml = batch * nq * n_splits * 2.

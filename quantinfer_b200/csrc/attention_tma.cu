@@ -1,0 +1,504 @@
+// The attention kernels of attention_mma.cu with their key/value tiles fetched by
+// TMA instead of per-thread cp.async: one thread issues, per 64-key tile, a few
+// cp.async.bulk.tensor copies (one per page piece and 64-column half) into a ring
+// of shared-memory stages guarded by mbarriers, and every other thread only does
+// tensor-core work. The page pool of a layer is seen as a matrix
+// [num_pages * kv_heads * page_size, head_dim]; positions of one page and kv head
+// are consecutive rows, so a box of min(page_size, 64) rows is one page piece.
+// Needs a page size that is a power of two >= 8 (a box must be whole multiples
+// of the 8-row swizzle pattern); other page sizes use the cp.async kernels.
+//
+// Rows of a page beyond a request's length hold older or zero data; they are
+// finite (the pool is zeroed once and only finite values are written) and their
+// scores are masked, so they contribute exactly zero.
+//
+// No load uses cluster multicast. Every mbarrier wait is bounded; when a bound
+// runs out the kernel sets kStatusWaitTimeout and leaves.
+#include "attention_frag.cuh"
+
+#include <cuda.h>
+
+namespace {
+
+using namespace qi_attn;
+
+constexpr int kTileKeys = 64;
+constexpr uint32_t kSpinLimit = 1u << 24;
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+    for (uint32_t i = 0; i < kSpinLimit; ++i)
+        if (mbar_try_wait(bar, parity)) return true;
+    return false;
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y) : "memory");
+}
+
+// Issues the copies of keys [t0, t0 + 64) of kv head hk for K and V into one stage.
+// `needed` = [lo, hi): a missing page inside it is an error; outside it any page will do.
+template <int D>
+__device__ __forceinline__ void issue_kv_tile(uint32_t stage_smem, uint32_t bar, const CUtensorMap* map_k,
+                                              const CUtensorMap* map_v, const int* __restrict__ table,
+                                              int max_blocks, int page_size, int box_rows, int num_pages, int nkv,
+                                              int hk, int t0, int lo, int hi, int* __restrict__ status) {
+    constexpr int kHalfBytes = kTileKeys * 128;
+    constexpr int kTileBytes = kTileKeys * D * 2;
+    mbar_expect_tx(bar, 2 * kTileBytes);
+    for (int r0 = 0; r0 < kTileKeys; r0 += box_rows) {
+        const int key = t0 + r0;
+        const int blk = key / page_size;
+        int page = blk < max_blocks ? table[blk] : -1;
+        if (page < 0 || page >= num_pages) {
+            if (key < hi && key + box_rows > lo && status) atomicOr(status, qi::kStatusBadPage);
+            page = 0;
+        }
+        const int row = (page * nkv + hk) * page_size + (key % page_size);
+#pragma unroll
+        for (int h = 0; h < D / 64; ++h) {
+            tma_load_2d(stage_smem + h * kHalfBytes + r0 * 128, map_k, bar, h * 64, row);
+            tma_load_2d(stage_smem + kTileBytes + h * kHalfBytes + r0 * 128, map_v, bar, h * 64, row);
+        }
+    }
+}
+
+// ------------------------------------------------------------------ prefill
+
+constexpr int kPrefillRows = 128;
+constexpr int kPrefillThreads = 256;
+constexpr int kPrefillStages = 3;
+
+template <int D>
+__global__ void __launch_bounds__(kPrefillThreads, 1)
+attention_prefill_tma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                             const __grid_constant__ CUtensorMap map_v, qi::bf16* __restrict__ out,
+                             const int* __restrict__ block_table, int max_blocks, int page_size, int box_rows,
+                             int num_pages, const int* __restrict__ q_start, const int* __restrict__ start_pos,
+                             const int* __restrict__ tile_req, const int* __restrict__ tile_q0, int nq, int nkv,
+                             float scale_log2e, int window, int* __restrict__ status) {
+    extern __shared__ uint8_t smem_raw[];
+    constexpr int kTileBytes = kTileKeys * D * 2;
+    constexpr int kQBytes = kPrefillRows * D * 2;
+    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    const uint32_t q_s = base, kv_s = base + kQBytes;
+    const uint32_t bars = kv_s + kPrefillStages * 2 * kTileBytes;   // full[stages], q
+    auto full_bar = [&](int s) { return bars + 8u * s; };
+    const uint32_t q_bar = bars + 8u * kPrefillStages;
+
+    const int tile = blockIdx.x, h = blockIdx.y;
+    const int hk = h / (nq / nkv);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int r = tile_req[tile], q0 = tile_q0[tile];
+    const int rows_valid = min(kPrefillRows, q_start[r + 1] - q0);
+    const int pos0 = start_pos[r] + (q0 - q_start[r]);
+    const int* table = block_table + (size_t)r * max_blocks;
+    const int hi = pos0 + rows_valid;
+    const int lo = (window > 0 && pos0 - window + 1 > 0) ? pos0 - window + 1 : 0;
+    const int t_begin = (lo / kTileKeys) * kTileKeys;
+    const int n_tiles = (hi - t_begin + kTileKeys - 1) / kTileKeys;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kPrefillStages; ++s) mbar_init(full_bar(s), 1);
+        mbar_init(q_bar, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        mbar_expect_tx(q_bar, kQBytes);
+#pragma unroll
+        for (int hh = 0; hh < D / 64; ++hh)
+            tma_load_2d(q_s + hh * (kPrefillRows * 128), &map_q, q_bar, h * D + hh * 64, q0);
+        for (int i = 0; i < kPrefillStages && i < n_tiles; ++i)
+            issue_kv_tile<D>(kv_s + i * 2 * kTileBytes, full_bar(i), &map_k, &map_v, table, max_blocks, page_size, box_rows,
+                             num_pages, nkv, hk, t_begin + i * kTileKeys, lo, hi, status);
+    }
+
+    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+    float o[D / 8][4];
+#pragma unroll
+    for (int n = 0; n < D / 8; ++n)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) o[n][e] = 0.f;
+    uint32_t qa[D / 16][4];
+    const int g = lane >> 2, t4 = lane & 3;
+    const int row_pos[2] = {pos0 + warp * 16 + g, pos0 + warp * 16 + g + 8};
+    const int warp_max_pos = pos0 + warp * 16 + 15;
+    const bool warp_active = warp * 16 < rows_valid;
+    bool ok = mbar_wait(q_bar, 0);
+    if (ok) load_q_frags<D, TmaSwizzle<kPrefillRows>>(qa, q_s, warp * 16, lane);
+
+    for (int i = 0; i < n_tiles && ok; ++i) {
+        const int stage = i % kPrefillStages;
+        const int t0 = t_begin + i * kTileKeys;
+        ok = mbar_wait(full_bar(stage), (uint32_t)(i / kPrefillStages) & 1u);
+        if (!ok) break;
+        if (warp_active && t0 <= warp_max_pos) {
+            const uint32_t k_s = kv_s + stage * 2 * kTileBytes, v_s = k_s + kTileBytes;
+            float s[8][4];
+            qk_tile<D, 8, TmaSwizzle<kTileKeys>>(s, qa, k_s, 0, lane);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int key = t0 + j * 8 + t4 * 2 + (e & 1);
+                    const int pos = row_pos[e >> 1];
+                    const bool valid = key <= pos && key >= lo && key < hi && (window <= 0 || key > pos - window);
+                    s[j][e] = valid ? s[j][e] * scale_log2e : -INFINITY;
+                }
+            }
+            softmax_tile<D, 8>(s, m, l, o);
+            pv_tile<D, 8, TmaSwizzle<kTileKeys>>(o, s, v_s, 0, lane);
+        }
+        __syncthreads();   // every warp is done with this stage
+        if (threadIdx.x == 0 && i + kPrefillStages < n_tiles)
+            issue_kv_tile<D>(kv_s + stage * 2 * kTileBytes, full_bar(stage), &map_k, &map_v, table, max_blocks, page_size,
+                             box_rows, num_pages, nkv, hk, t0 + kPrefillStages * kTileKeys, lo, hi, status);
+    }
+    if (!ok) {
+        if (lane == 0 && status) atomicOr(status, qi::kStatusWaitTimeout);
+        return;
+    }
+#pragma unroll
+    for (int rr = 0; rr < 2; ++rr) {
+        l[rr] += __shfl_xor_sync(0xffffffffu, l[rr], 1);
+        l[rr] += __shfl_xor_sync(0xffffffffu, l[rr], 2);
+    }
+#pragma unroll
+    for (int rr = 0; rr < 2; ++rr) {
+        const int row = warp * 16 + g + rr * 8;
+        if (row >= rows_valid) continue;
+        const float inv = l[rr] > 0.f ? 1.f / l[rr] : 0.f;
+        qi::bf16* orow = out + ((size_t)(q0 + row) * nq + h) * D;
+#pragma unroll
+        for (int n = 0; n < D / 8; ++n)
+            *reinterpret_cast<uint32_t*>(orow + n * 8 + t4 * 2) = pack_bf16(o[n][rr * 2] * inv, o[n][rr * 2 + 1] * inv);
+    }
+}
+
+// ------------------------------------------------------------------ decode
+
+constexpr int kDecodeThreads = 128;
+constexpr int kDecodeStages = 4;
+
+template <int D>
+__global__ void __launch_bounds__(kDecodeThreads)
+attention_decode_tma_kernel(const qi::bf16* __restrict__ q, const __grid_constant__ CUtensorMap map_k,
+                            const __grid_constant__ CUtensorMap map_v, const int* __restrict__ block_table,
+                            int max_blocks, int page_size, int box_rows, int num_pages,
+                            const int* __restrict__ kv_len, const int* __restrict__ q_start,
+                            float* __restrict__ ws_o, float* __restrict__ ws_ml, int nq, int nkv, float scale_log2e,
+                            int window, int chunk, int* __restrict__ status) {
+    extern __shared__ uint8_t smem_raw[];
+    constexpr int kTileBytes = kTileKeys * D * 2;
+    constexpr int kQBytes = 16 * D * 2;
+    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t* aligned = smem_raw + (base - smem_u32(smem_raw));
+    const uint32_t kv_s = base;                                       // stages x (K, V), later the merge buffers
+    const uint32_t q_s = base + kDecodeStages * 2 * kTileBytes;       // [16, D], row swizzle
+    uint8_t* q_tile = aligned + kDecodeStages * 2 * kTileBytes;
+    const uint32_t bars = q_s + kQBytes;
+    auto full_bar = [&](int s) { return bars + 8u * s; };
+
+    const int split = blockIdx.x, hk = blockIdx.y, b = blockIdx.z;
+    const int n_splits = gridDim.x;
+    const int G = nq / nkv;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int g = lane >> 2, t4 = lane & 3;
+    const int S = kv_len[b];
+    const int lo = (window > 0 && S - window > 0) ? S - window : 0;
+    const int k0 = max(split * chunk, lo);
+    const int k1 = min(S, (split + 1) * chunk);
+    const size_t part = ((size_t)b * nq + (size_t)hk * G) * n_splits + split;
+
+    if (k0 >= k1) {
+        if (threadIdx.x < G) {
+            float* ml = ws_ml + (part + (size_t)threadIdx.x * n_splits) * 2;
+            ml[0] = -INFINITY;
+            ml[1] = 0.f;
+        }
+        return;
+    }
+    const int* table = block_table + (size_t)b * max_blocks;
+    const int tok = q_start[b];
+    const int t_begin = (k0 / kTileKeys) * kTileKeys;
+    const int n_tiles = (k1 - t_begin + kTileKeys - 1) / kTileKeys;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kDecodeStages; ++s) mbar_init(full_bar(s), 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    constexpr int kChunks = D / 8;
+    for (int idx = threadIdx.x; idx < 16 * kChunks; idx += kDecodeThreads) {
+        const int row = idx / kChunks, c = idx % kChunks;
+        uint4 v = make_uint4(0u, 0u, 0u, 0u);
+        if (row < G) v = *reinterpret_cast<const uint4*>(q + ((size_t)tok * nq + (size_t)hk * G + row) * D + c * 8);
+        *reinterpret_cast<uint4*>(q_tile + RowSwizzle<D>::off(row, c)) = v;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < kDecodeStages && i < n_tiles; ++i)
+            issue_kv_tile<D>(kv_s + i * 2 * kTileBytes, full_bar(i), &map_k, &map_v, table, max_blocks, page_size, box_rows,
+                             num_pages, nkv, hk, t_begin + i * kTileKeys, k0, k1, status);
+    }
+    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+    float o[D / 8][4];
+#pragma unroll
+    for (int n = 0; n < D / 8; ++n)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) o[n][e] = 0.f;
+    uint32_t qa[D / 16][4];
+    load_q_frags<D, RowSwizzle<D>>(qa, q_s, 0, lane);
+
+    bool ok = true;
+    for (int i = 0; i < n_tiles; ++i) {
+        const int stage = i % kDecodeStages;
+        const int t0 = t_begin + i * kTileKeys;
+        ok = mbar_wait(full_bar(stage), (uint32_t)(i / kDecodeStages) & 1u);
+        if (!ok) break;
+        const int wkey0 = t0 + warp * 16;   // each warp takes 16 of the tile's 64 keys
+        if (wkey0 < k1 && wkey0 + 16 > k0) {
+            const uint32_t k_s = kv_s + stage * 2 * kTileBytes, v_s = k_s + kTileBytes;
+            float s[2][4];
+            qk_tile<D, 2, TmaSwizzle<kTileKeys>>(s, qa, k_s, warp * 16, lane);
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int key = wkey0 + j * 8 + t4 * 2 + (e & 1);
+                    s[j][e] = (key >= k0 && key < k1) ? s[j][e] * scale_log2e : -INFINITY;
+                }
+            }
+            softmax_tile<D, 2>(s, m, l, o);
+            pv_tile<D, 2, TmaSwizzle<kTileKeys>>(o, s, v_s, warp * 16, lane);
+        }
+        __syncthreads();
+        if (threadIdx.x == 0 && i + kDecodeStages < n_tiles)
+            issue_kv_tile<D>(kv_s + stage * 2 * kTileBytes, full_bar(stage), &map_k, &map_v, table, max_blocks, page_size,
+                             box_rows, num_pages, nkv, hk, t0 + kDecodeStages * kTileKeys, k0, k1, status);
+    }
+    if (!ok) {
+        if (lane == 0 && status) atomicOr(status, qi::kStatusWaitTimeout);
+        return;
+    }
+#pragma unroll
+    for (int rr = 0; rr < 2; ++rr) {
+        l[rr] += __shfl_xor_sync(0xffffffffu, l[rr], 1);
+        l[rr] += __shfl_xor_sync(0xffffffffu, l[rr], 2);
+    }
+    // merge the four warps (each saw different keys) through shared memory, in warp order;
+    // every copy into the stages has completed (each tile's barrier was waited for)
+    float* sm_o = reinterpret_cast<float*>(aligned);             // [4][16][D]
+    float* sm_m = sm_o + 4 * 16 * D;                             // [4][16]
+    float* sm_l = sm_m + 4 * 16;                                 // [4][16]
+#pragma unroll
+    for (int rr = 0; rr < 2; ++rr) {
+        const int row = g + rr * 8;
+        if (t4 == 0) {
+            sm_m[warp * 16 + row] = m[rr];
+            sm_l[warp * 16 + row] = l[rr];
+        }
+#pragma unroll
+        for (int n = 0; n < D / 8; ++n) {
+            sm_o[(warp * 16 + row) * D + n * 8 + t4 * 2] = o[n][rr * 2];
+            sm_o[(warp * 16 + row) * D + n * 8 + t4 * 2 + 1] = o[n][rr * 2 + 1];
+        }
+    }
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < G * D; idx += kDecodeThreads) {
+        const int row = idx / D, col = idx % D;
+        float M = -INFINITY;
+        for (int w = 0; w < 4; ++w) M = fmaxf(M, sm_m[w * 16 + row]);
+        float L = 0.f, O = 0.f;
+        for (int w = 0; w < 4; ++w) {
+            const float mw = sm_m[w * 16 + row];
+            if (mw == -INFINITY) continue;
+            const float f = exp2f(mw - M);
+            L += sm_l[w * 16 + row] * f;
+            O += sm_o[(w * 16 + row) * D + col] * f;
+        }
+        const size_t p = part + (size_t)row * n_splits;
+        ws_o[p * D + col] = O;
+        if (col == 0) {
+            ws_ml[p * 2] = M;
+            ws_ml[p * 2 + 1] = L;
+        }
+    }
+}
+
+// out[b, h, :] = sum_s o_s 2^(m_s - M) / sum_s l_s 2^(m_s - M), key ranges in order.
+template <int D>
+__global__ void attention_merge_kernel(const float* __restrict__ ws_o, const float* __restrict__ ws_ml,
+                                       const int* __restrict__ q_start, qi::bf16* __restrict__ out, int nq,
+                                       int n_splits) {
+    const int h = blockIdx.x, b = blockIdx.y;
+    const size_t base = ((size_t)b * nq + h) * n_splits;
+    float M = -INFINITY;
+    for (int s = 0; s < n_splits; ++s) M = fmaxf(M, ws_ml[(base + s) * 2]);
+    const int tok = q_start[b];
+    for (int col = threadIdx.x; col < D; col += blockDim.x) {
+        float L = 0.f, O = 0.f;
+        for (int s = 0; s < n_splits; ++s) {
+            const float ms = ws_ml[(base + s) * 2];
+            if (ms == -INFINITY) continue;
+            const float f = exp2f(ms - M);
+            L += ws_ml[(base + s) * 2 + 1] * f;
+            O += ws_o[(base + s) * D + col] * f;
+        }
+        out[((size_t)tok * nq + h) * D + col] = __float2bfloat16_rn(L > 0.f ? O / L : 0.f);
+    }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encode() {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+    }
+    return fn;
+}
+
+// Map of a row-major bf16 matrix [rows, cols] with boxes of [box_rows, 64] and the 128-byte swizzle.
+int make_map(CUtensorMap* map, const void* ptr, long long rows, int cols, int box_rows) {
+    EncodeTiledFn enc = get_encode();
+    if (!enc) return qi::fail("attention: cuTensorMapEncodeTiled is not available from the driver");
+    cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)cols * 2};
+    cuuint32_t box[2] = {64u, (cuuint32_t)box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return qi::fail("attention: cuTensorMapEncodeTiled failed with code %d (rows=%lld cols=%d box=%d)", (int)r, rows, cols, box_rows);
+    return 0;
+}
+
+template <int D> constexpr int prefill_smem() { return kPrefillRows * D * 2 + kPrefillStages * 2 * kTileKeys * D * 2 + 64 + 1024; }
+template <int D> constexpr int decode_smem() { return kDecodeStages * 2 * kTileKeys * D * 2 + 16 * D * 2 + 64 + 1024; }
+
+template <int D>
+int launch_prefill(const void* q, void* out, const void* k_pages, const void* v_pages, const int* block_table,
+                   int max_blocks, int page_size, int num_pages, const int* q_start, const int* start_pos,
+                   const int* tile_req, const int* tile_q0, int n_tiles, int n_tokens, int nq, int nkv, float scale,
+                   int window, int* status, cudaStream_t stream) {
+    auto kern = attention_prefill_tma_kernel<D>;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, prefill_smem<D>());
+        if (e != cudaSuccess) return qi::fail("attention_prefill: cannot reserve shared memory: %s", cudaGetErrorString(e));
+        configured = true;
+    }
+    const int box_rows = page_size < kTileKeys ? page_size : kTileKeys;
+    CUtensorMap mq, mk, mv;
+    if (make_map(&mq, q, n_tokens, nq * D, kPrefillRows)) return 1;
+    if (make_map(&mk, k_pages, (long long)num_pages * nkv * page_size, D, box_rows)) return 1;
+    if (make_map(&mv, v_pages, (long long)num_pages * nkv * page_size, D, box_rows)) return 1;
+    dim3 grid(n_tiles, nq);
+    kern<<<grid, kPrefillThreads, prefill_smem<D>(), stream>>>(
+        mq, mk, mv, (qi::bf16*)out, block_table, max_blocks, page_size, box_rows, num_pages, q_start, start_pos,
+        tile_req, tile_q0, nq, nkv, scale * 1.4426950408889634f, window, status);
+    return qi::check_launch("attention_prefill_tma");
+}
+
+template <int D>
+int launch_decode(const void* q, void* out, const void* k_pages, const void* v_pages, const int* block_table,
+                  int max_blocks, int page_size, int num_pages, const int* kv_len, const int* q_start, int batch,
+                  int nq, int nkv, float scale, int window, int chunk, int n_splits, float* ws_o, float* ws_ml,
+                  int* status, cudaStream_t stream) {
+    auto kern = attention_decode_tma_kernel<D>;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, decode_smem<D>());
+        if (e != cudaSuccess) return qi::fail("attention_decode: cannot reserve shared memory: %s", cudaGetErrorString(e));
+        configured = true;
+    }
+    const int box_rows = page_size < kTileKeys ? page_size : kTileKeys;
+    CUtensorMap mk, mv;
+    if (make_map(&mk, k_pages, (long long)num_pages * nkv * page_size, D, box_rows)) return 1;
+    if (make_map(&mv, v_pages, (long long)num_pages * nkv * page_size, D, box_rows)) return 1;
+    dim3 grid(n_splits, nkv, batch);
+    kern<<<grid, kDecodeThreads, decode_smem<D>(), stream>>>(
+        (const qi::bf16*)q, mk, mv, block_table, max_blocks, page_size, box_rows, num_pages, kv_len, q_start, ws_o,
+        ws_ml, nq, nkv, scale * 1.4426950408889634f, window, chunk, status);
+    if (int rc = qi::check_launch("attention_decode_tma")) return rc;
+    attention_merge_kernel<D><<<dim3(nq, batch), D >= 128 ? 128 : 64, 0, stream>>>(ws_o, ws_ml, q_start,
+                                                                                 (qi::bf16*)out, nq, n_splits);
+    return qi::check_launch("attention_merge");
+}
+
+bool pow2(int v) { return v > 0 && (v & (v - 1)) == 0; }
+
+}  // namespace
+
+// 1 if the TMA-fed attention kernels take this geometry.
+extern "C" int qi_attention_tma_supported(int nq, int nkv, int d, int page_size) {
+    return (d == 64 || d == 128) && nkv > 0 && nq % nkv == 0 && nq / nkv <= 16 && pow2(page_size) && page_size >= 8;
+}
+
+// Query rows per CTA of qi_attention_prefill_tma: the tile lists must be cut to this.
+extern "C" int qi_attention_prefill_tma_rows() { return kPrefillRows; }
+
+extern "C" int qi_attention_prefill_tma(const void* q, void* out, const void* k_pages, const void* v_pages,
+                                        const int* block_table, int max_blocks, int page_size, int num_pages,
+                                        const int* q_start, const int* start_pos, const int* tile_req,
+                                        const int* tile_q0, int n_tiles, int n_tokens, int nq, int nkv, int d,
+                                        float scale, int window, int* status, cudaStream_t stream) {
+    QI_REQUIRE(qi_attention_tma_supported(nq, nkv, d, page_size),
+               "attention_prefill_tma: heads %d/%d of size %d with pages of %d are not covered", nq, nkv, d, page_size);
+    QI_REQUIRE(max_blocks > 0 && num_pages > 0 && window >= 0 && n_tokens > 0, "attention_prefill_tma: bad sizes");
+    QI_REQUIRE(((uintptr_t)q & 15) == 0 && ((uintptr_t)k_pages & 15) == 0 && ((uintptr_t)v_pages & 15) == 0,
+               "attention_prefill_tma: tensors must be 16-byte aligned");
+    QI_REQUIRE((long long)num_pages * nkv * page_size < 2147483647LL, "attention_prefill_tma: the page pool has too many rows");
+    QI_REQUIRE(n_tiles >= 0 && nq <= 65535, "attention_prefill_tma: grid too large");
+    if (n_tiles == 0) return 0;
+    if (d == 64)
+        return launch_prefill<64>(q, out, k_pages, v_pages, block_table, max_blocks, page_size, num_pages, q_start,
+                                  start_pos, tile_req, tile_q0, n_tiles, n_tokens, nq, nkv, scale, window, status, stream);
+    return launch_prefill<128>(q, out, k_pages, v_pages, block_table, max_blocks, page_size, num_pages, q_start,
+                               start_pos, tile_req, tile_q0, n_tiles, n_tokens, nq, nkv, scale, window, status, stream);
+}
+
+// Workspace floats: ws_o = batch * nq * n_splits * d, ws_ml = batch * nq * n_splits * 2.
+extern "C" int qi_attention_decode_tma(const void* q, void* out, const void* k_pages, const void* v_pages,
+                                       const int* block_table, int max_blocks, int page_size, int num_pages,
+                                       const int* kv_len, const int* q_start, int batch, int nq, int nkv, int d,
+                                       float scale, int window, int chunk, int n_splits, float* ws_o, float* ws_ml,
+                                       int* status, cudaStream_t stream) {
+    QI_REQUIRE(qi_attention_tma_supported(nq, nkv, d, page_size),
+               "attention_decode_tma: heads %d/%d of size %d with pages of %d are not covered", nq, nkv, d, page_size);
+    QI_REQUIRE(max_blocks > 0 && num_pages > 0 && window >= 0, "attention_decode_tma: bad sizes");
+    QI_REQUIRE(chunk > 0 && chunk % kTileKeys == 0, "attention_decode_tma: the key range per CTA (%d) must be a positive multiple of %d", chunk, kTileKeys);
+    QI_REQUIRE(n_splits > 0 && n_splits <= 65535 && nkv <= 65535 && batch <= 65535, "attention_decode_tma: grid too large");
+    QI_REQUIRE(ws_o && ws_ml, "attention_decode_tma: workspace missing");
+    QI_REQUIRE(((uintptr_t)q & 15) == 0 && ((uintptr_t)k_pages & 15) == 0 && ((uintptr_t)v_pages & 15) == 0,
+               "attention_decode_tma: tensors must be 16-byte aligned");
+    QI_REQUIRE((long long)num_pages * nkv * page_size < 2147483647LL, "attention_decode_tma: the page pool has too many rows");
+    if (batch == 0) return 0;
+    if (d == 64)
+        return launch_decode<64>(q, out, k_pages, v_pages, block_table, max_blocks, page_size, num_pages, kv_len,
+                                 q_start, batch, nq, nkv, scale, window, chunk, n_splits, ws_o, ws_ml, status, stream);
+    return launch_decode<128>(q, out, k_pages, v_pages, block_table, max_blocks, page_size, num_pages, kv_len,
+                              q_start, batch, nq, nkv, scale, window, chunk, n_splits, ws_o, ws_ml, status, stream);
+}

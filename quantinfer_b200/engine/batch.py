@@ -12,7 +12,7 @@ Device arrays (int32), all views of one buffer that crosses in one copy:
     token_ids[n]   positions[n]   token_req[n]      per token (token_req: index of its entry)
     q_start[b+1]   start_pos[b]   kv_len[b]   slot_ids[b]      per entry
     logit_rows[r]                                    rows of the flattened batch whose logits are wanted
-    tile_req[t]    tile_q0[t]                        blocks of up to 64 query rows of one entry (longest context first)
+    tile_req[t]    tile_q0[t]                        blocks of up to 128 query rows of one entry (longest context first)
     block_tables[g][b, max_blocks]                   per layer group
 """
 
@@ -32,7 +32,7 @@ class StepEntry:
     want: Sequence[int] = ()
 
 
-QUERY_TILE = 64   # query rows per CTA of the flash attention kernel
+QUERY_TILE = 128   # query rows per entry of the tile lists (kernels.QUERY_TILE)
 
 
 def _align(n: int, a: int = 4) -> int:

@@ -24,7 +24,7 @@ STATUS_BAD_PAGE = 2
 STATUS_NON_FINITE = 4
 STATUS_WAIT_TIMEOUT = 8
 
-ABI_VERSION = 2
+ABI_VERSION = 3
 
 _lib = None
 _lib_lock = threading.Lock()
@@ -279,11 +279,20 @@ def attention_mma_supported(nq: int, nkv: int, d: int) -> bool:
     return bool(library().qi_attention_mma_supported(nq, nkv, d))
 
 
+QUERY_TILE = 128   # query rows per entry of a batch's tile lists
+
+
+def attention_tma_supported(nq: int, nkv: int, d: int, page_size: int) -> bool:
+    """Whether the TMA-fed attention kernels take this geometry (bfloat16 only)."""
+    return bool(library().qi_attention_tma_supported(nq, nkv, d, page_size))
+
+
 def attention_prefill(q, out, k_pages, v_pages, block_table, q_start, start_pos, tile_req, tile_q0,
-                      nq, nkv, d, scale: float, window: int, status) -> None:
+                      nq, nkv, d, scale: float, window: int, status, use_tma: bool | None = None) -> None:
     """Causal paged GQA flash attention (bfloat16, head size 64 or 128) for spans of any
     length. `tile_req[i]`, `tile_q0[i]`: request index and first flat token of the i-th
-    block of up to 64 query rows."""
+    block of up to QUERY_TILE query rows. Keys and values come by TMA when the page size
+    allows it (a power of two >= 8), else by cp.async; `use_tma` forces the choice."""
     _req(q, "q", torch.bfloat16, 2)
     _req(out, "out", torch.bfloat16, 2)
     _req(k_pages, "k_pages", torch.bfloat16, 4)
@@ -297,10 +306,19 @@ def attention_prefill(q, out, k_pages, v_pages, block_table, q_start, start_pos,
         raise KernelError(f"attention_prefill: pages {tuple(k_pages.shape)} do not match {nkv} kv heads of {d}")
     if tile_req.numel() != tile_q0.numel():
         raise KernelError("attention_prefill: tile lists differ in length")
+    if use_tma is None:
+        use_tma = attention_tma_supported(nq, nkv, d, k_pages.shape[2])
+    if use_tma:
+        rc = library().qi_attention_prefill_tma(
+            _ptr(q), _ptr(out), _ptr(k_pages), _ptr(v_pages), _ptr(block_table), block_table.shape[1],
+            k_pages.shape[2], k_pages.shape[0], _ptr(q_start), _ptr(start_pos), _ptr(tile_req), _ptr(tile_q0),
+            tile_req.numel(), q.shape[0], nq, nkv, d, C.c_float(scale), int(window or 0), _ptr(status), _stream())
+        _check(rc, "attention_prefill_tma")
+        return
     rc = library().qi_attention_prefill(
         _ptr(q), _ptr(out), _ptr(k_pages), _ptr(v_pages), _ptr(block_table), block_table.shape[1],
         k_pages.shape[2], k_pages.shape[0], _ptr(q_start), _ptr(start_pos), _ptr(tile_req), _ptr(tile_q0),
-        tile_req.numel(), nq, nkv, d, C.c_float(scale), int(window or 0), _ptr(status), _stream())
+        tile_req.numel(), QUERY_TILE, nq, nkv, d, C.c_float(scale), int(window or 0), _ptr(status), _stream())
     _check(rc, "attention_prefill")
 
 
@@ -313,7 +331,8 @@ def attention_decode_plan(batch: int, nkv: int, max_kv_len: int):
 
 
 def attention_decode(q, out, k_pages, v_pages, block_table, kv_len, q_start, nq, nkv, d, scale: float,
-                     window: int, chunk: int, n_splits: int, status, workspace=None) -> None:
+                     window: int, chunk: int, n_splits: int, status, workspace=None,
+                     use_tma: bool | None = None) -> None:
     """Paged GQA attention for one query token per request (bfloat16, head size 64 or
     128), keys split into `n_splits` ranges of `chunk` positions. `workspace`: float32,
     at least batch * nq * n_splits * (d + 2) elements (allocated when None)."""
@@ -336,7 +355,10 @@ def attention_decode(q, out, k_pages, v_pages, block_table, kv_len, q_start, nq,
         raise KernelError(f"attention_decode: workspace has {workspace.numel()} floats, {need} are needed")
     ws_o = workspace
     ws_ml = workspace[batch * nq * n_splits * d:]
-    rc = library().qi_attention_decode(
+    if use_tma is None:
+        use_tma = attention_tma_supported(nq, nkv, d, k_pages.shape[2])
+    fn = library().qi_attention_decode_tma if use_tma else library().qi_attention_decode
+    rc = fn(
         _ptr(q), _ptr(out), _ptr(k_pages), _ptr(v_pages), _ptr(block_table), block_table.shape[1],
         k_pages.shape[2], k_pages.shape[0], _ptr(kv_len), _ptr(q_start), batch, nq, nkv, d, C.c_float(scale),
         int(window or 0), chunk, n_splits, _ptr(ws_o), _ptr(ws_ml), _ptr(status), _stream())
