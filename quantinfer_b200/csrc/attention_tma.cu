@@ -194,7 +194,7 @@ attention_prefill_tma_kernel(const __grid_constant__ CUtensorMap map_q, const __
 // ------------------------------------------------------------------ decode
 
 constexpr int kDecodeThreads = 128;
-constexpr int kDecodeStages = 4;
+constexpr int kDecodeStages = 3;
 
 template <int D>
 __global__ void __launch_bounds__(kDecodeThreads)

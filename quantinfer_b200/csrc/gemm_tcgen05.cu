@@ -170,7 +170,7 @@ __device__ __forceinline__ float silu_mul(float g, float u) { return g / (1.0f +
 // EPI = 0: store the product. EPI = 1: the product's columns come in pairs (gate, up) and
 // the kernel stores silu(gate) * up, half as wide (the feed-forward's activation fused in).
 template <int BN, int STAGES, bool SWAP, typename TOut, int EPI>
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__(kThreads)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                     TOut* __restrict__ out, int rows_a, int rows_b, int K, long long ld_out,
                     int kb_per_split, long long split_stride, int* __restrict__ status) {
@@ -434,9 +434,9 @@ template <bool SWAP, typename TOut, int EPI = 0>
 int launch_bn(int bn, const CUtensorMap& ma, const CUtensorMap& mb, TOut* out, int rows_a, int rows_b, int K,
               long long ld, int splits, int kb_per_split, long long split_stride, int* status, cudaStream_t stream) {
     switch (bn) {
-        case 16: return launch<16, 8, SWAP, TOut, EPI>(ma, mb, out, rows_a, rows_b, K, ld, splits, kb_per_split, split_stride, status, stream);
-        case 32: return launch<32, 8, SWAP, TOut, EPI>(ma, mb, out, rows_a, rows_b, K, ld, splits, kb_per_split, split_stride, status, stream);
-        case 64: return launch<64, 8, SWAP, TOut, EPI>(ma, mb, out, rows_a, rows_b, K, ld, splits, kb_per_split, split_stride, status, stream);
+        case 16: return launch<16, 4, SWAP, TOut, EPI>(ma, mb, out, rows_a, rows_b, K, ld, splits, kb_per_split, split_stride, status, stream);
+        case 32: return launch<32, 4, SWAP, TOut, EPI>(ma, mb, out, rows_a, rows_b, K, ld, splits, kb_per_split, split_stride, status, stream);
+        case 64: return launch<64, 4, SWAP, TOut, EPI>(ma, mb, out, rows_a, rows_b, K, ld, splits, kb_per_split, split_stride, status, stream);
         case 128: return launch<128, 6, SWAP, TOut, EPI>(ma, mb, out, rows_a, rows_b, K, ld, splits, kb_per_split, split_stride, status, stream);
         case 256: return launch<256, 4, SWAP, TOut, EPI>(ma, mb, out, rows_a, rows_b, K, ld, splits, kb_per_split, split_stride, status, stream);
     }

@@ -34,6 +34,7 @@ _DTYPES = {"float32": torch.float32, "fp32": torch.float32, "bfloat16": torch.bf
            torch.float32: torch.float32, torch.bfloat16: torch.bfloat16}
 
 DEFAULT_PAGE_SIZE = 64
+KV_BUCKET = 512   # a decode graph serves contexts up to the next multiple of this
 
 
 def parse_dtype(name) -> torch.dtype:
@@ -167,21 +168,24 @@ class Engine:
         return (self.use_graphs and len(entries) <= self.max_graph_batch
                 and all(len(e.tokens) == 1 and list(e.want) == [0] for e in entries))
 
-    def _graph_step(self, entries) -> torch.Tensor:
+    def _graph_step(self, entries, extra_positions: int = 0):
         """A batch of single decode tokens, all wanting their logits: the packed batch has a
         fixed layout per batch size, so the forward pass is captured once per size and
         replayed; each step only copies the batch's arrays into the graph's buffer."""
         starts, slots, buf, layout, q_start, lens = self._pack(entries)
         host, event = self._stage(buf)
         b = len(entries)
-        g = self._graphs.get(b)
+        # kernels in a graph size their grids for a bound on the context, not for the
+        # requests' lengths: one graph per batch size and per bucket of the longest context
+        bound = min(self.max_seq_len, -(-(max(starts) + 1 + extra_positions) // KV_BUCKET) * KV_BUCKET)
+        g = self._graphs.get((b, bound))
         if g is None:
             meta = torch.empty(buf.size, dtype=torch.int32, device=self.device)
             meta.copy_(host, non_blocking=True)
             event.record()
             batch = batch_from_packed(meta, layout, entries, starts, slots, q_start, lens,
                                       len(self.cache.groups), self.cache.max_blocks)
-            batch.max_kv_len = self.max_seq_len      # kernels in a graph size their grids for the limit
+            batch.max_kv_len = bound
             batch.extra["graph"] = True
             logits = self.model.forward(batch, self._views)   # eager: warms up and gives this step's result
             torch.cuda.synchronize()
@@ -191,14 +195,14 @@ class Engine:
                 static_logits = self.model.forward(batch, self._views)
             if self._graph_pool is None:
                 self._graph_pool = graph.pool()
-            self._graphs[b] = g = {"graph": graph, "meta": meta, "batch": batch, "logits": static_logits,
+            self._graphs[(b, bound)] = g = {"graph": graph, "meta": meta, "batch": batch, "logits": static_logits,
                                    "layout": layout, "launches": kernels.launches - before}
-            return logits
+            return logits, g
         g["meta"].copy_(host, non_blocking=True)
         event.record()
         g["graph"].replay()
         kernels.launches += g["launches"]
-        return g["logits"]
+        return g["logits"], g
 
     def step(self, entries: Sequence[StepEntry], check_status: bool = True) -> torch.Tensor:
         """Runs one batch; returns float32 logits [wanted places, vocab] on the device,
@@ -214,7 +218,7 @@ class Engine:
                 self.cache.prepare(e.request_id, len(e.tokens))
                 prepared.append(e.request_id)
             if self._graph_eligible(entries):
-                logits = self._graph_step(entries)
+                logits, _ = self._graph_step(entries)
             else:
                 batch = self.make_batch(entries)
                 logits = self.model.forward(batch, self._views)
@@ -245,8 +249,7 @@ class Engine:
             for e in entries:
                 self.cache.prepare(e.request_id, n_steps)
                 prepared.append(e.request_id)
-            logits = self._graph_step(entries)          # step 0 (captures the graph at first use)
-            g = self._graphs[b]
+            logits, g = self._graph_step(entries, extra_positions=n_steps - 1)   # step 0 (captures at first use)
             lay = g["layout"]
 
             def part(name):
