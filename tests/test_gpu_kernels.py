@@ -1,0 +1,356 @@
+"""Each kernel alone against a plain float32/float64 reference of the same operation, at
+sizes other than the engine's: widths that are no power of two, odd row counts, head
+sizes in steps of 16, several page sizes. Inputs are built so that faults show: a far
+key that dominates a softmax, a window's edge, values in unused pages that would
+poison a result if read."""
+
+import math
+
+import pytest
+import torch
+
+from kernel_refs import build_pages, ref_paged_attention
+from plain.plain_qwen3 import plain_sample
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def _k():
+    from quantinfer_b200 import kernels
+    return kernels
+
+
+def _status():
+    return torch.zeros(1, dtype=torch.int32, device=DEV)
+
+
+def I(x):
+    return torch.tensor(x, dtype=torch.int32, device=DEV)
+
+
+# ------------------------------------------------------------------ embedding, norms
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("vocab, hidden", [(37, 20), (300, 168), (1000, 4096)])
+def test_embedding(dtype, vocab, hidden):
+    torch.manual_seed(0)
+    table = torch.randn(vocab, hidden).to(dtype).to(DEV)
+    ids = torch.randint(0, vocab, (13,), dtype=torch.int32)
+    out = torch.empty(13, hidden, dtype=torch.float32, device=DEV)
+    st = _status()
+    _k().embedding(table, ids.to(DEV), out, st)
+    assert torch.equal(out.cpu(), table.float().cpu()[ids.long()]) and st.item() == 0
+    bad = ids.clone()
+    bad[3] = vocab
+    _k().embedding(table, bad.to(DEV), out, st)
+    assert st.item() == _k().STATUS_BAD_TOKEN and float(out[3].abs().max()) == 0.0
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("rows, hidden", [(1, 20), (7, 168), (5, 4096), (3, 1000)])
+def test_add_rmsnorm(dtype, rows, hidden):
+    torch.manual_seed(1)
+    resid = torch.randn(rows, hidden)
+    delta = torch.randn(rows, hidden).to(dtype)
+    gain = 1 + 0.1 * torch.randn(hidden)
+    eps = 3e-6
+    x = resid.double() + delta.double()
+    ref = x * torch.rsqrt((x * x).mean(-1, keepdim=True) + eps) * gain.double()
+    r = resid.to(DEV)
+    out = torch.empty(rows, hidden, dtype=dtype, device=DEV)
+    _k().add_rmsnorm(r, delta.to(DEV), gain.to(DEV), eps, out)
+    tol = 1e-5 if dtype == torch.float32 else 2e-2
+    assert float((out.double().cpu() - ref).abs().max()) < tol
+    assert float((r.double().cpu() - x).abs().max()) < 1e-6           # the residual stream was updated
+    # no delta, row gather, residual untouched
+    r2 = resid.to(DEV)
+    pick = I([rows - 1, 0])
+    out2 = torch.empty(2, hidden, dtype=dtype, device=DEV)
+    _k().add_rmsnorm(r2, None, gain.to(DEV), eps, out2, rows=pick)
+    x2 = resid.double()[[rows - 1, 0]]
+    ref2 = x2 * torch.rsqrt((x2 * x2).mean(-1, keepdim=True) + eps) * gain.double()
+    assert float((out2.double().cpu() - ref2).abs().max()) < tol and torch.equal(r2.cpu(), resid)
+
+
+def test_add_rmsnorm_takes_split_partials():
+    torch.manual_seed(2)
+    resid, parts = torch.randn(6, 264), torch.randn(3, 6, 264)
+    gain = torch.ones(264)
+    x = resid.double() + parts.double().sum(0)
+    ref = x * torch.rsqrt((x * x).mean(-1, keepdim=True) + 1e-6)
+    out = torch.empty(6, 264, dtype=torch.bfloat16, device=DEV)
+    r = resid.to(DEV)
+    _k().add_rmsnorm(r, parts.to(DEV), gain.to(DEV), 1e-6, out)
+    assert float((out.double().cpu() - ref).abs().max()) < 2e-2 and float((r.double().cpu() - x).abs().max()) < 1e-5
+
+
+# ------------------------------------------------------------------ matrix products
+
+@pytest.mark.parametrize("tx, tw, ty", [(torch.float32,) * 3, (torch.bfloat16,) * 3,
+                                        (torch.bfloat16, torch.float32, torch.bfloat16),
+                                        (torch.bfloat16, torch.bfloat16, torch.float32)])
+@pytest.mark.parametrize("M, N, K", [(1, 7, 5), (65, 130, 33), (200, 517, 168)])
+def test_gemm_simt(tx, tw, ty, M, N, K):
+    torch.manual_seed(3)
+    x, w = torch.randn(M, K).to(tx), torch.randn(N, K).to(tw)
+    out = torch.empty(M, N, dtype=ty, device=DEV)
+    _k().gemm_simt(x.to(DEV), w.to(DEV), out)
+    ref = x.double() @ w.double().t()
+    tol = 1e-4 if ty == torch.float32 else 0.15
+    assert float((out.double().cpu() - ref).abs().max()) < tol
+
+
+@pytest.mark.parametrize("M, N, K, plan", [
+    (128, 128, 64, (False, 128, 1)), (100, 72, 136, (False, 64, 1)), (300, 520, 264, None),
+    (4, 128, 64, (True, 16, 1)), (1, 384, 96, None), (33, 517, 168, (True, 64, 2)),
+    (64, 1000, 2048, None), (200, 300, 4096, None), (700, 328, 168, (False, 256, 1)), (17, 264, 1032, (True, 32, 4)),
+])
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
+def test_gemm_tcgen05(M, N, K, plan, out_dtype):
+    torch.manual_seed(4)
+    x, w = (torch.randn(M, K) * 0.5).bfloat16(), (torch.randn(N, K) * 0.5).bfloat16()
+    out = torch.full((M, N), 7.0, dtype=out_dtype, device=DEV)
+    st = _status()
+    _k().gemm_bf16(x.to(DEV), w.to(DEV), out, plan=plan, status=st)
+    ref = x.double() @ w.double().t()
+    err = float((out.double().cpu() - ref).abs().max())
+    scale = float(ref.abs().max())
+    assert st.item() == 0
+    assert err < (2e-4 if out_dtype == torch.float32 else scale * 2 ** -7), (err, scale)
+
+
+@pytest.mark.parametrize("M, N, K", [(5, 256, 136), (130, 328, 264), (64, 4096, 512)])
+def test_gemm_tcgen05_silu_epilogue_and_partials(M, N, K):
+    torch.manual_seed(5)
+    x, w = (torch.randn(M, K) * 0.3).bfloat16(), (torch.randn(N, K) * 0.3).bfloat16()
+    act = torch.empty(M, N // 2, dtype=torch.bfloat16, device=DEV)
+    _k().gemm_bf16(x.to(DEV), w.to(DEV), act, epilogue="silu_mul")
+    y = x.double() @ w.double().t()
+    g, u = y[:, 0::2], y[:, 1::2]
+    ref = g / (1 + torch.exp(-g)) * u
+    assert float((act.double().cpu() - ref).abs().max()) < max(0.05, float(ref.abs().max()) * 2 ** -7)
+    parts = _k().gemm_bf16(x.to(DEV), w.to(DEV), None, plan=(True if M <= 256 else False, 16 if M <= 16 else 256 if M > 64 else 64, 2),
+                           keep_partials=True)
+    assert parts.shape == (2, M, N) and float((parts.double().sum(0).cpu() - y).abs().max()) < 2e-4
+
+
+# ------------------------------------------------------------------ q/k norm, rotation, cache write
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("nq, nkv, d, rot, ps", [(4, 2, 16, 16, 4), (6, 3, 48, 48, 32), (8, 1, 128, 128, 64),
+                                                (3, 3, 34, 34, 5), (4, 2, 32, 16, 8)])
+def test_qk_norm_rope_kv(dtype, nq, nkv, d, rot, ps):
+    torch.manual_seed(6)
+    n, theta, eps = 9, 5e4, 1e-5
+    positions = [3, 4, 5, 0, 17, 18, 19, 20, 63]
+    token_req = [0, 0, 0, 1, 2, 2, 2, 2, 2]
+    qkv = torch.randn(n, (nq + 2 * nkv) * d).to(dtype)
+    qg, kg = 1 + 0.1 * torch.randn(d), 1 + 0.1 * torch.randn(d)
+    inv_freq = torch.pow(torch.tensor(theta), -(2.0 * torch.arange(rot // 2)) / rot)
+    cos, sin = _k().rope_table(inv_freq.to(DEV), 64)
+    ang = torch.arange(64, dtype=torch.float32)[:, None] * inv_freq[None, :]
+    assert float((cos.cpu() - torch.cos(ang)).abs().max()) < 2e-6 and float((sin.cpu() - torch.sin(ang)).abs().max()) < 2e-6
+    max_blocks = -(-64 // ps)
+    num_pages = 3 * max_blocks + 2
+    table = torch.full((3, max_blocks), -1, dtype=torch.int32)
+    perm = torch.randperm(num_pages).tolist()
+    for r in range(3):
+        for b in range(max_blocks):
+            table[r, b] = perm.pop()
+    kp = torch.zeros(num_pages, nkv, ps, d, dtype=dtype, device=DEV)
+    vp = torch.zeros_like(kp)
+    q_out = torch.empty(n, nq * d, dtype=dtype, device=DEV)
+    st = _status()
+    _k().qk_norm_rope_kv(qkv.to(DEV), q_out, qg.to(DEV), kg.to(DEV), eps, cos, sin, rot, I(positions), I(token_req),
+                         table.to(DEV), ps, kp, vp, nq, nkv, d, st)
+    assert st.item() == 0
+
+    def norm_rot(x, gain, pos):
+        x = x.double()
+        x = x * torch.rsqrt((x * x).mean(-1, keepdim=True) + eps) * gain.double()
+        half = rot // 2
+        c, s = torch.cos(ang[pos].double()), torch.sin(ang[pos].double())
+        a, b = x[..., :half], x[..., half:rot]
+        return torch.cat([a * c - b * s, a * s + b * c, x[..., rot:]], dim=-1)
+
+    tol = 1e-5 if dtype == torch.float32 else 3e-2
+    x = qkv.reshape(n, nq + 2 * nkv, d)
+    for t in range(n):
+        ref_q = norm_rot(x[t, :nq], qg, positions[t])
+        assert float((q_out[t].double().cpu().reshape(nq, d) - ref_q).abs().max()) < tol
+        page, row = int(table[token_req[t], positions[t] // ps]), positions[t] % ps
+        ref_k = norm_rot(x[t, nq:nq + nkv], kg, positions[t])
+        assert float((kp[page, :, row].double().cpu() - ref_k).abs().max()) < tol
+        assert torch.equal(vp[page, :, row].cpu(), x[t, nq + nkv:])          # values are stored as they are
+    written = {(int(table[token_req[t], positions[t] // ps]), positions[t] % ps) for t in range(n)}
+    assert int((kp.abs().sum(dim=(1, 3)) > 0).sum()) == len(written)          # nothing else was touched
+
+
+# ------------------------------------------------------------------ attention
+
+def _attention_case(nq, nkv, d, ctx, new, ps, window, dtype, mode):
+    """ctx[r] cached positions and new[r] query tokens per request. One query per request
+    has a far key that dominates its softmax, so a missed or misplaced key changes the result."""
+    torch.manual_seed(7)
+    k = _k()
+    R = len(ctx)
+    tot = [c + n for c, n in zip(ctx, new)]
+    k_seq = [torch.randn(t, nkv, d).to(dtype).float() for t in tot]
+    v_seq = [torch.randn(t, nkv, d).to(dtype).float() for t in tot]
+    n = sum(new)
+    q = (torch.randn(n, nq * d) * 1.5).to(dtype).float()
+    positions, token_req, q_start = [], [], [0]
+    for r in range(R):
+        positions += list(range(ctx[r], tot[r]))
+        token_req += [r] * new[r]
+        q_start.append(q_start[-1] + new[r])
+    for r in range(R):
+        t = q_start[r + 1] - 1
+        far = max(0, tot[r] - window) if window else min(1, tot[r] - 1)   # the window's far edge, or nearly the first key
+        q[t, :d] = 0
+        q[t, 0] = 8.0
+        k_seq[r][far, 0, :] = 0
+        k_seq[r][far, 0, 0] = 8.0
+    num_pages = sum(-(-t // ps) for t in tot) + 3
+    kp, vp, table = build_pages(k_seq, v_seq, ps, num_pages, nkv, d, dtype, DEV)
+    scale = d ** -0.5
+    ref = ref_paged_attention(q, k_seq, v_seq, positions, token_req, nq, nkv, d, scale, window)
+    qd = q.to(dtype).to(DEV)
+    out = torch.zeros_like(qd)
+    st = _status()
+    if mode == "generic":
+        k.attention_generic(qd, out, kp, vp, table, I(positions), I(token_req), nq, nkv, d, scale, window, st)
+    elif mode.startswith("decode"):
+        chunk, splits = k.attention_decode_plan(R, nkv, max(tot) + 70)
+        k.attention_decode(qd, out, kp, vp, table, I(tot), I(q_start), nq, nkv, d, scale, window, chunk, splits, st,
+                           use_tma=mode.endswith("tma"))
+    else:
+        tiles = [(r, q_start[r] + t0) for r in range(R) for t0 in range(0, new[r], k.QUERY_TILE)]
+        k.attention_prefill(qd, out, kp, vp, table, I(q_start), I(ctx), I([t[0] for t in tiles]),
+                            I([t[1] for t in tiles]), nq, nkv, d, scale, window, st, use_tma=mode.endswith("tma"))
+    assert st.item() == 0
+    return float((out.double().cpu() - ref).abs().max())
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("nq, nkv, d, ctx, new, ps, window", [
+    (4, 2, 16, [0, 5], [33, 1], 4, 0), (6, 3, 48, [40, 0], [7, 100], 32, 0), (8, 1, 32, [300], [3], 8, 0),
+    (4, 4, 80, [0], [70], 16, 0), (8, 2, 128, [200, 0], [2, 130], 64, 0), (2, 1, 256, [30], [10], 16, 0),
+    (6, 3, 64, [40, 0], [90, 150], 32, 50), (4, 2, 16, [100], [1], 7, 9),
+])
+def test_attention_generic(dtype, nq, nkv, d, ctx, new, ps, window):
+    err = _attention_case(nq, nkv, d, ctx, new, ps, window, dtype, "generic")
+    assert err < (2e-5 if dtype == torch.float32 else 1.2e-2)
+
+
+@pytest.mark.parametrize("mode", ["prefill", "prefill_tma"])
+@pytest.mark.parametrize("nq, nkv, d, ctx, new, ps, window", [
+    (4, 2, 64, [0], [64], 16, 0), (4, 2, 64, [0, 0], [100, 3], 16, 0), (8, 2, 128, [0, 37, 200], [130, 64, 1], 64, 0),
+    (8, 1, 128, [5, 300], [70, 2], 8, 0), (6, 3, 64, [40, 0], [90, 150], 32, 50), (8, 2, 128, [100, 0], [300, 257], 128, 0),
+    (16, 1, 64, [129], [127], 32, 0),
+])
+def test_attention_prefill_kernels(mode, nq, nkv, d, ctx, new, ps, window):
+    assert _attention_case(nq, nkv, d, ctx, new, ps, window, torch.bfloat16, mode) < 1.2e-2
+
+
+def test_attention_prefill_without_tma_takes_any_page_size():
+    assert _attention_case(4, 2, 64, [10, 0], [90, 31], 24, 0, torch.bfloat16, "prefill") < 1.2e-2
+    assert _attention_case(4, 2, 64, [10, 77], [1, 1], 24, 0, torch.bfloat16, "decode") < 1.2e-2
+
+
+@pytest.mark.parametrize("mode", ["decode", "decode_tma"])
+@pytest.mark.parametrize("nq, nkv, d, ctx, ps, window", [
+    (4, 2, 64, [63], 16, 0), (4, 2, 64, [10, 200, 64], 16, 0), (32, 8, 128, [2047, 100, 513, 0], 64, 0),
+    (8, 1, 128, [700, 3], 8, 0), (8, 2, 128, [300, 90], 32, 64), (8, 2, 128, [1000, 90], 256, 0),
+])
+def test_attention_decode_kernels(mode, nq, nkv, d, ctx, ps, window):
+    assert _attention_case(nq, nkv, d, ctx, [1] * len(ctx), ps, window, torch.bfloat16, mode) < 1.2e-2
+
+
+def test_attention_kernels_refuse_what_they_do_not_cover():
+    from quantinfer_b200.errors import KernelError
+
+    k = _k()
+    assert not k.attention_mma_supported(4, 2, 48) and not k.attention_tma_supported(4, 2, 64, 24)
+    q = torch.zeros(1, 4 * 48, dtype=torch.bfloat16, device=DEV)
+    pages = torch.zeros(2, 2, 16, 48, dtype=torch.bfloat16, device=DEV)
+    with pytest.raises(KernelError, match="not covered"):
+        k.attention_prefill(q, torch.empty_like(q), pages, pages, I([[0]]), I([0, 1]), I([0]), I([0]), I([0]), 4, 2, 48,
+                            1.0, 0, _status(), use_tma=False)
+    with pytest.raises(KernelError, match="limit"):
+        big = torch.zeros(1, 2 * 272, dtype=torch.float32, device=DEV)
+        k.attention_generic(big, torch.empty_like(big), torch.zeros(1, 2, 4, 272, device=DEV),
+                            torch.zeros(1, 2, 4, 272, device=DEV), I([[0]]), I([0]), I([0]), 2, 2, 272, 1.0, 0, _status())
+
+
+# ------------------------------------------------------------------ activation, sampling
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("interleaved", [False, True])
+def test_silu_mul(dtype, interleaved):
+    torch.manual_seed(8)
+    g, u = torch.randn(5, 57).to(dtype) * 3, torch.randn(5, 57).to(dtype)
+    gu = torch.stack([g, u], dim=2).reshape(5, 114) if interleaved else torch.cat([g, u], dim=1)
+    out = torch.empty(5, 57, dtype=dtype, device=DEV)
+    _k().silu_mul(gu.contiguous().to(DEV), out, interleaved=interleaved)
+    ref = g.double() / (1 + torch.exp(-g.double())) * u.double()
+    assert float((out.double().cpu() - ref).abs().max()) < (1e-6 if dtype == torch.float32 else 3e-2)
+
+
+def _sample(logits, temperature=None, top_k=None, top_p=None, seed=None, counter=None):
+    rows = logits.shape[0]
+    st = _status()
+    out = torch.empty(rows, dtype=torch.int32, device=DEV)
+    f = lambda v, dt: None if v is None else torch.tensor(v, dtype=dt, device=DEV)
+    _k().sample(logits.to(DEV), f(temperature, torch.float32), f(top_k, torch.int32), f(top_p, torch.float32),
+                f(seed, torch.int64), f(counter, torch.int32), out, st)
+    return out.cpu().tolist(), st.item()
+
+
+def test_sample_greedy_first_maximum():
+    x = torch.randn(4, 1000)
+    x[1, 17] = x[1, 900] = 50.0          # a tie: the lowest index wins
+    x[2, 999] = 60.0
+    toks, st = _sample(x)
+    assert st == 0 and toks == [int(x[0].argmax()), 17, 999, int(x[3].argmax())]
+    x[3, 5] = float("nan")
+    assert _sample(x)[1] == _k().STATUS_NON_FINITE
+
+
+@pytest.mark.parametrize("vocab", [50, 517, 4099])
+def test_sample_matches_the_plain_sampler(vocab):
+    torch.manual_seed(9)
+    rows = 24
+    x = torch.randn(rows, vocab) * 2
+    x[:, 3] = x[:, 11]                    # ties inside the candidate set
+    temps = [0.0, 0.8, 1.3, 0.5] * 6
+    ks = [0, 0, 5, 20, 0, 1] * 4
+    ps = [0.0, 0.0, 0.0, 0.0, 0.9, 0.5, 0.3, 1.0] * 3
+    seeds = [7 + (r << 33) for r in range(rows)]
+    counters = list(range(rows))
+    toks, st = _sample(x, temps, ks, ps, seeds, counters)
+    assert st == 0
+    for r in range(rows):
+        expect = plain_sample(x[r], temps[r], ks[r] or None, ps[r] or None, seeds[r], counters[r])
+        assert toks[r] == expect, (r, temps[r], ks[r], ps[r])
+
+
+def test_sample_follows_the_distribution_and_the_counter():
+    x = torch.tensor([[0.0, 2.0, 1.0, -1.0, 2.0]]).repeat(4000, 1)
+    toks, _ = _sample(x, [1.0] * 4000, None, None, [12345] * 4000, list(range(4000)))
+    p = torch.softmax(x[0], 0)
+    freq = torch.bincount(torch.tensor(toks), minlength=5).double() / 4000
+    assert float((freq - p.double()).abs().max()) < 0.03
+    again, _ = _sample(x[:50], [1.0] * 50, None, None, [12345] * 50, list(range(50)))
+    assert again == toks[:50]            # same seed and counter, same token
+    other, _ = _sample(x[:50], [1.0] * 50, None, None, [12346] * 50, list(range(50)))
+    assert other != toks[:50]
+
+
+def test_advance_decode():
+    tok, pos, sp, kv, ctr = I([5, 6]), I([10, 20]), I([10, 20]), I([11, 21]), I([0, 3])
+    hist = torch.zeros(2, dtype=torch.int32, device=DEV)
+    _k().advance_decode(tok, pos, sp, kv, ctr, I([77, 88]), hist)
+    assert tok.tolist() == [77, 88] and pos.tolist() == [11, 21] and sp.tolist() == [11, 21]
+    assert kv.tolist() == [12, 22] and ctr.tolist() == [1, 4] and hist.tolist() == [77, 88]
