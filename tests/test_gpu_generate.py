@@ -1,0 +1,193 @@
+"""Generation through the entry points: greedy and sampled tokens against the plain
+implementation, the command line's output, long decoding, the first tokens of a
+sequence, batches through the scheduler, and decoding that stays on the device."""
+
+import json
+import os
+import subprocess
+import sys
+from pathlib import Path
+
+import pytest
+import torch
+
+from helpers import PAGE_SIZES, random_tokens, vocab_of
+from plain.plain_qwen3 import plain_forward, plain_generate, plain_load
+
+pytestmark = pytest.mark.gpu
+ROOT = Path(__file__).resolve().parent.parent
+
+
+@pytest.mark.parametrize("name", ["A", "B", "D"])
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_greedy_generation_matches_plain(tiny_folders, name, dtype):
+    import quantinfer_b200
+
+    folder = tiny_folders[name]
+    cfg, w = plain_load(folder)
+    with quantinfer_b200.Model(folder, dtype=dtype, page_size=PAGE_SIZES[name], cache_tokens=1024, max_requests=4) as m:
+        for n in (5, 17, 33):
+            prompt = random_tokens(n, vocab_of(folder), seed=n)
+            expect = plain_generate(w, cfg, prompt, 8)
+            got = m.generate_tokens(prompt, max_new_tokens=8, eos_token_id=None)
+            if dtype == "float32":
+                assert got == expect
+            else:
+                # bfloat16 may pick another token where two logits are nearly tied; up to
+                # the first such place the tokens agree, and that place must be a near-tie
+                i = next((j for j in range(8) if got[j] != expect[j]), 8)
+                if i < 8:
+                    logits = plain_forward(w, cfg, prompt + expect[:i])[-1]
+                    assert abs(float(logits[got[i]] - logits[expect[i]])) < 0.05
+    with pytest.raises(quantinfer_b200.QuantInferError, match="closed"):
+        m.generate_tokens([1], max_new_tokens=1)
+
+
+def test_sampled_generation_matches_plain_under_a_seed(tiny_folders):
+    import quantinfer_b200
+
+    folder = tiny_folders["A"]
+    cfg, w = plain_load(folder)
+    prompt = random_tokens(9, 256, seed=4)
+    with quantinfer_b200.Model(folder, dtype="float32", page_size=16, cache_tokens=512, max_requests=4) as m:
+        for kw in (dict(temperature=0.8, seed=11), dict(temperature=1.2, top_k=20, seed=5), dict(temperature=0.7, top_p=0.8, seed=2**40 + 3)):
+            expect = plain_generate(w, cfg, prompt, 10, **kw)
+            assert m.generate_tokens(prompt, max_new_tokens=10, eos_token_id=None, **kw) == expect
+        # the same request inside a batch draws the same tokens: the stream belongs to the request
+        alone = m.generate_tokens(prompt, max_new_tokens=10, eos_token_id=None, temperature=0.8, seed=11)
+        batch = m.generate_batch([prompt, random_tokens(30, 256, 1), random_tokens(3, 256, 2)], max_new_tokens=10,
+                                 eos_token_id=None, temperature=0.8, seed=11)
+        assert batch[0] == alone and len(batch[1]) == 10
+        # EOS: emitted, then the request stops
+        eos = alone[3]
+        out = m.generate_tokens(prompt, max_new_tokens=10, eos_token_id=eos, temperature=0.8, seed=11)
+        assert out == alone[:alone.index(eos) + 1]
+        with pytest.raises(ValueError):
+            m.generate_tokens(prompt, max_new_tokens=0)
+        with pytest.raises(ValueError):
+            m.generate_tokens([256], max_new_tokens=1)
+        with pytest.raises(ValueError):
+            m.generate_tokens(prompt, max_new_tokens=200)          # exceeds max_position_embeddings
+        with pytest.raises(quantinfer_b200.QuantInferError):
+            m.tokenize("text")
+
+
+def test_batch_through_the_scheduler_equals_each_alone(tiny_folders):
+    """Config B's workload: four requests of 1/9/40/71 tokens, prompt portions of 16 beside decode tokens."""
+    import quantinfer_b200
+
+    folder = tiny_folders["B"]
+    cfg, w = plain_load(folder)
+    prompts = [random_tokens(n, 384, seed=n) for n in (1, 9, 40, 71)]
+    with quantinfer_b200.Model(folder, dtype="float32", page_size=8, cache_tokens=512, max_requests=4,
+                               max_batch_tokens=24, chunk_size=16) as m:
+        got = m.generate_batch(prompts, max_new_tokens=12, eos_token_id=None)
+    for p, g in zip(prompts, got):
+        assert g == plain_generate(w, cfg, p, 12)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_long_decoding_and_first_tokens(tiny_folders, dtype):
+    """A 3-token prompt, then 250 tokens decoded one by one (pages fill and new ones are taken many
+    times, graphs are replayed across context buckets); every position's logits against the plain
+    whole sequence, the very first positions included."""
+    from quantinfer_b200.engine import Engine, StepEntry
+
+    folder = tiny_folders["D"]
+    ids = random_tokens(253, 300, seed=9)
+    cfg, w = plain_load(folder)
+    expect = plain_forward(w, cfg, ids)
+    eng = Engine.from_folder(folder, dtype=dtype, page_size=16, max_tokens=320, max_requests=2)
+    eng.open("r")
+    rows = [eng.step([StepEntry("r", ids[:1], [0])]).cpu(), eng.step([StepEntry("r", ids[1:3], [0, 1])]).cpu()]
+    for t in range(3, len(ids)):
+        rows.append(eng.step([StepEntry("r", [ids[t]], [0])]).cpu())
+    got = torch.cat(rows)
+    diff = (got - expect).abs().max(dim=1).values
+    tol = 2e-5 if dtype == "float32" else 3e-2
+    assert float(diff.max()) <= tol, f"first position above the tolerance: {int((diff > tol).nonzero()[0])}"
+
+
+def test_decode_on_device_equals_step_by_step(tiny_folders):
+    from quantinfer_b200.engine import Engine, StepEntry
+    from quantinfer_b200.sampling import GenerationConfig, Sampler
+
+    folder = tiny_folders["D"]
+    prompts = [random_tokens(n, 300, seed=n) for n in (20, 70, 5)]
+    cfgs = [GenerationConfig(max_new_tokens=64, temperature=t, seed=s) for t, s in ((0.0, 0), (0.9, 5), (0.6, 9))]
+
+    def run(on_device):
+        eng = Engine.from_folder(folder, dtype="bfloat16", page_size=16, max_tokens=1024, max_requests=4)
+        sampler = Sampler(eng.device, eng.runtime.status)
+        first = []
+        for i, p in enumerate(prompts):
+            eng.open(i)
+            logits = eng.step([StepEntry(i, p, [len(p) - 1])])
+            first.append(sampler.sample(logits, [(cfgs[i], 0)])[0])
+        rows = [(c, 1) for c in cfgs]
+        if on_device:
+            return first, eng.decode_on_device([0, 1, 2], first, 40, rows, sampler).cpu().tolist()
+        hist, cur = [], first
+        for n in range(40):
+            logits = eng.step([StepEntry(i, [cur[i]], [0]) for i in range(3)])
+            cur = sampler.sample(logits, [(c, 1 + n) for c in cfgs])
+            hist.append(cur)
+        return first, hist
+
+    assert run(True) == run(False)
+
+
+def test_command_line(tiny_folders, tmp_path):
+    folder = tiny_folders["A"]
+    cfg, w = plain_load(folder)
+    prompt = [5, 17, 3, 200, 9]
+    expect = plain_generate(w, cfg, prompt, 8)
+    report = tmp_path / "report.json"
+    cmd = [sys.executable, str(ROOT / "bin" / "quantinfer"), "generate", "--input", str(folder), "--tokens", "5, 17,3,200 ,9",
+           "--max-new-tokens", "8", "--dtype", "float32", "--page-size", "16", "--profile", "--profile-report", str(report)]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stderr
+    lines = dict(l.split("=", 1) for l in r.stdout.strip().splitlines())
+    assert lines["prompt_tokens"] == str(prompt) and lines["generated_tokens"] == str(expect)
+    assert lines["decode_tokens"] == "8" and float(lines["prefill_ms"]) > 0 and float(lines["decode_tokens_per_sec"]) > 0
+    for key in ("model_load_ms", "ttft_ms", "profile_decode_ms", "kv_cache_bytes", "kv_cache_capacity_bytes", "max_sequence_length", "peak_rss_kib"):
+        assert key in lines
+    # the cache holds prompt + generated - 1 positions: 2 layers x 12 positions x 2 kv heads x 16 x (k, v) x 4 bytes
+    assert int(lines["kv_cache_bytes"]) == 2 * 12 * 2 * 16 * 2 * 4
+    assert json.loads(report.read_text())["decode_tokens"] == 8
+    r2 = subprocess.run(cmd, capture_output=True, text=True, timeout=300)
+    assert r2.returncode == 2 and "already exists" in r2.stderr
+    for bad, msg in ((["--prompt", "hi"], "exactly one"), (["--bogus"], "unknown option"), (["--max-new-tokens", "200"], "exceed"),
+                     (["--eos-token-id", "999"], "outside the model vocabulary")):
+        args = [a for a in cmd[:-3]] + bad if bad[0] != "--max-new-tokens" else [a for a in cmd[:-3] if a not in ("--max-new-tokens", "8")] + bad
+        r3 = subprocess.run(args, capture_output=True, text=True, timeout=300)
+        assert r3.returncode == 2 and msg in r3.stderr, (bad, r3.stderr)
+
+
+def test_random_weights_command_and_engine_errors(tmp_path):
+    from quantinfer_b200.engine import Engine, StepEntry
+    from quantinfer_b200.errors import OutOfPages, QuantInferError
+    from helpers import TINY_CONFIGS
+
+    (tmp_path / "cfg.json").write_text(json.dumps(TINY_CONFIGS["C"]))
+    out = tmp_path / "model"
+    r = subprocess.run([sys.executable, str(ROOT / "bin" / "quantinfer"), "random-weights", "--config", str(tmp_path / "cfg.json"),
+                        "--output", str(out), "--seed", "2"], capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0 and (out / "model.safetensors").is_file() and (out / "config.json").is_file()
+    eng = Engine.from_folder(out, dtype="float32", page_size=32, max_tokens=128, max_requests=2)
+    eng.open("a")
+    with pytest.raises(QuantInferError, match="outside the vocabulary"):
+        eng.step([StepEntry("a", [517], [0])])
+    with pytest.raises(QuantInferError, match="at least one token"):
+        eng.step([StepEntry("a", [], [])])
+    with pytest.raises(QuantInferError, match="not open"):
+        eng.step([StepEntry("zzz", [1], [0])])
+    with pytest.raises(QuantInferError, match="wanted place"):
+        eng.step([StepEntry("a", [1, 2], [2])])
+    eng.step([StepEntry("a", list(range(100)), [])])
+    eng.open("b")
+    free = eng.cache.free_pages()
+    with pytest.raises(OutOfPages):                      # 4 pages in all, 4 taken by a
+        eng.step([StepEntry("a", [1], [0]), StepEntry("b", list(range(40)), [])])
+    assert eng.cache.free_pages() == free and eng.length("a") == 100 and eng.length("b") == 0   # nothing advanced
+    eng.cache.check_invariants()

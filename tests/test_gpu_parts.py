@@ -1,0 +1,354 @@
+"""Each part alone against the plain implementation's function for it, and what makes
+the parts general: layers that differ inside one model, a windowed layer with pages
+of its own, a run order that names a layer twice or lets a layer read another
+layer's cache, and a toy mixer with per-request state that is registered, built and
+stepped from here without touching the framework's files."""
+
+import dataclasses
+
+import pytest
+import torch
+
+from plain.plain_qwen3 import (plain_apply_rope, plain_embedding, plain_feed_forward, plain_gqa_attention,
+                               plain_linear, plain_rms_norm, plain_rope_tables)
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+TOL = {torch.float32: 3e-5, torch.bfloat16: 4e-2}
+
+
+def _runtime(dtype):
+    from quantinfer_b200.parts import Runtime
+    return Runtime(dtype, DEV)
+
+
+def _batch(lengths, starts, cache, want_all=True):
+    """A StepBatch for entries of the given lengths at the given start positions."""
+    from quantinfer_b200.engine.batch import StepEntry, batch_from_packed, pack_batch
+
+    entries = [StepEntry(i, [0] * n, list(range(n)) if want_all else []) for i, n in enumerate(lengths)]
+    slots = [cache.get(i).slot for i in range(len(lengths))]
+    buf, layout, q_start, lens = pack_batch(entries, starts, slots, cache.host_tables, cache.max_blocks)
+    dev = torch.from_numpy(buf).to(DEV)
+    return batch_from_packed(dev, layout, entries, starts, slots, q_start, lens, len(cache.groups), cache.max_blocks)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_norm_part(dtype):
+    from quantinfer_b200.config import NormSpec
+    from quantinfer_b200.parts import build_part
+
+    torch.manual_seed(0)
+    spec = NormSpec(size=168, eps=2e-5, prefix="n.")
+    part = build_part("norm", spec, _runtime(dtype))
+    assert list(part.tensor_needs()) == ["n.weight"]
+    gain = 1 + 0.1 * torch.randn(168)
+    part.load({"n.weight": gain})
+    resid, delta = torch.randn(5, 168), torch.randn(5, 168).to(dtype)
+    r = resid.to(DEV)
+    out = part.forward(r, delta.to(DEV))
+    ref = plain_rms_norm(resid + delta.float(), gain, 2e-5)
+    assert float((out.float().cpu() - ref).abs().max()) < TOL[dtype]
+    assert float((r.cpu() - (resid + delta.float())).abs().max()) < 1e-6
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_feed_forward_part(dtype):
+    from quantinfer_b200.config import FeedForwardSpec
+    from quantinfer_b200.parts import build_part
+
+    torch.manual_seed(1)
+    spec = FeedForwardSpec(hidden_size=72, intermediate_size=136, prefix="m.")
+    part = build_part("ffn", spec, _runtime(dtype))
+    w = {"m.gate_proj.weight": (torch.randn(136, 72) * 0.1).to(dtype), "m.up_proj.weight": (torch.randn(136, 72) * 0.1).to(dtype),
+         "m.down_proj.weight": (torch.randn(72, 136) * 0.1).to(dtype)}
+    assert {k: v.shape for k, v in part.tensor_needs().items()} == {k: tuple(v.shape) for k, v in w.items()}
+    part.load(w)
+    x = torch.randn(9, 72).to(dtype)
+    y = part.forward(x.to(DEV))
+    if y.dim() == 3:
+        y = y.sum(0)
+    ref = plain_feed_forward(x.float(), {k: v.float() for k, v in w.items()}, "m.")
+    assert float((y.float().cpu() - ref).abs().max()) < TOL[dtype]
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_embedding_and_head_parts(dtype):
+    from quantinfer_b200.config import EmbeddingSpec, HeadSpec
+    from quantinfer_b200.parts import build_part
+
+    torch.manual_seed(2)
+    rt = _runtime(dtype)
+    emb = build_part("embedding", EmbeddingSpec(517, 40, "e."), rt)
+    table = torch.randn(517, 40).to(dtype)
+    emb.load({"e.weight": table})
+    ids = [0, 516, 33]
+    out = emb.forward(torch.tensor(ids, dtype=torch.int32, device=DEV))
+    assert out.dtype == torch.float32 and torch.equal(out.cpu(), plain_embedding(table.float(), ids))
+    tied = build_part("head", HeadSpec(517, 40, True, "h."), rt)
+    assert tied.tensor_needs() == {}
+    tied.tie(emb)
+    x = torch.randn(3, 40).to(dtype)
+    logits = tied.forward(x.to(DEV))
+    assert logits.dtype == torch.float32
+    assert float((logits.cpu() - plain_linear(x.float(), table.float())).abs().max()) < TOL[dtype] * 10
+    untied = build_part("head", HeadSpec(517, 40, False, "h."), rt)
+    assert list(untied.tensor_needs()) == ["h.weight"]
+
+
+def _attention_weights(spec, dtype, sharp=3.0):
+    d, nq, nkv, h = spec.head_dim, spec.num_heads, spec.num_kv_heads, spec.hidden_size
+    p = spec.prefix
+    return {p + "q_proj.weight": (torch.randn(nq * d, h) * 0.2).to(dtype), p + "k_proj.weight": (torch.randn(nkv * d, h) * 0.2).to(dtype),
+            p + "v_proj.weight": (torch.randn(nkv * d, h) * 0.2).to(dtype), p + "o_proj.weight": (torch.randn(h, nq * d) * 0.2).to(dtype),
+            # large q/k gains make the softmax peaked, so that one wrong key changes the output visibly
+            p + "q_norm.weight": sharp * (1 + 0.1 * torch.randn(d)), p + "k_norm.weight": 1 + 0.1 * torch.randn(d)}
+
+
+def _plain_attention(x, w, spec, window=None):
+    p, d, nq, nkv = spec.prefix, spec.head_dim, spec.num_heads, spec.num_kv_heads
+    T = x.shape[0]
+    f = {k: v.float() for k, v in w.items()}
+    q = plain_rms_norm(plain_linear(x, f[p + "q_proj.weight"]).reshape(T, nq, d), f[p + "q_norm.weight"], spec.qk_norm_eps)
+    k = plain_rms_norm(plain_linear(x, f[p + "k_proj.weight"]).reshape(T, nkv, d), f[p + "k_norm.weight"], spec.qk_norm_eps)
+    v = plain_linear(x, f[p + "v_proj.weight"]).reshape(T, nkv, d)
+    cos, sin = plain_rope_tables(spec.position.theta, d, list(range(T)))
+    a = plain_gqa_attention(plain_apply_rope(q, cos, sin), plain_apply_rope(k, cos, sin), v, window)
+    return plain_linear(a.reshape(T, nq * d), f[p + "o_proj.weight"])
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("nq, nkv, d, window, page", [(4, 2, 16, None, 4), (6, 3, 48, None, 32), (4, 2, 64, None, 16),
+                                                      (8, 1, 32, 11, 8), (4, 2, 64, 40, 16)])
+def test_attention_part_in_portions(dtype, nq, nkv, d, window, page):
+    """The mixer alone over a paged cache: one sequence fed in portions equals the plain
+    whole-sequence attention, with a window and without."""
+    from quantinfer_b200.cache import CacheManager
+    from quantinfer_b200.config import AttentionSpec, PositionSpec
+    from quantinfer_b200.parts import build_part
+
+    torch.manual_seed(3)
+    hidden, T = 56, 150
+    spec = AttentionSpec(hidden, nq, nkv, d, PositionSpec(d, d, 30000.0, 256), qk_norm=True, qk_norm_eps=1e-5,
+                         window=window, prefix="a.")
+    rt = _runtime(dtype)
+    part = build_part("mixer", spec, rt)
+    w = _attention_weights(spec, dtype)
+    part.load(w)
+    cache = CacheManager([part.cache_need()], page, 64, 2, 256, dtype, DEV)
+    cache.open(0)
+    x = torch.randn(T, hidden).to(dtype)
+    ref = _plain_attention(x.float(), w, spec, window)
+    outs, pos = [], 0
+    for n in (70, 1, 1, 2, 33, 1, 42):
+        cache.prepare(0, n)
+        batch = _batch([n], [pos], cache)
+        y = part.forward(x[pos:pos + n].to(DEV), batch, cache.view(0))
+        outs.append(y.sum(0) if y.dim() == 3 else y)
+        cache.commit(0)
+        pos += n
+    got = torch.cat(outs).float().cpu()
+    assert rt.status.item() == 0
+    # bfloat16: values here reach |8|, where one bfloat16 step is 2^-5; six roundings of
+    # intermediates feed a peaked softmax, so the bound is 2^-6 of the largest value
+    tol = 1e-4 if dtype == torch.float32 else float(ref.abs().max()) * 2 ** -6
+    assert float((got - ref).abs().max()) < tol
+    if window:
+        assert cache.free_pages() > 64 - -(-T // page)      # pages that the window passed went back
+
+
+# ------------------------------------------------------------------ generality of the model
+
+class _SpecTools:
+    @staticmethod
+    def tiny_spec(layers, order=None, hidden=48, vocab=97):
+        from quantinfer_b200.config import (EmbeddingSpec, HeadSpec, LayerCall, ModelSpec, NormSpec)
+
+        order = order or tuple(LayerCall(i, i) for i in range(len(layers)))
+        return ModelSpec("Test", vocab, hidden, 128, EmbeddingSpec(vocab, hidden, "emb."), tuple(layers), tuple(order),
+                         NormSpec(hidden, 1e-6, "final."), HeadSpec(vocab, hidden, True, "head."))
+
+    @staticmethod
+    def layer(i, hidden=48, nq=4, nkv=2, d=16, inter=80, window=None, mixer=None):
+        from quantinfer_b200.config import AttentionSpec, FeedForwardSpec, LayerSpec, NormSpec, PositionSpec
+
+        p = f"l{i}."
+        mixer = mixer or AttentionSpec(hidden, nq, nkv, d, PositionSpec(d, d, 1e4, 128), qk_norm=True, window=window,
+                                       prefix=p + "attn.")
+        return LayerSpec(NormSpec(hidden, 1e-6, p + "n1."), mixer, NormSpec(hidden, 1e-6, p + "n2."),
+                         FeedForwardSpec(hidden, inter, "silu", p + "mlp."))
+
+
+def _engine(spec, dtype="float32", seed=0, **kw):
+    from quantinfer_b200.engine import Engine, tensor_needs_of_spec
+    from quantinfer_b200.weights import random_tensors
+
+    tensors = random_tensors(tensor_needs_of_spec(spec), seed, torch.bfloat16)
+    for k in tensors:
+        if k.endswith("q_norm.weight"):
+            tensors[k] = tensors[k] * 3.0
+    return Engine(spec, tensors, dtype=dtype, page_size=8, max_tokens=512, max_requests=4, **kw), tensors
+
+
+def _plain_model(tensors, spec, ids):
+    """The plain forward pass for a spec built here: per call of the run order, the plain
+    parts, with the cache-sharing rule (a reading layer uses the writer's keys and values)."""
+    w = {k: v.float() for k, v in tensors.items()}
+    h = plain_embedding(w["emb.weight"], ids)
+    T = len(ids)
+    kv = {}
+    for call in spec.order:
+        L = spec.layers[call.layer]
+        a = L.mixer
+        n = plain_rms_norm(h, w[L.mixer_norm.prefix + "weight"], L.mixer_norm.eps)
+        p, d = a.prefix, a.head_dim
+        q = plain_rms_norm(plain_linear(n, w[p + "q_proj.weight"]).reshape(T, a.num_heads, d), w[p + "q_norm.weight"], a.qk_norm_eps)
+        cos, sin = plain_rope_tables(a.position.theta, d, list(range(T)))
+        q = plain_apply_rope(q, cos, sin)
+        if call.writes_cache:
+            k = plain_rms_norm(plain_linear(n, w[p + "k_proj.weight"]).reshape(T, a.num_kv_heads, d), w[p + "k_norm.weight"], a.qk_norm_eps)
+            kv[call.cache] = (plain_apply_rope(k, cos, sin), plain_linear(n, w[p + "v_proj.weight"]).reshape(T, a.num_kv_heads, d))
+        k, v = kv[call.cache]
+        att = plain_gqa_attention(q, k, v, a.window).reshape(T, a.num_heads * d)
+        h = h + plain_linear(att, w[p + "o_proj.weight"])
+        n = plain_rms_norm(h, w[L.ffn_norm.prefix + "weight"], L.ffn_norm.eps)
+        h = h + plain_feed_forward(n, w, L.ffn.prefix)
+    return plain_linear(plain_rms_norm(h, w["final.weight"], spec.final_norm.eps), w["emb.weight"])
+
+
+def _run_in_portions(eng, ids, cuts):
+    from quantinfer_b200.engine import StepEntry
+
+    eng.open("r")
+    rows, pos = [], 0
+    for n in cuts:
+        rows.append(eng.step([StepEntry("r", ids[pos:pos + n], list(range(n)))]).cpu())
+        pos += n
+    eng.close("r")
+    eng.cache.check_invariants()
+    return torch.cat(rows)
+
+
+def test_layers_that_differ_and_a_windowed_group():
+    """Layer 0: 4 heads of 16 with a window of 9; layer 1: 3 heads of 32, MQA, all keys; layer 2: as layer 0
+    without window. The windowed layer gets a page group of its own and gives pages back."""
+    T = _SpecTools
+    layers = [T.layer(0, window=9), T.layer(1, nq=3, nkv=1, d=32, inter=56), T.layer(2, inter=100)]
+    spec = T.tiny_spec(layers)
+    eng, tensors = _engine(spec)
+    assert len(eng.cache.groups) == 3
+    ids = [int(x) for x in torch.randint(0, 97, (90,))]
+    got = _run_in_portions(eng, ids, (40, 1, 1, 17, 2, 29))
+    ref = _plain_model(tensors, spec, ids)
+    assert float((got - ref).abs().max()) < 5e-5
+
+
+def test_order_names_a_layer_twice_and_shares_a_cache():
+    """Run order: layer 0, layer 1, layer 0 again (its weights reused, a cache entry of its own), then
+    layer 2 reading the keys and values that the first call of layer 0 wrote."""
+    from quantinfer_b200.config import LayerCall
+
+    T = _SpecTools
+    layers = [T.layer(0), T.layer(1, inter=56), T.layer(2)]
+    order = (LayerCall(0, 0), LayerCall(1, 1), LayerCall(0, 2), LayerCall(2, 0, writes_cache=False))
+    spec = T.tiny_spec(layers, order)
+    eng, tensors = _engine(spec)
+    assert eng.spec.cache_entries() == 3 and len(eng.cache.groups) == 1
+    ids = [int(x) for x in torch.randint(0, 97, (70,))]
+    got = _run_in_portions(eng, ids, (33, 1, 1, 1, 30, 4))
+    ref = _plain_model(tensors, spec, ids)
+    assert float((got - ref).abs().max()) < 5e-5
+
+
+def test_bad_run_orders_are_refused():
+    from quantinfer_b200.config import LayerCall
+    from quantinfer_b200.errors import ConfigError
+
+    T = _SpecTools
+    layers = [T.layer(0), T.layer(1)]
+    for order in [(LayerCall(0, 0), LayerCall(1, 0)),                       # two writers of one entry
+                  (LayerCall(0, 1, writes_cache=False), LayerCall(1, 1)),    # read before written
+                  (LayerCall(0, 0), LayerCall(5, 1))]:                       # no such layer
+        with pytest.raises(ConfigError):
+            T.tiny_spec(layers, order).validate()
+    # a reader whose mixer keeps something else than the writer
+    spec = T.tiny_spec([T.layer(0), T.layer(1, nq=3, nkv=1, d=32)], (LayerCall(0, 0), LayerCall(1, 0, writes_cache=False)))
+    with pytest.raises(ConfigError, match="keeps something else"):
+        _engine(spec)
+
+
+# ------------------------------------------------------------------ a toy mixer with state of its own
+
+@dataclasses.dataclass(frozen=True)
+class ToyStateSpec:
+    hidden_size: int
+    decay: float
+    prefix: str = ""
+    kind: str = "toy_running_mean"
+
+
+def _register_toy():
+    from quantinfer_b200.cache import StateNeed
+    from quantinfer_b200.parts import Part, register_part
+    from quantinfer_b200.weights import TensorNeed
+
+    class ToyRunningMean(Part):
+        """y_t = W (s_t), s_t = decay * s_{t-1} + x_t: a recurrence over the sequence whose state s lives
+        in the request's slot. Written with torch operations: it is a test double, not a kernel."""
+
+        @classmethod
+        def needs_of_spec(cls, spec):
+            return {spec.prefix + "mix.weight": TensorNeed((spec.hidden_size, spec.hidden_size))}
+
+        def load(self, tensors):
+            self.w = tensors[self.spec.prefix + "mix.weight"].to(self.runtime.device, torch.float32)
+
+        def cache_need(self):
+            return StateNeed((self.spec.hidden_size,), torch.float32)
+
+        def forward(self, x, batch, cache):
+            out = torch.empty_like(x, dtype=torch.float32)
+            for i in range(batch.n_requests):
+                a, z, slot = batch.h_q_start[i], batch.h_q_start[i + 1], batch.h_slot_ids[i]
+                s = cache.state[slot].clone()
+                for t in range(a, z):
+                    s = self.spec.decay * s + x[t].float()
+                    out[t] = s
+                cache.state[slot] = s
+            return (out @ self.w.t()).to(x.dtype)
+
+    register_part("mixer", "toy_running_mean", ToyRunningMean)
+
+
+def test_toy_mixer_with_state_is_registered_built_and_stepped():
+    from quantinfer_b200.engine import StepEntry
+
+    _register_toy()
+    T = _SpecTools
+    layers = [T.layer(0), T.layer(1, mixer=ToyStateSpec(48, 0.9, "l1.toy.")), T.layer(2)]
+    spec = T.tiny_spec(layers)
+    eng, tensors = _engine(spec, use_graphs=False)
+    assert "l1.toy.mix.weight" in tensors and len(eng.cache.groups) == 1 and list(eng.cache.states) == [1]
+    ids_a = [int(x) for x in torch.randint(0, 97, (40,))]
+    ids_b = [int(x) for x in torch.randint(0, 97, (25,))]
+
+    def whole(ids):
+        eng.open("w")
+        out = eng.step([StepEntry("w", ids, list(range(len(ids))))]).cpu()
+        eng.close("w")
+        return out
+
+    ref_a, ref_b = whole(ids_a), whole(ids_b)
+    # the same two requests interleaved in portions; slots are reused, so a state that
+    # was not reset at open or that leaked between requests would show
+    eng.open("a"), eng.open("b")
+    got_a, got_b = [], []
+    got_a.append(eng.step([StepEntry("a", ids_a[:10], list(range(10)))]).cpu())
+    out = eng.step([StepEntry("a", ids_a[10:11], [0]), StepEntry("b", ids_b[:20], list(range(20)))]).cpu()
+    got_a.append(out[:1]), got_b.append(out[1:])
+    out = eng.step([StepEntry("b", ids_b[20:], list(range(5))), StepEntry("a", ids_a[11:], list(range(29)))]).cpu()
+    got_b.append(out[:5]), got_a.append(out[5:])
+    eng.close("a"), eng.close("b")
+    assert float((torch.cat(got_a) - ref_a).abs().max()) < 2e-5
+    assert float((torch.cat(got_b) - ref_b).abs().max()) < 2e-5
+    assert not torch.allclose(ref_a[5], whole(ids_a[5:])[0])       # the recurrence does depend on its past
