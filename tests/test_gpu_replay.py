@@ -62,3 +62,49 @@ def test_trace_run_program(tiny_folders, dtype):
     got = run_trace_cli(folder, dtype, steps, peak)
     worst, where = worst_diff(got, _expect(folder, "B"))
     assert worst <= TOL[dtype], f"worst difference {worst} at (request, position) {where}"
+
+
+def _sharp_folder(tiny_folders, tmp_path_factory, name):
+    """The same model with its q_norm gains tripled: attention scores spread over +-10 or more, the
+    softmax of each query is dominated by a few keys, and one wrong, missing or stale key changes the
+    logits far beyond rounding. Random N(0, 0.02) weights alone give nearly uniform attention, which
+    would hide such a fault from the bfloat16 comparison."""
+    import shutil
+
+    from safetensors.torch import load_file, save_file
+
+    dst = tmp_path_factory.mktemp("sharp") / name
+    shutil.copytree(tiny_folders[name], dst)
+    t = load_file(str(dst / "model.safetensors"))
+    for k in t:
+        if k.endswith("q_norm.weight"):
+            t[k] = t[k] * 3.0
+    save_file(t, str(dst / "model.safetensors"))
+    return dst
+
+
+@pytest.mark.parametrize("name", ["A", "D"])
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_replay_with_peaked_attention(tiny_folders, tmp_path_factory, name, dtype):
+    folder = _sharp_folder(tiny_folders, tmp_path_factory, name)
+    reqs = _requests(folder, name)
+    expect = plain_rows(folder, reqs)
+    budget = round64(max(LENGTHS[name])) + 2 * 128
+    steps, peak = mixed_trace(reqs, seed=11, max_live=4, max_tokens=budget)
+    got = run_trace_engine(folder, dtype, steps, peak, PAGE_SIZES[name])
+    worst, where = worst_diff(got, expect)
+    assert worst <= TOL[dtype], f"worst difference {worst} at (request, position) {where}"
+    # the point of the sharper model: one wrong key must show. Changing a single early token changes
+    # the last position's logits by far more than the bfloat16 tolerance.
+    from plain.plain_qwen3 import plain_forward, plain_load
+
+    cfg, w = plain_load(folder)
+    rid = max(reqs, key=lambda r: len(reqs[r]))
+    ids = list(reqs[rid])
+    base = plain_forward(w, cfg, ids)[-1]
+    sensitivity = 0.0
+    for pos in (1, len(ids) // 4, len(ids) // 2, 3 * len(ids) // 4, len(ids) - 2):
+        other = list(ids)
+        other[pos] = (other[pos] + 1) % vocab_of(folder)
+        sensitivity = max(sensitivity, float((base - plain_forward(w, cfg, other)[-1]).abs().max()))
+    assert sensitivity > 3 * TOL["bfloat16"], sensitivity
