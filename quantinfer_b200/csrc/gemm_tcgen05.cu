@@ -3,8 +3,8 @@
 // Both operands are read along K ("K-major"), which is the checkpoint's
 // [out, in] layout for w, so nothing is transposed at load.
 //
-// One CTA computes one 128 x BN tile of  D = A . B^T  where A and B are the two
-// row-major operands. For many tokens A = x and B = w. For few tokens (decode)
+// The output is cut into 128 x BN tiles of  D = A . B^T  where A and B are the two
+// row-major operands; a CTA computes its share of the tiles one after the other. For many tokens A = x and B = w. For few tokens (decode)
 // the operands are swapped: A = w, so the 128 rows of the MMA ride the weight's
 // output dimension and the small token count rides the MMA's N (16..256); the
 // epilogue then stores the tile transposed. A skinny product is bound by the
@@ -53,6 +53,10 @@ __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
 
 __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
 
 __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
@@ -161,7 +165,7 @@ struct Smem {
     static constexpr int kABytes = BM * BK * 2;
     static constexpr int kBBytes = BN * BK * 2;
     static constexpr int kStageBytes = kABytes + kBBytes;
-    static constexpr int kBarrierBytes = 8 * (2 * STAGES + 1) + 16;
+    static constexpr int kBarrierBytes = 8 * (2 * STAGES + 4) + 16;
     static constexpr int kTotal = STAGES * kStageBytes + kBarrierBytes + 1024;  // + alignment slack
 };
 
@@ -169,36 +173,46 @@ __device__ __forceinline__ float silu_mul(float g, float u) { return g / (1.0f +
 
 // EPI = 0: store the product. EPI = 1: the product's columns come in pairs (gate, up) and
 // the kernel stores silu(gate) * up, half as wide (the feed-forward's activation fused in).
+//
+// The kernel is persistent: CTA c takes tiles c, c + gridDim.x, ... of the linear tile
+// list (A tiles fastest, then B tiles, then K splits, so CTAs that run together share a
+// B tile in L2). The accumulator in tensor memory is double-buffered: while the
+// epilogue warps drain one buffer, the MMA warp already fills the other with the next
+// tile, and the TMA ring runs on across tile borders.
 template <int BN, int STAGES, bool SWAP, typename TOut, int EPI>
 __global__ void __launch_bounds__(kThreads)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                     TOut* __restrict__ out, int rows_a, int rows_b, int K, long long ld_out,
-                    int kb_per_split, long long split_stride, int* __restrict__ status) {
+                    int kb_per_split, int n_splits, long long split_stride, int* __restrict__ status) {
     extern __shared__ uint8_t smem_raw[];
     using L = Smem<BN, STAGES>;
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* aligned = smem_raw + (base - smem_u32(smem_raw));
-    const uint32_t bars = base + STAGES * L::kStageBytes;       // full[STAGES], empty[STAGES], accum
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(aligned + STAGES * L::kStageBytes + 8 * (2 * STAGES + 1));
+    // barriers: full[STAGES], empty[STAGES], acc_full[2], acc_empty[2]
+    const uint32_t bars = base + STAGES * L::kStageBytes;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(aligned + STAGES * L::kStageBytes + 8 * (2 * STAGES + 4));
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
     auto full_bar = [&](int s) { return bars + 8u * s; };
     auto empty_bar = [&](int s) { return bars + 8u * (STAGES + s); };
-    const uint32_t accum_bar = bars + 8u * (2 * STAGES);
+    auto acc_full_bar = [&](int a) { return bars + 8u * (2 * STAGES + a); };
+    auto acc_empty_bar = [&](int a) { return bars + 8u * (2 * STAGES + 2 + a); };
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int tile_a = blockIdx.x, tile_b = blockIdx.y, split = blockIdx.z;
+    const int tiles_a = (rows_a + BM - 1) / BM, tiles_b = (rows_b + BN - 1) / BN;
+    const int total_tiles = tiles_a * tiles_b * n_splits;
     const int kb_total = (K + BK - 1) / BK;
-    const int kb_begin = split * kb_per_split;
-    const int kb_end = min(kb_total, kb_begin + kb_per_split);
-    const int n_kb = max(kb_end - kb_begin, 0);
-    constexpr uint32_t kTmemCols = BN < 32 ? 32 : BN;
+    constexpr uint32_t kAccCols = BN < 32 ? 32 : BN;        // columns of one accumulator
+    constexpr uint32_t kTmemCols = 2 * kAccCols;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
             mbar_init(full_bar(s), 1);
             mbar_init(empty_bar(s), 1);
         }
-        mbar_init(accum_bar, 1);
+        for (int a = 0; a < 2; ++a) {
+            mbar_init(acc_full_bar(a), 1);
+            mbar_init(acc_empty_bar(a), 4);     // one arrival per epilogue warp
+        }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -211,158 +225,192 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
 
+    auto give_up = [&]() {
+        if (!*abort_flag) {
+            *abort_flag = 1;
+            if (status) atomicOr(status, qi::kStatusWaitTimeout);
+        }
+    };
+
     if (warp == 0) {
         // ---------------- TMA producer ----------------
         if (lane == 0) {
-            int issued = 0;
-            for (int i = 0; i < n_kb; ++i) {
-                const int s = i % STAGES;
-                const uint32_t round = (uint32_t)(i / STAGES);
-                if (!mbar_wait(empty_bar(s), (round & 1u) ^ 1u, abort_flag, status)) {
-                    if (!*abort_flag) { *abort_flag = 1; if (status) atomicOr(status, qi::kStatusWaitTimeout); }
-                    break;
+            uint32_t it = 0;          // k blocks issued so far, over all tiles
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+                const int tile_a = tile % tiles_a, tile_b = (tile / tiles_a) % tiles_b, split = tile / (tiles_a * tiles_b);
+                const int kb_begin = split * kb_per_split;
+                const int n_kb = max(min(kb_total, kb_begin + kb_per_split) - kb_begin, 0);
+                for (int i = 0; i < n_kb; ++i, ++it) {
+                    const int s = it % STAGES;
+                    if (!mbar_wait(empty_bar(s), ((it / STAGES) & 1u) ^ 1u, abort_flag, status)) {
+                        give_up();
+                        ok = false;
+                        break;
+                    }
+                    mbar_expect_tx(full_bar(s), L::kStageBytes);
+                    const uint32_t a_dst = base + s * L::kStageBytes;
+                    const int k0 = (kb_begin + i) * BK;
+                    tma_load_2d(a_dst, &map_a, full_bar(s), k0, tile_a * BM);
+                    tma_load_2d(a_dst + L::kABytes, &map_b, full_bar(s), k0, tile_b * BN);
                 }
-                mbar_expect_tx(full_bar(s), L::kStageBytes);
-                const uint32_t a_dst = base + s * L::kStageBytes;
-                const uint32_t b_dst = a_dst + L::kABytes;
-                const int k0 = (kb_begin + i) * BK;
-                tma_load_2d(a_dst, &map_a, full_bar(s), k0, tile_a * BM);
-                tma_load_2d(b_dst, &map_b, full_bar(s), k0, tile_b * BN);
-                issued = i + 1;
             }
             if (*abort_flag) {
-                // Copies still in flight write into this CTA's shared memory: wait for the
-                // stages armed last (at most STAGES of them) before the CTA may exit.
-                for (int i = max(issued - STAGES, 0); i < issued; ++i) {
-                    const int s = i % STAGES;
-                    const uint32_t round = (uint32_t)(i / STAGES);
+                // Copies still in flight write into this CTA's shared memory: wait (bounded) for the
+                // stages armed last before the CTA may exit.
+                const uint32_t first = it > (uint32_t)STAGES ? it - STAGES : 0u;
+                for (uint32_t i = first; i < it; ++i)
                     for (uint32_t t = 0; t < (1u << 20); ++t)
-                        if (mbar_try_wait(full_bar(s), round & 1u)) break;
-                }
+                        if (mbar_try_wait(full_bar(i % STAGES), (i / STAGES) & 1u)) break;
             }
         }
     } else if (warp == 1) {
         // ---------------- MMA issuer ----------------
         if (lane == 0) {
             constexpr uint32_t idesc = make_idesc(BM, BN);
+            uint32_t it = 0;
+            int j = 0;                // tiles this CTA has started
             bool ok = true;
-            for (int i = 0; i < n_kb && ok; ++i) {
-                const int s = i % STAGES;
-                const uint32_t round = (uint32_t)(i / STAGES);
-                if (!mbar_wait(full_bar(s), round & 1u, abort_flag, status)) {
-                    if (!*abort_flag) { *abort_flag = 1; if (status) atomicOr(status, qi::kStatusWaitTimeout); }
-                    ok = false;
+            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++j) {
+                const int split = tile / (tiles_a * tiles_b);
+                const int kb_begin = split * kb_per_split;
+                const int n_kb = max(min(kb_total, kb_begin + kb_per_split) - kb_begin, 0);
+                const int acc = j & 1;
+                // the epilogue must have drained this accumulator (first use of each passes at once)
+                if (!mbar_wait(acc_empty_bar(acc), (((uint32_t)j >> 1) & 1u) ^ 1u, abort_flag, status)) {
+                    give_up();
                     break;
                 }
                 tc_fence_after();
-                const uint32_t a_addr = base + s * L::kStageBytes;
-                const uint64_t adesc = make_smem_desc(a_addr);
-                const uint64_t bdesc = make_smem_desc(a_addr + L::kABytes);
+                const uint32_t tmem_d = tmem_base + (uint32_t)acc * kAccCols;
+                for (int i = 0; i < n_kb; ++i, ++it) {
+                    const int s = it % STAGES;
+                    if (!mbar_wait(full_bar(s), (it / STAGES) & 1u, abort_flag, status)) {
+                        give_up();
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after();
+                    const uint32_t a_addr = base + s * L::kStageBytes;
+                    const uint64_t adesc = make_smem_desc(a_addr);
+                    const uint64_t bdesc = make_smem_desc(a_addr + L::kABytes);
 #pragma unroll
-                for (int k = 0; k < BK / UMMA_K; ++k) {
-                    // 16 bf16 = 32 bytes further along the swizzled row: +2 in units of 16 bytes
-                    umma_bf16(tmem_base, adesc + 2u * k, bdesc + 2u * k, idesc, (i > 0 || k > 0) ? 1u : 0u);
+                    for (int k = 0; k < BK / UMMA_K; ++k) {
+                        // 16 bf16 = 32 bytes further along the swizzled row: +2 in units of 16 bytes
+                        umma_bf16(tmem_d, adesc + 2u * k, bdesc + 2u * k, idesc, (i > 0 || k > 0) ? 1u : 0u);
+                    }
+                    umma_commit(empty_bar(s));   // the stage is free once these MMAs have read it
                 }
-                umma_commit(empty_bar(s));   // the stage is free once these MMAs have read it
+                if (ok) umma_commit(acc_full_bar(acc));  // the accumulator is complete
             }
-            if (ok) umma_commit(accum_bar);  // the accumulator is complete
         }
     } else {
         // ---------------- epilogue (warps 2..5) ----------------
         const int quarter = warp & 3;   // the 32 TMEM lanes this warp may read
-        bool ok = true;
-        if (n_kb > 0) {
-            ok = mbar_wait(accum_bar, 0, abort_flag, status);
-            if (!ok && !*abort_flag) { *abort_flag = 1; if (status && lane == 0) atomicOr(status, qi::kStatusWaitTimeout); }
-        }
-        tc_fence_after();
-        const int a_row = tile_a * BM + quarter * 32 + lane;
-        TOut* obase = out + (size_t)split * split_stride;
-        constexpr int kChunk = BN >= 32 ? 32 : 16;
-#pragma unroll 1
-        for (int c0 = 0; c0 < BN; c0 += kChunk) {
-            uint32_t r[32];
-            if (n_kb > 0 && ok) {
-                const uint32_t addr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c0;
-                if (kChunk == 32) tmem_ld32(addr, r); else tmem_ld16(addr, r);
-                tmem_ld_wait();
-            } else {
-#pragma unroll
-                for (int j = 0; j < 32; ++j) r[j] = 0u;   // an empty K range contributes zeros
+        int j = 0;
+        for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++j) {
+            const int tile_a = tile % tiles_a, tile_b = (tile / tiles_a) % tiles_b, split = tile / (tiles_a * tiles_b);
+            const int kb_begin = split * kb_per_split;
+            const int n_kb = max(min(kb_total, kb_begin + kb_per_split) - kb_begin, 0);
+            const int acc = j & 1;
+            if (!mbar_wait(acc_full_bar(acc), ((uint32_t)j >> 1) & 1u, abort_flag, status)) {
+                if (lane == 0) give_up();
+                break;
             }
-            if (!ok) continue;
-            const int b0 = tile_b * BN + c0;
-            if (SWAP && EPI == 1) {
-                // rows of A come in pairs (gate, up): even lanes hold gate, their neighbours up
+            tc_fence_after();
+            const int a_row = tile_a * BM + quarter * 32 + lane;
+            TOut* obase = out + (size_t)split * split_stride;
+            constexpr int kChunk = BN >= 32 ? 32 : 16;
+#pragma unroll 1
+            for (int c0 = 0; c0 < BN; c0 += kChunk) {
+                uint32_t r[32];
+                if (n_kb > 0) {
+                    const uint32_t addr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)acc * kAccCols + (uint32_t)c0;
+                    if (kChunk == 32) tmem_ld32(addr, r); else tmem_ld16(addr, r);
+                    tmem_ld_wait();
+                } else {
 #pragma unroll
-                for (int j = 0; j < kChunk; ++j) {
-                    const float mine = __uint_as_float(r[j]);
-                    const float other = __shfl_xor_sync(0xffffffffu, mine, 1);
-                    if ((lane & 1) == 0 && a_row + 1 < rows_a && b0 + j < rows_b)
-                        store1<TOut>(obase + (size_t)(b0 + j) * ld_out + (a_row >> 1), silu_mul(mine, other));
+                    for (int q = 0; q < 32; ++q) r[q] = 0u;   // an empty K range contributes zeros
                 }
-            } else if (SWAP) {
-                // out[b, a]: for a fixed column the warp's lanes write consecutive addresses
-                if (a_row < rows_a) {
-#pragma unroll
-                    for (int j = 0; j < kChunk; ++j)
-                        if (b0 + j < rows_b) store1<TOut>(obase + (size_t)(b0 + j) * ld_out + a_row, __uint_as_float(r[j]));
+                if (c0 + kChunk >= BN) {
+                    // everything of this accumulator is in registers: hand it back to the MMA warp
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(acc_empty_bar(acc));
                 }
-            } else if (EPI == 1) {
-                if (a_row < rows_a) {
-                    TOut* orow = obase + (size_t)a_row * ld_out + (b0 >> 1);
-                    const bool full = b0 + kChunk <= rows_b;
-                    const bool aligned16 = ((reinterpret_cast<uintptr_t>(orow) & 15u) == 0);
-                    if (full && aligned16 && sizeof(TOut) == 2) {
+                const int b0 = tile_b * BN + c0;
+                if (SWAP && EPI == 1) {
+                    // rows of A come in pairs (gate, up): even lanes hold gate, their neighbours up
 #pragma unroll
-                        for (int j = 0; j < kChunk; j += 16) {
-                            uint4 v;
-                            uint32_t* vw = reinterpret_cast<uint32_t*>(&v);
-#pragma unroll
-                            for (int q = 0; q < 4; ++q) {
-                                __nv_bfloat162 pr = __floats2bfloat162_rn(
-                                    silu_mul(__uint_as_float(r[j + 4 * q]), __uint_as_float(r[j + 4 * q + 1])),
-                                    silu_mul(__uint_as_float(r[j + 4 * q + 2]), __uint_as_float(r[j + 4 * q + 3])));
-                                vw[q] = *reinterpret_cast<uint32_t*>(&pr);
-                            }
-                            *reinterpret_cast<uint4*>(reinterpret_cast<qi::bf16*>(orow) + (j >> 1)) = v;
-                        }
-                    } else {
-#pragma unroll
-                        for (int j = 0; j < kChunk; j += 2)
-                            if (b0 + j + 1 < rows_b)
-                                store1<TOut>(orow + (j >> 1), silu_mul(__uint_as_float(r[j]), __uint_as_float(r[j + 1])));
+                    for (int q = 0; q < kChunk; ++q) {
+                        const float mine = __uint_as_float(r[q]);
+                        const float other = __shfl_xor_sync(0xffffffffu, mine, 1);
+                        if ((lane & 1) == 0 && a_row + 1 < rows_a && b0 + q < rows_b)
+                            store1<TOut>(obase + (size_t)(b0 + q) * ld_out + (a_row >> 1), silu_mul(mine, other));
                     }
-                }
-            } else {
-                if (a_row < rows_a) {
-                    TOut* orow = obase + (size_t)a_row * ld_out + b0;
-                    const bool full = b0 + kChunk <= rows_b;
-                    const bool aligned16 = ((reinterpret_cast<uintptr_t>(orow) & 15u) == 0);
-                    if (full && aligned16 && sizeof(TOut) == 2) {
+                } else if (SWAP) {
+                    // out[b, a]: for a fixed column the warp's lanes write consecutive addresses
+                    if (a_row < rows_a) {
 #pragma unroll
-                        for (int j = 0; j < kChunk; j += 8) {
-                            uint4 v;
-                            __nv_bfloat162 p0 = __floats2bfloat162_rn(__uint_as_float(r[j + 0]), __uint_as_float(r[j + 1]));
-                            __nv_bfloat162 p1 = __floats2bfloat162_rn(__uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
-                            __nv_bfloat162 p2 = __floats2bfloat162_rn(__uint_as_float(r[j + 4]), __uint_as_float(r[j + 5]));
-                            __nv_bfloat162 p3 = __floats2bfloat162_rn(__uint_as_float(r[j + 6]), __uint_as_float(r[j + 7]));
-                            v.x = *reinterpret_cast<uint32_t*>(&p0);
-                            v.y = *reinterpret_cast<uint32_t*>(&p1);
-                            v.z = *reinterpret_cast<uint32_t*>(&p2);
-                            v.w = *reinterpret_cast<uint32_t*>(&p3);
-                            *reinterpret_cast<uint4*>(reinterpret_cast<qi::bf16*>(orow) + j) = v;
+                        for (int q = 0; q < kChunk; ++q)
+                            if (b0 + q < rows_b) store1<TOut>(obase + (size_t)(b0 + q) * ld_out + a_row, __uint_as_float(r[q]));
+                    }
+                } else if (EPI == 1) {
+                    if (a_row < rows_a) {
+                        TOut* orow = obase + (size_t)a_row * ld_out + (b0 >> 1);
+                        const bool full = b0 + kChunk <= rows_b;
+                        const bool aligned16 = ((reinterpret_cast<uintptr_t>(orow) & 15u) == 0);
+                        if (full && aligned16 && sizeof(TOut) == 2) {
+#pragma unroll
+                            for (int q0 = 0; q0 < kChunk; q0 += 16) {
+                                uint4 v;
+                                uint32_t* vw = reinterpret_cast<uint32_t*>(&v);
+#pragma unroll
+                                for (int q = 0; q < 4; ++q) {
+                                    __nv_bfloat162 pr = __floats2bfloat162_rn(
+                                        silu_mul(__uint_as_float(r[q0 + 4 * q]), __uint_as_float(r[q0 + 4 * q + 1])),
+                                        silu_mul(__uint_as_float(r[q0 + 4 * q + 2]), __uint_as_float(r[q0 + 4 * q + 3])));
+                                    vw[q] = *reinterpret_cast<uint32_t*>(&pr);
+                                }
+                                *reinterpret_cast<uint4*>(reinterpret_cast<qi::bf16*>(orow) + (q0 >> 1)) = v;
+                            }
+                        } else {
+#pragma unroll
+                            for (int q = 0; q < kChunk; q += 2)
+                                if (b0 + q + 1 < rows_b)
+                                    store1<TOut>(orow + (q >> 1), silu_mul(__uint_as_float(r[q]), __uint_as_float(r[q + 1])));
                         }
-                    } else if (full && aligned16 && sizeof(TOut) == 4) {
+                    }
+                } else {
+                    if (a_row < rows_a) {
+                        TOut* orow = obase + (size_t)a_row * ld_out + b0;
+                        const bool full = b0 + kChunk <= rows_b;
+                        const bool aligned16 = ((reinterpret_cast<uintptr_t>(orow) & 15u) == 0);
+                        if (full && aligned16 && sizeof(TOut) == 2) {
 #pragma unroll
-                        for (int j = 0; j < kChunk; j += 4) {
-                            uint4 v = make_uint4(r[j], r[j + 1], r[j + 2], r[j + 3]);
-                            *reinterpret_cast<uint4*>(reinterpret_cast<float*>(orow) + j) = v;
+                            for (int q = 0; q < kChunk; q += 8) {
+                                uint4 v;
+                                __nv_bfloat162 p0 = __floats2bfloat162_rn(__uint_as_float(r[q + 0]), __uint_as_float(r[q + 1]));
+                                __nv_bfloat162 p1 = __floats2bfloat162_rn(__uint_as_float(r[q + 2]), __uint_as_float(r[q + 3]));
+                                __nv_bfloat162 p2 = __floats2bfloat162_rn(__uint_as_float(r[q + 4]), __uint_as_float(r[q + 5]));
+                                __nv_bfloat162 p3 = __floats2bfloat162_rn(__uint_as_float(r[q + 6]), __uint_as_float(r[q + 7]));
+                                v.x = *reinterpret_cast<uint32_t*>(&p0);
+                                v.y = *reinterpret_cast<uint32_t*>(&p1);
+                                v.z = *reinterpret_cast<uint32_t*>(&p2);
+                                v.w = *reinterpret_cast<uint32_t*>(&p3);
+                                *reinterpret_cast<uint4*>(reinterpret_cast<qi::bf16*>(orow) + q) = v;
+                            }
+                        } else if (full && aligned16 && sizeof(TOut) == 4) {
+#pragma unroll
+                            for (int q = 0; q < kChunk; q += 4) {
+                                uint4 v = make_uint4(r[q], r[q + 1], r[q + 2], r[q + 3]);
+                                *reinterpret_cast<uint4*>(reinterpret_cast<float*>(orow) + q) = v;
+                            }
+                        } else {
+#pragma unroll
+                            for (int q = 0; q < kChunk; ++q)
+                                if (b0 + q < rows_b) store1<TOut>(orow + q, __uint_as_float(r[q]));
                         }
-                    } else {
-#pragma unroll
-                        for (int j = 0; j < kChunk; ++j)
-                            if (b0 + j < rows_b) store1<TOut>(orow + j, __uint_as_float(r[j]));
                     }
                 }
             }
@@ -414,6 +462,16 @@ int make_map(CUtensorMap* map, const void* ptr, int rows, int K, int box_rows) {
     return 0;
 }
 
+int sm_count() {
+    static int n = 0;
+    if (!n) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+    }
+    return n;
+}
+
 template <int BN, int STAGES, bool SWAP, typename TOut, int EPI>
 int launch(const CUtensorMap& ma, const CUtensorMap& mb, TOut* out, int rows_a, int rows_b, int K, long long ld,
            int splits, int kb_per_split, long long split_stride, int* status, cudaStream_t stream) {
@@ -425,8 +483,12 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, TOut* out, int rows_a, 
         if (e != cudaSuccess) return qi::fail("gemm_bf16: cannot reserve %d bytes of shared memory: %s", smem, cudaGetErrorString(e));
         configured = true;
     }
-    dim3 grid((rows_a + BM - 1) / BM, (rows_b + BN - 1) / BN, splits);
-    kern<<<grid, kThreads, smem, stream>>>(ma, mb, out, rows_a, rows_b, K, ld, kb_per_split, split_stride, status);
+    const long long tiles = (long long)((rows_a + BM - 1) / BM) * ((rows_b + BN - 1) / BN) * splits;
+    // as many CTAs as fit on the GPU at once (by shared memory); each walks its share of the tiles
+    const int per_sm = (227 * 1024) / smem > 0 ? (227 * 1024) / smem : 1;
+    const long long resident = (long long)sm_count() * per_sm;
+    const unsigned grid = (unsigned)(tiles < resident ? tiles : resident);
+    kern<<<grid, kThreads, smem, stream>>>(ma, mb, out, rows_a, rows_b, K, ld, kb_per_split, splits, split_stride, status);
     return qi::check_launch("gemm_bf16");
 }
 
@@ -481,7 +543,7 @@ extern "C" int qi_gemm_bf16(const void* x, const void* w, void* out, int out_dty
     const void* a = swap ? w : x;
     const void* b = swap ? x : w;
     const int rows_a = swap ? N : M, rows_b = swap ? M : N;
-    QI_REQUIRE((rows_a + BM - 1) / BM <= 2147483647 && (rows_b + bn - 1) / bn <= 65535 && splits <= 65535, "gemm_bf16: grid too large");
+    QI_REQUIRE((long long)((rows_a + BM - 1) / BM) * ((rows_b + bn - 1) / bn) * splits < 2147483647LL, "gemm_bf16: too many tiles");
     CUtensorMap ma, mb;
     if (make_map(&ma, a, rows_a, K, BM)) return 1;
     if (make_map(&mb, b, rows_b, K, bn)) return 1;
