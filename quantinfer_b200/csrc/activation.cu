@@ -11,6 +11,7 @@ namespace {
 template <typename T>
 __global__ void silu_mul_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int n_tokens,
                                 int inter, int interleaved) {
+    qi::pdl_enter();
     const size_t total = (size_t)n_tokens * inter;
     for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
          idx += (size_t)gridDim.x * blockDim.x) {
@@ -32,8 +33,8 @@ extern "C" int qi_silu_mul(const void* gate_up, void* out, int dtype, int n_toke
     size_t blocks = (total + 255) / 256;
     if (blocks > 148 * 32) blocks = 148 * 32;
     QI_DISPATCH_DTYPE(dtype, T, {
-        silu_mul_kernel<T><<<(unsigned)blocks, 256, 0, stream>>>((const T*)gate_up, (T*)out, n_tokens,
-                                                               inter, interleaved);
+        qi::launch(silu_mul_kernel<T>, dim3((unsigned)blocks), dim3(256), 0, stream, (const T*)gate_up, (T*)out, n_tokens, inter,
+                   interleaved);
     });
     return qi::check_launch("silu_mul");
 }

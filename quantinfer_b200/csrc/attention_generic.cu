@@ -37,6 +37,7 @@ attention_generic_kernel(const T* __restrict__ q, T* __restrict__ out, const T* 
     float* part_m = part_acc + kWarps * d;      // [kWarps]
     float* part_l = part_m + kWarps;            // [kWarps]
 
+    qi::pdl_enter();
     const int t = blockIdx.y, h = blockIdx.x;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int hk = h / (nq / nkv);
@@ -142,7 +143,7 @@ extern "C" int qi_attention_generic(const void* q, void* out, int dtype, const v
         const int nt = n_tokens - t0 < 65535 ? n_tokens - t0 : 65535;
         dim3 grid(nq, nt);
         QI_DISPATCH_DTYPE(dtype, T, {
-            attention_generic_kernel<T><<<grid, kWarps * 32, smem, stream>>>(
+            qi::launch(attention_generic_kernel<T>, grid, dim3(kWarps * 32), smem, stream,
                 (const T*)q + (size_t)t0 * nq * d, (T*)out + (size_t)t0 * nq * d, (const T*)k_pages,
                 (const T*)v_pages, block_table, max_blocks, page_size, num_pages, positions + t0,
                 token_req + t0, nq, nkv, d, scale, window, status);

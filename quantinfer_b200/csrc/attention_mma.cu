@@ -80,6 +80,7 @@ attention_prefill_kernel(const qi::bf16* __restrict__ q, qi::bf16* __restrict__ 
     uint8_t* kv_tile = smem + kTileBytes;                 // 2 x (K, V)
     const uint32_t q_s = smem_u32(q_tile), kv_s = smem_u32(kv_tile);
 
+    qi::pdl_enter();
     const int tile = blockIdx.x, h = blockIdx.y;
     const int hk = h / (nq / nkv);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -194,6 +195,7 @@ attention_decode_kernel(const qi::bf16* __restrict__ q, const qi::bf16* __restri
     uint8_t* kv_tile = smem + kQBytes;            // 2 x (K, V)
     const uint32_t q_s = smem_u32(q_tile), kv_s = smem_u32(kv_tile);
 
+    qi::pdl_enter();
     const int split = blockIdx.x, hk = blockIdx.y, b = blockIdx.z;
     const int n_splits = gridDim.x;
     const int G = nq / nkv;
@@ -329,6 +331,7 @@ template <int D>
 __global__ void attention_decode_merge_kernel(const float* __restrict__ ws_o, const float* __restrict__ ws_ml,
                                               const int* __restrict__ q_start, qi::bf16* __restrict__ out, int nq,
                                               int n_splits) {
+    qi::pdl_enter();
     const int h = blockIdx.x, b = blockIdx.y;
     const size_t base = ((size_t)b * nq + h) * n_splits;
     float M = -INFINITY;
@@ -367,7 +370,7 @@ int launch_prefill(const void* q, void* out, const void* k_pages, const void* v_
         configured = true;
     }
     dim3 grid(n_tiles, nq, tile_rows / kTileKeys);
-    kern<<<grid, kThreads, prefill_smem<D>(), stream>>>(
+    qi::launch(kern, grid, dim3(kThreads), prefill_smem<D>(), stream,
         (const qi::bf16*)q, (qi::bf16*)out, (const qi::bf16*)k_pages, (const qi::bf16*)v_pages, block_table, max_blocks,
         page_size, num_pages, q_start, start_pos, tile_req, tile_q0, nq, nkv, scale * 1.4426950408889634f, window, status);
     return qi::check_launch("attention_prefill");
@@ -386,11 +389,11 @@ int launch_decode(const void* q, void* out, const void* k_pages, const void* v_p
         configured = true;
     }
     dim3 grid(n_splits, nkv, batch);
-    kern<<<grid, kThreads, decode_smem<D>(), stream>>>(
+    qi::launch(kern, grid, dim3(kThreads), decode_smem<D>(), stream,
         (const qi::bf16*)q, (const qi::bf16*)k_pages, (const qi::bf16*)v_pages, block_table, max_blocks, page_size,
         num_pages, kv_len, q_start, ws_o, ws_ml, nq, nkv, scale * 1.4426950408889634f, window, chunk, status);
     if (int rc = qi::check_launch("attention_decode")) return rc;
-    attention_decode_merge_kernel<D><<<dim3(nq, batch), D >= 128 ? 128 : 64, 0, stream>>>(
+    qi::launch(attention_decode_merge_kernel<D>, dim3(nq, batch), dim3(D >= 128 ? 128 : 64), 0, stream,
         ws_o, ws_ml, q_start, (qi::bf16*)out, nq, n_splits);
     return qi::check_launch("attention_decode_merge");
 }

@@ -101,6 +101,7 @@ attention_prefill_tma_kernel(const __grid_constant__ CUtensorMap map_q, const __
     auto full_bar = [&](int s) { return bars + 8u * s; };
     const uint32_t q_bar = bars + 8u * kPrefillStages;
 
+    qi::pdl_enter();
     const int tile = blockIdx.x, h = blockIdx.y;
     const int hk = h / (nq / nkv);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -215,6 +216,7 @@ attention_decode_tma_kernel(const qi::bf16* __restrict__ q, const __grid_constan
     const uint32_t bars = q_s + kQBytes;
     auto full_bar = [&](int s) { return bars + 8u * s; };
 
+    qi::pdl_enter();
     const int split = blockIdx.x, hk = blockIdx.y, b = blockIdx.z;
     const int n_splits = gridDim.x;
     const int G = nq / nkv;
@@ -346,6 +348,7 @@ template <int D>
 __global__ void attention_merge_kernel(const float* __restrict__ ws_o, const float* __restrict__ ws_ml,
                                        const int* __restrict__ q_start, qi::bf16* __restrict__ out, int nq,
                                        int n_splits) {
+    qi::pdl_enter();
     const int h = blockIdx.x, b = blockIdx.y;
     const size_t base = ((size_t)b * nq + h) * n_splits;
     float M = -INFINITY;
@@ -416,7 +419,7 @@ int launch_prefill(const void* q, void* out, const void* k_pages, const void* v_
     if (make_map(&mk, k_pages, (long long)num_pages * nkv * page_size, D, box_rows)) return 1;
     if (make_map(&mv, v_pages, (long long)num_pages * nkv * page_size, D, box_rows)) return 1;
     dim3 grid(n_tiles, nq);
-    kern<<<grid, kPrefillThreads, prefill_smem<D>(), stream>>>(
+    qi::launch(kern, grid, dim3(kPrefillThreads), prefill_smem<D>(), stream,
         mq, mk, mv, (qi::bf16*)out, block_table, max_blocks, page_size, box_rows, num_pages, q_start, start_pos,
         tile_req, tile_q0, nq, nkv, scale * 1.4426950408889634f, window, status);
     return qi::check_launch("attention_prefill_tma");
@@ -439,12 +442,12 @@ int launch_decode(const void* q, void* out, const void* k_pages, const void* v_p
     if (make_map(&mk, k_pages, (long long)num_pages * nkv * page_size, D, box_rows)) return 1;
     if (make_map(&mv, v_pages, (long long)num_pages * nkv * page_size, D, box_rows)) return 1;
     dim3 grid(n_splits, nkv, batch);
-    kern<<<grid, kDecodeThreads, decode_smem<D>(), stream>>>(
+    qi::launch(kern, grid, dim3(kDecodeThreads), decode_smem<D>(), stream,
         (const qi::bf16*)q, mk, mv, block_table, max_blocks, page_size, box_rows, num_pages, kv_len, q_start, ws_o,
         ws_ml, nq, nkv, scale * 1.4426950408889634f, window, chunk, status);
     if (int rc = qi::check_launch("attention_decode_tma")) return rc;
-    attention_merge_kernel<D><<<dim3(nq, batch), D >= 128 ? 128 : 64, 0, stream>>>(ws_o, ws_ml, q_start,
-                                                                                 (qi::bf16*)out, nq, n_splits);
+    qi::launch(attention_merge_kernel<D>, dim3(nq, batch), dim3(D >= 128 ? 128 : 64), 0, stream, ws_o, ws_ml, q_start,
+               (qi::bf16*)out, nq, n_splits);
     return qi::check_launch("attention_merge");
 }
 

@@ -3,6 +3,8 @@
 
 #include <stdarg.h>
 #include <stdio.h>
+#include <stdlib.h>
+#include <string.h>
 
 namespace qi {
 
@@ -21,6 +23,15 @@ int fail(const char* fmt, ...) {
     vsnprintf(g_error, sizeof(g_error), fmt, ap);
     va_end(ap);
     return 1;
+}
+
+bool pdl_enabled() {
+    static int state = -1;
+    if (state < 0) {
+        const char* v = getenv("QUANTINFER_B200_PDL");
+        state = (v && strcmp(v, "0") == 0) ? 0 : 1;
+    }
+    return state == 1;
 }
 
 int check_launch(const char* what) {

@@ -60,6 +60,37 @@ __device__ __forceinline__ float block_sum(float v, float* scratch) {
     return total;
 }
 
+// Programmatic dependent launch: every kernel lets the next kernel of the stream be
+// scheduled as soon as all of its own blocks have started (so that launch latency and
+// the next kernel's set-up overlap this kernel's run), and waits for the previous kernel
+// to have completed, with its writes visible, before it touches global memory. Both are
+// no-ops for a kernel launched without the attribute.
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_enter() {
+    pdl_launch_dependents();
+    pdl_wait();
+}
+
+bool pdl_enabled();   // host: false when QUANTINFER_B200_PDL=0
+
+// Launches `kern` with the programmatic-serialization attribute (when enabled).
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                          Args&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl_enabled() ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
+}
+
 // Host side: error message channel.
 void set_error(const char* fmt, ...);
 int fail(const char* fmt, ...);   // stores the message, returns 1

@@ -12,6 +12,7 @@ template <typename TW>
 __global__ void embedding_kernel(const TW* __restrict__ table, const int* __restrict__ ids,
                                  float* __restrict__ out, int hidden, int vocab,
                                  int* __restrict__ status) {
+    qi::pdl_enter();
     const int t = blockIdx.x;
     const int id = ids[t];
     float* dst = out + (size_t)t * hidden;
@@ -34,8 +35,8 @@ extern "C" int qi_embedding(const void* table, int table_dtype, const int* ids, 
     if (n_tokens == 0) return 0;
     const int threads = hidden >= 1024 ? 256 : (hidden >= 256 ? 128 : 64);
     QI_DISPATCH_DTYPE(table_dtype, TW, {
-        embedding_kernel<TW><<<n_tokens, threads, 0, stream>>>((const TW*)table, ids, out, hidden,
-                                                              vocab, status);
+        qi::launch(embedding_kernel<TW>, dim3(n_tokens), dim3(threads), 0, stream, (const TW*)table, ids, out, hidden, vocab,
+                   status);
     });
     return qi::check_launch("embedding");
 }

@@ -20,6 +20,7 @@ gemm_simt_kernel(const TX* __restrict__ x, const TW* __restrict__ w, TY* __restr
                  int N, int K, long long ldx, long long ldw, long long ldy) {
     __shared__ float xs[BK][BM + 4];
     __shared__ float ws[BK][BN + 4];
+    qi::pdl_enter();
     const int tid = threadIdx.x;
     const int tx = tid % 16, ty = tid / 16;  // tx over N, ty over M
     const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
@@ -76,8 +77,8 @@ template <typename TX, typename TW, typename TY>
 int launch(const void* x, const void* w, void* y, int M, int N, int K, long long ldx,
            long long ldw, long long ldy, cudaStream_t stream) {
     dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
-    gemm_simt_kernel<TX, TW, TY><<<grid, 256, 0, stream>>>((const TX*)x, (const TW*)w, (TY*)y, M, N,
-                                                           K, ldx, ldw, ldy);
+    qi::launch(gemm_simt_kernel<TX, TW, TY>, grid, dim3(256), 0, stream, (const TX*)x, (const TW*)w, (TY*)y, M, N, K, ldx, ldw,
+               ldy);
     return qi::check_launch("gemm_simt");
 }
 

@@ -197,6 +197,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     auto acc_full_bar = [&](int a) { return bars + 8u * (2 * STAGES + a); };
     auto acc_empty_bar = [&](int a) { return bars + 8u * (2 * STAGES + 2 + a); };
 
+    qi::pdl_launch_dependents();   // the next kernel may be scheduled while this one runs
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int tiles_a = (rows_a + BM - 1) / BM, tiles_b = (rows_b + BN - 1) / BN;
     const int total_tiles = tiles_a * tiles_b * n_splits;
@@ -224,6 +225,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    qi::pdl_wait();                // set-up done; the previous kernel's results are needed from here on
 
     auto give_up = [&]() {
         if (!*abort_flag) {
@@ -424,6 +426,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 // Adds split-K partial sums in split order: out[i] = sum_s partial[s, i].
 template <typename TOut>
 __global__ void splitk_reduce_kernel(const float* __restrict__ partial, TOut* __restrict__ out, size_t n, int splits) {
+    qi::pdl_enter();
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
         float s = 0.f;
         for (int k = 0; k < splits; ++k) s += partial[(size_t)k * n + i];
@@ -488,7 +491,8 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, TOut* out, int rows_a, 
     const int per_sm = (227 * 1024) / smem > 0 ? (227 * 1024) / smem : 1;
     const long long resident = (long long)sm_count() * per_sm;
     const unsigned grid = (unsigned)(tiles < resident ? tiles : resident);
-    kern<<<grid, kThreads, smem, stream>>>(ma, mb, out, rows_a, rows_b, K, ld, kb_per_split, splits, split_stride, status);
+    qi::launch(kern, dim3(grid), dim3(kThreads), smem, stream, ma, mb, out, rows_a, rows_b, K, ld, kb_per_split, splits,
+               split_stride, status);
     return qi::check_launch("gemm_bf16");
 }
 
@@ -557,8 +561,8 @@ extern "C" int qi_gemm_bf16(const void* x, const void* w, void* out, int out_dty
         if (out) {
             const size_t n = (size_t)M * N;
             unsigned blocks = (unsigned)((n + 255) / 256 < 148 * 8 ? (n + 255) / 256 : 148 * 8);
-            if (out_dtype == qi::kF32) splitk_reduce_kernel<float><<<blocks, 256, 0, stream>>>(ws, (float*)out, n, splits);
-            else splitk_reduce_kernel<qi::bf16><<<blocks, 256, 0, stream>>>(ws, (qi::bf16*)out, n, splits);
+            if (out_dtype == qi::kF32) qi::launch(splitk_reduce_kernel<float>, dim3(blocks), dim3(256), 0, stream, (const float*)ws, (float*)out, n, splits);
+            else qi::launch(splitk_reduce_kernel<qi::bf16>, dim3(blocks), dim3(256), 0, stream, (const float*)ws, (qi::bf16*)out, n, splits);
             return qi::check_launch("splitk_reduce");
         }
         return 0;

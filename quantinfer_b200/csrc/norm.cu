@@ -20,6 +20,7 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ resid, const TD* __restri
                                    TO* __restrict__ out, const int* __restrict__ rows, int hidden,
                                    int write_resid) {
     __shared__ float scratch[32];
+    qi::pdl_enter();
     const int r = blockIdx.x;
     const int s = rows ? rows[r] : r;
     float* xr = resid + (size_t)s * hidden;
@@ -85,6 +86,7 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ resid, const TD* __re
                                        const float* __restrict__ gain, float eps, TO* __restrict__ out,
                                        const int* __restrict__ rows, int hidden, int write_resid) {
     __shared__ float scratch[32];
+    qi::pdl_enter();
     const int r = blockIdx.x;
     const int s = rows ? rows[r] : r;
     float* xr = resid + (size_t)s * hidden;
@@ -130,6 +132,7 @@ template <typename T>
 __global__ void rmsnorm_kernel(const T* __restrict__ x, const float* __restrict__ gain, float eps,
                                T* __restrict__ out, int width) {
     __shared__ float scratch[32];
+    qi::pdl_enter();
     const T* xr = x + (size_t)blockIdx.x * width;
     float sumsq = 0.f;
     for (int i = threadIdx.x; i < width; i += blockDim.x) {
@@ -166,9 +169,8 @@ extern "C" int qi_add_rmsnorm(float* resid, const void* delta, int delta_dtype, 
         if (threads > 512) threads = 512;
         QI_DISPATCH_DTYPE(dd, TD, {
             QI_DISPATCH_DTYPE(out_dtype, TO, {
-                add_rmsnorm_vec_kernel<TD, TO><<<n_rows, threads, 0, stream>>>(
-                    resid, (const TD*)delta, delta_splits, (size_t)delta_split_stride, gain, eps,
-                    (TO*)out, rows, hidden, write_resid);
+                qi::launch(add_rmsnorm_vec_kernel<TD, TO>, dim3(n_rows), dim3(threads), 0, stream, resid, (const TD*)delta,
+                           delta_splits, (size_t)delta_split_stride, gain, eps, (TO*)out, rows, hidden, write_resid);
             });
         });
         return qi::check_launch("add_rmsnorm");
@@ -176,9 +178,8 @@ extern "C" int qi_add_rmsnorm(float* resid, const void* delta, int delta_dtype, 
     const int threads = pick_threads(hidden);
     QI_DISPATCH_DTYPE(dd, TD, {
         QI_DISPATCH_DTYPE(out_dtype, TO, {
-            add_rmsnorm_kernel<TD, TO><<<n_rows, threads, 0, stream>>>(
-                resid, (const TD*)delta, delta_splits, (size_t)delta_split_stride, gain, eps,
-                (TO*)out, rows, hidden, write_resid);
+            qi::launch(add_rmsnorm_kernel<TD, TO>, dim3(n_rows), dim3(threads), 0, stream, resid, (const TD*)delta,
+                       delta_splits, (size_t)delta_split_stride, gain, eps, (TO*)out, rows, hidden, write_resid);
         });
     });
     return qi::check_launch("add_rmsnorm");
@@ -191,7 +192,7 @@ extern "C" int qi_rmsnorm(const void* x, const float* gain, float eps, void* out
     if (n_rows == 0) return 0;
     const int threads = pick_threads(width);
     QI_DISPATCH_DTYPE(dtype, T, {
-        rmsnorm_kernel<T><<<n_rows, threads, 0, stream>>>((const T*)x, gain, eps, (T*)out, width);
+        qi::launch(rmsnorm_kernel<T>, dim3(n_rows), dim3(threads), 0, stream, (const T*)x, gain, eps, (T*)out, width);
     });
     return qi::check_launch("rmsnorm");
 }

@@ -28,6 +28,7 @@ __global__ void qk_norm_rope_kv_kernel(
     const int* __restrict__ token_req, const int* __restrict__ block_table, int max_blocks,
     int page_size, int num_pages, T* __restrict__ k_pages, T* __restrict__ v_pages, int nq, int nkv,
     int d, int* __restrict__ status) {
+    qi::pdl_enter();
     const int t = blockIdx.x;
     const int head = blockIdx.y * kWarpsPerBlock + (threadIdx.x >> 5);
     const int lane = threadIdx.x & 31;
@@ -120,6 +121,7 @@ __global__ void qk_norm_rope_kv_vec_kernel(
     const int* __restrict__ token_req, const int* __restrict__ block_table, int max_blocks,
     int page_size, int num_pages, T* __restrict__ k_pages, T* __restrict__ v_pages, int nq, int nkv,
     int d, int* __restrict__ status) {
+    qi::pdl_enter();
     const int t = blockIdx.x;
     const int head = blockIdx.y * kWarpsPerBlock + (threadIdx.x >> 5);
     const int lane = threadIdx.x & 31;
@@ -222,14 +224,14 @@ extern "C" int qi_qk_norm_rope_kv(const void* qkv, void* q_out, int dtype, const
     if (d % 4 == 0 && (rot == d || rot == 0) && ((uintptr_t)qkv & 7) == 0 && ((uintptr_t)q_out & 7) == 0 &&
         ((uintptr_t)k_pages & 7) == 0 && ((uintptr_t)v_pages & 7) == 0) {
         QI_DISPATCH_DTYPE(dtype, T, {
-            qk_norm_rope_kv_vec_kernel<T><<<grid, kWarpsPerBlock * 32, 0, stream>>>(
+            qi::launch(qk_norm_rope_kv_vec_kernel<T>, grid, dim3(kWarpsPerBlock * 32), 0, stream,
                 (const T*)qkv, (T*)q_out, q_gain, k_gain, eps, cos_t, sin_t, positions, token_req,
                 block_table, max_blocks, page_size, num_pages, (T*)k_pages, (T*)v_pages, nq, nkv, d, status);
         });
         return qi::check_launch("qk_norm_rope_kv");
     }
     QI_DISPATCH_DTYPE(dtype, T, {
-        qk_norm_rope_kv_kernel<T><<<grid, kWarpsPerBlock * 32, 0, stream>>>(
+        qi::launch(qk_norm_rope_kv_kernel<T>, grid, dim3(kWarpsPerBlock * 32), 0, stream,
             (const T*)qkv, (T*)q_out, q_gain, k_gain, eps, cos_t, sin_t, rot, positions, token_req,
             block_table, max_blocks, page_size, num_pages, (T*)k_pages, (T*)v_pages, nq, nkv, d,
             status);

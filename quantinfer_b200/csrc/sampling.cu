@@ -90,6 +90,7 @@ sample_kernel(const float* __restrict__ logits, int vocab, const float* __restri
     __shared__ long long warp_eq[kNumWarps];
     __shared__ int result;
 
+    qi::pdl_enter();
     const int row = blockIdx.x;
     const float* x = logits + (size_t)row * vocab;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -310,6 +311,7 @@ __global__ void advance_decode_kernel(int* __restrict__ token_ids, int* __restri
                                       int* __restrict__ start_pos, int* __restrict__ kv_len,
                                       int* __restrict__ counter, const int* __restrict__ sampled,
                                       int* __restrict__ history, int b) {
+    qi::pdl_enter();
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= b) return;
     const int t = sampled[i];
@@ -327,8 +329,8 @@ extern "C" int qi_advance_decode(int* token_ids, int* positions, int* start_pos,
                                  const int* sampled, int* history, int b, cudaStream_t stream) {
     QI_REQUIRE(b >= 0, "advance_decode: bad batch size %d", b);
     if (b == 0) return 0;
-    advance_decode_kernel<<<(b + 127) / 128, 128, 0, stream>>>(token_ids, positions, start_pos, kv_len, counter,
-                                                             sampled, history, b);
+    qi::launch(advance_decode_kernel, dim3((b + 127) / 128), dim3(128), 0, stream, token_ids, positions, start_pos, kv_len,
+               counter, sampled, history, b);
     return qi::check_launch("advance_decode");
 }
 
@@ -337,7 +339,7 @@ extern "C" int qi_sample(const float* logits, int rows, int vocab, const float* 
                          const int* counter, int* out_token, int* status, cudaStream_t stream) {
     QI_REQUIRE(rows >= 0 && vocab > 0, "sample: bad sizes rows=%d vocab=%d", rows, vocab);
     if (rows == 0) return 0;
-    sample_kernel<<<rows, kThreads, 0, stream>>>(logits, vocab, temperature, top_k, top_p, seed,
-                                                 counter, out_token, status);
+    qi::launch(sample_kernel, dim3(rows), dim3(kThreads), 0, stream, logits, vocab, temperature, top_k, top_p, seed, counter,
+               out_token, status);
     return qi::check_launch("sample");
 }
