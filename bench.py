@@ -246,6 +246,8 @@ def main() -> int:
     # ---- end to end through the Python entry point -----------------------------------
     model = Model.from_engine(engine, max_batch_tokens=PROMPT_LEN)
     prompts = [prompt() for _ in range(args.batch)]
+    # warm-up through the same entry point (W decode steps): graphs are captured, buffers pinned
+    model.generate_batch(prompts, max_new_tokens=args.warmup + 1, eos_token_id=None)
     stamps = []
     model.generate_batch(prompts, max_new_tokens=n_new, eos_token_id=None,
                          on_event=lambda ev: stamps.append((time.perf_counter(), ev.request_id)))
@@ -259,7 +261,8 @@ def main() -> int:
             after += 1
     e2e_value = after / (stamps[-1][0] - t_all_first) if t_all_first and after else None
     e2e = {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": engine.h2d_bytes,
-           "d2h_bytes_per_step": 4 * args.batch + 4}
+           "d2h_bytes_per_step": 4 * args.batch + 4,
+           "ms_per_step": (stamps[-1][0] - t_all_first) * 1e3 / max(after // max(args.batch, 1), 1) if t_all_first and after else None}
 
     line = {
         "metric": "decode tokens/s (Qwen3-8B sizes, random bf16 weights, 1 B200)",

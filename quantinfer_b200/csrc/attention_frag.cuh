@@ -99,11 +99,12 @@ __device__ __forceinline__ void pv_tile(float (&o)[D / 8][4], const float (&p)[N
     }
 }
 
-// Online softmax over one tile of scores (already scaled by scale * log2 e, masked with
-// -inf): updates the running maximum m and sum l of the two rows this thread holds
-// (g and g + 8), rescales o, and leaves the weights in s.
+// Online softmax over one tile of raw scores (masked entries are -inf): with
+// c = scale * log2 e, updates the running maximum m (of c * score) and the sum l of the
+// two rows this thread holds (g and g + 8), rescales o, and leaves the weights
+// 2^(c * score - m) in s.
 template <int D, int NT>
-__device__ __forceinline__ void softmax_tile(float (&s)[NT][4], float (&m)[2], float (&l)[2], float (&o)[D / 8][4]) {
+__device__ __forceinline__ void softmax_tile(float (&s)[NT][4], float (&m)[2], float (&l)[2], float (&o)[D / 8][4], float c) {
     float mx[2] = {-INFINITY, -INFINITY};
 #pragma unroll
     for (int j = 0; j < NT; ++j) {
@@ -115,12 +116,13 @@ __device__ __forceinline__ void softmax_tile(float (&s)[NT][4], float (&m)[2], f
         mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
         mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
     }
-    float corr[2], mn[2];
+    float corr[2], ms[2];
 #pragma unroll
     for (int r = 0; r < 2; ++r) {
-        mn[r] = fmaxf(m[r], mx[r]);
-        corr[r] = (m[r] == -INFINITY) ? 0.f : exp2f(m[r] - mn[r]);   // mn is finite whenever m is
-        m[r] = mn[r];
+        const float mn = fmaxf(m[r], mx[r] * c);           // c > 0; -inf stays -inf
+        ms[r] = (mn == -INFINITY) ? 0.f : mn;               // a row with no key yet: every weight is 2^-inf = 0
+        corr[r] = exp2f(m[r] - ms[r]);                      // m = -inf gives 0
+        m[r] = mn;
     }
     float sum[2] = {0.f, 0.f};
 #pragma unroll
@@ -128,7 +130,7 @@ __device__ __forceinline__ void softmax_tile(float (&s)[NT][4], float (&m)[2], f
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
             const int r = e >> 1;
-            const float p = (s[j][e] == -INFINITY) ? 0.f : exp2f(s[j][e] - mn[r]);
+            const float p = exp2f(fmaf(s[j][e], c, -ms[r]));
             s[j][e] = p;
             sum[r] += p;
         }

@@ -116,7 +116,7 @@ attention_prefill_kernel(const qi::bf16* __restrict__ q, qi::bf16* __restrict__ 
     uint32_t qa[D / 16][4];
     const int g = lane >> 2, t4 = lane & 3;
     const int row_pos[2] = {pos0 + warp * 16 + g, pos0 + warp * 16 + g + 8};
-    const int warp_max_pos = pos0 + warp * 16 + 15;
+    const int warp_max_pos = pos0 + warp * 16 + 15, warp_min_pos = pos0 + warp * 16;
 
     for (int i = 0; i < n_tiles; ++i) {
         const int buf = i & 1;
@@ -143,17 +143,22 @@ attention_prefill_kernel(const qi::bf16* __restrict__ q, qi::bf16* __restrict__ 
             const uint32_t k_s = kv_s + buf * 2 * kTileBytes, v_s = k_s + kTileBytes;
             float s[8][4];
             qk_tile<D, 8, RowSwizzle<D>>(s, qa, k_s, 0, lane);
+            // a tile that lies wholly inside every row's key range needs no mask
+            const bool inner = t0 + kTileKeys - 1 <= warp_min_pos && t0 >= lo && t0 + kTileKeys <= hi &&
+                               (window <= 0 || t0 > warp_max_pos - window);
+            if (!inner) {
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
+                for (int j = 0; j < 8; ++j) {
 #pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    const int key = t0 + j * 8 + t4 * 2 + (e & 1);
-                    const int pos = row_pos[e >> 1];
-                    const bool ok = key <= pos && key >= lo && key < hi && (window <= 0 || key > pos - window);
-                    s[j][e] = ok ? s[j][e] * scale_log2e : -INFINITY;
+                    for (int e = 0; e < 4; ++e) {
+                        const int key = t0 + j * 8 + t4 * 2 + (e & 1);
+                        const int pos = row_pos[e >> 1];
+                        const bool valid = key <= pos && key >= lo && key < hi && (window <= 0 || key > pos - window);
+                        if (!valid) s[j][e] = -INFINITY;
+                    }
                 }
             }
-            softmax_tile<D, 8>(s, m, l, o);
+            softmax_tile<D, 8>(s, m, l, o, scale_log2e);
             pv_tile<D, 8, RowSwizzle<D>>(o, s, v_s, 0, lane);
         }
         __syncthreads();
@@ -272,10 +277,10 @@ attention_decode_kernel(const qi::bf16* __restrict__ q, const qi::bf16* __restri
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
                     const int key = wkey0 + j * 8 + t4 * 2 + (e & 1);
-                    s[j][e] = (key >= k0 && key < k1) ? s[j][e] * scale_log2e : -INFINITY;
+                    if (key < k0 || key >= k1) s[j][e] = -INFINITY;
                 }
             }
-            softmax_tile<D, 2>(s, m, l, o);
+            softmax_tile<D, 2>(s, m, l, o, scale_log2e);
             pv_tile<D, 2, RowSwizzle<D>>(o, s, v_s, warp * 16, lane);
         }
         __syncthreads();

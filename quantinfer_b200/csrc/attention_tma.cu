@@ -24,6 +24,7 @@ using namespace qi_attn;
 
 constexpr int kTileKeys = 64;
 constexpr uint32_t kSpinLimit = 1u << 24;
+constexpr int kMaxTableEntries = 2048;   // block table entries one CTA keeps in shared memory
 
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
@@ -55,16 +56,16 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
 // `needed` = [lo, hi): a missing page inside it is an error; outside it any page will do.
 template <int D>
 __device__ __forceinline__ void issue_kv_tile(uint32_t stage_smem, uint32_t bar, const CUtensorMap* map_k,
-                                              const CUtensorMap* map_v, const int* __restrict__ table,
-                                              int max_blocks, int page_size, int box_rows, int num_pages, int nkv,
+                                              const CUtensorMap* map_v, const int* table, int blk0,
+                                              int n_blk, int page_size, int box_rows, int num_pages, int nkv,
                                               int hk, int t0, int lo, int hi, int* __restrict__ status) {
     constexpr int kHalfBytes = kTileKeys * 128;
     constexpr int kTileBytes = kTileKeys * D * 2;
     mbar_expect_tx(bar, 2 * kTileBytes);
     for (int r0 = 0; r0 < kTileKeys; r0 += box_rows) {
         const int key = t0 + r0;
-        const int blk = key / page_size;
-        int page = blk < max_blocks ? table[blk] : -1;
+        const int blk = key / page_size - blk0;     // `table` holds the entries blk0 .. blk0 + n_blk - 1
+        int page = blk < n_blk ? table[blk] : -1;
         if (page < 0 || page >= num_pages) {
             if (key < hi && key + box_rows > lo && status) atomicOr(status, qi::kStatusBadPage);
             page = 0;
@@ -100,6 +101,7 @@ attention_prefill_tma_kernel(const __grid_constant__ CUtensorMap map_q, const __
     const uint32_t bars = kv_s + kPrefillStages * 2 * kTileBytes;   // full[stages], q
     auto full_bar = [&](int s) { return bars + 8u * s; };
     const uint32_t q_bar = bars + 8u * kPrefillStages;
+    int* s_table = reinterpret_cast<int*>(smem_raw + (bars + 64u - smem_u32(smem_raw)));   // block table entries of this tile's keys
 
     qi::pdl_enter();
     const int tile = blockIdx.x, h = blockIdx.y;
@@ -113,6 +115,11 @@ attention_prefill_tma_kernel(const __grid_constant__ CUtensorMap map_q, const __
     const int lo = (window > 0 && pos0 - window + 1 > 0) ? pos0 - window + 1 : 0;
     const int t_begin = (lo / kTileKeys) * kTileKeys;
     const int n_tiles = (hi - t_begin + kTileKeys - 1) / kTileKeys;
+    // all table entries the issuing thread will need, fetched by everybody at once (one
+    // round trip instead of one per tile on the issuing thread's critical path)
+    const int blk0 = t_begin / page_size;
+    const int n_blk = min(min((t_begin + n_tiles * kTileKeys + page_size - 1) / page_size, max_blocks) - blk0, kMaxTableEntries);
+    for (int i = threadIdx.x; i < n_blk; i += blockDim.x) s_table[i] = table[blk0 + i];
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kPrefillStages; ++s) mbar_init(full_bar(s), 1);
@@ -126,7 +133,7 @@ attention_prefill_tma_kernel(const __grid_constant__ CUtensorMap map_q, const __
         for (int hh = 0; hh < D / 64; ++hh)
             tma_load_2d(q_s + hh * (kPrefillRows * 128), &map_q, q_bar, h * D + hh * 64, q0);
         for (int i = 0; i < kPrefillStages && i < n_tiles; ++i)
-            issue_kv_tile<D>(kv_s + i * 2 * kTileBytes, full_bar(i), &map_k, &map_v, table, max_blocks, page_size, box_rows,
+            issue_kv_tile<D>(kv_s + i * 2 * kTileBytes, full_bar(i), &map_k, &map_v, s_table, blk0, n_blk, page_size, box_rows,
                              num_pages, nkv, hk, t_begin + i * kTileKeys, lo, hi, status);
     }
 
@@ -139,7 +146,7 @@ attention_prefill_tma_kernel(const __grid_constant__ CUtensorMap map_q, const __
     uint32_t qa[D / 16][4];
     const int g = lane >> 2, t4 = lane & 3;
     const int row_pos[2] = {pos0 + warp * 16 + g, pos0 + warp * 16 + g + 8};
-    const int warp_max_pos = pos0 + warp * 16 + 15;
+    const int warp_max_pos = pos0 + warp * 16 + 15, warp_min_pos = pos0 + warp * 16;
     const bool warp_active = warp * 16 < rows_valid;
     bool ok = mbar_wait(q_bar, 0);
     if (ok) load_q_frags<D, TmaSwizzle<kPrefillRows>>(qa, q_s, warp * 16, lane);
@@ -153,22 +160,27 @@ attention_prefill_tma_kernel(const __grid_constant__ CUtensorMap map_q, const __
             const uint32_t k_s = kv_s + stage * 2 * kTileBytes, v_s = k_s + kTileBytes;
             float s[8][4];
             qk_tile<D, 8, TmaSwizzle<kTileKeys>>(s, qa, k_s, 0, lane);
+            // a tile that lies wholly inside every row's key range needs no mask
+            const bool inner = t0 + kTileKeys - 1 <= warp_min_pos && t0 >= lo && t0 + kTileKeys <= hi &&
+                               (window <= 0 || t0 > warp_max_pos - window);
+            if (!inner) {
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
+                for (int j = 0; j < 8; ++j) {
 #pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    const int key = t0 + j * 8 + t4 * 2 + (e & 1);
-                    const int pos = row_pos[e >> 1];
-                    const bool valid = key <= pos && key >= lo && key < hi && (window <= 0 || key > pos - window);
-                    s[j][e] = valid ? s[j][e] * scale_log2e : -INFINITY;
+                    for (int e = 0; e < 4; ++e) {
+                        const int key = t0 + j * 8 + t4 * 2 + (e & 1);
+                        const int pos = row_pos[e >> 1];
+                        const bool valid = key <= pos && key >= lo && key < hi && (window <= 0 || key > pos - window);
+                        if (!valid) s[j][e] = -INFINITY;
+                    }
                 }
             }
-            softmax_tile<D, 8>(s, m, l, o);
+            softmax_tile<D, 8>(s, m, l, o, scale_log2e);
             pv_tile<D, 8, TmaSwizzle<kTileKeys>>(o, s, v_s, 0, lane);
         }
         __syncthreads();   // every warp is done with this stage
         if (threadIdx.x == 0 && i + kPrefillStages < n_tiles)
-            issue_kv_tile<D>(kv_s + stage * 2 * kTileBytes, full_bar(stage), &map_k, &map_v, table, max_blocks, page_size,
+            issue_kv_tile<D>(kv_s + stage * 2 * kTileBytes, full_bar(stage), &map_k, &map_v, s_table, blk0, n_blk, page_size,
                              box_rows, num_pages, nkv, hk, t0 + kPrefillStages * kTileKeys, lo, hi, status);
     }
     if (!ok) {
@@ -215,6 +227,7 @@ attention_decode_tma_kernel(const qi::bf16* __restrict__ q, const __grid_constan
     uint8_t* q_tile = aligned + kDecodeStages * 2 * kTileBytes;
     const uint32_t bars = q_s + kQBytes;
     auto full_bar = [&](int s) { return bars + 8u * s; };
+    int* s_table = reinterpret_cast<int*>(aligned + kDecodeStages * 2 * kTileBytes + kQBytes + 64);
 
     qi::pdl_enter();
     const int split = blockIdx.x, hk = blockIdx.y, b = blockIdx.z;
@@ -228,7 +241,8 @@ attention_decode_tma_kernel(const qi::bf16* __restrict__ q, const __grid_constan
     const int k1 = min(S, (split + 1) * chunk);
     const size_t part = ((size_t)b * nq + (size_t)hk * G) * n_splits + split;
 
-    if (k0 >= k1) {
+    const int tok = q_start[b];
+    if (k0 >= k1) {   // nothing of this range belongs to the request: an empty partial
         if (threadIdx.x < G) {
             float* ml = ws_ml + (part + (size_t)threadIdx.x * n_splits) * 2;
             ml[0] = -INFINITY;
@@ -237,9 +251,11 @@ attention_decode_tma_kernel(const qi::bf16* __restrict__ q, const __grid_constan
         return;
     }
     const int* table = block_table + (size_t)b * max_blocks;
-    const int tok = q_start[b];
     const int t_begin = (k0 / kTileKeys) * kTileKeys;
     const int n_tiles = (k1 - t_begin + kTileKeys - 1) / kTileKeys;
+    const int blk0 = t_begin / page_size;
+    const int n_blk = min(min((t_begin + n_tiles * kTileKeys + page_size - 1) / page_size, max_blocks) - blk0, kMaxTableEntries);
+    for (int i = threadIdx.x; i < n_blk; i += blockDim.x) s_table[i] = table[blk0 + i];
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kDecodeStages; ++s) mbar_init(full_bar(s), 1);
@@ -255,7 +271,7 @@ attention_decode_tma_kernel(const qi::bf16* __restrict__ q, const __grid_constan
     __syncthreads();
     if (threadIdx.x == 0) {
         for (int i = 0; i < kDecodeStages && i < n_tiles; ++i)
-            issue_kv_tile<D>(kv_s + i * 2 * kTileBytes, full_bar(i), &map_k, &map_v, table, max_blocks, page_size, box_rows,
+            issue_kv_tile<D>(kv_s + i * 2 * kTileBytes, full_bar(i), &map_k, &map_v, s_table, blk0, n_blk, page_size, box_rows,
                              num_pages, nkv, hk, t_begin + i * kTileKeys, k0, k1, status);
     }
     float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
@@ -283,15 +299,15 @@ attention_decode_tma_kernel(const qi::bf16* __restrict__ q, const __grid_constan
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
                     const int key = wkey0 + j * 8 + t4 * 2 + (e & 1);
-                    s[j][e] = (key >= k0 && key < k1) ? s[j][e] * scale_log2e : -INFINITY;
+                    if (key < k0 || key >= k1) s[j][e] = -INFINITY;
                 }
             }
-            softmax_tile<D, 2>(s, m, l, o);
+            softmax_tile<D, 2>(s, m, l, o, scale_log2e);
             pv_tile<D, 2, TmaSwizzle<kTileKeys>>(o, s, v_s, warp * 16, lane);
         }
         __syncthreads();
         if (threadIdx.x == 0 && i + kDecodeStages < n_tiles)
-            issue_kv_tile<D>(kv_s + stage * 2 * kTileBytes, full_bar(stage), &map_k, &map_v, table, max_blocks, page_size,
+            issue_kv_tile<D>(kv_s + stage * 2 * kTileBytes, full_bar(stage), &map_k, &map_v, s_table, blk0, n_blk, page_size,
                              box_rows, num_pages, nkv, hk, t0 + kDecodeStages * kTileKeys, k0, k1, status);
     }
     if (!ok) {
@@ -343,7 +359,9 @@ attention_decode_tma_kernel(const qi::bf16* __restrict__ q, const __grid_constan
     }
 }
 
-// out[b, h, :] = sum_s o_s 2^(m_s - M) / sum_s l_s 2^(m_s - M), key ranges in order.
+// out[b, h, :] = sum_s o_s 2^(m_s - M) / sum_s l_s 2^(m_s - M), key ranges in order. A separate
+// kernel: merging inside the decode kernel (last CTA by ticket) was measured slower, the
+// merge then sits on the tail of the slowest CTA.
 template <int D>
 __global__ void attention_merge_kernel(const float* __restrict__ ws_o, const float* __restrict__ ws_ml,
                                        const int* __restrict__ q_start, qi::bf16* __restrict__ out, int nq,
@@ -352,16 +370,18 @@ __global__ void attention_merge_kernel(const float* __restrict__ ws_o, const flo
     const int h = blockIdx.x, b = blockIdx.y;
     const size_t base = ((size_t)b * nq + h) * n_splits;
     float M = -INFINITY;
+#pragma unroll 4
     for (int s = 0; s < n_splits; ++s) M = fmaxf(M, ws_ml[(base + s) * 2]);
     const int tok = q_start[b];
     for (int col = threadIdx.x; col < D; col += blockDim.x) {
         float L = 0.f, O = 0.f;
+#pragma unroll 4
         for (int s = 0; s < n_splits; ++s) {
             const float ms = ws_ml[(base + s) * 2];
-            if (ms == -INFINITY) continue;
-            const float f = exp2f(ms - M);
+            const float o = ws_o[(base + s) * D + col];
+            const float f = (ms == -INFINITY) ? 0.f : exp2f(ms - M);
             L += ws_ml[(base + s) * 2 + 1] * f;
-            O += ws_o[(base + s) * D + col] * f;
+            O += (ms == -INFINITY) ? 0.f : o * f;      // an empty range's slot holds no data
         }
         out[((size_t)tok * nq + h) * D + col] = __float2bfloat16_rn(L > 0.f ? O / L : 0.f);
     }
@@ -398,8 +418,8 @@ int make_map(CUtensorMap* map, const void* ptr, long long rows, int cols, int bo
     return 0;
 }
 
-template <int D> constexpr int prefill_smem() { return kPrefillRows * D * 2 + kPrefillStages * 2 * kTileKeys * D * 2 + 64 + 1024; }
-template <int D> constexpr int decode_smem() { return kDecodeStages * 2 * kTileKeys * D * 2 + 16 * D * 2 + 64 + 1024; }
+template <int D> constexpr int prefill_smem() { return kPrefillRows * D * 2 + kPrefillStages * 2 * kTileKeys * D * 2 + 64 + 4 * kMaxTableEntries + 1024; }
+template <int D> constexpr int decode_smem() { return kDecodeStages * 2 * kTileKeys * D * 2 + 16 * D * 2 + 64 + 4 * kMaxTableEntries + 1024; }
 
 template <int D>
 int launch_prefill(const void* q, void* out, const void* k_pages, const void* v_pages, const int* block_table,
@@ -446,8 +466,8 @@ int launch_decode(const void* q, void* out, const void* k_pages, const void* v_p
         (const qi::bf16*)q, mk, mv, block_table, max_blocks, page_size, box_rows, num_pages, kv_len, q_start, ws_o,
         ws_ml, nq, nkv, scale * 1.4426950408889634f, window, chunk, status);
     if (int rc = qi::check_launch("attention_decode_tma")) return rc;
-    qi::launch(attention_merge_kernel<D>, dim3(nq, batch), dim3(D >= 128 ? 128 : 64), 0, stream, ws_o, ws_ml, q_start,
-               (qi::bf16*)out, nq, n_splits);
+    qi::launch(attention_merge_kernel<D>, dim3(nq, batch), dim3(D >= 128 ? 128 : 64), 0, stream, (const float*)ws_o,
+               (const float*)ws_ml, q_start, (qi::bf16*)out, nq, n_splits);
     return qi::check_launch("attention_merge");
 }
 
@@ -456,8 +476,9 @@ bool pow2(int v) { return v > 0 && (v & (v - 1)) == 0; }
 }  // namespace
 
 // 1 if the TMA-fed attention kernels take this geometry.
-extern "C" int qi_attention_tma_supported(int nq, int nkv, int d, int page_size) {
-    return (d == 64 || d == 128) && nkv > 0 && nq % nkv == 0 && nq / nkv <= 16 && pow2(page_size) && page_size >= 8;
+extern "C" int qi_attention_tma_supported(int nq, int nkv, int d, int page_size, int max_blocks) {
+    return (d == 64 || d == 128) && nkv > 0 && nq % nkv == 0 && nq / nkv <= 16 && pow2(page_size) && page_size >= 8 &&
+           max_blocks > 0 && max_blocks <= kMaxTableEntries;
 }
 
 // Query rows per CTA of qi_attention_prefill_tma: the tile lists must be cut to this.
@@ -468,8 +489,8 @@ extern "C" int qi_attention_prefill_tma(const void* q, void* out, const void* k_
                                         const int* q_start, const int* start_pos, const int* tile_req,
                                         const int* tile_q0, int n_tiles, int n_tokens, int nq, int nkv, int d,
                                         float scale, int window, int* status, cudaStream_t stream) {
-    QI_REQUIRE(qi_attention_tma_supported(nq, nkv, d, page_size),
-               "attention_prefill_tma: heads %d/%d of size %d with pages of %d are not covered", nq, nkv, d, page_size);
+    QI_REQUIRE(qi_attention_tma_supported(nq, nkv, d, page_size, max_blocks),
+               "attention_prefill_tma: heads %d/%d of size %d with %d pages of %d per request are not covered", nq, nkv, d, max_blocks, page_size);
     QI_REQUIRE(max_blocks > 0 && num_pages > 0 && window >= 0 && n_tokens > 0, "attention_prefill_tma: bad sizes");
     QI_REQUIRE(((uintptr_t)q & 15) == 0 && ((uintptr_t)k_pages & 15) == 0 && ((uintptr_t)v_pages & 15) == 0,
                "attention_prefill_tma: tensors must be 16-byte aligned");
@@ -489,8 +510,8 @@ extern "C" int qi_attention_decode_tma(const void* q, void* out, const void* k_p
                                        const int* kv_len, const int* q_start, int batch, int nq, int nkv, int d,
                                        float scale, int window, int chunk, int n_splits, float* ws_o, float* ws_ml,
                                        int* status, cudaStream_t stream) {
-    QI_REQUIRE(qi_attention_tma_supported(nq, nkv, d, page_size),
-               "attention_decode_tma: heads %d/%d of size %d with pages of %d are not covered", nq, nkv, d, page_size);
+    QI_REQUIRE(qi_attention_tma_supported(nq, nkv, d, page_size, max_blocks),
+               "attention_decode_tma: heads %d/%d of size %d with %d pages of %d per request are not covered", nq, nkv, d, max_blocks, page_size);
     QI_REQUIRE(max_blocks > 0 && num_pages > 0 && window >= 0, "attention_decode_tma: bad sizes");
     QI_REQUIRE(chunk > 0 && chunk % kTileKeys == 0, "attention_decode_tma: the key range per CTA (%d) must be a positive multiple of %d", chunk, kTileKeys);
     QI_REQUIRE(n_splits > 0 && n_splits <= 65535 && nkv <= 65535 && batch <= 65535, "attention_decode_tma: grid too large");

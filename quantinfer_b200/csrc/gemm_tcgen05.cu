@@ -429,6 +429,7 @@ __global__ void splitk_reduce_kernel(const float* __restrict__ partial, TOut* __
     qi::pdl_enter();
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
         float s = 0.f;
+#pragma unroll 4
         for (int k = 0; k < splits; ++k) s += partial[(size_t)k * n + i];
         store1<TOut>(out + i, s);
     }

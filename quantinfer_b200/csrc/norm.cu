@@ -91,11 +91,45 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ resid, const TD* __re
     const int s = rows ? rows[r] : r;
     float* xr = resid + (size_t)s * hidden;
     const TD* dr = delta ? delta + (size_t)s * hidden : nullptr;
+    TO* orow = out + (size_t)r * hidden;
+    if (hidden <= (int)blockDim.x * 8) {
+        // the whole row fits the block once: values stay in registers between the two passes and
+        // the gain is fetched together with the inputs (one round of loads instead of three)
+        const int i = threadIdx.x * 8;
+        const bool active = i < hidden;
+        float x[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f}, d[8], g[8];
+        if (active) {
+            Vec8<float>::load(xr + i, x);
+            Vec8<float>::load(gain + i, g);
+            if (dr) {
+#pragma unroll 4
+                for (int k = 0; k < delta_splits; ++k) {
+                    Vec8<TD>::load(dr + k * delta_split_stride + i, d);
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) x[j] += d[j];
+                }
+            }
+            if (write_resid) Vec8<float>::store(xr + i, x);
+        }
+        float sumsq = 0.f;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) sumsq += x[j] * x[j];
+        const float total = qi::block_sum(sumsq, scratch);
+        const float inv = 1.0f / sqrtf(total / (float)hidden + eps);
+        if (active) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) x[j] = x[j] * inv * g[j];
+            Vec8<TO>::store(orow + i, x);
+        }
+        return;
+    }
     float sumsq = 0.f;
     for (int i = threadIdx.x * 8; i < hidden; i += blockDim.x * 8) {
         float x[8], d[8];
         Vec8<float>::load(xr + i, x);
         if (dr) {
+            // the loads of four splits go out together; the sums stay in split order
+#pragma unroll 4
             for (int k = 0; k < delta_splits; ++k) {
                 Vec8<TD>::load(dr + k * delta_split_stride + i, d);
 #pragma unroll
@@ -108,7 +142,6 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ resid, const TD* __re
     }
     const float total = qi::block_sum(sumsq, scratch);
     const float inv = 1.0f / sqrtf(total / (float)hidden + eps);
-    TO* orow = out + (size_t)r * hidden;
     for (int i = threadIdx.x * 8; i < hidden; i += blockDim.x * 8) {
         float x[8], d[8], g[8];
         Vec8<float>::load(xr + i, x);   // the same thread wrote it in the first pass when write_resid

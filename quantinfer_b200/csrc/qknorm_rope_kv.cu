@@ -113,9 +113,24 @@ template <> struct Pair<qi::bf16> {
     }
 };
 
-template <typename T>
+// Sum over the K splits of a product's 32-bit partial sums (one split: the value itself).
+template <typename TIn>
+__device__ __forceinline__ float2 load_pair(const TIn* p, int splits, size_t stride) {
+    float2 v = Pair<TIn>::load(p);
+#pragma unroll 4
+    for (int k = 1; k < splits; ++k) {
+        const float2 w = Pair<TIn>::load(p + k * stride);
+        v.x += w.x;
+        v.y += w.y;
+    }
+    return v;
+}
+
+// TIn = T: qkv is the projection's output. TIn = float with splits > 1: qkv holds the
+// projection's K-split partial sums [splits, n, width], added here in split order.
+template <typename TIn, typename T>
 __global__ void qk_norm_rope_kv_vec_kernel(
-    const T* __restrict__ qkv, T* __restrict__ q_out, const float* __restrict__ q_gain,
+    const TIn* __restrict__ qkv, int splits, size_t split_stride, T* __restrict__ q_out, const float* __restrict__ q_gain,
     const float* __restrict__ k_gain, float eps, const float* __restrict__ cos_t,
     const float* __restrict__ sin_t, const int* __restrict__ positions,
     const int* __restrict__ token_req, const int* __restrict__ block_table, int max_blocks,
@@ -127,7 +142,7 @@ __global__ void qk_norm_rope_kv_vec_kernel(
     const int lane = threadIdx.x & 31;
     const int total_heads = nq + 2 * nkv;
     if (head >= total_heads) return;
-    const T* src = qkv + (size_t)t * total_heads * d + (size_t)head * d;
+    const TIn* src = qkv + (size_t)t * total_heads * d + (size_t)head * d;
     const int pos = positions[t];
     const bool is_q = head < nq;
     const bool is_k = !is_q && head < nq + nkv;
@@ -146,7 +161,7 @@ __global__ void qk_norm_rope_kv_vec_kernel(
     }
     if (!is_q && !is_k) {
         for (int i = 2 * lane; i < d; i += 64) {
-            const float2 v = Pair<T>::load(src + i);
+            const float2 v = load_pair<TIn>(src + i, splits, split_stride);
             Pair<T>::store(dst + i, v.x, v.y);
         }
         return;
@@ -157,14 +172,14 @@ __global__ void qk_norm_rope_kv_vec_kernel(
     if (gain) {
         float ss = 0.f;
         for (int i = 2 * lane; i < d; i += 64) {
-            const float2 v = Pair<T>::load(src + i);
+            const float2 v = load_pair<TIn>(src + i, splits, split_stride);
             ss += v.x * v.x + v.y * v.y;
         }
         ss = qi::warp_sum(ss);
         inv = 1.0f / sqrtf(ss / (float)d + eps);
     }
     for (int p = 2 * lane; p < half; p += 64) {
-        float2 a = Pair<T>::load(src + p), b = Pair<T>::load(src + p + half);
+        float2 a = load_pair<TIn>(src + p, splits, split_stride), b = load_pair<TIn>(src + p + half, splits, split_stride);
         if (gain) {
             const float2 ga = *reinterpret_cast<const float2*>(gain + p), gb = *reinterpret_cast<const float2*>(gain + p + half);
             a.x = a.x * inv * ga.x; a.y = a.y * inv * ga.y;
@@ -202,7 +217,8 @@ extern "C" int qi_rope_table(const float* inv_freq, float* cos_t, float* sin_t, 
 }
 
 // q_gain/k_gain null: no norm. cos_t null: no rotation. k_pages null: no cache write.
-extern "C" int qi_qk_norm_rope_kv(const void* qkv, void* q_out, int dtype, const float* q_gain,
+// qkv_splits > 1: `qkv` holds float32 partial sums [qkv_splits, n_tokens, width] of the projection.
+extern "C" int qi_qk_norm_rope_kv(const void* qkv, int qkv_splits, void* q_out, int dtype, const float* q_gain,
                                   const float* k_gain, float eps, const float* cos_t,
                                   const float* sin_t, int rot, int table_positions,
                                   const int* positions, const int* token_req,
@@ -221,11 +237,23 @@ extern "C" int qi_qk_norm_rope_kv(const void* qkv, void* q_out, int dtype, const
     dim3 grid(n_tokens, (heads + kWarpsPerBlock - 1) / kWarpsPerBlock);
     QI_REQUIRE(grid.y <= 65535, "qk_norm_rope_kv: too many heads");
     if (!cos_t) rot = 0;
-    if (d % 4 == 0 && (rot == d || rot == 0) && ((uintptr_t)qkv & 7) == 0 && ((uintptr_t)q_out & 7) == 0 &&
-        ((uintptr_t)k_pages & 7) == 0 && ((uintptr_t)v_pages & 7) == 0) {
+    QI_REQUIRE(qkv_splits >= 1, "qk_norm_rope_kv: qkv_splits must be >= 1");
+    const bool vec = d % 4 == 0 && (rot == d || rot == 0) && ((uintptr_t)qkv & 7) == 0 && ((uintptr_t)q_out & 7) == 0 &&
+                     ((uintptr_t)k_pages & 7) == 0 && ((uintptr_t)v_pages & 7) == 0;
+    if (qkv_splits > 1) {
+        QI_REQUIRE(vec, "qk_norm_rope_kv: partial sums as input need head_dim %% 4 == 0 and rotation over the whole head");
+        const size_t stride = (size_t)n_tokens * heads * d;
         QI_DISPATCH_DTYPE(dtype, T, {
-            qi::launch(qk_norm_rope_kv_vec_kernel<T>, grid, dim3(kWarpsPerBlock * 32), 0, stream,
-                (const T*)qkv, (T*)q_out, q_gain, k_gain, eps, cos_t, sin_t, positions, token_req,
+            qi::launch(qk_norm_rope_kv_vec_kernel<float, T>, grid, dim3(kWarpsPerBlock * 32), 0, stream,
+                (const float*)qkv, qkv_splits, stride, (T*)q_out, q_gain, k_gain, eps, cos_t, sin_t, positions, token_req,
+                block_table, max_blocks, page_size, num_pages, (T*)k_pages, (T*)v_pages, nq, nkv, d, status);
+        });
+        return qi::check_launch("qk_norm_rope_kv");
+    }
+    if (vec) {
+        QI_DISPATCH_DTYPE(dtype, T, {
+            qi::launch(qk_norm_rope_kv_vec_kernel<T, T>, grid, dim3(kWarpsPerBlock * 32), 0, stream,
+                (const T*)qkv, 1, (size_t)0, (T*)q_out, q_gain, k_gain, eps, cos_t, sin_t, positions, token_req,
                 block_table, max_blocks, page_size, num_pages, (T*)k_pages, (T*)v_pages, nq, nkv, d, status);
         });
         return qi::check_launch("qk_norm_rope_kv");

@@ -24,7 +24,7 @@ STATUS_BAD_PAGE = 2
 STATUS_NON_FINITE = 4
 STATUS_WAIT_TIMEOUT = 8
 
-ABI_VERSION = 3
+ABI_VERSION = 4
 
 _lib = None
 _lib_lock = threading.Lock()
@@ -208,15 +208,23 @@ def qk_norm_rope_kv(qkv, q_out, q_gain, k_gain, eps, cos, sin, rotary_dim, posit
                     block_table, page_size, k_pages, v_pages, nq, nkv, d, status) -> None:
     """Per-head q/k RMSNorm, rotation, and the write of k and v into cache pages.
 
-    qkv [n, (nq + 2 nkv) d]; q_out [n, nq d]; gains float32 [d] or None; cos/sin
+    qkv [n, (nq + 2 nkv) d], or float32 [splits, n, (nq + 2 nkv) d] partial sums of a
+    K-split projection (added here); q_out [n, nq d]; gains float32 [d] or None; cos/sin
     float32 [positions, rotary_dim / 2] or None; k_pages/v_pages
     [num_pages, nkv, page_size, d] or None (no write); block_table int32
     [requests, max_blocks].
     """
-    _req(qkv, "qkv", ndim=2)
-    _req(q_out, "q_out", qkv.dtype, 2)
-    n = qkv.shape[0]
-    if qkv.shape[1] != (nq + 2 * nkv) * d or tuple(q_out.shape) != (n, nq * d):
+    _req(qkv, "qkv")
+    _req(q_out, "q_out", ndim=2)
+    splits = 1
+    if qkv.dim() == 3:
+        splits = qkv.shape[0]
+        if qkv.dtype != torch.float32:
+            raise KernelError("qk_norm_rope_kv: partial sums must be float32")
+    elif qkv.dim() != 2 or qkv.dtype != q_out.dtype:
+        raise KernelError(f"qk_norm_rope_kv: qkv {tuple(qkv.shape)} {qkv.dtype} does not fit q_out {q_out.dtype}")
+    n = qkv.shape[-2]
+    if qkv.shape[-1] != (nq + 2 * nkv) * d or tuple(q_out.shape) != (n, nq * d):
         raise KernelError(f"qk_norm_rope_kv: qkv {tuple(qkv.shape)} / q_out {tuple(q_out.shape)} do not match heads {nq}+2*{nkv} of {d}")
     for g, name in ((q_gain, "q_gain"), (k_gain, "k_gain")):
         if g is not None:
@@ -234,14 +242,14 @@ def qk_norm_rope_kv(qkv, q_out, q_gain, k_gain, eps, cos, sin, rotary_dim, posit
     _req(token_req, "token_req", torch.int32, 1)
     num_pages, max_blocks = 0, 0
     if k_pages is not None:
-        _req(k_pages, "k_pages", qkv.dtype, 4)
-        _req(v_pages, "v_pages", qkv.dtype, 4)
+        _req(k_pages, "k_pages", q_out.dtype, 4)
+        _req(v_pages, "v_pages", q_out.dtype, 4)
         _req(block_table, "block_table", torch.int32, 2)
         if tuple(k_pages.shape[1:]) != (nkv, page_size, d) or k_pages.shape != v_pages.shape:
             raise KernelError(f"qk_norm_rope_kv: pages {tuple(k_pages.shape)} do not match (pages, {nkv}, {page_size}, {d})")
         num_pages, max_blocks = k_pages.shape[0], block_table.shape[1]
     rc = library().qi_qk_norm_rope_kv(
-        _ptr(qkv), _ptr(q_out), _code(qkv), _ptr(q_gain), _ptr(k_gain), C.c_float(eps), _ptr(cos),
+        _ptr(qkv), splits, _ptr(q_out), _code(q_out), _ptr(q_gain), _ptr(k_gain), C.c_float(eps), _ptr(cos),
         _ptr(sin), rotary_dim, table_positions, _ptr(positions), _ptr(token_req), _ptr(block_table),
         max_blocks, page_size, num_pages, _ptr(k_pages), _ptr(v_pages), n, nq, nkv, d, _ptr(status),
         _stream())
@@ -282,9 +290,9 @@ def attention_mma_supported(nq: int, nkv: int, d: int) -> bool:
 QUERY_TILE = 128   # query rows per entry of a batch's tile lists
 
 
-def attention_tma_supported(nq: int, nkv: int, d: int, page_size: int) -> bool:
+def attention_tma_supported(nq: int, nkv: int, d: int, page_size: int, max_blocks: int = 1) -> bool:
     """Whether the TMA-fed attention kernels take this geometry (bfloat16 only)."""
-    return bool(library().qi_attention_tma_supported(nq, nkv, d, page_size))
+    return bool(library().qi_attention_tma_supported(nq, nkv, d, page_size, max_blocks))
 
 
 def attention_prefill(q, out, k_pages, v_pages, block_table, q_start, start_pos, tile_req, tile_q0,
@@ -307,7 +315,7 @@ def attention_prefill(q, out, k_pages, v_pages, block_table, q_start, start_pos,
     if tile_req.numel() != tile_q0.numel():
         raise KernelError("attention_prefill: tile lists differ in length")
     if use_tma is None:
-        use_tma = attention_tma_supported(nq, nkv, d, k_pages.shape[2])
+        use_tma = attention_tma_supported(nq, nkv, d, k_pages.shape[2], block_table.shape[1])
     if use_tma:
         rc = library().qi_attention_prefill_tma(
             _ptr(q), _ptr(out), _ptr(k_pages), _ptr(v_pages), _ptr(block_table), block_table.shape[1],
@@ -356,7 +364,7 @@ def attention_decode(q, out, k_pages, v_pages, block_table, kv_len, q_start, nq,
     ws_o = workspace
     ws_ml = workspace[batch * nq * n_splits * d:]
     if use_tma is None:
-        use_tma = attention_tma_supported(nq, nkv, d, k_pages.shape[2])
+        use_tma = attention_tma_supported(nq, nkv, d, k_pages.shape[2], block_table.shape[1])
     fn = library().qi_attention_decode_tma if use_tma else library().qi_attention_decode
     rc = fn(
         _ptr(q), _ptr(out), _ptr(k_pages), _ptr(v_pages), _ptr(block_table), block_table.shape[1],

@@ -74,10 +74,11 @@ class Attention(Part):
     def forward(self, x, batch, cache):
         rt = self.runtime
         n = x.shape[0]
-        qkv = self.qkv(x)
+        pos = self.position
+        # K-split partial sums of the projection are added by the next kernel where it can take them
+        qkv = self.qkv(x, keep_partials=self.d % 4 == 0 and (pos is None or pos.rotary_dim == self.d))
         q = torch.empty((n, self.nq * self.d), dtype=x.dtype, device=x.device)
         table = batch.block_tables[cache.group]
-        pos = self.position
         kernels.qk_norm_rope_kv(
             qkv, q, self.q_gain, self.k_gain, self.spec.qk_norm_eps,
             pos.cos if pos else None, pos.sin if pos else None, pos.rotary_dim if pos else 0,
