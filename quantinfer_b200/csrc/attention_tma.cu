@@ -15,6 +15,7 @@
 // No load uses cluster multicast. Every mbarrier wait is bounded; when a bound
 // runs out the kernel sets kStatusWaitTimeout and leaves.
 #include "attention_frag.cuh"
+#include "attention_noalloc.h"
 
 #include <cuda.h>
 
@@ -525,4 +526,56 @@ extern "C" int qi_attention_decode_tma(const void* q, void* out, const void* k_p
                                  q_start, batch, nq, nkv, scale, window, chunk, n_splits, ws_o, ws_ml, status, stream);
     return launch_decode<128>(q, out, k_pages, v_pages, block_table, max_blocks, page_size, num_pages, kv_len,
                               q_start, batch, nq, nkv, scale, window, chunk, n_splits, ws_o, ws_ml, status, stream);
+}
+
+// ------------------------------------------------------------------ the entry point that allocates nothing
+
+namespace {
+
+// Partial results of qi_attention_decode_tma_static. In host code this name is only a
+// stand-in for the symbol, not a device address: the address comes from
+// cudaGetSymbolAddress below.
+static __device__ __align__(256) unsigned char g_decode_scratch[QI_DECODE_STATIC_SCRATCH_BYTES];
+
+constexpr int kMaxDevices = 64;
+float* g_decode_scratch_ptr[kMaxDevices] = {};
+
+// The array's address on the current device, looked up once per device.
+int decode_scratch(float** ptr) {
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return qi::fail("attention_decode_tma_static: cudaGetDevice failed: %s", cudaGetErrorString(e));
+    if (dev < 0 || dev >= kMaxDevices) return qi::fail("attention_decode_tma_static: device index %d is not supported", dev);
+    if (!g_decode_scratch_ptr[dev]) {
+        void* p = nullptr;
+        e = cudaGetSymbolAddress(&p, g_decode_scratch);
+        if (e != cudaSuccess || !p)
+            return qi::fail("attention_decode_tma_static: cudaGetSymbolAddress failed on device %d: %s", dev, cudaGetErrorString(e));
+        g_decode_scratch_ptr[dev] = static_cast<float*>(p);
+    }
+    *ptr = g_decode_scratch_ptr[dev];
+    return 0;
+}
+
+}  // namespace
+
+extern "C" unsigned long long qi_attention_decode_static_scratch_bytes(void) { return QI_DECODE_STATIC_SCRATCH_BYTES; }
+
+extern "C" int qi_attention_decode_tma_static(const void* q, void* out, const void* k_pages, const void* v_pages,
+                                              const int* block_table, int max_blocks, int page_size, int num_pages,
+                                              const int* kv_len, const int* q_start, int batch, int nq, int nkv, int d,
+                                              float scale, int window, int chunk, int n_splits, int* status,
+                                              cudaStream_t stream) {
+    QI_REQUIRE(batch >= 0 && nq > 0 && d > 0 && n_splits > 0, "attention_decode_tma_static: bad sizes");
+    const unsigned long long need = 4ull * (unsigned long long)batch * nq * n_splits * (unsigned long long)(d + 2);
+    QI_REQUIRE(need <= QI_DECODE_STATIC_SCRATCH_BYTES,
+               "attention_decode_tma_static: %d requests x %d heads x %d key ranges of size %d need %llu bytes of scratch, "
+               "the static array holds %u; use fewer key ranges, a smaller batch, or qi_attention_decode_tma with a workspace",
+               batch, nq, n_splits, d, need, QI_DECODE_STATIC_SCRATCH_BYTES);
+    float* scratch = nullptr;
+    if (decode_scratch(&scratch)) return 1;
+    float* ws_o = scratch;
+    float* ws_ml = scratch + (size_t)batch * nq * n_splits * d;
+    return qi_attention_decode_tma(q, out, k_pages, v_pages, block_table, max_blocks, page_size, num_pages, kv_len,
+                                   q_start, batch, nq, nkv, d, scale, window, chunk, n_splits, ws_o, ws_ml, status, stream);
 }
