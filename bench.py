@@ -179,7 +179,7 @@ def main() -> int:
         args.skip_points = True
     # ---- prefill: one 2,048-token prompt in one step ---------------------------
     times = []
-    for i in range(0 if args.only == "decode" else 2 + 3):
+    for i in range(0 if args.only == "decode" else 2 + 5):
         engine.open("p")
         toks = prompt()
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
