@@ -42,7 +42,7 @@ class Model:
         self._engine = Engine.from_folder(
             path, dtype=dtype, device=device, page_size=page_size or DEFAULT_PAGE_SIZE,
             max_tokens=cache_tokens, max_requests=max_requests, use_graphs=use_graphs)
-        self._sampler = Sampler(self._engine.device, self._engine.runtime.status)
+        self._sampler = Sampler.for_engine(self._engine)
         self._max_batch_tokens = max_batch_tokens
         self._chunk_size = chunk_size
         self._open = True
@@ -53,7 +53,7 @@ class Model:
         self = cls.__new__(cls)
         self._lock = RLock()
         self._engine = engine
-        self._sampler = Sampler(engine.device, engine.runtime.status)
+        self._sampler = Sampler.for_engine(engine)
         self._max_batch_tokens = max_batch_tokens
         self._chunk_size = chunk_size
         self._open = True
@@ -143,7 +143,9 @@ class Model:
             self._require_open()
             eng = self._engine
             prompts = [[_unsigned(t, EOS_AUTO, "token ID") for t in p] for p in prompts]
-            sched = Scheduler(eng.cache, eng.step, self._sampler.sample, vocab_size=eng.spec.vocab_size,
+            # the sampler reads the step's status word together with the tokens: one wait per step
+            sched = Scheduler(eng.cache, lambda entries: eng.step(entries, check_status=False), self._sampler.sample,
+                              vocab_size=eng.spec.vocab_size,
                               max_sequences=eng.cache.max_requests,
                               max_tokens=max(self._max_batch_tokens, eng.cache.max_requests),
                               chunk_size=self._chunk_size)

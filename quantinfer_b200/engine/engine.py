@@ -86,6 +86,7 @@ class Engine:
         self._graphs = {}
         self._graph_pool = None
         self.h2d_bytes = 0
+        self.h2d_bytes_max = 0
 
     # ---- construction ------------------------------------------------------
 
@@ -146,6 +147,7 @@ class Engine:
             self._staging_event[turn].synchronize()  # the copy that last used this buffer is done
         host[:buf.size].numpy()[:] = buf
         self.h2d_bytes = int(buf.size) * 4
+        self.h2d_bytes_max = max(self.h2d_bytes_max, self.h2d_bytes)
         return host[:buf.size], self._staging_event[turn]
 
     def _pack(self, entries: Sequence[StepEntry]):
@@ -281,9 +283,4 @@ class Engine:
         code = int(self.runtime.status.item())
         if code:
             self.runtime.status.zero_()
-            what = [name for bit, name in ((kernels.STATUS_BAD_TOKEN, "a token id outside the vocabulary"),
-                                           (kernels.STATUS_BAD_PAGE, "a position without a cache page"),
-                                           (kernels.STATUS_NON_FINITE, "non-finite logits"),
-                                           (kernels.STATUS_WAIT_TIMEOUT, "a bounded wait inside a kernel ran out"))
-                    if code & bit]
-            raise QuantInferError("the step failed on the device: " + "; ".join(what))
+            raise QuantInferError("the step failed on the device: " + "; ".join(kernels.status_names(code)))

@@ -26,6 +26,14 @@ STATUS_WAIT_TIMEOUT = 8
 
 ABI_VERSION = 4
 
+
+def status_names(code: int) -> list:
+    """What the bits of a device status word mean."""
+    return [name for bit, name in ((STATUS_BAD_TOKEN, "a token id outside the vocabulary"),
+                                   (STATUS_BAD_PAGE, "a position without a cache page"),
+                                   (STATUS_NON_FINITE, "non-finite logits"),
+                                   (STATUS_WAIT_TIMEOUT, "a bounded wait inside a kernel ran out")) if code & bit]
+
 _lib = None
 _lib_lock = threading.Lock()
 

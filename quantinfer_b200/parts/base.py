@@ -43,13 +43,15 @@ class Runtime:
     device: torch.device
     status: torch.Tensor = None
     shared: dict = field(default_factory=dict)
+    io: torch.Tensor = None      # int32: [0] is the status word, the rest takes sampled tokens (one D2H reads both)
 
     def __post_init__(self):
         if self.dtype not in (torch.float32, torch.bfloat16):
             raise ConfigError(f"the activation type must be float32 or bfloat16, got {self.dtype}")
         self.device = torch.device(self.device)
         if self.status is None:
-            self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
+            self.io = torch.zeros(1 + 8192, dtype=torch.int32, device=self.device)
+            self.status = self.io[0:1]
 
 
 def register_part(category: str, kind: str, cls: type) -> None:

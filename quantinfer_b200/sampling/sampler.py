@@ -16,13 +16,24 @@ import numpy as np
 import torch
 
 from .. import kernels
+from ..errors import QuantInferError
 from .params import GenerationConfig
 
 
 class Sampler:
-    def __init__(self, device, status: torch.Tensor | None = None):
+    def __init__(self, device, status: torch.Tensor | None = None, io: torch.Tensor | None = None):
+        """`io` (int32, [0] the status word, then room for tokens) lets `sample` read the
+        tokens and the status of the step that produced the logits in one transfer."""
         self.device = torch.device(device)
-        self.status = status if status is not None else torch.zeros(1, dtype=torch.int32, device=self.device)
+        self.io = io
+        if io is not None:
+            self.status = io[0:1]
+        else:
+            self.status = status if status is not None else torch.zeros(1, dtype=torch.int32, device=self.device)
+
+    @classmethod
+    def for_engine(cls, engine) -> "Sampler":
+        return cls(engine.device, io=engine.runtime.io)
 
     def sample(self, logits: torch.Tensor, rows: Sequence[tuple]) -> list:
         """`rows[i] = (GenerationConfig, emitted)` for row i of `logits`. Returns token ids."""
@@ -31,7 +42,18 @@ class Sampler:
             raise ValueError(f"{n} rows of logits for {len(rows)} requests")
         if n == 0:
             return []
-        return self.sample_async(logits, rows).cpu().tolist()
+        params = self.device_params(rows)
+        if self.io is None or n + 1 > self.io.numel():
+            return self.sample_with(logits, params).cpu().tolist()
+        out = self.io[1:1 + n]
+        kernels.sample(logits, params["temperature"], params["top_k"], params["top_p"], params["seed"],
+                       params["counter"], out, self.status)
+        host = self.io[:1 + n].cpu().tolist()          # waits for the step; status and tokens together
+        if host[0]:
+            self.status.zero_()
+            raise QuantInferError(f"the step failed on the device (status {host[0]}: "
+                                  + "; ".join(kernels.status_names(host[0])) + ")")
+        return host[1:]
 
     def sample_async(self, logits: torch.Tensor, rows: Sequence[tuple]) -> torch.Tensor:
         """As `sample`, but returns the device tensor of tokens without waiting."""
