@@ -1,0 +1,504 @@
+// Causal paged GQA flash attention for prefill on the 5th-generation tensor cores
+// (tcgen05.mma with accumulators in tensor memory), head size 128, bfloat16.
+//
+// One CTA takes 128 query rows of one request and one query head and walks the keys in
+// tiles of 128. Per tile two products run on the tensor core:
+//     S = Q . K^T      (128 x 128, K = head size)     -> tensor memory, 32-bit
+//     O_j = P . V      (128 x 128, K = 128 keys)      -> tensor memory, 32-bit
+// and between them the softmax threads (one per query row) read their row of S from
+// tensor memory, update the running maximum and sum, write the weights P as bfloat16 into
+// shared memory in the layout the tensor core reads (rows of 128 bytes, 128-byte swizzle),
+// and add the finished O_{j-1} to the row's accumulator, which lives in registers:
+//     o = o * 2^(m_{j-1} - m_j) + O_j
+// so nothing in tensor memory ever has to be rescaled. S and O_j are double-buffered
+// (4 x 128 columns = all of tensor memory), so the tensor core computes S of the next tile
+// while the softmax of this one runs.
+//
+// Roles (192 threads): warp 0 issues TMA loads of Q and of the K/V tiles (page pieces
+// through the block table, as in attention_tma.cu); warp 1 allocates tensor memory and
+// issues the MMAs; warps 2-5 are the softmax threads. K is read as a K-major operand, V as
+// an MN-major operand (its rows are keys, the product contracts over keys), P and Q as
+// K-major operands.
+//
+// Formulas: as attention_mma.cu (reference: crates/quantinfer-runtime/src/attention.rs:105-135).
+// No load uses cluster multicast. Every mbarrier wait is bounded; on expiry the kernel sets
+// kStatusWaitTimeout and its roles leave their loops, tensor memory is freed and it returns.
+#include "common.cuh"
+#include "attention_frag.cuh"
+
+#include <cuda.h>
+#include <math.h>
+
+namespace {
+
+using qi_attn::smem_u32;
+
+constexpr int BM = 128;          // query rows per CTA
+constexpr int BN = 128;          // keys per tile
+constexpr int D = 128;           // head size
+constexpr int kStages = 2;       // K/V ring
+constexpr int kThreads = 192;
+constexpr int kHalfBytes = 128 * 128;             // 128 rows x 128 bytes: one 64-column half of a tile
+constexpr int kTileBytes = 2 * kHalfBytes;        // Q, K, V or P tile: 32 KB
+constexpr int kMaxTableEntries = 2048;
+constexpr uint32_t kSpinLimit = 1u << 24;
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+    for (uint32_t i = 0; i < kSpinLimit; ++i) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((i & 1023u) == 1023u && *abort_flag) return false;
+    }
+    return false;
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t cols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() {
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t addr, uint32_t cols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %6, %7, %8}, p;\n\t}"
+        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(0), "r"(0), "r"(0), "r"(0) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t addr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(addr));
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// K-major operand tile (rows of 128 bytes, 128-byte swizzle): see gemm_tcgen05.cu.
+__device__ __forceinline__ uint64_t desc_k_major(uint32_t smem_addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr & 0x3FFFFu) >> 4);
+    d |= (uint64_t)1 << 16;                      // leading byte offset: unused for swizzled K-major
+    d |= (uint64_t)(1024 >> 4) << 32;            // stride byte offset: 8 rows x 128 bytes
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)2 << 61;                      // 128-byte swizzle
+    return d;
+}
+// MN-major operand (V: rows are keys = the contraction dimension, 64 head-dim elements per
+// 128-byte row, two such halves side by side): leading byte offset = distance between the
+// halves, stride byte offset = distance between groups of 8 keys.
+__device__ __forceinline__ uint64_t desc_mn_major(uint32_t smem_addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr & 0x3FFFFu) >> 4);
+    d |= (uint64_t)(kHalfBytes >> 4) << 16;
+    d |= (uint64_t)(1024 >> 4) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)2 << 61;
+    return d;
+}
+// kind::f16 instruction descriptor: D = F32, A = B = BF16, M = 128, N = 128; bit 16 = B is MN-major.
+constexpr uint32_t idesc(bool b_mn_major) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | (b_mn_major ? (1u << 16) : 0u) | ((uint32_t)(BN >> 3) << 17) |
+           ((uint32_t)(BM >> 4) << 24);
+}
+
+struct Bars {   // byte offsets of the mbarriers from the barrier base
+    static constexpr int q_full = 0;
+    static constexpr int kv_full = 8;                     // [kStages]
+    static constexpr int kv_empty = kv_full + 8 * kStages; // [kStages]
+    static constexpr int s_full = kv_empty + 8 * kStages;  // [2]
+    static constexpr int s_free = s_full + 16;             // [2]
+    static constexpr int o_full = s_free + 16;             // [2]
+    static constexpr int o_free = o_full + 16;             // [2]
+    static constexpr int p_ready = o_free + 16;            // [1]
+    static constexpr int p_free = p_ready + 8;             // [1]
+    static constexpr int total = p_free + 8;
+};
+
+constexpr int kSmemBytes = kTileBytes /*Q*/ + kStages * 2 * kTileBytes /*K,V*/ + kTileBytes /*P*/ + 256 /*barriers*/ +
+                           4 * kMaxTableEntries + 1024 /*alignment*/;
+
+__global__ void __launch_bounds__(kThreads, 1)
+attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                                 const __grid_constant__ CUtensorMap map_v, qi::bf16* __restrict__ out,
+                                 const int* __restrict__ block_table, int max_blocks, int page_size, int box_rows,
+                                 int num_pages, const int* __restrict__ q_start, const int* __restrict__ start_pos,
+                                 const int* __restrict__ tile_req, const int* __restrict__ tile_q0, int nq, int nkv,
+                                 float scale_log2e, int window, int* __restrict__ status) {
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t* aligned = smem_raw + (base - smem_u32(smem_raw));
+    const uint32_t q_s = base;
+    const uint32_t kv_s = q_s + kTileBytes;                       // stage s: K at kv_s + s * 2 tiles, V one tile further
+    const uint32_t p_s = kv_s + kStages * 2 * kTileBytes;
+    uint8_t* p_tile = aligned + kTileBytes + kStages * 2 * kTileBytes;
+    const uint32_t bars = p_s + kTileBytes;
+    uint8_t* bar_mem = aligned + 2 * kTileBytes + kStages * 2 * kTileBytes;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_mem + Bars::total);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(bar_mem + Bars::total + 4);
+    int* s_table = reinterpret_cast<int*>(bar_mem + 256);
+
+    qi::pdl_enter();
+    const int tile = blockIdx.x, h = blockIdx.y;
+    const int hk = h / (nq / nkv);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int r = tile_req[tile], q0 = tile_q0[tile];
+    const int rows_valid = min(BM, q_start[r + 1] - q0);
+    const int pos0 = start_pos[r] + (q0 - q_start[r]);
+    const int* table = block_table + (size_t)r * max_blocks;
+    const int hi = pos0 + rows_valid;                                            // keys < hi
+    const int lo = (window > 0 && pos0 - window + 1 > 0) ? pos0 - window + 1 : 0;
+    const int t_begin = (lo / BN) * BN;
+    const int n_tiles = (hi - t_begin + BN - 1) / BN;
+    const int blk0 = t_begin / page_size;
+    const int n_blk = min(min((t_begin + n_tiles * BN + page_size - 1) / page_size, max_blocks) - blk0, kMaxTableEntries);
+    for (int i = threadIdx.x; i < n_blk; i += blockDim.x) s_table[i] = table[blk0 + i];
+
+    if (threadIdx.x == 0) {
+        mbar_init(bars + Bars::q_full, 1);
+        for (int s = 0; s < kStages; ++s) {
+            mbar_init(bars + Bars::kv_full + 8 * s, 1);
+            mbar_init(bars + Bars::kv_empty + 8 * s, 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(bars + Bars::s_full + 8 * b, 1);
+            mbar_init(bars + Bars::s_free + 8 * b, 4);    // one arrival per softmax warp
+            mbar_init(bars + Bars::o_full + 8 * b, 1);
+            mbar_init(bars + Bars::o_free + 8 * b, 4);
+        }
+        mbar_init(bars + Bars::p_ready, 4);
+        mbar_init(bars + Bars::p_free, 1);
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        tmem_alloc(smem_u32(tmem_slot), 512);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    const uint32_t tmem_s = tmem_base;            // S buffers: columns 0..127, 128..255
+    const uint32_t tmem_o = tmem_base + 256;      // O_j buffers: columns 256..383, 384..511
+
+    auto give_up = [&]() {
+        if (!*abort_flag) {
+            *abort_flag = 1;
+            if (status) atomicOr(status, qi::kStatusWaitTimeout);
+        }
+    };
+
+    if (warp == 0) {
+        // ---------------- TMA producer ----------------
+        if (lane == 0) {
+            mbar_expect_tx(bars + Bars::q_full, kTileBytes);
+            tma_load_2d(q_s, &map_q, bars + Bars::q_full, h * D, q0);
+            tma_load_2d(q_s + kHalfBytes, &map_q, bars + Bars::q_full, h * D + 64, q0);
+            int issued = 0;
+            for (int j = 0; j < n_tiles; ++j) {
+                const int s = j % kStages;
+                if (!mbar_wait(bars + Bars::kv_empty + 8 * s, (((uint32_t)j / kStages) & 1u) ^ 1u, abort_flag)) {
+                    give_up();
+                    break;
+                }
+                const uint32_t full = bars + Bars::kv_full + 8 * s;
+                const uint32_t k_dst = kv_s + s * 2 * kTileBytes, v_dst = k_dst + kTileBytes;
+                mbar_expect_tx(full, 2 * kTileBytes);
+                const int t0 = t_begin + j * BN;
+                for (int r0 = 0; r0 < BN; r0 += box_rows) {
+                    const int key = t0 + r0;
+                    const int blk = key / page_size - blk0;
+                    int page = blk < n_blk ? s_table[blk] : -1;
+                    if (page < 0 || page >= num_pages) {
+                        if (key < hi && key + box_rows > lo && status) atomicOr(status, qi::kStatusBadPage);
+                        page = 0;
+                    }
+                    const int row = (page * nkv + hk) * page_size + (key % page_size);
+                    tma_load_2d(k_dst + r0 * 128, &map_k, full, 0, row);
+                    tma_load_2d(k_dst + kHalfBytes + r0 * 128, &map_k, full, 64, row);
+                    tma_load_2d(v_dst + r0 * 128, &map_v, full, 0, row);
+                    tma_load_2d(v_dst + kHalfBytes + r0 * 128, &map_v, full, 64, row);
+                }
+                issued = j + 1;
+            }
+            if (*abort_flag) {   // copies in flight write into this CTA's shared memory: wait (bounded) for them
+                for (int j = max(issued - kStages, 0); j < issued; ++j)
+                    for (uint32_t t = 0; t < (1u << 20); ++t)
+                        if (mbar_try_wait(bars + Bars::kv_full + 8 * (j % kStages), ((uint32_t)j / kStages) & 1u)) break;
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer ----------------
+        if (lane == 0) {
+            constexpr uint32_t idesc_qk = idesc(false), idesc_pv = idesc(true);
+            bool ok = mbar_wait(bars + Bars::q_full, 0, abort_flag);
+            if (!ok) give_up();
+            auto issue_qk = [&](int j) -> bool {
+                const int s = j % kStages, b = j & 1;
+                if (!mbar_wait(bars + Bars::kv_full + 8 * s, ((uint32_t)j / kStages) & 1u, abort_flag)) return false;
+                if (!mbar_wait(bars + Bars::s_free + 8 * b, (((uint32_t)j >> 1) & 1u) ^ 1u, abort_flag)) return false;
+                tc_fence_after();
+                const uint32_t k_addr = kv_s + s * 2 * kTileBytes;
+#pragma unroll
+                for (int ks = 0; ks < D / 16; ++ks) {
+                    const uint64_t adesc = desc_k_major(q_s + (ks >> 2) * kHalfBytes) + 2u * (ks & 3);
+                    const uint64_t bdesc = desc_k_major(k_addr + (ks >> 2) * kHalfBytes) + 2u * (ks & 3);
+                    umma_bf16(tmem_s + b * BN, adesc, bdesc, idesc_qk, ks > 0 ? 1u : 0u);
+                }
+                umma_commit(bars + Bars::s_full + 8 * b);
+                return true;
+            };
+            if (ok && n_tiles > 0) ok = issue_qk(0);
+            for (int j = 0; j < n_tiles && ok; ++j) {
+                if (j + 1 < n_tiles) ok = issue_qk(j + 1);       // the tensor core works on S of the next tile
+                if (!ok) break;                                  // while the softmax of this one runs
+                const int s = j % kStages, b = j & 1;
+                if (!mbar_wait(bars + Bars::p_ready, (uint32_t)j & 1u, abort_flag) ||
+                    !mbar_wait(bars + Bars::o_free + 8 * b, (((uint32_t)j >> 1) & 1u) ^ 1u, abort_flag)) {
+                    ok = false;
+                    break;
+                }
+                tc_fence_after();
+                const uint32_t v_addr = kv_s + s * 2 * kTileBytes + kTileBytes;
+#pragma unroll
+                for (int kk = 0; kk < BN / 16; ++kk) {
+                    const uint64_t adesc = desc_k_major(p_s + (kk >> 2) * kHalfBytes) + 2u * (kk & 3);
+                    const uint64_t bdesc = desc_mn_major(v_addr + kk * 16 * 128);
+                    umma_bf16(tmem_o + b * D, adesc, bdesc, idesc_pv, kk > 0 ? 1u : 0u);
+                }
+                umma_commit(bars + Bars::o_full + 8 * b);          // O_j is complete
+                umma_commit(bars + Bars::kv_empty + 8 * s);        // K_j and V_j have been read
+                umma_commit(bars + Bars::p_free);                  // P may be overwritten
+            }
+            if (!ok) give_up();
+        }
+    } else {
+        // ---------------- softmax threads (warps 2..5), one query row each ----------------
+        const int quarter = warp & 3;
+        const int row = quarter * 32 + lane;
+        const int pos = pos0 + row;
+        const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
+        float m = -INFINITY, l = 0.f, corr_prev = 1.f;
+        float o[D];
+#pragma unroll
+        for (int i = 0; i < D; ++i) o[i] = 0.f;
+        bool ok = true;
+
+        // adds the finished O_j (tile j) to the row's accumulator, scaled to the current maximum
+        auto drain = [&](int j, float corr) -> bool {
+            const int b = j & 1;
+            if (!mbar_wait(bars + Bars::o_full + 8 * b, ((uint32_t)j >> 1) & 1u, abort_flag)) return false;
+            tc_fence_after();
+#pragma unroll
+            for (int c0 = 0; c0 < D; c0 += 32) {
+                uint32_t v[32];
+                tmem_ld32(tmem_o + lane_addr + b * D + c0, v);
+                tmem_ld_wait();
+#pragma unroll
+                for (int i = 0; i < 32; ++i) o[c0 + i] = fmaf(o[c0 + i], corr, __uint_as_float(v[i]));
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bars + Bars::o_free + 8 * b);
+            return true;
+        };
+
+        for (int j = 0; j < n_tiles && ok; ++j) {
+            const int b = j & 1;
+            const int t0 = t_begin + j * BN;
+            if (!mbar_wait(bars + Bars::s_full + 8 * b, ((uint32_t)j >> 1) & 1u, abort_flag)) { ok = false; break; }
+            tc_fence_after();
+            // keys this row may see in this tile: columns [c_lo, c_hi)
+            int c_hi = min(min(pos, hi - 1) - t0 + 1, BN);
+            int c_lo = max(lo, window > 0 ? pos - window + 1 : 0) - t0;
+            if (c_lo < 0) c_lo = 0;
+            if (c_hi < 0) c_hi = 0;
+            // pass 1: the row's maximum
+            float mx = -INFINITY;
+#pragma unroll 1
+            for (int c0 = 0; c0 < BN; c0 += 32) {
+                uint32_t v[32];
+                tmem_ld32(tmem_s + lane_addr + b * BN + c0, v);
+                tmem_ld_wait();
+                if (c0 >= c_lo && c0 + 32 <= c_hi) {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(v[i]));
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i)
+                        if (c0 + i >= c_lo && c0 + i < c_hi) mx = fmaxf(mx, __uint_as_float(v[i]));
+                }
+            }
+            const float m_new = fmaxf(m, mx * scale_log2e);
+            const float ms = (m_new == -INFINITY) ? 0.f : m_new;
+            const float corr = exp2f(m - ms);              // m = -inf gives 0
+            m = m_new;
+            // the previous tile's P must have been consumed before P is overwritten
+            if (j > 0 && !mbar_wait(bars + Bars::p_free, ((uint32_t)(j - 1)) & 1u, abort_flag)) { ok = false; break; }
+            // pass 2: weights, their sum, and P in the tensor core's layout
+            float sum = 0.f;
+#pragma unroll 1
+            for (int c0 = 0; c0 < BN; c0 += 32) {
+                uint32_t v[32];
+                tmem_ld32(tmem_s + lane_addr + b * BN + c0, v);
+                tmem_ld_wait();
+                float p[32];
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                    const bool valid = c0 + i >= c_lo && c0 + i < c_hi;
+                    p[i] = valid ? exp2f(fmaf(__uint_as_float(v[i]), scale_log2e, -ms)) : 0.f;
+                    sum += p[i];
+                }
+                // columns c0..c0+31 = four 16-byte chunks of this row in half (c0 / 64)
+                uint8_t* prow = p_tile + (c0 >> 6) * kHalfBytes + row * 128;
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    const int chunk = ((c0 & 63) >> 3) + q;
+                    uint4 w;
+                    w.x = qi_attn::pack_bf16(p[8 * q + 0], p[8 * q + 1]);
+                    w.y = qi_attn::pack_bf16(p[8 * q + 2], p[8 * q + 3]);
+                    w.z = qi_attn::pack_bf16(p[8 * q + 4], p[8 * q + 5]);
+                    w.w = qi_attn::pack_bf16(p[8 * q + 6], p[8 * q + 7]);
+                    *reinterpret_cast<uint4*>(prow + ((chunk ^ (row & 7)) << 4)) = w;
+                }
+            }
+            l = l * corr + sum;
+            // S has been read and P written: make P visible to the tensor core, then signal
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) {
+                mbar_arrive(bars + Bars::s_free + 8 * b);
+                mbar_arrive(bars + Bars::p_ready);
+            }
+            // while the tensor core computes O_j, fold O_{j-1} into the accumulator
+            if (j > 0) ok = drain(j - 1, corr_prev);
+            corr_prev = corr;
+        }
+        if (ok && n_tiles > 0) ok = drain(n_tiles - 1, corr_prev);
+        if (!ok) {
+            if (lane == 0) give_up();
+        } else if (row < rows_valid) {
+            const float inv = l > 0.f ? 1.f / l : 0.f;
+            qi::bf16* orow = out + ((size_t)(q0 + row) * nq + h) * D;
+#pragma unroll
+            for (int c0 = 0; c0 < D; c0 += 8) {
+                uint4 w;
+                w.x = qi_attn::pack_bf16(o[c0 + 0] * inv, o[c0 + 1] * inv);
+                w.y = qi_attn::pack_bf16(o[c0 + 2] * inv, o[c0 + 3] * inv);
+                w.z = qi_attn::pack_bf16(o[c0 + 4] * inv, o[c0 + 5] * inv);
+                w.w = qi_attn::pack_bf16(o[c0 + 6] * inv, o[c0 + 7] * inv);
+                *reinterpret_cast<uint4*>(orow + c0) = w;
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) tmem_dealloc(tmem_base, 512);
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encode() {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+    }
+    return fn;
+}
+
+int make_map(CUtensorMap* map, const void* ptr, long long rows, int cols, int box_rows) {
+    EncodeTiledFn enc = get_encode();
+    if (!enc) return qi::fail("attention_prefill_tcgen05: cuTensorMapEncodeTiled is not available from the driver");
+    cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)cols * 2};
+    cuuint32_t box[2] = {64u, (cuuint32_t)box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return qi::fail("attention_prefill_tcgen05: cuTensorMapEncodeTiled failed with code %d", (int)r);
+    return 0;
+}
+
+bool pow2(int v) { return v > 0 && (v & (v - 1)) == 0; }
+
+}  // namespace
+
+// 1 if the tcgen05 prefill attention takes this geometry.
+extern "C" int qi_attention_prefill_tcgen05_supported(int nq, int nkv, int d, int page_size, int max_blocks) {
+    return d == D && nkv > 0 && nq % nkv == 0 && pow2(page_size) && page_size >= 8 && max_blocks > 0 &&
+           max_blocks <= kMaxTableEntries;
+}
+
+// Same arguments as qi_attention_prefill_tma; the tile lists are cut to 128 query rows.
+extern "C" int qi_attention_prefill_tcgen05(const void* q, void* out, const void* k_pages, const void* v_pages,
+                                            const int* block_table, int max_blocks, int page_size, int num_pages,
+                                            const int* q_start, const int* start_pos, const int* tile_req,
+                                            const int* tile_q0, int n_tiles, int n_tokens, int nq, int nkv, int d,
+                                            float scale, int window, int* status, cudaStream_t stream) {
+    QI_REQUIRE(qi_attention_prefill_tcgen05_supported(nq, nkv, d, page_size, max_blocks),
+               "attention_prefill_tcgen05: heads %d/%d of size %d with %d pages of %d per request are not covered", nq, nkv,
+               d, max_blocks, page_size);
+    QI_REQUIRE(num_pages > 0 && window >= 0 && n_tokens > 0, "attention_prefill_tcgen05: bad sizes");
+    QI_REQUIRE(((uintptr_t)q & 15) == 0 && ((uintptr_t)k_pages & 15) == 0 && ((uintptr_t)v_pages & 15) == 0,
+               "attention_prefill_tcgen05: tensors must be 16-byte aligned");
+    QI_REQUIRE((long long)num_pages * nkv * page_size < 2147483647LL, "attention_prefill_tcgen05: the page pool has too many rows");
+    QI_REQUIRE(n_tiles >= 0 && nq <= 65535, "attention_prefill_tcgen05: grid too large");
+    if (n_tiles == 0) return 0;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(attention_prefill_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+        if (e != cudaSuccess) return qi::fail("attention_prefill_tcgen05: cannot reserve %d bytes of shared memory: %s", kSmemBytes, cudaGetErrorString(e));
+        configured = true;
+    }
+    const int box_rows = page_size < BN ? page_size : BN;
+    CUtensorMap mq, mk, mv;
+    if (make_map(&mq, q, n_tokens, nq * D, BM)) return 1;
+    if (make_map(&mk, k_pages, (long long)num_pages * nkv * page_size, D, box_rows)) return 1;
+    if (make_map(&mv, v_pages, (long long)num_pages * nkv * page_size, D, box_rows)) return 1;
+    qi::launch(attention_prefill_tcgen05_kernel, dim3(n_tiles, nq), dim3(kThreads), kSmemBytes, stream, mq, mk, mv,
+               (qi::bf16*)out, block_table, max_blocks, page_size, box_rows, num_pages, q_start, start_pos, tile_req,
+               tile_q0, nq, nkv, scale * 1.4426950408889634f, window, status);
+    return qi::check_launch("attention_prefill_tcgen05");
+}

@@ -261,10 +261,10 @@ extern "C" int qi_qk_norm_rope_kv(const void* qkv, int qkv_splits, void* q_out, 
     QI_REQUIRE(grid.y <= 65535, "qk_norm_rope_kv: too many heads");
     if (!cos_t) rot = 0;
     QI_REQUIRE(qkv_splits >= 1, "qk_norm_rope_kv: qkv_splits must be >= 1");
-    // many tokens: one block per token walks all heads (cos/sin fetched once per token);
-    // few tokens (decode): a block per four heads, so that the heads run side by side
+    // many tokens: each warp takes two heads of its token (cos/sin fetched once for both);
+    // few tokens (decode): a warp per head, so that the heads run side by side
     const int vec_threads = 128;
-    const dim3 vec_grid(n_tokens, n_tokens >= 512 ? 1 : (heads + 3) / 4);
+    const dim3 vec_grid(n_tokens, n_tokens >= 512 ? (heads + 7) / 8 : (heads + 3) / 4);
     const bool vec = d % 4 == 0 && (rot == d || rot == 0) && ((uintptr_t)qkv & 7) == 0 && ((uintptr_t)q_out & 7) == 0 &&
                      ((uintptr_t)k_pages & 7) == 0 && ((uintptr_t)v_pages & 7) == 0;
     if (qkv_splits > 1) {

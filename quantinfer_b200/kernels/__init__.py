@@ -303,12 +303,25 @@ def attention_tma_supported(nq: int, nkv: int, d: int, page_size: int, max_block
     return bool(library().qi_attention_tma_supported(nq, nkv, d, page_size, max_blocks))
 
 
+def attention_prefill_tcgen05_supported(nq: int, nkv: int, d: int, page_size: int, max_blocks: int = 1) -> bool:
+    """Whether the tcgen05 prefill attention takes this geometry (bfloat16, head size 128)."""
+    return bool(library().qi_attention_prefill_tcgen05_supported(nq, nkv, d, page_size, max_blocks))
+
+
 def attention_prefill(q, out, k_pages, v_pages, block_table, q_start, start_pos, tile_req, tile_q0,
-                      nq, nkv, d, scale: float, window: int, status, use_tma: bool | None = None) -> None:
+                      nq, nkv, d, scale: float, window: int, status, use_tma: bool | None = None,
+                      impl: str | None = None) -> None:
     """Causal paged GQA flash attention (bfloat16, head size 64 or 128) for spans of any
     length. `tile_req[i]`, `tile_q0[i]`: request index and first flat token of the i-th
-    block of up to QUERY_TILE query rows. Keys and values come by TMA when the page size
-    allows it (a power of two >= 8), else by cp.async; `use_tma` forces the choice."""
+    block of up to QUERY_TILE query rows.
+
+    Three kernels: "tcgen05" (head size 128, page size a power of two >= 8: tcgen05.mma with
+    accumulators in tensor memory, TMA loads), "tma" (mma.sync with TMA loads, same page
+    sizes, head size 64 or 128) and "cpasync" (mma.sync, any page size). `impl` forces one;
+    the default is the first that takes the geometry. `use_tma` is the older switch between
+    the last two."""
+    if impl is None and use_tma is not None:
+        impl = "tma" if use_tma else "cpasync"
     _req(q, "q", torch.bfloat16, 2)
     _req(out, "out", torch.bfloat16, 2)
     _req(k_pages, "k_pages", torch.bfloat16, 4)
@@ -322,9 +335,23 @@ def attention_prefill(q, out, k_pages, v_pages, block_table, q_start, start_pos,
         raise KernelError(f"attention_prefill: pages {tuple(k_pages.shape)} do not match {nkv} kv heads of {d}")
     if tile_req.numel() != tile_q0.numel():
         raise KernelError("attention_prefill: tile lists differ in length")
-    if use_tma is None:
-        use_tma = attention_tma_supported(nq, nkv, d, k_pages.shape[2], block_table.shape[1])
-    if use_tma:
+    if impl is None:
+        if attention_prefill_tcgen05_supported(nq, nkv, d, k_pages.shape[2], block_table.shape[1]):
+            impl = "tcgen05"
+        elif attention_tma_supported(nq, nkv, d, k_pages.shape[2], block_table.shape[1]):
+            impl = "tma"
+        else:
+            impl = "cpasync"
+    if impl == "tcgen05":
+        rc = library().qi_attention_prefill_tcgen05(
+            _ptr(q), _ptr(out), _ptr(k_pages), _ptr(v_pages), _ptr(block_table), block_table.shape[1],
+            k_pages.shape[2], k_pages.shape[0], _ptr(q_start), _ptr(start_pos), _ptr(tile_req), _ptr(tile_q0),
+            tile_req.numel(), q.shape[0], nq, nkv, d, C.c_float(scale), int(window or 0), _ptr(status), _stream())
+        _check(rc, "attention_prefill_tcgen05")
+        return
+    if impl not in ("tma", "cpasync"):
+        raise KernelError(f"attention_prefill: unknown kernel {impl!r}")
+    if impl == "tma":
         rc = library().qi_attention_prefill_tma(
             _ptr(q), _ptr(out), _ptr(k_pages), _ptr(v_pages), _ptr(block_table), block_table.shape[1],
             k_pages.shape[2], k_pages.shape[0], _ptr(q_start), _ptr(start_pos), _ptr(tile_req), _ptr(tile_q0),
