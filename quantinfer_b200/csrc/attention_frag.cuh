@@ -27,6 +27,12 @@ __device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], 
         : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
         : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
+// 2^x on the special-function unit (about 2 ulp), for score differences <= 0.
+__device__ __forceinline__ float ex2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<uint32_t*>(&v);
@@ -121,7 +127,7 @@ __device__ __forceinline__ void softmax_tile(float (&s)[NT][4], float (&m)[2], f
     for (int r = 0; r < 2; ++r) {
         const float mn = fmaxf(m[r], mx[r] * c);           // c > 0; -inf stays -inf
         ms[r] = (mn == -INFINITY) ? 0.f : mn;               // a row with no key yet: every weight is 2^-inf = 0
-        corr[r] = exp2f(m[r] - ms[r]);                      // m = -inf gives 0
+        corr[r] = ex2(m[r] - ms[r]);                        // m = -inf gives 0
         m[r] = mn;
     }
     float sum[2] = {0.f, 0.f};
@@ -130,7 +136,7 @@ __device__ __forceinline__ void softmax_tile(float (&s)[NT][4], float (&m)[2], f
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
             const int r = e >> 1;
-            const float p = exp2f(fmaf(s[j][e], c, -ms[r]));
+            const float p = ex2(fmaf(s[j][e], c, -ms[r]));
             s[j][e] = p;
             sum[r] += p;
         }

@@ -2,23 +2,28 @@
 // (tcgen05.mma with accumulators in tensor memory), head size 128, bfloat16.
 //
 // One CTA takes 128 query rows of one request and one query head and walks the keys in
-// tiles of 128. Per tile two products run on the tensor core:
-//     S = Q . K^T      (128 x 128, K = head size)     -> tensor memory, 32-bit
-//     O_j = P . V      (128 x 128, K = 128 keys)      -> tensor memory, 32-bit
-// and between them the softmax threads (one per query row) read their row of S from
-// tensor memory, update the running maximum and sum, write the weights P as bfloat16 into
-// shared memory in the layout the tensor core reads (rows of 128 bytes, 128-byte swizzle),
-// and add the finished O_{j-1} to the row's accumulator, which lives in registers:
-//     o = o * 2^(m_{j-1} - m_j) + O_j
-// so nothing in tensor memory ever has to be rescaled. S and O_j are double-buffered
-// (4 x 128 columns = all of tensor memory), so the tensor core computes S of the next tile
-// while the softmax of this one runs.
+// tiles of 64. Per tile two products run on the tensor core:
+//     S = Q . K^T      (128 x 64,  K = head size)    -> tensor memory, 32-bit
+//     O_j = P . V      (128 x 128, K = 64 keys)      -> tensor memory, 32-bit
+// Two groups of 128 softmax threads (one thread per query row in each group) take the
+// tiles in turn: group b has the tiles of parity b, with an S buffer, a P buffer and an O_j
+// buffer of its own, so that one group's softmax overlaps the other group's products. A
+// softmax thread reads its row of S from tensor memory, updates its running maximum and
+// sum, writes the weights P as bfloat16 into shared memory in the layout the tensor core
+// reads (rows of 128 bytes, 128-byte swizzle), and adds the finished O_{j-2} to the row's
+// accumulator, which lives in registers:
+//     o = o * 2^(m_before - m_after) + O_j
+// so nothing in tensor memory ever has to be rescaled. At the end the two groups' partial
+// results (maximum, sum, accumulator over their own tiles) are merged through shared
+// memory like the ranges of a split-key attention.
 //
-// Roles (192 threads): warp 0 issues TMA loads of Q and of the K/V tiles (page pieces
-// through the block table, as in attention_tma.cu); warp 1 allocates tensor memory and
-// issues the MMAs; warps 2-5 are the softmax threads. K is read as a K-major operand, V as
-// an MN-major operand (its rows are keys, the product contracts over keys), P and Q as
-// K-major operands.
+// Roles (384 threads = three groups of four warps): warps 0-3 and 4-7 are the two softmax
+// groups; in the third group warp 8 issues TMA loads of Q and of the K/V tiles (page pieces
+// through the block table, as in attention_tma.cu), warp 9 allocates tensor memory and
+// issues the MMAs, warps 10-11 idle. The third group hands most of its registers to the
+// softmax groups (setmaxnreg), whose threads keep a whole output row in registers. K is read as a K-major
+// operand, V as an MN-major operand (its rows are keys, the product contracts over keys),
+// P and Q as K-major operands.
 //
 // Formulas: as attention_mma.cu (reference: crates/quantinfer-runtime/src/attention.rs:105-135).
 // No load uses cluster multicast. Every mbarrier wait is bounded; on expiry the kernel sets
@@ -34,12 +39,15 @@ namespace {
 using qi_attn::smem_u32;
 
 constexpr int BM = 128;          // query rows per CTA
-constexpr int BN = 128;          // keys per tile
+constexpr int BN = 64;           // keys per tile
 constexpr int D = 128;           // head size
-constexpr int kStages = 2;       // K/V ring
-constexpr int kThreads = 192;
-constexpr int kHalfBytes = 128 * 128;             // 128 rows x 128 bytes: one 64-column half of a tile
-constexpr int kTileBytes = 2 * kHalfBytes;        // Q, K, V or P tile: 32 KB
+constexpr int kStages = 3;       // K/V ring
+constexpr int kThreads = 384;    // two softmax groups of four warps, then a group with the producer and the MMA warp
+constexpr int kHalfBytes = 128 * 128;             // Q: 128 rows x 128 bytes, one 64-column half
+constexpr int kQBytes = 2 * kHalfBytes;           // 32 KB
+constexpr int kKVHalfBytes = BN * 128;            // K or V: 64 keys x 128 bytes, one 64-column half
+constexpr int kKVBytes = 2 * kKVHalfBytes;        // 16 KB
+constexpr int kPBytes = BM * 128;                 // P: 128 rows x 64 keys (128 bytes): 16 KB
 constexpr int kMaxTableEntries = 2048;
 constexpr uint32_t kSpinLimit = 1u << 24;
 
@@ -105,6 +113,7 @@ __device__ __forceinline__ void tmem_ld32(uint32_t addr, uint32_t (&r)[32]) {
           "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
         : "r"(addr));
 }
+using qi_attn::ex2;
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
 // K-major operand tile (rows of 128 bytes, 128-byte swizzle): see gemm_tcgen05.cu.
@@ -123,15 +132,15 @@ __device__ __forceinline__ uint64_t desc_k_major(uint32_t smem_addr) {
 __device__ __forceinline__ uint64_t desc_mn_major(uint32_t smem_addr) {
     uint64_t d = 0;
     d |= (uint64_t)((smem_addr & 0x3FFFFu) >> 4);
-    d |= (uint64_t)(kHalfBytes >> 4) << 16;
+    d |= (uint64_t)(kKVHalfBytes >> 4) << 16;
     d |= (uint64_t)(1024 >> 4) << 32;
     d |= (uint64_t)1 << 46;
     d |= (uint64_t)2 << 61;
     return d;
 }
-// kind::f16 instruction descriptor: D = F32, A = B = BF16, M = 128, N = 128; bit 16 = B is MN-major.
-constexpr uint32_t idesc(bool b_mn_major) {
-    return (1u << 4) | (1u << 7) | (1u << 10) | (b_mn_major ? (1u << 16) : 0u) | ((uint32_t)(BN >> 3) << 17) |
+// kind::f16 instruction descriptor: D = F32, A = B = BF16, M = 128, N = n; bit 16 = B is MN-major.
+constexpr uint32_t idesc(int n, bool b_mn_major) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | (b_mn_major ? (1u << 16) : 0u) | ((uint32_t)(n >> 3) << 17) |
            ((uint32_t)(BM >> 4) << 24);
 }
 
@@ -143,13 +152,14 @@ struct Bars {   // byte offsets of the mbarriers from the barrier base
     static constexpr int s_free = s_full + 16;             // [2]
     static constexpr int o_full = s_free + 16;             // [2]
     static constexpr int o_free = o_full + 16;             // [2]
-    static constexpr int p_ready = o_free + 16;            // [1]
-    static constexpr int p_free = p_ready + 8;             // [1]
-    static constexpr int total = p_free + 8;
+    static constexpr int p_ready = o_free + 16;            // [2]
+    static constexpr int p_free = p_ready + 16;            // [2]
+    static constexpr int total = p_free + 16;
 };
 
-constexpr int kSmemBytes = kTileBytes /*Q*/ + kStages * 2 * kTileBytes /*K,V*/ + kTileBytes /*P*/ + 256 /*barriers*/ +
-                           4 * kMaxTableEntries + 1024 /*alignment*/;
+constexpr int kSmemBytes = kQBytes + kStages * 2 * kKVBytes + 2 * kPBytes + 256 /*barriers*/ + 4 * kMaxTableEntries +
+                           1024 /*alignment*/;
+static_assert(kStages * 2 * kKVBytes >= BM * (D + 2) * 4, "the K/V ring doubles as the merge buffer of the two softmax groups");
 
 __global__ void __launch_bounds__(kThreads, 1)
 attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
@@ -162,17 +172,20 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* aligned = smem_raw + (base - smem_u32(smem_raw));
     const uint32_t q_s = base;
-    const uint32_t kv_s = q_s + kTileBytes;                       // stage s: K at kv_s + s * 2 tiles, V one tile further
-    const uint32_t p_s = kv_s + kStages * 2 * kTileBytes;
-    uint8_t* p_tile = aligned + kTileBytes + kStages * 2 * kTileBytes;
-    const uint32_t bars = p_s + kTileBytes;
-    uint8_t* bar_mem = aligned + 2 * kTileBytes + kStages * 2 * kTileBytes;
+    const uint32_t kv_s = q_s + kQBytes;                          // stage s: K at kv_s + s * 2 * kKVBytes, V one tile further
+    const uint32_t p_s = kv_s + kStages * 2 * kKVBytes;           // P of group b at p_s + b * kPBytes
+    uint8_t* kv_mem = aligned + kQBytes;
+    uint8_t* p_mem = kv_mem + kStages * 2 * kKVBytes;
+    const uint32_t bars = p_s + 2 * kPBytes;
+    uint8_t* bar_mem = p_mem + 2 * kPBytes;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_mem + Bars::total);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(bar_mem + Bars::total + 4);
     int* s_table = reinterpret_cast<int*>(bar_mem + 256);
 
     qi::pdl_enter();
-    const int tile = blockIdx.x, h = blockIdx.y;
+    // blockIdx.x is the head: CTAs that start together work on the same query rows of neighbouring heads
+    // (which share keys and values), and the tile list's order (most keys first) holds across all heads
+    const int tile = blockIdx.y, h = blockIdx.x;
     const int hk = h / (nq / nkv);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int r = tile_req[tile], q0 = tile_q0[tile];
@@ -195,16 +208,16 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
         }
         for (int b = 0; b < 2; ++b) {
             mbar_init(bars + Bars::s_full + 8 * b, 1);
-            mbar_init(bars + Bars::s_free + 8 * b, 4);    // one arrival per softmax warp
+            mbar_init(bars + Bars::s_free + 8 * b, 4);    // one arrival per warp of the group
             mbar_init(bars + Bars::o_full + 8 * b, 1);
             mbar_init(bars + Bars::o_free + 8 * b, 4);
+            mbar_init(bars + Bars::p_ready + 8 * b, 4);
+            mbar_init(bars + Bars::p_free + 8 * b, 1);
         }
-        mbar_init(bars + Bars::p_ready, 4);
-        mbar_init(bars + Bars::p_free, 1);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == 1) {
+    if (warp == 9) {
         tmem_alloc(smem_u32(tmem_slot), 512);
         tmem_relinquish();
     }
@@ -212,8 +225,8 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
-    const uint32_t tmem_s = tmem_base;            // S buffers: columns 0..127, 128..255
-    const uint32_t tmem_o = tmem_base + 256;      // O_j buffers: columns 256..383, 384..511
+    const uint32_t tmem_s = tmem_base;            // S of group b: columns b * 64 .. b * 64 + 63
+    const uint32_t tmem_o = tmem_base + 128;      // O_j of group b: columns 128 + b * 128 ..
 
     auto give_up = [&]() {
         if (!*abort_flag) {
@@ -222,10 +235,12 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
         }
     };
 
-    if (warp == 0) {
+    if (warp >= 8) {
+      asm volatile("setmaxnreg.dec.sync.aligned.u32 40;" ::: "memory");    // the whole group gives registers back
+      if (warp == 8) {
         // ---------------- TMA producer ----------------
         if (lane == 0) {
-            mbar_expect_tx(bars + Bars::q_full, kTileBytes);
+            mbar_expect_tx(bars + Bars::q_full, kQBytes);
             tma_load_2d(q_s, &map_q, bars + Bars::q_full, h * D, q0);
             tma_load_2d(q_s + kHalfBytes, &map_q, bars + Bars::q_full, h * D + 64, q0);
             int issued = 0;
@@ -236,8 +251,8 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
                     break;
                 }
                 const uint32_t full = bars + Bars::kv_full + 8 * s;
-                const uint32_t k_dst = kv_s + s * 2 * kTileBytes, v_dst = k_dst + kTileBytes;
-                mbar_expect_tx(full, 2 * kTileBytes);
+                const uint32_t k_dst = kv_s + s * 2 * kKVBytes, v_dst = k_dst + kKVBytes;
+                mbar_expect_tx(full, 2 * kKVBytes);
                 const int t0 = t_begin + j * BN;
                 for (int r0 = 0; r0 < BN; r0 += box_rows) {
                     const int key = t0 + r0;
@@ -249,9 +264,9 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
                     }
                     const int row = (page * nkv + hk) * page_size + (key % page_size);
                     tma_load_2d(k_dst + r0 * 128, &map_k, full, 0, row);
-                    tma_load_2d(k_dst + kHalfBytes + r0 * 128, &map_k, full, 64, row);
+                    tma_load_2d(k_dst + kKVHalfBytes + r0 * 128, &map_k, full, 64, row);
                     tma_load_2d(v_dst + r0 * 128, &map_v, full, 0, row);
-                    tma_load_2d(v_dst + kHalfBytes + r0 * 128, &map_v, full, 64, row);
+                    tma_load_2d(v_dst + kKVHalfBytes + r0 * 128, &map_v, full, 64, row);
                 }
                 issued = j + 1;
             }
@@ -261,75 +276,80 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
                         if (mbar_try_wait(bars + Bars::kv_full + 8 * (j % kStages), ((uint32_t)j / kStages) & 1u)) break;
             }
         }
-    } else if (warp == 1) {
+      } else if (warp == 9) {
         // ---------------- MMA issuer ----------------
         if (lane == 0) {
-            constexpr uint32_t idesc_qk = idesc(false), idesc_pv = idesc(true);
+            constexpr uint32_t idesc_qk = idesc(BN, false), idesc_pv = idesc(D, true);
             bool ok = mbar_wait(bars + Bars::q_full, 0, abort_flag);
-            if (!ok) give_up();
             auto issue_qk = [&](int j) -> bool {
                 const int s = j % kStages, b = j & 1;
+                const uint32_t u = (uint32_t)j >> 1;                 // the group's own tile count
                 if (!mbar_wait(bars + Bars::kv_full + 8 * s, ((uint32_t)j / kStages) & 1u, abort_flag)) return false;
-                if (!mbar_wait(bars + Bars::s_free + 8 * b, (((uint32_t)j >> 1) & 1u) ^ 1u, abort_flag)) return false;
+                if (!mbar_wait(bars + Bars::s_free + 8 * b, (u & 1u) ^ 1u, abort_flag)) return false;
                 tc_fence_after();
-                const uint32_t k_addr = kv_s + s * 2 * kTileBytes;
+                const uint32_t k_addr = kv_s + s * 2 * kKVBytes;
 #pragma unroll
                 for (int ks = 0; ks < D / 16; ++ks) {
                     const uint64_t adesc = desc_k_major(q_s + (ks >> 2) * kHalfBytes) + 2u * (ks & 3);
-                    const uint64_t bdesc = desc_k_major(k_addr + (ks >> 2) * kHalfBytes) + 2u * (ks & 3);
+                    const uint64_t bdesc = desc_k_major(k_addr + (ks >> 2) * kKVHalfBytes) + 2u * (ks & 3);
                     umma_bf16(tmem_s + b * BN, adesc, bdesc, idesc_qk, ks > 0 ? 1u : 0u);
                 }
                 umma_commit(bars + Bars::s_full + 8 * b);
                 return true;
             };
-            if (ok && n_tiles > 0) ok = issue_qk(0);
+            // S of the first two tiles, then for every tile: P.V as soon as its P is ready, and S two tiles on
+            for (int j = 0; j < 2 && j < n_tiles && ok; ++j) ok = issue_qk(j);
             for (int j = 0; j < n_tiles && ok; ++j) {
-                if (j + 1 < n_tiles) ok = issue_qk(j + 1);       // the tensor core works on S of the next tile
-                if (!ok) break;                                  // while the softmax of this one runs
                 const int s = j % kStages, b = j & 1;
-                if (!mbar_wait(bars + Bars::p_ready, (uint32_t)j & 1u, abort_flag) ||
-                    !mbar_wait(bars + Bars::o_free + 8 * b, (((uint32_t)j >> 1) & 1u) ^ 1u, abort_flag)) {
+                const uint32_t u = (uint32_t)j >> 1;
+                if (!mbar_wait(bars + Bars::p_ready + 8 * b, u & 1u, abort_flag) ||
+                    !mbar_wait(bars + Bars::o_free + 8 * b, (u & 1u) ^ 1u, abort_flag)) {
                     ok = false;
                     break;
                 }
                 tc_fence_after();
-                const uint32_t v_addr = kv_s + s * 2 * kTileBytes + kTileBytes;
+                const uint32_t v_addr = kv_s + s * 2 * kKVBytes + kKVBytes;
 #pragma unroll
                 for (int kk = 0; kk < BN / 16; ++kk) {
-                    const uint64_t adesc = desc_k_major(p_s + (kk >> 2) * kHalfBytes) + 2u * (kk & 3);
+                    const uint64_t adesc = desc_k_major(p_s + b * kPBytes) + 2u * kk;
                     const uint64_t bdesc = desc_mn_major(v_addr + kk * 16 * 128);
                     umma_bf16(tmem_o + b * D, adesc, bdesc, idesc_pv, kk > 0 ? 1u : 0u);
                 }
                 umma_commit(bars + Bars::o_full + 8 * b);          // O_j is complete
                 umma_commit(bars + Bars::kv_empty + 8 * s);        // K_j and V_j have been read
-                umma_commit(bars + Bars::p_free);                  // P may be overwritten
+                umma_commit(bars + Bars::p_free + 8 * b);          // the group's P may be overwritten
+                if (j + 2 < n_tiles) ok = issue_qk(j + 2);
             }
             if (!ok) give_up();
         }
+      }
     } else {
-        // ---------------- softmax threads (warps 2..5), one query row each ----------------
-        const int quarter = warp & 3;
+        // ---------------- softmax threads: group b = warps 4 b .. 4 b + 3, one query row each ----------------
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 232;" ::: "memory");     // a whole output row lives in registers
+        const int b = warp >> 2;
+        const int quarter = warp & 3;                 // the 32 tensor-memory lanes this warp may read
         const int row = quarter * 32 + lane;
         const int pos = pos0 + row;
         const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
+        uint8_t* p_tile = p_mem + b * kPBytes;
         float m = -INFINITY, l = 0.f, corr_prev = 1.f;
         float o[D];
 #pragma unroll
         for (int i = 0; i < D; ++i) o[i] = 0.f;
         bool ok = true;
 
-        // adds the finished O_j (tile j) to the row's accumulator, scaled to the current maximum
-        auto drain = [&](int j, float corr) -> bool {
-            const int b = j & 1;
-            if (!mbar_wait(bars + Bars::o_full + 8 * b, ((uint32_t)j >> 1) & 1u, abort_flag)) return false;
+        // adds the group's finished O (its u-th tile) to the row's accumulator, scaled to the current maximum
+        auto drain = [&](uint32_t u, float corr) -> bool {
+            if (!mbar_wait(bars + Bars::o_full + 8 * b, u & 1u, abort_flag)) return false;
             tc_fence_after();
 #pragma unroll
-            for (int c0 = 0; c0 < D; c0 += 32) {
-                uint32_t v[32];
-                tmem_ld32(tmem_o + lane_addr + b * D + c0, v);
+            for (int c0 = 0; c0 < D; c0 += 64) {
+                uint32_t v[64];      // two loads in flight per wait
+                tmem_ld32(tmem_o + lane_addr + b * D + c0, *reinterpret_cast<uint32_t(*)[32]>(&v[0]));
+                tmem_ld32(tmem_o + lane_addr + b * D + c0 + 32, *reinterpret_cast<uint32_t(*)[32]>(&v[32]));
                 tmem_ld_wait();
 #pragma unroll
-                for (int i = 0; i < 32; ++i) o[c0 + i] = fmaf(o[c0 + i], corr, __uint_as_float(v[i]));
+                for (int i = 0; i < 64; ++i) o[c0 + i] = fmaf(o[c0 + i], corr, __uint_as_float(v[i]));
             }
             tc_fence_before();
             __syncwarp();
@@ -337,98 +357,119 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
             return true;
         };
 
-        for (int j = 0; j < n_tiles && ok; ++j) {
-            const int b = j & 1;
+        uint32_t u = 0;
+        for (int j = b; j < n_tiles && ok; j += 2, ++u) {
             const int t0 = t_begin + j * BN;
-            if (!mbar_wait(bars + Bars::s_full + 8 * b, ((uint32_t)j >> 1) & 1u, abort_flag)) { ok = false; break; }
+            // the product of the group's previous tile has long finished: fold it in first, so that
+            // the tensor core can start P.V of this tile the moment P is ready
+            if (u > 0) {
+                ok = drain(u - 1, corr_prev);
+                if (!ok) break;
+            }
+            if (!mbar_wait(bars + Bars::s_full + 8 * b, u & 1u, abort_flag)) { ok = false; break; }
             tc_fence_after();
             // keys this row may see in this tile: columns [c_lo, c_hi)
             int c_hi = min(min(pos, hi - 1) - t0 + 1, BN);
             int c_lo = max(lo, window > 0 ? pos - window + 1 : 0) - t0;
             if (c_lo < 0) c_lo = 0;
             if (c_hi < 0) c_hi = 0;
-            // pass 1: the row's maximum
+            uint32_t sv[BN];
+            tmem_ld32(tmem_s + lane_addr + b * BN, *reinterpret_cast<uint32_t(*)[32]>(&sv[0]));
+            tmem_ld32(tmem_s + lane_addr + b * BN + 32, *reinterpret_cast<uint32_t(*)[32]>(&sv[32]));
+            tmem_ld_wait();
+            // S is in registers: the tensor core may write the group's next S
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bars + Bars::s_free + 8 * b);
             float mx = -INFINITY;
-#pragma unroll 1
-            for (int c0 = 0; c0 < BN; c0 += 32) {
-                uint32_t v[32];
-                tmem_ld32(tmem_s + lane_addr + b * BN + c0, v);
-                tmem_ld_wait();
-                if (c0 >= c_lo && c0 + 32 <= c_hi) {
+            if (c_lo == 0 && c_hi == BN) {
+                float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};     // four chains instead of one
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(v[i]));
-                } else {
+                for (int i = 0; i < BN; i += 4) {
 #pragma unroll
-                    for (int i = 0; i < 32; ++i)
-                        if (c0 + i >= c_lo && c0 + i < c_hi) mx = fmaxf(mx, __uint_as_float(v[i]));
+                    for (int e = 0; e < 4; ++e) mx4[e] = fmaxf(mx4[e], __uint_as_float(sv[i + e]));
                 }
+                mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+            } else {
+#pragma unroll
+                for (int i = 0; i < BN; ++i)
+                    if (i >= c_lo && i < c_hi) mx = fmaxf(mx, __uint_as_float(sv[i]));
             }
             const float m_new = fmaxf(m, mx * scale_log2e);
             const float ms = (m_new == -INFINITY) ? 0.f : m_new;
-            const float corr = exp2f(m - ms);              // m = -inf gives 0
+            const float corr = ex2(m - ms);                // m = -inf gives 0
             m = m_new;
-            // the previous tile's P must have been consumed before P is overwritten
-            if (j > 0 && !mbar_wait(bars + Bars::p_free, ((uint32_t)(j - 1)) & 1u, abort_flag)) { ok = false; break; }
-            // pass 2: weights, their sum, and P in the tensor core's layout
+            // the group's previous P must have been consumed before P is overwritten
+            if (u > 0 && !mbar_wait(bars + Bars::p_free + 8 * b, (u - 1) & 1u, abort_flag)) { ok = false; break; }
             float sum = 0.f;
-#pragma unroll 1
-            for (int c0 = 0; c0 < BN; c0 += 32) {
-                uint32_t v[32];
-                tmem_ld32(tmem_s + lane_addr + b * BN + c0, v);
-                tmem_ld_wait();
-                float p[32];
+            uint8_t* prow = p_tile + row * 128;
+            const bool unmasked = c_lo == 0 && c_hi == BN;      // all but the tiles on the diagonal and at a window's edge
 #pragma unroll
-                for (int i = 0; i < 32; ++i) {
-                    const bool valid = c0 + i >= c_lo && c0 + i < c_hi;
-                    p[i] = valid ? exp2f(fmaf(__uint_as_float(v[i]), scale_log2e, -ms)) : 0.f;
-                    sum += p[i];
-                }
-                // columns c0..c0+31 = four 16-byte chunks of this row in half (c0 / 64)
-                uint8_t* prow = p_tile + (c0 >> 6) * kHalfBytes + row * 128;
+            for (int q = 0; q < BN / 8; ++q) {
+                float p[8];
+                if (unmasked) {
 #pragma unroll
-                for (int q = 0; q < 4; ++q) {
-                    const int chunk = ((c0 & 63) >> 3) + q;
-                    uint4 w;
-                    w.x = qi_attn::pack_bf16(p[8 * q + 0], p[8 * q + 1]);
-                    w.y = qi_attn::pack_bf16(p[8 * q + 2], p[8 * q + 3]);
-                    w.z = qi_attn::pack_bf16(p[8 * q + 4], p[8 * q + 5]);
-                    w.w = qi_attn::pack_bf16(p[8 * q + 6], p[8 * q + 7]);
-                    *reinterpret_cast<uint4*>(prow + ((chunk ^ (row & 7)) << 4)) = w;
+                    for (int i = 0; i < 8; ++i) p[i] = ex2(fmaf(__uint_as_float(sv[8 * q + i]), scale_log2e, -ms));
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        const int c = 8 * q + i;
+                        p[i] = (c >= c_lo && c < c_hi) ? ex2(fmaf(__uint_as_float(sv[c]), scale_log2e, -ms)) : 0.f;
+                    }
                 }
+                sum += ((p[0] + p[1]) + (p[2] + p[3])) + ((p[4] + p[5]) + (p[6] + p[7]));
+                uint4 w;
+                w.x = qi_attn::pack_bf16(p[0], p[1]);
+                w.y = qi_attn::pack_bf16(p[2], p[3]);
+                w.z = qi_attn::pack_bf16(p[4], p[5]);
+                w.w = qi_attn::pack_bf16(p[6], p[7]);
+                *reinterpret_cast<uint4*>(prow + ((q ^ (row & 7)) << 4)) = w;
             }
             l = l * corr + sum;
-            // S has been read and P written: make P visible to the tensor core, then signal
+            // P is written: make it visible to the tensor core, then signal
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-            tc_fence_before();
             __syncwarp();
-            if (lane == 0) {
-                mbar_arrive(bars + Bars::s_free + 8 * b);
-                mbar_arrive(bars + Bars::p_ready);
-            }
-            // while the tensor core computes O_j, fold O_{j-1} into the accumulator
-            if (j > 0) ok = drain(j - 1, corr_prev);
+            if (lane == 0) mbar_arrive(bars + Bars::p_ready + 8 * b);
             corr_prev = corr;
         }
-        if (ok && n_tiles > 0) ok = drain(n_tiles - 1, corr_prev);
-        if (!ok) {
-            if (lane == 0) give_up();
-        } else if (row < rows_valid) {
-            const float inv = l > 0.f ? 1.f / l : 0.f;
+        if (ok && u > 0) ok = drain(u - 1, corr_prev);
+        if (!ok && lane == 0) give_up();
+
+        // merge the two groups: group 1 hands its partial result over through the K/V ring,
+        // which nobody reads any more once both groups have drained their last product
+        asm volatile("bar.sync 1, 256;" ::: "memory");
+        float* mrg = reinterpret_cast<float*>(kv_mem) + (size_t)row * (D + 2);
+        if (b == 1) {
+            mrg[0] = m;
+            mrg[1] = l;
+#pragma unroll
+            for (int i = 0; i < D; ++i) mrg[2 + i] = o[i];
+        }
+        asm volatile("bar.sync 1, 256;" ::: "memory");
+        if (b == 0 && !*abort_flag && row < rows_valid) {
+            const float m1 = mrg[0], l1 = mrg[1];
+            const float M = fmaxf(m, m1);
+            const float f0 = (m == -INFINITY) ? 0.f : exp2f(m - M), f1 = (m1 == -INFINITY) ? 0.f : exp2f(m1 - M);
+            const float L = l * f0 + l1 * f1;
+            const float inv = L > 0.f ? 1.f / L : 0.f;
             qi::bf16* orow = out + ((size_t)(q0 + row) * nq + h) * D;
 #pragma unroll
             for (int c0 = 0; c0 < D; c0 += 8) {
+                float y[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) y[i] = (o[c0 + i] * f0 + mrg[2 + c0 + i] * f1) * inv;
                 uint4 w;
-                w.x = qi_attn::pack_bf16(o[c0 + 0] * inv, o[c0 + 1] * inv);
-                w.y = qi_attn::pack_bf16(o[c0 + 2] * inv, o[c0 + 3] * inv);
-                w.z = qi_attn::pack_bf16(o[c0 + 4] * inv, o[c0 + 5] * inv);
-                w.w = qi_attn::pack_bf16(o[c0 + 6] * inv, o[c0 + 7] * inv);
+                w.x = qi_attn::pack_bf16(y[0], y[1]);
+                w.y = qi_attn::pack_bf16(y[2], y[3]);
+                w.z = qi_attn::pack_bf16(y[4], y[5]);
+                w.w = qi_attn::pack_bf16(y[6], y[7]);
                 *reinterpret_cast<uint4*>(orow + c0) = w;
             }
         }
     }
     tc_fence_before();
     __syncthreads();
-    if (warp == 1) tmem_dealloc(tmem_base, 512);
+    if (warp == 9) tmem_dealloc(tmem_base, 512);
 }
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -484,7 +525,7 @@ extern "C" int qi_attention_prefill_tcgen05(const void* q, void* out, const void
     QI_REQUIRE(((uintptr_t)q & 15) == 0 && ((uintptr_t)k_pages & 15) == 0 && ((uintptr_t)v_pages & 15) == 0,
                "attention_prefill_tcgen05: tensors must be 16-byte aligned");
     QI_REQUIRE((long long)num_pages * nkv * page_size < 2147483647LL, "attention_prefill_tcgen05: the page pool has too many rows");
-    QI_REQUIRE(n_tiles >= 0 && nq <= 65535, "attention_prefill_tcgen05: grid too large");
+    QI_REQUIRE(n_tiles >= 0 && n_tiles <= 65535, "attention_prefill_tcgen05: more than 65535 query tiles in one step");
     if (n_tiles == 0) return 0;
     static bool configured = false;
     if (!configured) {
@@ -497,7 +538,7 @@ extern "C" int qi_attention_prefill_tcgen05(const void* q, void* out, const void
     if (make_map(&mq, q, n_tokens, nq * D, BM)) return 1;
     if (make_map(&mk, k_pages, (long long)num_pages * nkv * page_size, D, box_rows)) return 1;
     if (make_map(&mv, v_pages, (long long)num_pages * nkv * page_size, D, box_rows)) return 1;
-    qi::launch(attention_prefill_tcgen05_kernel, dim3(n_tiles, nq), dim3(kThreads), kSmemBytes, stream, mq, mk, mv,
+    qi::launch(attention_prefill_tcgen05_kernel, dim3(nq, n_tiles), dim3(kThreads), kSmemBytes, stream, mq, mk, mv,
                (qi::bf16*)out, block_table, max_blocks, page_size, box_rows, num_pages, q_start, start_pos, tile_req,
                tile_q0, nq, nkv, scale * 1.4426950408889634f, window, status);
     return qi::check_launch("attention_prefill_tcgen05");

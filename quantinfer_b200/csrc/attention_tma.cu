@@ -105,7 +105,8 @@ attention_prefill_tma_kernel(const __grid_constant__ CUtensorMap map_q, const __
     int* s_table = reinterpret_cast<int*>(smem_raw + (bars + 64u - smem_u32(smem_raw)));   // block table entries of this tile's keys
 
     qi::pdl_enter();
-    const int tile = blockIdx.x, h = blockIdx.y;
+    // blockIdx.x is the head, so that the tile list's order (most keys first) holds across all heads
+    const int tile = blockIdx.y, h = blockIdx.x;
     const int hk = h / (nq / nkv);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int r = tile_req[tile], q0 = tile_q0[tile];
@@ -439,7 +440,7 @@ int launch_prefill(const void* q, void* out, const void* k_pages, const void* v_
     if (make_map(&mq, q, n_tokens, nq * D, kPrefillRows)) return 1;
     if (make_map(&mk, k_pages, (long long)num_pages * nkv * page_size, D, box_rows)) return 1;
     if (make_map(&mv, v_pages, (long long)num_pages * nkv * page_size, D, box_rows)) return 1;
-    dim3 grid(n_tiles, nq);
+    dim3 grid(nq, n_tiles);
     qi::launch(kern, grid, dim3(kPrefillThreads), prefill_smem<D>(), stream,
         mq, mk, mv, (qi::bf16*)out, block_table, max_blocks, page_size, box_rows, num_pages, q_start, start_pos,
         tile_req, tile_q0, nq, nkv, scale * 1.4426950408889634f, window, status);
@@ -496,7 +497,7 @@ extern "C" int qi_attention_prefill_tma(const void* q, void* out, const void* k_
     QI_REQUIRE(((uintptr_t)q & 15) == 0 && ((uintptr_t)k_pages & 15) == 0 && ((uintptr_t)v_pages & 15) == 0,
                "attention_prefill_tma: tensors must be 16-byte aligned");
     QI_REQUIRE((long long)num_pages * nkv * page_size < 2147483647LL, "attention_prefill_tma: the page pool has too many rows");
-    QI_REQUIRE(n_tiles >= 0 && nq <= 65535, "attention_prefill_tma: grid too large");
+    QI_REQUIRE(n_tiles >= 0 && n_tiles <= 65535, "attention_prefill_tma: more than 65535 query tiles in one step");
     if (n_tiles == 0) return 0;
     if (d == 64)
         return launch_prefill<64>(q, out, k_pages, v_pages, block_table, max_blocks, page_size, num_pages, q_start,

@@ -128,8 +128,6 @@ __device__ __forceinline__ float2 load_pair(const TIn* p, int splits, size_t str
 
 // TIn = T: qkv is the projection's output. TIn = float with splits > 1: qkv holds the
 // projection's K-split partial sums [splits, n, width], added here in split order.
-// blockIdx.x is the token; the warps of the gridDim.y blocks of a token take its heads in
-// turn, and each lane keeps the cos/sin of its pairs in registers for all its heads.
 template <typename TIn, typename T>
 __global__ void qk_norm_rope_kv_vec_kernel(
     const TIn* __restrict__ qkv, int splits, size_t split_stride, T* __restrict__ q_out, const float* __restrict__ q_gain,
@@ -140,81 +138,60 @@ __global__ void qk_norm_rope_kv_vec_kernel(
     int d, int* __restrict__ status) {
     qi::pdl_enter();
     const int t = blockIdx.x;
-    const int warp = threadIdx.x >> 5, n_warps = blockDim.x >> 5;
+    const int head = blockIdx.y * kWarpsPerBlock + (threadIdx.x >> 5);
     const int lane = threadIdx.x & 31;
     const int total_heads = nq + 2 * nkv;
+    if (head >= total_heads) return;
+    const TIn* src = qkv + (size_t)t * total_heads * d + (size_t)head * d;
     const int pos = positions[t];
-    const int half = d / 2;
-    constexpr int kIter = kMaxHeadDim / 128;     // pairs of one lane: p = 2 * lane + 64 * it
-    float2 c[kIter], sn[kIter];
-#pragma unroll
-    for (int it = 0; it < kIter; ++it) {
-        const int p = 2 * lane + 64 * it;
-        c[it] = make_float2(1.f, 1.f);
-        sn[it] = make_float2(0.f, 0.f);
-        if (cos_t && p < half) {
-            c[it] = *reinterpret_cast<const float2*>(cos_t + (size_t)pos * half + p);
-            sn[it] = *reinterpret_cast<const float2*>(sin_t + (size_t)pos * half + p);
-        }
-    }
-    int page = -1;
-    if (k_pages != nullptr) {
-        page = block_table[(size_t)token_req[t] * max_blocks + pos / page_size];
+    const bool is_q = head < nq;
+    const bool is_k = !is_q && head < nq + nkv;
+    T* dst;
+    if (is_q) {
+        dst = q_out + (size_t)t * nq * d + (size_t)head * d;
+    } else {
+        if (k_pages == nullptr) return;
+        const int hk = is_k ? head - nq : head - nq - nkv;
+        const int page = block_table[(size_t)token_req[t] * max_blocks + pos / page_size];
         if (page < 0 || page >= num_pages) {
-            if (threadIdx.x == 0 && status) atomicOr(status, qi::kStatusBadPage);
-            page = -1;
+            if (lane == 0 && status) atomicOr(status, qi::kStatusBadPage);
+            return;
         }
+        dst = (is_k ? k_pages : v_pages) + (((size_t)page * nkv + hk) * page_size + (pos % page_size)) * (size_t)d;
     }
-    for (int head = blockIdx.y * n_warps + warp; head < total_heads; head += gridDim.y * n_warps) {
-        const TIn* src = qkv + (size_t)t * total_heads * d + (size_t)head * d;
-        const bool is_q = head < nq;
-        const bool is_k = !is_q && head < nq + nkv;
-        T* dst;
-        if (is_q) {
-            dst = q_out + (size_t)t * nq * d + (size_t)head * d;
-        } else {
-            if (page < 0) continue;      // no cache write asked for, or no page: nothing to store
-            const int hk = is_k ? head - nq : head - nq - nkv;
-            dst = (is_k ? k_pages : v_pages) + (((size_t)page * nkv + hk) * page_size + (pos % page_size)) * (size_t)d;
+    if (!is_q && !is_k) {
+        for (int i = 2 * lane; i < d; i += 64) {
+            const float2 v = load_pair<TIn>(src + i, splits, split_stride);
+            Pair<T>::store(dst + i, v.x, v.y);
         }
-        if (!is_q && !is_k) {
-            for (int i = 2 * lane; i < d; i += 64) {
-                const float2 v = load_pair<TIn>(src + i, splits, split_stride);
-                Pair<T>::store(dst + i, v.x, v.y);
-            }
-            continue;
-        }
-        const float* gain = is_q ? q_gain : k_gain;
-        float2 a[kIter], b[kIter];
+        return;
+    }
+    const int half = d / 2;
+    const float* gain = is_q ? q_gain : k_gain;
+    float inv = 1.f;
+    if (gain) {
         float ss = 0.f;
-#pragma unroll
-        for (int it = 0; it < kIter; ++it) {
-            const int p = 2 * lane + 64 * it;
-            if (p < half) {
-                a[it] = load_pair<TIn>(src + p, splits, split_stride);
-                b[it] = load_pair<TIn>(src + p + half, splits, split_stride);
-                ss += a[it].x * a[it].x + a[it].y * a[it].y + b[it].x * b[it].x + b[it].y * b[it].y;
-            }
+        for (int i = 2 * lane; i < d; i += 64) {
+            const float2 v = load_pair<TIn>(src + i, splits, split_stride);
+            ss += v.x * v.x + v.y * v.y;
         }
-        float inv = 1.f;
+        ss = qi::warp_sum(ss);
+        inv = 1.0f / sqrtf(ss / (float)d + eps);
+    }
+    for (int p = 2 * lane; p < half; p += 64) {
+        float2 a = load_pair<TIn>(src + p, splits, split_stride), b = load_pair<TIn>(src + p + half, splits, split_stride);
         if (gain) {
-            ss = qi::warp_sum(ss);
-            inv = 1.0f / sqrtf(ss / (float)d + eps);
+            const float2 ga = *reinterpret_cast<const float2*>(gain + p), gb = *reinterpret_cast<const float2*>(gain + p + half);
+            a.x = a.x * inv * ga.x; a.y = a.y * inv * ga.y;
+            b.x = b.x * inv * gb.x; b.y = b.y * inv * gb.y;
         }
-#pragma unroll
-        for (int it = 0; it < kIter; ++it) {
-            const int p = 2 * lane + 64 * it;
-            if (p < half) {
-                float2 x = a[it], y = b[it];
-                if (gain) {
-                    const float2 ga = *reinterpret_cast<const float2*>(gain + p), gb = *reinterpret_cast<const float2*>(gain + p + half);
-                    x.x = x.x * inv * ga.x; x.y = x.y * inv * ga.y;
-                    y.x = y.x * inv * gb.x; y.y = y.y * inv * gb.y;
-                }
-                Pair<T>::store(dst + p, x.x * c[it].x - y.x * sn[it].x, x.y * c[it].y - y.y * sn[it].y);
-                Pair<T>::store(dst + p + half, x.x * sn[it].x + y.x * c[it].x, x.y * sn[it].y + y.y * c[it].y);
-            }
+        float2 c = make_float2(1.f, 1.f), sn = make_float2(0.f, 0.f);
+        if (cos_t) {
+            c = *reinterpret_cast<const float2*>(cos_t + (size_t)pos * half + p);
+            sn = *reinterpret_cast<const float2*>(sin_t + (size_t)pos * half + p);
         }
+        Pair<T>::store(dst + p, a.x * c.x - b.x * sn.x, a.y * c.y - b.y * sn.y);
+        Pair<T>::store(dst + p + half, a.x * sn.x + b.x * c.x, a.y * sn.y + b.y * c.y);
     }
 }
 
@@ -261,17 +238,13 @@ extern "C" int qi_qk_norm_rope_kv(const void* qkv, int qkv_splits, void* q_out, 
     QI_REQUIRE(grid.y <= 65535, "qk_norm_rope_kv: too many heads");
     if (!cos_t) rot = 0;
     QI_REQUIRE(qkv_splits >= 1, "qk_norm_rope_kv: qkv_splits must be >= 1");
-    // many tokens: each warp takes two heads of its token (cos/sin fetched once for both);
-    // few tokens (decode): a warp per head, so that the heads run side by side
-    const int vec_threads = 128;
-    const dim3 vec_grid(n_tokens, n_tokens >= 512 ? (heads + 7) / 8 : (heads + 3) / 4);
     const bool vec = d % 4 == 0 && (rot == d || rot == 0) && ((uintptr_t)qkv & 7) == 0 && ((uintptr_t)q_out & 7) == 0 &&
                      ((uintptr_t)k_pages & 7) == 0 && ((uintptr_t)v_pages & 7) == 0;
     if (qkv_splits > 1) {
         QI_REQUIRE(vec, "qk_norm_rope_kv: partial sums as input need head_dim %% 4 == 0 and rotation over the whole head");
         const size_t stride = (size_t)n_tokens * heads * d;
         QI_DISPATCH_DTYPE(dtype, T, {
-            qi::launch(qk_norm_rope_kv_vec_kernel<float, T>, vec_grid, dim3(vec_threads), 0, stream,
+            qi::launch(qk_norm_rope_kv_vec_kernel<float, T>, grid, dim3(kWarpsPerBlock * 32), 0, stream,
                 (const float*)qkv, qkv_splits, stride, (T*)q_out, q_gain, k_gain, eps, cos_t, sin_t, positions, token_req,
                 block_table, max_blocks, page_size, num_pages, (T*)k_pages, (T*)v_pages, nq, nkv, d, status);
         });
@@ -279,7 +252,7 @@ extern "C" int qi_qk_norm_rope_kv(const void* qkv, int qkv_splits, void* q_out, 
     }
     if (vec) {
         QI_DISPATCH_DTYPE(dtype, T, {
-            qi::launch(qk_norm_rope_kv_vec_kernel<T, T>, vec_grid, dim3(vec_threads), 0, stream,
+            qi::launch(qk_norm_rope_kv_vec_kernel<T, T>, grid, dim3(kWarpsPerBlock * 32), 0, stream,
                 (const T*)qkv, 1, (size_t)0, (T*)q_out, q_gain, k_gain, eps, cos_t, sin_t, positions, token_req,
                 block_table, max_blocks, page_size, num_pages, (T*)k_pages, (T*)v_pages, nq, nkv, d, status);
         });

@@ -227,8 +227,9 @@ def _attention_case(nq, nkv, d, ctx, new, ps, window, dtype, mode):
                            use_tma=mode.endswith("tma"))
     else:
         tiles = [(r, q_start[r] + t0) for r in range(R) for t0 in range(0, new[r], k.QUERY_TILE)]
+        impl = {"prefill": "cpasync", "prefill_tma": "tma", "prefill_tcgen05": "tcgen05"}[mode]
         k.attention_prefill(qd, out, kp, vp, table, I(q_start), I(ctx), I([t[0] for t in tiles]),
-                            I([t[1] for t in tiles]), nq, nkv, d, scale, window, st, use_tma=mode.endswith("tma"))
+                            I([t[1] for t in tiles]), nq, nkv, d, scale, window, st, impl=impl)
     assert st.item() == 0
     return float((out.double().cpu() - ref).abs().max())
 
@@ -252,6 +253,17 @@ def test_attention_generic(dtype, nq, nkv, d, ctx, new, ps, window):
 ])
 def test_attention_prefill_kernels(mode, nq, nkv, d, ctx, new, ps, window):
     assert _attention_case(nq, nkv, d, ctx, new, ps, window, torch.bfloat16, mode) < 1.2e-2
+
+
+@pytest.mark.parametrize("nq, nkv, ctx, new, ps, window", [
+    (8, 2, [0], [128], 64, 0), (8, 2, [0], [17], 64, 0), (8, 2, [0, 37, 200], [130, 64, 1], 64, 0), (8, 1, [5, 300], [70, 2], 8, 0),
+    (8, 2, [100, 0], [300, 257], 128, 0), (4, 4, [40, 0], [90, 150], 32, 50), (32, 8, [0], [1024], 64, 0), (2, 1, [700], [129], 16, 100),
+])
+def test_attention_prefill_tcgen05(nq, nkv, ctx, new, ps, window):
+    """The tensor-memory kernel (head size 128): spans that end inside a tile, several requests, page
+    pieces smaller and larger than a tile, a window, an odd number of key tiles (the two softmax groups
+    then hold different numbers of tiles)."""
+    assert _attention_case(nq, nkv, 128, ctx, new, ps, window, torch.bfloat16, "prefill_tcgen05") < 1.2e-2
 
 
 def test_attention_prefill_without_tma_takes_any_page_size():
