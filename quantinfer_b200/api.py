@@ -34,7 +34,9 @@ class Model:
     """A model folder loaded onto one GPU."""
 
     def __init__(self, path, *, dtype="bfloat16", device="cuda:0", page_size=None, cache_tokens=None,
-                 max_requests=8, max_batch_tokens=2048, chunk_size=None, use_graphs=True):
+                 max_requests=8, max_batch_tokens=2048, chunk_size=None, use_graphs=True, run_ahead=True):
+        """`run_ahead`: decode steps are launched before the host has read the tokens of the
+        step before (engine/pipeline.py); the tokens do not change, they arrive one step late."""
         from .engine import Engine
         from .engine.engine import DEFAULT_PAGE_SIZE
 
@@ -45,10 +47,11 @@ class Model:
         self._sampler = Sampler.for_engine(self._engine)
         self._max_batch_tokens = max_batch_tokens
         self._chunk_size = chunk_size
+        self._run_ahead = run_ahead
         self._open = True
 
     @classmethod
-    def from_engine(cls, engine, *, max_batch_tokens=2048, chunk_size=None) -> "Model":
+    def from_engine(cls, engine, *, max_batch_tokens=2048, chunk_size=None, run_ahead=True) -> "Model":
         """A Model over an engine that already exists (random weights made on the device, tests)."""
         self = cls.__new__(cls)
         self._lock = RLock()
@@ -56,6 +59,7 @@ class Model:
         self._sampler = Sampler.for_engine(engine)
         self._max_batch_tokens = max_batch_tokens
         self._chunk_size = chunk_size
+        self._run_ahead = run_ahead
         self._open = True
         return self
 
@@ -137,6 +141,7 @@ class Model:
         """Generates for every prompt (lists of token ids on the host); returns the
         lists of generated ids in the order of the prompts. Request i draws with
         seed + i."""
+        from .engine.pipeline import DecodePipeline
         from .engine.scheduler import FailedEvent, Scheduler, TokenEvent
 
         with self._lock:
@@ -148,7 +153,9 @@ class Model:
                               vocab_size=eng.spec.vocab_size,
                               max_sequences=eng.cache.max_requests,
                               max_tokens=max(self._max_batch_tokens, eng.cache.max_requests),
-                              chunk_size=self._chunk_size)
+                              chunk_size=self._chunk_size,
+                              pipeline=DecodePipeline(eng, self._sampler) if self._run_ahead and eng.use_graphs else None)
+            self.last_scheduler = sched
             ids = []
             for i, p in enumerate(prompts):
                 if not p:

@@ -170,10 +170,12 @@ class Engine:
         return (self.use_graphs and len(entries) <= self.max_graph_batch
                 and all(len(e.tokens) == 1 and list(e.want) == [0] for e in entries))
 
-    def _graph_step(self, entries, extra_positions: int = 0):
+    def _graph_step(self, entries, extra_positions: int = 0, device_tokens=None):
         """A batch of single decode tokens, all wanting their logits: the packed batch has a
         fixed layout per batch size, so the forward pass is captured once per size and
-        replayed; each step only copies the batch's arrays into the graph's buffer."""
+        replayed; each step only copies the batch's arrays into the graph's buffer. With
+        `device_tokens` (int32 [entries], on the device) the token ids are taken from there
+        instead of from the entries, without the host seeing them."""
         starts, slots, buf, layout, q_start, lens = self._pack(entries)
         host, event = self._stage(buf)
         b = len(entries)
@@ -185,6 +187,8 @@ class Engine:
             meta = torch.empty(buf.size, dtype=torch.int32, device=self.device)
             meta.copy_(host, non_blocking=True)
             event.record()
+            if device_tokens is not None:
+                meta[:b].copy_(device_tokens)      # token_ids is the first part of the layout
             batch = batch_from_packed(meta, layout, entries, starts, slots, q_start, lens,
                                       len(self.cache.groups), self.cache.max_blocks)
             batch.max_kv_len = bound
@@ -202,6 +206,8 @@ class Engine:
             return logits, g
         g["meta"].copy_(host, non_blocking=True)
         event.record()
+        if device_tokens is not None:
+            g["meta"][:b].copy_(device_tokens)
         g["graph"].replay()
         kernels.launches += g["launches"]
         return g["logits"], g

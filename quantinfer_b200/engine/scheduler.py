@@ -26,6 +26,16 @@ extended by the tokens it has emitted, to be recomputed; the step is planned
 again. Its sampler stream continues (the counter is the number of emitted
 tokens), so its output does not change.
 
+Running ahead: with a `pipeline` (an object with `launch(request_ids, tokens,
+rows, prev)` that returns a pending result with `result()` and `discard()`),
+steps whose entries are all decode tokens are launched without waiting for the
+tokens of the step before, as long as the same requests go on: the device feeds
+its own sampled tokens into the next step, and the host reads them one step
+late. A request that ends on an EOS it could not foresee has then run one step
+too many; that step's token for it is dropped. A step is never launched ahead
+for a request whose pending token is its last by `max_new_tokens`, nor when
+another request waits to be admitted or is still in its prompt.
+
 The scheduler is host code over three callables and needs no device:
 `step_fn(entries) -> logits`, `sample_fn(logits, [(config, emitted)]) -> tokens`,
 and a :class:`CacheManager` for admission and for open/close.
@@ -88,7 +98,7 @@ class Request:
 class Scheduler:
     def __init__(self, cache, step_fn: Callable, sample_fn: Callable, *, vocab_size: int,
                  max_sequences: int = 8, max_tokens: int = 512, chunk_size: Optional[int] = None,
-                 clock: Callable[[], float] = time.monotonic):
+                 clock: Callable[[], float] = time.monotonic, pipeline=None):
         """Defaults 8 sequences and 512 tokens per step are those the reference's
         server drives its scheduler with (apps/quantinfer-server/src/config.rs:32-45)."""
         if max_sequences <= 0 or max_tokens <= 0:
@@ -110,6 +120,9 @@ class Scheduler:
         self.steps = 0
         self.preemptions = 0
         self._hold_admission = False   # set by a preemption until some request gives pages back
+        self.pipeline = pipeline
+        self._inflight = None          # (requests, pending result) of a launched decode step
+        self.steps_ahead = 0           # steps launched before the tokens of the step before were read
 
     # ---- submission --------------------------------------------------------
 
@@ -193,10 +206,21 @@ class Scheduler:
         for r in list(self.running) + list(self.waiting):
             if r.deadline is not None and now >= r.deadline:
                 events.append(self._stop(r, TIMED_OUT))
+        if self._inflight is not None:
+            events += self._resolve()
+            if events or self._inflight is not None:
+                return events
         while True:
             plan = self.plan()
             if not plan:
                 return events
+            if self.pipeline is not None and all(not r.prefilling for r, _, _ in plan):
+                reqs = [r for r, _, _ in plan]
+                pending = self._launch(reqs, None)
+                if pending is not None:
+                    self._inflight = (reqs, pending)
+                    self.steps += 1
+                    return events + self._resolve()
             entries = [StepEntry(r.id, tokens, [len(tokens) - 1] if want else []) for r, tokens, want in plan]
             try:
                 logits = self.step_fn(entries)
@@ -219,10 +243,17 @@ class Scheduler:
             for r, _, _ in plan:
                 events.append(self._fail(r, str(exc)))
             return events
-        now = self.clock()
         for r, tokens, want in plan:
             r.cached += len(tokens) if r.prefilling else 0
-        for (r, _), token in zip(wanting, sampled):
+        return events + self._take([r for r, _ in wanting], sampled)
+
+    def _take(self, reqs, sampled) -> list:
+        """Books one sampled token for each request that is still running."""
+        events = []
+        now = self.clock()
+        for r, token in zip(reqs, sampled):
+            if r.stop_reason is not None or r not in self.running:
+                continue            # ended meanwhile: the token of a step that ran ahead is dropped
             if r.deadline is not None and now >= r.deadline:
                 events.append(self._stop(r, TIMED_OUT))
                 continue
@@ -240,6 +271,51 @@ class Scheduler:
             else:
                 self._finish(r, reason)
                 events.append(TokenEvent(r.id, token, reason))
+        return events
+
+    # ---- decode steps that run ahead ------------------------------------------------
+
+    def _launch(self, reqs, prev):
+        """Launches a decode step for `reqs` through the pipeline; None if it does not take it."""
+        ahead = 0 if prev is None else 1
+        rows = [(r.config, len(r.emitted) + ahead) for r in reqs]
+        tokens = None if prev is not None else [r.next_token for r in reqs]
+        try:
+            return self.pipeline.launch([r.id for r in reqs], tokens, rows, prev)
+        except OutOfPages:
+            return None             # the ordinary path decides what to do about it
+
+    def _may_run_ahead(self, reqs) -> bool:
+        self._admit()
+        return (len(self.running) == len(reqs) and all(a is b for a, b in zip(self.running, reqs))
+                and all(not r.prefilling and len(r.emitted) + 1 < r.config.max_new_tokens for r in reqs))
+
+    def _resolve(self) -> list:
+        """Reads the tokens of the step in flight, after launching the next one if the same
+        requests are sure to go on (short of an EOS)."""
+        reqs, pending = self._inflight
+        self._inflight = None
+        ahead = None
+        if self._may_run_ahead(reqs):
+            try:
+                ahead = self._launch(reqs, pending)
+            except Exception as exc:
+                pending.discard()
+                return [self._fail(r, str(exc)) for r in reqs if r in self.running]
+        try:
+            sampled = pending.result()
+        except Exception as exc:
+            if ahead is not None:
+                ahead.discard()
+            return [self._fail(r, str(exc)) for r in reqs if r in self.running]
+        events = self._take(reqs, sampled)
+        if ahead is not None:
+            if any(r in self.running for r in reqs):
+                self._inflight = (reqs, ahead)
+                self.steps += 1
+                self.steps_ahead += 1
+            else:
+                ahead.discard()
         return events
 
     def run(self, on_event: Optional[Callable] = None) -> list:

@@ -30,6 +30,9 @@ class Sampler:
             self.status = io[0:1]
         else:
             self.status = status if status is not None else torch.zeros(1, dtype=torch.int32, device=self.device)
+        self._pinned = [None] * 4        # staging for the per-row options, used in turn
+        self._pinned_event = [None] * 4
+        self._turn = 0
 
     @classmethod
     def for_engine(cls, engine) -> "Sampler":
@@ -77,7 +80,22 @@ class Sampler:
         buf[2 * n:3 * n] = np.asarray([cfg.top_p if cfg.top_p else 0.0 for cfg, _ in rows], dtype=np.float32).view(np.int32)
         buf[3 * n:4 * n] = [emitted for _, emitted in rows]
         buf[4 * n:6 * n] = np.asarray([cfg.seed for cfg, _ in rows], dtype=np.uint64).view(np.int32)
-        dev = torch.from_numpy(buf).to(self.device)
+        dev = self._to_device(buf)
         return {"temperature": dev[0:n].view(torch.float32), "top_k": dev[n:2 * n],
                 "top_p": dev[2 * n:3 * n].view(torch.float32), "seed": dev[4 * n:6 * n].view(torch.int64),
                 "counter": dev[3 * n:4 * n]}
+
+    def _to_device(self, buf: np.ndarray) -> torch.Tensor:
+        """Copies through pinned memory without waiting for the stream (steps may run ahead of the host)."""
+        turn = self._turn
+        self._turn = (turn + 1) % len(self._pinned)
+        host = self._pinned[turn]
+        if host is None or host.numel() < buf.size:
+            host = self._pinned[turn] = torch.empty(max(2 * buf.size, 256), dtype=torch.int32, pin_memory=True)
+            self._pinned_event[turn] = torch.cuda.Event()
+        else:
+            self._pinned_event[turn].synchronize()      # the copy that last used this buffer is done
+        host[:buf.size].numpy()[:] = buf
+        dev = host[:buf.size].to(self.device, non_blocking=True)
+        self._pinned_event[turn].record()
+        return dev
