@@ -231,7 +231,11 @@ attention_decode_tma_kernel(const qi::bf16* __restrict__ q, const __grid_constan
     auto full_bar = [&](int s) { return bars + 8u * s; };
     int* s_table = reinterpret_cast<int*>(aligned + kDecodeStages * 2 * kTileBytes + kQBytes + 64);
 
-    qi::pdl_enter();
+    // Lengths and block tables were copied before the step began, and keys and values of earlier
+    // positions were written by earlier steps: only the newest key (position S - 1) and the
+    // queries come from the kernel before this one. So the first tiles are requested before the
+    // wait for that kernel, unless they hold the newest key.
+    qi::pdl_launch_dependents();
     const int split = blockIdx.x, hk = blockIdx.y, b = blockIdx.z;
     const int n_splits = gridDim.x;
     const int G = nq / nkv;
@@ -245,6 +249,7 @@ attention_decode_tma_kernel(const qi::bf16* __restrict__ q, const __grid_constan
 
     const int tok = q_start[b];
     if (k0 >= k1) {   // nothing of this range belongs to the request: an empty partial
+        qi::pdl_wait();
         if (threadIdx.x < G) {
             float* ml = ws_ml + (part + (size_t)threadIdx.x * n_splits) * 2;
             ml[0] = -INFINITY;
@@ -263,6 +268,16 @@ attention_decode_tma_kernel(const qi::bf16* __restrict__ q, const __grid_constan
         for (int s = 0; s < kDecodeStages; ++s) mbar_init(full_bar(s), 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
+    __syncthreads();
+    int issued = 0;     // thread 0: tiles requested so far
+    if (threadIdx.x == 0) {
+        for (; issued < kDecodeStages && issued < n_tiles; ++issued) {
+            if (t_begin + (issued + 1) * kTileKeys >= S) break;      // holds the newest key
+            issue_kv_tile<D>(kv_s + issued * 2 * kTileBytes, full_bar(issued), &map_k, &map_v, s_table, blk0, n_blk, page_size,
+                             box_rows, num_pages, nkv, hk, t_begin + issued * kTileKeys, k0, k1, status);
+        }
+    }
+    qi::pdl_wait();
     constexpr int kChunks = D / 8;
     for (int idx = threadIdx.x; idx < 16 * kChunks; idx += kDecodeThreads) {
         const int row = idx / kChunks, c = idx % kChunks;
@@ -272,7 +287,7 @@ attention_decode_tma_kernel(const qi::bf16* __restrict__ q, const __grid_constan
     }
     __syncthreads();
     if (threadIdx.x == 0) {
-        for (int i = 0; i < kDecodeStages && i < n_tiles; ++i)
+        for (int i = issued; i < kDecodeStages && i < n_tiles; ++i)
             issue_kv_tile<D>(kv_s + i * 2 * kTileBytes, full_bar(i), &map_k, &map_v, s_table, blk0, n_blk, page_size, box_rows,
                              num_pages, nkv, hk, t_begin + i * kTileKeys, k0, k1, status);
     }

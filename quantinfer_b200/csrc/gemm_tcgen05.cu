@@ -225,7 +225,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
-    qi::pdl_wait();                // set-up done; the previous kernel's results are needed from here on
+    // Set-up is done. Only the activations (and the output buffer) depend on the kernel before
+    // this one: the producer fetches the first weight tiles before it waits for that kernel, the
+    // epilogue warps wait before they write, and the MMA warp follows the producer's barriers.
 
     auto give_up = [&]() {
         if (!*abort_flag) {
@@ -237,6 +239,25 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     if (warp == 0) {
         // ---------------- TMA producer ----------------
         if (lane == 0) {
+            // The weights are the operand with the many rows: A when the operands are swapped
+            // (few tokens), else B. They are never written on the device, so the first stages'
+            // weight tiles of this CTA's first tile are requested before the wait.
+            uint32_t early = 0;
+            if (blockIdx.x < total_tiles) {
+                const int tile = blockIdx.x;
+                const int tile_a = tile % tiles_a, tile_b = (tile / tiles_a) % tiles_b, split = tile / (tiles_a * tiles_b);
+                const int kb_begin = split * kb_per_split;
+                const int n_kb = max(min(kb_total, kb_begin + kb_per_split) - kb_begin, 0);
+                early = (uint32_t)min(n_kb, STAGES);
+                for (uint32_t i = 0; i < early; ++i) {
+                    mbar_expect_tx(full_bar(i), L::kStageBytes);
+                    const uint32_t a_dst = base + i * L::kStageBytes;
+                    const int k0 = (kb_begin + (int)i) * BK;
+                    if (SWAP) tma_load_2d(a_dst, &map_a, full_bar(i), k0, tile_a * BM);
+                    else tma_load_2d(a_dst + L::kABytes, &map_b, full_bar(i), k0, tile_b * BN);
+                }
+            }
+            qi::pdl_wait();
             uint32_t it = 0;          // k blocks issued so far, over all tiles
             bool ok = true;
             for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
@@ -245,14 +266,20 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 const int n_kb = max(min(kb_total, kb_begin + kb_per_split) - kb_begin, 0);
                 for (int i = 0; i < n_kb; ++i, ++it) {
                     const int s = it % STAGES;
+                    const uint32_t a_dst = base + s * L::kStageBytes;
+                    const int k0 = (kb_begin + i) * BK;
+                    if (it < early) {
+                        // the weight tile of this stage is on its way already: add the activations
+                        if (SWAP) tma_load_2d(a_dst + L::kABytes, &map_b, full_bar(s), k0, tile_b * BN);
+                        else tma_load_2d(a_dst, &map_a, full_bar(s), k0, tile_a * BM);
+                        continue;
+                    }
                     if (!mbar_wait(empty_bar(s), ((it / STAGES) & 1u) ^ 1u, abort_flag, status)) {
                         give_up();
                         ok = false;
                         break;
                     }
                     mbar_expect_tx(full_bar(s), L::kStageBytes);
-                    const uint32_t a_dst = base + s * L::kStageBytes;
-                    const int k0 = (kb_begin + i) * BK;
                     tma_load_2d(a_dst, &map_a, full_bar(s), k0, tile_a * BM);
                     tma_load_2d(a_dst + L::kABytes, &map_b, full_bar(s), k0, tile_b * BN);
                 }
@@ -309,6 +336,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     } else {
         // ---------------- epilogue (warps 2..5) ----------------
         const int quarter = warp & 3;   // the 32 TMEM lanes this warp may read
+        qi::pdl_wait();                 // the output buffer may still be read by the kernel before
         int j = 0;
         for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++j) {
             const int tile_a = tile % tiles_a, tile_b = (tile / tiles_a) % tiles_b, split = tile / (tiles_a * tiles_b);
