@@ -169,6 +169,7 @@ struct Smem {
     static constexpr int kTotal = STAGES * kStageBytes + kBarrierBytes + 1024;  // + alignment slack
 };
 
+
 __device__ __forceinline__ float silu_mul(float g, float u) { return g / (1.0f + expf(-g)) * u; }
 
 // EPI = 0: store the product. EPI = 1: the product's columns come in pairs (gate, up) and
@@ -525,15 +526,20 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, TOut* out, int rows_a, 
     return qi::check_launch("gemm_bf16");
 }
 
+// Pipeline stages by tile width: 6 where two CTAs of 6 stages fit an SM (the first stages' weight
+// tiles are requested before the kernel waits for its predecessor, so deeper is better while
+// two CTAs stay resident), 4 for the widest tile.
+constexpr int stages_of(int bn) { return bn <= 32 ? 6 : bn == 128 ? 6 : 4; }
+
 template <bool SWAP, typename TOut, int EPI = 0>
 int launch_bn(int bn, const CUtensorMap& ma, const CUtensorMap& mb, TOut* out, int rows_a, int rows_b, int K,
               long long ld, int splits, int kb_per_split, long long split_stride, int* status, cudaStream_t stream) {
     switch (bn) {
-        case 16: return launch<16, 4, SWAP, TOut, EPI>(ma, mb, out, rows_a, rows_b, K, ld, splits, kb_per_split, split_stride, status, stream);
-        case 32: return launch<32, 4, SWAP, TOut, EPI>(ma, mb, out, rows_a, rows_b, K, ld, splits, kb_per_split, split_stride, status, stream);
-        case 64: return launch<64, 4, SWAP, TOut, EPI>(ma, mb, out, rows_a, rows_b, K, ld, splits, kb_per_split, split_stride, status, stream);
-        case 128: return launch<128, 6, SWAP, TOut, EPI>(ma, mb, out, rows_a, rows_b, K, ld, splits, kb_per_split, split_stride, status, stream);
-        case 256: return launch<256, 4, SWAP, TOut, EPI>(ma, mb, out, rows_a, rows_b, K, ld, splits, kb_per_split, split_stride, status, stream);
+        case 16: return launch<16, stages_of(16), SWAP, TOut, EPI>(ma, mb, out, rows_a, rows_b, K, ld, splits, kb_per_split, split_stride, status, stream);
+        case 32: return launch<32, stages_of(32), SWAP, TOut, EPI>(ma, mb, out, rows_a, rows_b, K, ld, splits, kb_per_split, split_stride, status, stream);
+        case 64: return launch<64, stages_of(64), SWAP, TOut, EPI>(ma, mb, out, rows_a, rows_b, K, ld, splits, kb_per_split, split_stride, status, stream);
+        case 128: return launch<128, stages_of(128), SWAP, TOut, EPI>(ma, mb, out, rows_a, rows_b, K, ld, splits, kb_per_split, split_stride, status, stream);
+        case 256: return launch<256, stages_of(256), SWAP, TOut, EPI>(ma, mb, out, rows_a, rows_b, K, ld, splits, kb_per_split, split_stride, status, stream);
     }
     return qi::fail("gemm_bf16: no kernel for a tile width of %d", bn);
 }
@@ -548,6 +554,7 @@ extern "C" int qi_gemm_bf16_plan(int M, int N, int K, int* swap, int* bn, int* s
         b = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : 256;
         const int tiles = (N + BM - 1) / BM;
         // enough CTAs to keep the weight stream busy on 148 SMs, at least 8 k blocks per split
+        // (filling every resident slot with 6 or 9 splits was measured no faster than powers of two)
         while (tiles * sp < 148 && sp * 2 <= 16 && kb_total / (sp * 2) >= 8) sp *= 2;
     } else {
         b = N >= 256 ? 256 : N > 64 ? 128 : N > 32 ? 64 : N > 16 ? 32 : 16;

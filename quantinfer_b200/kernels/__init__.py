@@ -366,9 +366,11 @@ def attention_prefill(q, out, k_pages, v_pages, block_table, q_start, start_pos,
 
 
 def attention_decode_plan(batch: int, nkv: int, max_kv_len: int):
-    """(keys per CTA, number of key ranges) for a decode batch: enough CTAs for 148 SMs,
-    ranges a multiple of 64 keys, independent of the requests' actual lengths."""
-    target = max(1, -(-592 // max(batch * nkv, 1)))
+    """(keys per CTA, number of key ranges) for a decode batch: as many CTAs as are resident
+    at once (two on each of 148 SMs) and no more, so that each requests its first tiles while
+    the kernel before it still runs; ranges a multiple of 64 keys, independent of the
+    requests' actual lengths."""
+    target = max(1, 296 // max(batch * nkv, 1))
     chunk = max(64, -(-(-(-max_kv_len // target)) // 64) * 64)
     return chunk, -(-max_kv_len // chunk)
 
