@@ -211,9 +211,10 @@ attention_prefill_tma_kernel(const __grid_constant__ CUtensorMap map_q, const __
 constexpr int kDecodeThreads = 128;
 constexpr int kDecodeStages = 3;
 
-template <int D>
+// DIRECT: the request's keys are one range, and the CTA writes the attention output itself.
+template <int D, bool DIRECT>
 __global__ void __launch_bounds__(kDecodeThreads)
-attention_decode_tma_kernel(const qi::bf16* __restrict__ q, const __grid_constant__ CUtensorMap map_k,
+attention_decode_tma_kernel(const qi::bf16* __restrict__ q, qi::bf16* __restrict__ out, const __grid_constant__ CUtensorMap map_k,
                             const __grid_constant__ CUtensorMap map_v, const int* __restrict__ block_table,
                             int max_blocks, int page_size, int box_rows, int num_pages,
                             const int* __restrict__ kv_len, const int* __restrict__ q_start,
@@ -250,6 +251,11 @@ attention_decode_tma_kernel(const qi::bf16* __restrict__ q, const __grid_constan
     const int tok = q_start[b];
     if (k0 >= k1) {   // nothing of this range belongs to the request: an empty partial
         qi::pdl_wait();
+        if (DIRECT) {
+            for (int idx = threadIdx.x; idx < G * D; idx += kDecodeThreads)
+                out[((size_t)tok * nq + (size_t)hk * G) * D + idx] = __float2bfloat16_rn(0.f);
+            return;
+        }
         if (threadIdx.x < G) {
             float* ml = ws_ml + (part + (size_t)threadIdx.x * n_splits) * 2;
             ml[0] = -INFINITY;
@@ -367,18 +373,24 @@ attention_decode_tma_kernel(const qi::bf16* __restrict__ q, const __grid_constan
             L += sm_l[w * 16 + row] * f;
             O += sm_o[(w * 16 + row) * D + col] * f;
         }
-        const size_t p = part + (size_t)row * n_splits;
-        ws_o[p * D + col] = O;
-        if (col == 0) {
-            ws_ml[p * 2] = M;
-            ws_ml[p * 2 + 1] = L;
+        if (DIRECT) {
+            out[((size_t)tok * nq + (size_t)hk * G + row) * D + col] = __float2bfloat16_rn(L > 0.f ? O / L : 0.f);
+        } else {
+            const size_t p = part + (size_t)row * n_splits;
+            ws_o[p * D + col] = O;
+            if (col == 0) {
+                ws_ml[p * 2] = M;
+                ws_ml[p * 2 + 1] = L;
+            }
         }
     }
 }
 
 // out[b, h, :] = sum_s o_s 2^(m_s - M) / sum_s l_s 2^(m_s - M), key ranges in order. A separate
 // kernel: merging inside the decode kernel (last CTA by ticket) was measured slower, the
-// merge then sits on the tail of the slowest CTA.
+// merge then sits on the tail of the slowest CTA; so was making the ranges of a (request, kv
+// head) one thread-block cluster that merges through distributed shared memory (4.31 against
+// 4.25 ms a step at batch 16, 7.39 against 7.25 at batch 64).
 template <int D>
 __global__ void attention_merge_kernel(const float* __restrict__ ws_o, const float* __restrict__ ws_ml,
                                        const int* __restrict__ q_start, qi::bf16* __restrict__ out, int nq,
@@ -467,10 +479,12 @@ int launch_decode(const void* q, void* out, const void* k_pages, const void* v_p
                   int max_blocks, int page_size, int num_pages, const int* kv_len, const int* q_start, int batch,
                   int nq, int nkv, float scale, int window, int chunk, int n_splits, float* ws_o, float* ws_ml,
                   int* status, cudaStream_t stream) {
-    auto kern = attention_decode_tma_kernel<D>;
+    auto kern = attention_decode_tma_kernel<D, false>;
+    auto kern_direct = attention_decode_tma_kernel<D, true>;
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, decode_smem<D>());
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(kern_direct, cudaFuncAttributeMaxDynamicSharedMemorySize, decode_smem<D>());
         if (e != cudaSuccess) return qi::fail("attention_decode: cannot reserve shared memory: %s", cudaGetErrorString(e));
         configured = true;
     }
@@ -479,8 +493,14 @@ int launch_decode(const void* q, void* out, const void* k_pages, const void* v_p
     if (make_map(&mk, k_pages, (long long)num_pages * nkv * page_size, D, box_rows)) return 1;
     if (make_map(&mv, v_pages, (long long)num_pages * nkv * page_size, D, box_rows)) return 1;
     dim3 grid(n_splits, nkv, batch);
+    if (n_splits == 1) {
+        qi::launch(kern_direct, grid, dim3(kDecodeThreads), decode_smem<D>(), stream,
+            (const qi::bf16*)q, (qi::bf16*)out, mk, mv, block_table, max_blocks, page_size, box_rows, num_pages, kv_len,
+            q_start, ws_o, ws_ml, nq, nkv, scale * 1.4426950408889634f, window, chunk, status);
+        return qi::check_launch("attention_decode_tma");
+    }
     qi::launch(kern, grid, dim3(kDecodeThreads), decode_smem<D>(), stream,
-        (const qi::bf16*)q, mk, mv, block_table, max_blocks, page_size, box_rows, num_pages, kv_len, q_start, ws_o,
+        (const qi::bf16*)q, (qi::bf16*)out, mk, mv, block_table, max_blocks, page_size, box_rows, num_pages, kv_len, q_start, ws_o,
         ws_ml, nq, nkv, scale * 1.4426950408889634f, window, chunk, status);
     if (int rc = qi::check_launch("attention_decode_tma")) return rc;
     qi::launch(attention_merge_kernel<D>, dim3(nq, batch), dim3(D >= 128 ? 128 : 64), 0, stream, (const float*)ws_o,

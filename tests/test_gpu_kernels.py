@@ -189,7 +189,7 @@ def test_qk_norm_rope_kv(dtype, nq, nkv, d, rot, ps):
 
 # ------------------------------------------------------------------ attention
 
-def _attention_case(nq, nkv, d, ctx, new, ps, window, dtype, mode):
+def _attention_case(nq, nkv, d, ctx, new, ps, window, dtype, mode, decode_chunk=0):
     """ctx[r] cached positions and new[r] query tokens per request. One query per request
     has a far key that dominates its softmax, so a missed or misplaced key changes the result."""
     torch.manual_seed(7)
@@ -223,6 +223,8 @@ def _attention_case(nq, nkv, d, ctx, new, ps, window, dtype, mode):
         k.attention_generic(qd, out, kp, vp, table, I(positions), I(token_req), nq, nkv, d, scale, window, st)
     elif mode.startswith("decode"):
         chunk, splits = k.attention_decode_plan(R, nkv, max(tot) + 70)
+        if decode_chunk:
+            chunk, splits = decode_chunk, -(-(max(tot) + 70) // decode_chunk)
         k.attention_decode(qd, out, kp, vp, table, I(tot), I(q_start), nq, nkv, d, scale, window, chunk, splits, st,
                            use_tma=mode.endswith("tma"))
     else:
@@ -278,6 +280,21 @@ def test_attention_prefill_without_tma_takes_any_page_size():
 ])
 def test_attention_decode_kernels(mode, nq, nkv, d, ctx, ps, window):
     assert _attention_case(nq, nkv, d, ctx, [1] * len(ctx), ps, window, torch.bfloat16, mode) < 1.2e-2
+
+
+@pytest.mark.parametrize("chunk, ctx, window", [
+    (2048, [2047, 100, 513, 0], 0),     # one range: the CTA writes the result itself
+    (2048, [2047, 100, 513, 0], 300),   # the same with a window
+    (1024, [1500, 100, 1023, 1024], 0), # two ranges, the second empty for the short requests
+    (512, [1999, 64, 700, 0], 0),       # five ranges
+    (256, [1700, 300, 255, 256], 200),  # a window: leading ranges are empty
+    (192, [1700, 300, 255, 256], 0),    # ten ranges
+])
+def test_attention_decode_key_ranges(chunk, ctx, window):
+    """One key range per request (the kernel writes the output itself) and several (partial results,
+    merged by a second kernel), with ranges that are empty for the shorter requests."""
+    assert _attention_case(8, 2, 128, ctx, [1] * len(ctx), 64, window, torch.bfloat16, "decode_tma", decode_chunk=chunk) < 1.2e-2
+    assert _attention_case(4, 1, 64, ctx[:2], [1, 1], 16, window, torch.bfloat16, "decode_tma", decode_chunk=chunk) < 1.2e-2
 
 
 def test_attention_kernels_refuse_what_they_do_not_cover():
