@@ -172,8 +172,136 @@ struct Smem {
 
 __device__ __forceinline__ float silu_mul(float g, float u) { return g / (1.0f + expf(-g)) * u; }
 
+// What the epilogue of the fused q/k/v projection needs (EPI = 2): the product's columns are
+// heads of 128 (nq query heads, then nkv key heads, then nkv value heads); query and key heads
+// get their RMSNorm (gain null: none) and the half-split rotation of the token's position (cos_t
+// null: none), values pass through; queries go to q_out [tokens, nq * 128], keys and values to
+// the token's place in the paged cache (k_pages null: nothing is written).
+struct RopeEpilogue {
+    qi::bf16* q_out;
+    const float* q_gain;
+    const float* k_gain;
+    const float* cos_t;      // [positions, 64]
+    const float* sin_t;
+    const int* positions;    // [tokens]
+    const int* token_req;    // [tokens]: row of the block table
+    const int* block_table;  // [requests, max_blocks]
+    qi::bf16* k_pages;       // [pages, nkv, page_size, 128]
+    qi::bf16* v_pages;
+    float eps;
+    int max_blocks, page_size, num_pages, nq, nkv;
+};
+
+__device__ __forceinline__ uint32_t pack2(float a, float b) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// One accumulator tile [128 tokens, BN columns] of the q/k/v projection: this thread owns token
+// `row` (TMEM lane) and walks the tile's heads. The norm's sum runs over the head's 128 columns
+// in column order; everything is 32-bit until the store.
+template <int BN>
+__device__ __forceinline__ void rope_epilogue(uint32_t tmem_tile, int col_base, int row, bool row_ok, int n_cols,
+                                              const RopeEpilogue& e, int* __restrict__ status) {
+    constexpr int D = 128, HALF = 64;
+    const int pos = row_ok ? e.positions[row] : 0;
+    int page = -2;           // -2: not looked up yet
+#pragma unroll 1
+    for (int hh = 0; hh < BN / D; ++hh) {
+        const int col0 = col_base + hh * D;
+        if (col0 >= n_cols) break;                       // the same for every thread of the CTA
+        const int head = col0 / D;
+        const bool is_q = head < e.nq, is_k = !is_q && head < e.nq + e.nkv;
+        const uint32_t t0 = tmem_tile + (uint32_t)(hh * D);
+        const float* gain = is_q ? e.q_gain : is_k ? e.k_gain : nullptr;
+        uint32_t lo[32], hi[32];
+        float inv = 1.f;
+        if (gain) {
+            float ss = 0.f;
+#pragma unroll 1
+            for (int c = 0; c < 4; ++c) {
+                tmem_ld32(t0 + 32u * c, lo);
+                tmem_ld_wait();
+#pragma unroll
+                for (int i = 0; i < 32; ++i) ss = fmaf(__uint_as_float(lo[i]), __uint_as_float(lo[i]), ss);
+            }
+            inv = 1.0f / sqrtf(ss / (float)D + e.eps);
+        }
+        qi::bf16* dst = nullptr;
+        if (row_ok) {
+            if (is_q) {
+                dst = e.q_out + ((size_t)row * e.nq + head) * D;
+            } else if (e.k_pages) {
+                if (page == -2) {
+                    page = e.block_table[(size_t)e.token_req[row] * e.max_blocks + pos / e.page_size];
+                    if (page < 0 || page >= e.num_pages) {
+                        if (status) atomicOr(status, qi::kStatusBadPage);
+                        page = -1;
+                    }
+                }
+                if (page >= 0) {
+                    const int hk = is_k ? head - e.nq : head - e.nq - e.nkv;
+                    dst = (is_k ? e.k_pages : e.v_pages) + (((size_t)page * e.nkv + hk) * e.page_size + (pos % e.page_size)) * (size_t)D;
+                }
+            }
+        }
+        const bool rotate = (is_q || is_k) && e.cos_t != nullptr;
+#pragma unroll 1
+        for (int c = 0; c < 2; ++c) {
+            tmem_ld32(t0 + 32u * c, lo);
+            tmem_ld32(t0 + (uint32_t)HALF + 32u * c, hi);
+            tmem_ld_wait();
+            if (!dst) continue;
+            float a[32], b[32];
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+                a[i] = __uint_as_float(lo[i]);
+                b[i] = __uint_as_float(hi[i]);
+            }
+            if (gain) {
+                const float4* ga = reinterpret_cast<const float4*>(gain + 32 * c);
+                const float4* gb = reinterpret_cast<const float4*>(gain + HALF + 32 * c);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    const float4 x = ga[i], y = gb[i];
+                    a[4 * i] = a[4 * i] * inv * x.x; a[4 * i + 1] = a[4 * i + 1] * inv * x.y;
+                    a[4 * i + 2] = a[4 * i + 2] * inv * x.z; a[4 * i + 3] = a[4 * i + 3] * inv * x.w;
+                    b[4 * i] = b[4 * i] * inv * y.x; b[4 * i + 1] = b[4 * i + 1] * inv * y.y;
+                    b[4 * i + 2] = b[4 * i + 2] * inv * y.z; b[4 * i + 3] = b[4 * i + 3] * inv * y.w;
+                }
+            }
+            if (rotate) {
+                const float4* cs = reinterpret_cast<const float4*>(e.cos_t + (size_t)pos * HALF + 32 * c);
+                const float4* sn = reinterpret_cast<const float4*>(e.sin_t + (size_t)pos * HALF + 32 * c);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    const float4 cc = cs[i], ss = sn[i];
+                    const float cv[4] = {cc.x, cc.y, cc.z, cc.w}, sv[4] = {ss.x, ss.y, ss.z, ss.w};
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const float x = a[4 * i + j], y = b[4 * i + j];
+                        a[4 * i + j] = x * cv[j] - y * sv[j];
+                        b[4 * i + j] = x * sv[j] + y * cv[j];
+                    }
+                }
+            }
+            uint4* d_lo = reinterpret_cast<uint4*>(dst + 32 * c);
+            uint4* d_hi = reinterpret_cast<uint4*>(dst + HALF + 32 * c);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                d_lo[i] = make_uint4(pack2(a[8 * i], a[8 * i + 1]), pack2(a[8 * i + 2], a[8 * i + 3]),
+                                     pack2(a[8 * i + 4], a[8 * i + 5]), pack2(a[8 * i + 6], a[8 * i + 7]));
+                d_hi[i] = make_uint4(pack2(b[8 * i], b[8 * i + 1]), pack2(b[8 * i + 2], b[8 * i + 3]),
+                                     pack2(b[8 * i + 4], b[8 * i + 5]), pack2(b[8 * i + 6], b[8 * i + 7]));
+            }
+        }
+    }
+}
+
 // EPI = 0: store the product. EPI = 1: the product's columns come in pairs (gate, up) and
 // the kernel stores silu(gate) * up, half as wide (the feed-forward's activation fused in).
+// EPI = 2 (operands not swapped): the product is the q/k/v projection and `rope` says where
+// its heads go (q/k norm, rotation and the cache write fused in; `out` is not used).
 //
 // The kernel is persistent: CTA c takes tiles c, c + gridDim.x, ... of the linear tile
 // list (A tiles fastest, then B tiles, then K splits, so CTAs that run together share a
@@ -184,7 +312,8 @@ template <int BN, int STAGES, bool SWAP, typename TOut, int EPI>
 __global__ void __launch_bounds__(kThreads)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                     TOut* __restrict__ out, int rows_a, int rows_b, int K, long long ld_out,
-                    int kb_per_split, int n_splits, long long split_stride, int* __restrict__ status) {
+                    int kb_per_split, int n_splits, long long split_stride, int* __restrict__ status,
+                    const RopeEpilogue rope) {
     extern __shared__ uint8_t smem_raw[];
     using L = Smem<BN, STAGES>;
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -350,6 +479,14 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             }
             tc_fence_after();
             const int a_row = tile_a * BM + quarter * 32 + lane;
+            if constexpr (EPI == 2 && BN % 128 == 0) {
+                rope_epilogue<BN>(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)acc * kAccCols, tile_b * BN, a_row,
+                                  a_row < rows_a, rows_b, rope, status);
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(acc_empty_bar(acc));
+                continue;
+            }
             TOut* obase = out + (size_t)split * split_stride;
             constexpr int kChunk = BN >= 32 ? 32 : 16;
 #pragma unroll 1
@@ -507,7 +644,8 @@ int sm_count() {
 
 template <int BN, int STAGES, bool SWAP, typename TOut, int EPI>
 int launch(const CUtensorMap& ma, const CUtensorMap& mb, TOut* out, int rows_a, int rows_b, int K, long long ld,
-           int splits, int kb_per_split, long long split_stride, int* status, cudaStream_t stream) {
+           int splits, int kb_per_split, long long split_stride, int* status, cudaStream_t stream,
+           const RopeEpilogue& rope = RopeEpilogue{}) {
     auto kern = gemm_tcgen05_kernel<BN, STAGES, SWAP, TOut, EPI>;
     constexpr int smem = Smem<BN, STAGES>::kTotal;
     static bool configured = false;
@@ -522,7 +660,7 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, TOut* out, int rows_a, 
     const long long resident = (long long)sm_count() * per_sm;
     const unsigned grid = (unsigned)(tiles < resident ? tiles : resident);
     qi::launch(kern, dim3(grid), dim3(kThreads), smem, stream, ma, mb, out, rows_a, rows_b, K, ld, kb_per_split, splits,
-               split_stride, status);
+               split_stride, status, rope);
     return qi::check_launch("gemm_bf16");
 }
 
@@ -611,4 +749,46 @@ extern "C" int qi_gemm_bf16(const void* x, const void* w, void* out, int out_dty
                     : launch_bn<false, float>(bn, ma, mb, (float*)out, rows_a, rows_b, K, N, 1, kb_per_split, 0, status, stream);
     return swap ? launch_bn<true, qi::bf16>(bn, ma, mb, (qi::bf16*)out, rows_a, rows_b, K, N, 1, kb_per_split, 0, status, stream)
                 : launch_bn<false, qi::bf16>(bn, ma, mb, (qi::bf16*)out, rows_a, rows_b, K, N, 1, kb_per_split, 0, status, stream);
+}
+
+// The q/k/v projection of many tokens with what follows it fused into the epilogue:
+// [q | k | v] = x[M, K] . w[(nq + 2 nkv) * 128, K]^T, then RMSNorm of every query and key head
+// (gains null: none), the half-split rotation by the token's position (cos_t null: none), queries
+// to q_out [M, nq * 128], keys and values to the paged cache (k_pages null: not written). Head size
+// 128, rotation over the whole head, bfloat16 throughout. The operands are not swapped, so this is
+// the path for prompts; few tokens go through qi_gemm_bf16 (K split) and qi_qk_norm_rope_kv.
+extern "C" int qi_gemm_bf16_qkv_rope(const void* x, const void* w, int M, int K, void* q_out, const float* q_gain,
+                                     const float* k_gain, float eps, const float* cos_t, const float* sin_t,
+                                     int table_positions, const int* positions, const int* token_req,
+                                     const int* block_table, int max_blocks, int page_size, int num_pages,
+                                     void* k_pages, void* v_pages, int nq, int nkv, int* status, cudaStream_t stream) {
+    QI_REQUIRE(M > 0 && K > 0 && nq > 0 && nkv > 0, "gemm_bf16_qkv_rope: bad sizes M=%d K=%d heads %d/%d", M, K, nq, nkv);
+    QI_REQUIRE(K % 8 == 0, "gemm_bf16_qkv_rope: K=%d must be a multiple of 8 (16-byte rows for TMA)", K);
+    QI_REQUIRE(((uintptr_t)x & 15) == 0 && ((uintptr_t)w & 15) == 0 && ((uintptr_t)q_out & 15) == 0 &&
+               ((uintptr_t)k_pages & 15) == 0 && ((uintptr_t)v_pages & 15) == 0,
+               "gemm_bf16_qkv_rope: operands, q_out and pages must be 16-byte aligned");
+    QI_REQUIRE(q_out && positions, "gemm_bf16_qkv_rope: q_out and positions are needed");
+    QI_REQUIRE((cos_t == nullptr) == (sin_t == nullptr) && (!cos_t || table_positions > 0), "gemm_bf16_qkv_rope: incomplete rotation table");
+    QI_REQUIRE(((uintptr_t)cos_t & 15) == 0 && ((uintptr_t)sin_t & 15) == 0 && ((uintptr_t)q_gain & 15) == 0 && ((uintptr_t)k_gain & 15) == 0,
+               "gemm_bf16_qkv_rope: gains and tables must be 16-byte aligned");
+    QI_REQUIRE((k_pages == nullptr) == (v_pages == nullptr), "gemm_bf16_qkv_rope: k and v pages must come together");
+    QI_REQUIRE(!k_pages || (page_size > 0 && max_blocks > 0 && num_pages > 0 && block_table && token_req),
+               "gemm_bf16_qkv_rope: incomplete page arguments");
+    const long long n_ll = (long long)(nq + 2 * nkv) * 128;
+    QI_REQUIRE(n_ll < 2147483647LL, "gemm_bf16_qkv_rope: too many heads");
+    const int N = (int)n_ll;
+    const int bn = N >= 256 ? 256 : 128;
+    const int kb_total = (K + BK - 1) / BK;
+    QI_REQUIRE((long long)((M + BM - 1) / BM) * ((N + bn - 1) / bn) < 2147483647LL, "gemm_bf16_qkv_rope: too many tiles");
+    CUtensorMap ma, mb;
+    if (make_map(&ma, x, M, K, BM)) return 1;
+    if (make_map(&mb, w, N, K, bn)) return 1;
+    RopeEpilogue e;
+    e.q_out = (qi::bf16*)q_out; e.q_gain = q_gain; e.k_gain = k_gain; e.cos_t = cos_t; e.sin_t = sin_t;
+    e.positions = positions; e.token_req = token_req; e.block_table = block_table;
+    e.k_pages = (qi::bf16*)k_pages; e.v_pages = (qi::bf16*)v_pages; e.eps = eps;
+    e.max_blocks = max_blocks; e.page_size = page_size; e.num_pages = num_pages; e.nq = nq; e.nkv = nkv;
+    if (bn == 256)
+        return launch<256, stages_of(256), false, qi::bf16, 2>(ma, mb, (qi::bf16*)nullptr, M, N, K, N, 1, kb_total, 0, status, stream, e);
+    return launch<128, stages_of(128), false, qi::bf16, 2>(ma, mb, (qi::bf16*)nullptr, M, N, K, N, 1, kb_total, 0, status, stream, e);
 }

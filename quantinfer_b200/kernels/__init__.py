@@ -465,6 +465,57 @@ def advance_decode(token_ids, positions, start_pos, kv_len, counter, sampled, hi
     _check(rc, "advance_decode")
 
 
+def gemm_qkv_rope_supported(M: int, K: int, d: int, rotary_dim: int, dtype, weight_dtype) -> bool:
+    """Whether `gemm_qkv_rope` takes this problem: many tokens (the operands are not swapped),
+    bfloat16, heads of 128, rotation over the whole head or none."""
+    return (M > 256 and K % 8 == 0 and d == 128 and rotary_dim in (0, d)
+            and dtype == torch.bfloat16 and weight_dtype == torch.bfloat16)
+
+
+def gemm_qkv_rope(x, w, q_out, q_gain, k_gain, eps, cos, sin, positions, token_req, block_table, page_size,
+                  k_pages, v_pages, nq, nkv, status) -> None:
+    """The q/k/v projection x[M, K] @ w[(nq + 2 nkv) 128, K]^T on the tcgen05 tensor cores with
+    the q/k RMSNorm, the rotation and the cache write in its epilogue: what `gemm_bf16` followed
+    by `qk_norm_rope_kv` computes, without the projection's output crossing memory.
+    Arguments as for `qk_norm_rope_kv`."""
+    d = 128
+    _req(x, "x", torch.bfloat16, 2)
+    _req(w, "w", torch.bfloat16, 2)
+    _req(q_out, "q_out", torch.bfloat16, 2)
+    M, K = x.shape
+    if tuple(w.shape) != ((nq + 2 * nkv) * d, K) or tuple(q_out.shape) != (M, nq * d):
+        raise KernelError(f"gemm_qkv_rope: x {tuple(x.shape)}, w {tuple(w.shape)}, q_out {tuple(q_out.shape)} do not match heads {nq}+2*{nkv} of {d}")
+    for g, name in ((q_gain, "q_gain"), (k_gain, "k_gain")):
+        if g is not None:
+            _req(g, name, torch.float32, 1)
+            if g.numel() != d:
+                raise KernelError(f"{name} has {g.numel()} elements, head_dim is {d}")
+    table_positions = 0
+    if cos is not None:
+        _req(cos, "cos", torch.float32, 2)
+        _req(sin, "sin", torch.float32, 2)
+        if cos.shape != sin.shape or cos.shape[1] * 2 != d:
+            raise KernelError("gemm_qkv_rope: rotation tables must cover the whole head")
+        table_positions = cos.shape[0]
+    _req(positions, "positions", torch.int32, 1)
+    _req(token_req, "token_req", torch.int32, 1)
+    if positions.numel() != M or token_req.numel() != M:
+        raise KernelError("gemm_qkv_rope: positions and token_req must have one entry per token")
+    num_pages, max_blocks = 0, 0
+    if k_pages is not None:
+        _req(k_pages, "k_pages", torch.bfloat16, 4)
+        _req(v_pages, "v_pages", torch.bfloat16, 4)
+        _req(block_table, "block_table", torch.int32, 2)
+        if tuple(k_pages.shape[1:]) != (nkv, page_size, d) or k_pages.shape != v_pages.shape:
+            raise KernelError(f"gemm_qkv_rope: pages {tuple(k_pages.shape)} do not match (pages, {nkv}, {page_size}, {d})")
+        num_pages, max_blocks = k_pages.shape[0], block_table.shape[1]
+    rc = library().qi_gemm_bf16_qkv_rope(
+        _ptr(x), _ptr(w), M, K, _ptr(q_out), _ptr(q_gain), _ptr(k_gain), C.c_float(eps), _ptr(cos), _ptr(sin),
+        table_positions, _ptr(positions), _ptr(token_req), _ptr(block_table), max_blocks, page_size, num_pages,
+        _ptr(k_pages), _ptr(v_pages), nq, nkv, _ptr(status), _stream())
+    _check(rc, "gemm_qkv_rope")
+
+
 # --------------------------------------------------------------------------
 # tensor-core matrix product (bfloat16 operands, 32-bit accumulation)
 

@@ -75,10 +75,20 @@ class Attention(Part):
         rt = self.runtime
         n = x.shape[0]
         pos = self.position
-        # K-split partial sums of the projection are added by the next kernel where it can take them
-        qkv = self.qkv(x, keep_partials=self.d % 4 == 0 and (pos is None or pos.rotary_dim == self.d))
         q = torch.empty((n, self.nq * self.d), dtype=x.dtype, device=x.device)
         table = batch.block_tables[cache.group]
+        if kernels.gemm_qkv_rope_supported(n, x.shape[1], self.d, pos.rotary_dim if pos else 0, x.dtype, self.qkv.weight.dtype):
+            # many tokens: norm, rotation and the cache write ride in the projection's epilogue
+            kernels.gemm_qkv_rope(
+                x, self.qkv.weight, q, self.q_gain, self.k_gain, self.spec.qk_norm_eps,
+                pos.cos if pos else None, pos.sin if pos else None, batch.positions, batch.token_req, table,
+                cache.page_size, cache.k_pages if cache.writes else None, cache.v_pages if cache.writes else None,
+                self.nq, self.nkv, rt.status)
+            out = torch.empty_like(q)
+            self.attend(q, out, batch, cache, table)
+            return self.o(out, keep_partials=True)
+        # K-split partial sums of the projection are added by the next kernel where it can take them
+        qkv = self.qkv(x, keep_partials=self.d % 4 == 0 and (pos is None or pos.rotary_dim == self.d))
         kernels.qk_norm_rope_kv(
             qkv, q, self.q_gain, self.k_gain, self.spec.qk_norm_eps,
             pos.cos if pos else None, pos.sin if pos else None, pos.rotary_dim if pos else 0,

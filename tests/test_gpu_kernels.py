@@ -137,6 +137,70 @@ def test_gemm_tcgen05_silu_epilogue_and_partials(M, N, K):
 
 # ------------------------------------------------------------------ q/k norm, rotation, cache write
 
+@pytest.mark.parametrize("M, K, nq, nkv, ps, norm, rope, write", [
+    (300, 64, 2, 1, 16, True, True, True),      # 4 heads: two tiles of 256 columns; a ragged last row tile
+    (257, 136, 3, 1, 8, True, True, True),      # 5 heads: the last tile is half empty; K no multiple of 64
+    (513, 256, 1, 1, 64, False, True, True),    # 3 heads: one tile of 256 and a half; no norm
+    (384, 72, 1, 2, 32, True, False, True),     # no rotation
+    (260, 64, 2, 1, 16, True, True, False),     # reads another layer's cache: queries only
+])
+def test_gemm_qkv_rope(M, K, nq, nkv, ps, norm, rope, write):
+    """The q/k/v projection with norm, rotation and cache write in its epilogue, against a 64-bit
+    product followed by the formulas; heads that straddle tile borders, rows past the last token."""
+    torch.manual_seed(M + K)
+    d, eps, theta, max_pos = 128, 1e-5, 1e4, 700
+    k = _k()
+    assert k.gemm_qkv_rope_supported(M, K, d, d if rope else 0, torch.bfloat16, torch.bfloat16)
+    assert not k.gemm_qkv_rope_supported(200, K, d, d, torch.bfloat16, torch.bfloat16)
+    assert not k.gemm_qkv_rope_supported(M, K, 64, 64, torch.bfloat16, torch.bfloat16)
+    x = torch.randn(M, K).bfloat16()
+    w = (torch.randn((nq + 2 * nkv) * d, K) / K ** 0.5).bfloat16()
+    qg, kg = (1 + 0.1 * torch.randn(d), 1 + 0.1 * torch.randn(d)) if norm else (None, None)
+    inv_freq = torch.pow(torch.tensor(theta), -(2.0 * torch.arange(d // 2)) / d)
+    cos, sin = k.rope_table(inv_freq.to(DEV), max_pos) if rope else (None, None)
+    ang = torch.arange(max_pos, dtype=torch.float64)[:, None] * inv_freq.double()[None, :]
+    # two requests: the first holds 40 earlier positions, the second starts at 0
+    n0 = M // 3
+    positions = list(range(40, 40 + n0)) + list(range(0, M - n0))
+    token_req = [0] * n0 + [1] * (M - n0)
+    max_blocks = -(-max_pos // ps)
+    num_pages = 2 * max_blocks + 3
+    perm = torch.randperm(num_pages).tolist()
+    table = torch.tensor([[perm.pop() for _ in range(max_blocks)] for _ in range(2)], dtype=torch.int32)
+    kp = torch.zeros(num_pages, nkv, ps, d, dtype=torch.bfloat16, device=DEV)
+    vp = torch.zeros_like(kp)
+    q_out = torch.empty(M, nq * d, dtype=torch.bfloat16, device=DEV)
+    st = _status()
+    k.gemm_qkv_rope(x.to(DEV), w.to(DEV), q_out, qg.to(DEV) if norm else None, kg.to(DEV) if norm else None, eps, cos, sin,
+                    I(positions), I(token_req), table.to(DEV), ps, kp if write else None, vp if write else None, nq, nkv, st)
+    assert st.item() == 0
+    y = (x.double() @ w.double().T).reshape(M, nq + 2 * nkv, d)
+
+    def norm_rot(h, gain, pos):
+        if gain is not None:
+            h = h * torch.rsqrt((h * h).mean(-1, keepdim=True) + eps) * gain.double()
+        if not rope:
+            return h
+        c, s = torch.cos(ang[pos])[:, None, :], torch.sin(ang[pos])[:, None, :]
+        a, b = h[..., :d // 2], h[..., d // 2:]
+        return torch.cat([a * c - b * s, a * s + b * c], dim=-1)
+
+    pos_t = torch.tensor(positions)
+    ref_q = norm_rot(y[:, :nq], qg, pos_t)
+    ref_k = norm_rot(y[:, nq:nq + nkv], kg, pos_t)
+    ref_v = y[:, nq + nkv:]
+    tol = 2e-2    # bfloat16 output of values up to about 4
+    assert float((q_out.double().cpu().reshape(M, nq, d) - ref_q).abs().max()) < tol
+    if not write:
+        assert float(kp.abs().sum()) == 0 and float(vp.abs().sum()) == 0
+        return
+    pages = table[torch.tensor(token_req), pos_t // ps].long()
+    rows = pos_t % ps
+    assert float((kp.cpu()[pages, :, rows].double() - ref_k).abs().max()) < tol
+    assert float((vp.cpu()[pages, :, rows].double() - ref_v).abs().max()) < tol
+    assert int((kp.abs().sum(dim=(1, 3)) > 0).sum()) == M            # nothing else was touched
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("nq, nkv, d, rot, ps", [(4, 2, 16, 16, 4), (6, 3, 48, 48, 32), (8, 1, 128, 128, 64),
                                                 (3, 3, 34, 34, 5), (4, 2, 32, 16, 8)])
