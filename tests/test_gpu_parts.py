@@ -1,7 +1,7 @@
 """Each part alone against the plain implementation's function for it, and what makes
 the parts general: layers that differ inside one model, a windowed layer with pages
 of its own, a run order that names a layer twice or lets a layer read another
-layer's cache, and a toy mixer with per-request state that is registered, built and
+layer's cache, a toy feed-forward with routing and a toy position encoding, and a toy mixer with per-request state that is registered, built and
 stepped from here without touching the framework's files."""
 
 import dataclasses
@@ -352,3 +352,118 @@ def test_toy_mixer_with_state_is_registered_built_and_stepped():
     assert float((torch.cat(got_a) - ref_a).abs().max()) < 2e-5
     assert float((torch.cat(got_b) - ref_b).abs().max()) < 2e-5
     assert not torch.allclose(ref_a[5], whole(ids_a[5:])[0])       # the recurrence does depend on its past
+
+
+# ------------------------------------------------------------------ a toy feed-forward with routing, another position encoding
+
+@dataclasses.dataclass(frozen=True)
+class ToyRoutedSpec:
+    hidden_size: int
+    experts: int
+    prefix: str = ""
+    kind: str = "toy_top1_experts"
+
+
+@dataclasses.dataclass(frozen=True)
+class ToyAnglesSpec:
+    head_dim: int
+    rotary_dim: int
+    step: float
+    max_positions: int
+    kind: str = "toy_linear_angles"
+
+
+def _register_toy_ffn_and_position():
+    from quantinfer_b200.parts import Part, register_part
+    from quantinfer_b200.weights import TensorNeed
+
+    class ToyTop1Experts(Part):
+        """y = p_e * W_e x with e = argmax of the router's 32-bit logits and p its softmax: every token
+        takes one of `experts` small matrices. Written with torch operations: a test double."""
+
+        @classmethod
+        def needs_of_spec(cls, spec):
+            h, p = spec.hidden_size, spec.prefix
+            needs = {p + "router.weight": TensorNeed((spec.experts, h))}
+            for e in range(spec.experts):
+                needs[p + f"expert{e}.weight"] = TensorNeed((h, h))
+            return needs
+
+        def load(self, tensors):
+            p, dev = self.spec.prefix, self.runtime.device
+            self.router = tensors[p + "router.weight"].to(dev, torch.float32)
+            self.experts = torch.stack([tensors[p + f"expert{e}.weight"].to(dev, torch.float32) for e in range(self.spec.experts)])
+
+        def forward(self, x):
+            logits = x.float() @ self.router.t()
+            prob, which = torch.softmax(logits, dim=-1).max(dim=-1)
+            y = torch.einsum("nh,nkh->nk", x.float(), self.experts[which]) * prob[:, None]
+            return y.to(x.dtype)
+
+    class ToyLinearAngles(Part):
+        """Pair p of a head turns by position * step * (p + 1): the mixer's interface to a position
+        encoding is its cos/sin table [positions, rotary_dim / 2] and `rotary_dim`."""
+
+        def __init__(self, spec, runtime):
+            super().__init__(spec, runtime)
+            self.rotary_dim = spec.rotary_dim
+            ang = _toy_angles(spec, range(spec.max_positions)).to(runtime.device)
+            self.cos, self.sin = torch.cos(ang).contiguous(), torch.sin(ang).contiguous()
+
+    register_part("ffn", "toy_top1_experts", ToyTop1Experts)
+    register_part("position", "toy_linear_angles", ToyLinearAngles)
+
+
+def _toy_angles(spec, positions):
+    pos = torch.tensor(list(positions), dtype=torch.float32)
+    return pos[:, None] * (spec.step * torch.arange(1, spec.rotary_dim // 2 + 1, dtype=torch.float32))[None, :]
+
+
+def test_toy_feed_forward_with_routing_and_another_position_encoding():
+    """Layer 1 has a routed feed-forward and layer 2 a position encoding of its own, both registered
+    here; the model is built from the spec and stepped in portions, against the plain parts."""
+    from quantinfer_b200.config import AttentionSpec, LayerSpec, NormSpec
+    from plain.plain_qwen3 import plain_apply_rope
+
+    _register_toy_ffn_and_position()
+    T = _SpecTools
+    hidden, d = 48, 16
+    pos2 = ToyAnglesSpec(d, d, 0.013, 128)
+    l1 = T.layer(1)
+    l1 = LayerSpec(l1.mixer_norm, l1.mixer, l1.ffn_norm, ToyRoutedSpec(hidden, 3, "l1.moe."))
+    l2 = T.layer(2, mixer=AttentionSpec(hidden, 4, 2, d, pos2, qk_norm=True, window=None, prefix="l2.attn."))
+    spec = T.tiny_spec([T.layer(0), l1, l2])
+    eng, tensors = _engine(spec)
+    assert "l1.moe.router.weight" in tensors and "l1.moe.expert2.weight" in tensors
+    ids = [int(x) for x in torch.randint(0, 97, (60,))]
+    got = _run_in_portions(eng, ids, (21, 1, 1, 30, 2, 5))
+
+    w = {k: v.float() for k, v in tensors.items()}
+    h = plain_embedding(w["emb.weight"], ids)
+    n_tok = len(ids)
+    used = set()
+    for i, L in enumerate(spec.layers):
+        a = L.mixer
+        n = plain_rms_norm(h, w[L.mixer_norm.prefix + "weight"], L.mixer_norm.eps)
+        p = a.prefix
+        if a.position.kind == "toy_linear_angles":
+            ang = _toy_angles(a.position, range(n_tok))
+            cos, sin = torch.cos(ang), torch.sin(ang)
+        else:
+            cos, sin = plain_rope_tables(a.position.theta, d, list(range(n_tok)))
+        q = plain_rms_norm(plain_linear(n, w[p + "q_proj.weight"]).reshape(n_tok, a.num_heads, d), w[p + "q_norm.weight"], a.qk_norm_eps)
+        k = plain_rms_norm(plain_linear(n, w[p + "k_proj.weight"]).reshape(n_tok, a.num_kv_heads, d), w[p + "k_norm.weight"], a.qk_norm_eps)
+        v = plain_linear(n, w[p + "v_proj.weight"]).reshape(n_tok, a.num_kv_heads, d)
+        att = plain_gqa_attention(plain_apply_rope(q, cos, sin), plain_apply_rope(k, cos, sin), v, None).reshape(n_tok, a.num_heads * d)
+        h = h + plain_linear(att, w[p + "o_proj.weight"])
+        n = plain_rms_norm(h, w[L.ffn_norm.prefix + "weight"], L.ffn_norm.eps)
+        if L.ffn.kind == "toy_top1_experts":
+            fp = L.ffn.prefix
+            prob, which = torch.softmax(n @ w[fp + "router.weight"].t(), dim=-1).max(dim=-1)
+            used |= set(which.tolist())
+            h = h + torch.stack([w[fp + f"expert{int(e)}.weight"] @ n[t] for t, e in enumerate(which)]) * prob[:, None]
+        else:
+            h = h + plain_feed_forward(n, w, L.ffn.prefix)
+    ref = plain_linear(plain_rms_norm(h, w["final.weight"], spec.final_norm.eps), w["emb.weight"])
+    assert len(used) > 1, "the router sent every token to one expert: the test shows nothing"
+    assert float((got - ref).abs().max()) < 5e-5
