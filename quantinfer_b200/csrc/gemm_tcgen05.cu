@@ -684,18 +684,55 @@ int launch_bn(int bn, const CUtensorMap& ma, const CUtensorMap& mb, TOut* out, i
 
 }  // namespace
 
-// Workspace bytes `qi_gemm_bf16` needs for the split count it would choose (0: none).
-extern "C" int qi_gemm_bf16_plan(int M, int N, int K, int* swap, int* bn, int* splits) {
+// The orientation, tile width and K split `qi_gemm_bf16` uses when the caller does not say
+// (allow_split 0: the caller needs the whole sum in one CTA, as the fused activation does).
+//
+// Up to 64 tokens the product is a weight stream: the weights are the 128-row operand, the
+// tokens the narrow one, and K is split until about 148 CTAs pull weights.
+// Above that, the candidates (tokens as the narrow operand in one tile of 128 or 256 while they
+// fit; tokens as the 128-row operand with weight tiles of 256 or 128; K in 1 to 16 parts) are
+// compared by a count of k blocks per SM: waves of CTAs x (k blocks of a CTA + 12 for its start
+// and its epilogue) x the relative cost of a k block at that width, plus what the partial sums
+// cost to write and to read again (at 5.5 TB/s, in units of a 128 x 256 k block = 0.27 us).
+// Splitting K fills the SMs when there are few tiles (a 4096-wide product of 512 tokens has 64
+// tiles of 128 x 256) and evens out a ragged last wave; its price grows with the tokens. The
+// constants were fitted to a sweep of all candidates over 72 to 4,096 tokens at four layer
+// shapes: the choice is within 1% of the best candidate on average, 10% at worst.
+extern "C" int qi_gemm_bf16_plan(int M, int N, int K, int allow_split, int* swap, int* bn, int* splits) {
     const int kb_total = (K + BK - 1) / BK;
-    int sw = M <= 256 ? 1 : 0, b, sp = 1;
-    if (sw) {
-        b = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : 256;
+    int sw = 1, b = 256, sp = 1;
+    if (M <= 64) {
+        b = M <= 16 ? 16 : M <= 32 ? 32 : 64;
         const int tiles = (N + BM - 1) / BM;
         // enough CTAs to keep the weight stream busy on 148 SMs, at least 8 k blocks per split
         // (filling every resident slot with 6 or 9 splits was measured no faster than powers of two)
-        while (tiles * sp < 148 && sp * 2 <= 16 && kb_total / (sp * 2) >= 8) sp *= 2;
+        while (allow_split && tiles * sp < 148 && sp * 2 <= 16 && kb_total / (sp * 2) >= 8) sp *= 2;
     } else {
-        b = N >= 256 ? 256 : N > 64 ? 128 : N > 32 ? 64 : N > 16 ? 32 : 16;
+        const int sms = sm_count();
+        double best = 1e30;
+        const int split_choices[8] = {1, 2, 3, 4, 6, 8, 12, 16};
+        for (int cand = 0; cand < 3; ++cand) {
+            // 0: tokens narrow, one tile; 1, 2: tokens in rows of 128, weight tiles of 256, 128
+            if (cand == 0 && M > 256) continue;
+            const int c_swap = cand == 0, c_bn = cand == 0 ? (M <= 128 ? 128 : 256) : cand == 1 ? 256 : 128;
+            const int rows_a = c_swap ? N : M, rows_b = c_swap ? M : N;
+            const double k_cost = (c_bn == 256 ? 1.0 : 0.65) * (c_swap ? 1.05 : 1.0);
+            for (int si = 0; si < (allow_split ? 8 : 1); ++si) {
+                const int s = split_choices[si];
+                const int kbs = (kb_total + s - 1) / s;
+                if (s > 1 && ((s - 1) * kbs >= kb_total || kbs < 8)) continue;
+                const long long units = (long long)((rows_a + BM - 1) / BM) * ((rows_b + c_bn - 1) / c_bn) * s;
+                const long long waves = (units + sms - 1) / sms;
+                double cost = (double)waves * (kbs + 12) * k_cost;
+                if (s > 1) cost += (double)s * M * N * 8.0 / 5.5e12 / 0.27e-6;
+                if (cost < best * 0.999) {
+                    best = cost;
+                    sw = c_swap;
+                    b = c_bn;
+                    sp = s;
+                }
+            }
+        }
     }
     *swap = sw; *bn = b; *splits = sp;
     return 0;
@@ -777,7 +814,9 @@ extern "C" int qi_gemm_bf16_qkv_rope(const void* x, const void* w, int M, int K,
     const long long n_ll = (long long)(nq + 2 * nkv) * 128;
     QI_REQUIRE(n_ll < 2147483647LL, "gemm_bf16_qkv_rope: too many heads");
     const int N = (int)n_ll;
-    const int bn = N >= 256 ? 256 : 128;
+    int plan_swap, bn, plan_splits;
+    qi_gemm_bf16_plan(M > 256 ? M : 257, N, K, 0, &plan_swap, &bn, &plan_splits);   // the width for operands that are not swapped
+    if (bn < 128) bn = 128;                                                        // a tile holds whole heads
     const int kb_total = (K + BK - 1) / BK;
     QI_REQUIRE((long long)((M + BM - 1) / BM) * ((N + bn - 1) / bn) < 2147483647LL, "gemm_bf16_qkv_rope: too many tiles");
     CUtensorMap ma, mb;

@@ -24,7 +24,7 @@ STATUS_BAD_PAGE = 2
 STATUS_NON_FINITE = 4
 STATUS_WAIT_TIMEOUT = 8
 
-ABI_VERSION = 4
+ABI_VERSION = 5
 
 
 def status_names(code: int) -> list:
@@ -527,10 +527,11 @@ def gemm_bf16_supported(M: int, N: int, K: int, out_dtype) -> bool:
     return M > 0 and K % 8 == 0 and out_dtype in (torch.bfloat16, torch.float32)
 
 
-def gemm_bf16_plan(M: int, N: int, K: int):
-    """(swap operands, tile width, K splits) the library would choose."""
+def gemm_bf16_plan(M: int, N: int, K: int, allow_split: bool = True):
+    """(swap operands, tile width, K splits) the library would choose; allow_split=False for a
+    product whose epilogue needs the whole sum (the fused activation)."""
     swap, bn, splits = C.c_int(), C.c_int(), C.c_int()
-    library().qi_gemm_bf16_plan(M, N, K, C.byref(swap), C.byref(bn), C.byref(splits))
+    library().qi_gemm_bf16_plan(M, N, K, int(allow_split), C.byref(swap), C.byref(bn), C.byref(splits))
     return bool(swap.value), bn.value, splits.value
 
 
@@ -546,12 +547,12 @@ def gemm_bf16(x: torch.Tensor, w: torch.Tensor, out, plan=None, status=None, epi
     _req(w, "w", torch.bfloat16, 2)
     M, K = x.shape
     N = w.shape[0]
-    swap, bn, splits = plan if plan is not None else gemm_bf16_plan(M, N, K)
+    if epilogue not in (None, "silu_mul"):
+        raise KernelError(f"gemm_bf16: unknown epilogue {epilogue!r}")
+    swap, bn, splits = plan if plan is not None else gemm_bf16_plan(M, N, K, allow_split=epilogue is None)
     epi = 0
     if epilogue == "silu_mul":
         epi, splits = 1, 1
-    elif epilogue is not None:
-        raise KernelError(f"gemm_bf16: unknown epilogue {epilogue!r}")
     n_out = N // 2 if epi else N
     partial_only = keep_partials and splits > 1
     if not partial_only:
