@@ -9,7 +9,10 @@ device with CUDA events around K decode steps that run without the host in the
 loop (CUDA-graph replay, sampling and feeding the token back on the device).
 `e2e` is the same rate through the Python entry point (`Model.generate_batch`,
 host token lists in and out; every step copies its batch arrays from pinned
-host memory and reads the sampled tokens back). `prefill` is one 2,048-token
+host memory and reads the sampled tokens back), counted over the steps in which
+every request of the batch decodes: from the moment the last request has its
+first token until the first request ends (the scheduler starts requests one
+prompt after the other, so they also end one after the other). `prefill` is one 2,048-token
 prompt in one step; `points` are decode rates at batch 1 and 64; `roofline`
 relates the decode step to HBM bandwidth (weights once + the live cache).
 Weights are random (seeded) and token ids synthetic: there is no checkpoint or
@@ -251,22 +254,28 @@ def main() -> int:
     stamps = []
     engine.h2d_bytes_max = 0
     model.generate_batch(prompts, max_new_tokens=n_new, eos_token_id=None,
-                         on_event=lambda ev: stamps.append((time.perf_counter(), ev.request_id)))
+                         on_event=lambda ev: stamps.append((time.perf_counter(), ev.request_id, getattr(ev, "stop_reason", None))))
     # bytes a decode step of the full batch copies host -> device: its packed batch arrays (token ids,
     # positions, lengths, slots, block tables)
     h2d_max = max([g["meta"].numel() * 4 for (b, _), g in engine._graphs.items() if b == args.batch] or [engine.h2d_bytes_max])
-    seen, t_all_first, after = set(), None, 0
-    for t, rid in stamps:
+    # the window in which the whole batch decodes: after the last request's first token, up to the
+    # step in which the first request ends
+    seen, t_all_first, t_end, after = set(), None, None, 0
+    for t, rid, stop in stamps:
         if t_all_first is None:
             seen.add(rid)
             if len(seen) == args.batch:
                 t_all_first = t
-        else:
+        elif t - t_all_first < 1e-4:                 # the events of one step arrive together:
+            continue                                 # the rest of the step that gave the last first token
+        elif t_end is None or t - t_end < 1e-4:
             after += 1
-    e2e_value = after / (stamps[-1][0] - t_all_first) if t_all_first and after else None
-    e2e = {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": h2d_max,
-           "d2h_bytes_per_step": 4 * args.batch + 4,
-           "ms_per_step": (stamps[-1][0] - t_all_first) * 1e3 / max(after // max(args.batch, 1), 1) if t_all_first and after else None}
+            if stop is not None and t_end is None:
+                t_end = t
+    ok = t_all_first is not None and t_end is not None and after >= args.batch
+    e2e = {"value": after / (t_end - t_all_first) if ok else None, "unit": "tokens/s", "h2d_bytes_per_step": h2d_max,
+           "d2h_bytes_per_step": 4 * args.batch + 4, "steps": after // max(args.batch, 1) if ok else 0,
+           "ms_per_step": (t_end - t_all_first) * 1e3 / (after / args.batch) if ok else None}
 
     line = {
         "metric": "decode tokens/s (Qwen3-8B sizes, random bf16 weights, 1 B200)",

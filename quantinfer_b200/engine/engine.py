@@ -173,9 +173,10 @@ class Engine:
     def _graph_step(self, entries, extra_positions: int = 0, device_tokens=None):
         """A batch of single decode tokens, all wanting their logits: the packed batch has a
         fixed layout per batch size, so the forward pass is captured once per size and
-        replayed; each step only copies the batch's arrays into the graph's buffer. With
-        `device_tokens` (int32 [entries], on the device) the token ids are taken from there
-        instead of from the entries, without the host seeing them."""
+        replayed; each step only copies the batch's arrays into the graph's buffer (a kernel
+        reads them from the pinned buffer they were packed into). With `device_tokens`
+        (int32 [entries], on the device) the token ids are taken from there instead of from
+        the entries, without the host seeing them."""
         starts, slots, buf, layout, q_start, lens = self._pack(entries)
         host, event = self._stage(buf)
         b = len(entries)
@@ -185,10 +186,8 @@ class Engine:
         g = self._graphs.get((b, bound))
         if g is None:
             meta = torch.empty(buf.size, dtype=torch.int32, device=self.device)
-            meta.copy_(host, non_blocking=True)
+            kernels.stage_step(host, meta, device_tokens)      # token_ids is the first part of the layout
             event.record()
-            if device_tokens is not None:
-                meta[:b].copy_(device_tokens)      # token_ids is the first part of the layout
             batch = batch_from_packed(meta, layout, entries, starts, slots, q_start, lens,
                                       len(self.cache.groups), self.cache.max_blocks)
             batch.max_kv_len = bound
@@ -204,10 +203,8 @@ class Engine:
             self._graphs[(b, bound)] = g = {"graph": graph, "meta": meta, "batch": batch, "logits": static_logits,
                                    "layout": layout, "launches": kernels.launches - before}
             return logits, g
-        g["meta"].copy_(host, non_blocking=True)
+        kernels.stage_step(host, g["meta"], device_tokens)
         event.record()
-        if device_tokens is not None:
-            g["meta"][:b].copy_(device_tokens)
         g["graph"].replay()
         kernels.launches += g["launches"]
         return g["logits"], g

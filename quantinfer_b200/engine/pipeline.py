@@ -109,7 +109,7 @@ class DecodePipeline:
                 self._host[turn] = torch.empty(io.numel(), dtype=torch.int32, pin_memory=True)
                 self._events[turn] = torch.cuda.Event()
             host, event = self._host[turn], self._events[turn]
-            host[:1 + b].copy_(io[:1 + b], non_blocking=True)
+            kernels.publish(io, host, 1 + b)
             event.record()
         except Exception:
             for rid in prepared:

@@ -516,6 +516,36 @@ def gemm_qkv_rope(x, w, q_out, q_gain, k_gain, eps, cos, sin, positions, token_r
     _check(rc, "gemm_qkv_rope")
 
 
+def stage_step(host_meta: torch.Tensor, meta: torch.Tensor, device_tokens=None) -> None:
+    """meta[:n] = host_meta[:n] read by a kernel straight from pinned host memory (n =
+    host_meta.numel()); the first device_tokens.numel() entries come from `device_tokens`
+    (int32, on the device) when given."""
+    if not isinstance(host_meta, torch.Tensor) or host_meta.is_cuda or not host_meta.is_pinned() or host_meta.dtype != torch.int32:
+        raise KernelError("stage_step: host_meta must be a pinned int32 host tensor")
+    _req(meta, "meta", torch.int32, 1)
+    n = host_meta.numel()
+    if meta.numel() < n:
+        raise KernelError(f"stage_step: meta has {meta.numel()} entries, {n} are needed")
+    n_tok = 0
+    if device_tokens is not None:
+        _req(device_tokens, "device_tokens", torch.int32, 1)
+        n_tok = device_tokens.numel()
+    rc = library().qi_stage_step(C.c_void_p(host_meta.data_ptr()), _ptr(meta), n, _ptr(device_tokens), n_tok, _stream())
+    _check(rc, "stage_step")
+
+
+def publish(src: torch.Tensor, host_out: torch.Tensor, n: int) -> None:
+    """host_out[:n] = src[:n], written by a kernel into pinned host memory; read it after an
+    event recorded behind this call."""
+    _req(src, "src", torch.int32, 1)
+    if host_out.is_cuda or not host_out.is_pinned() or host_out.dtype != torch.int32:
+        raise KernelError("publish: host_out must be a pinned int32 host tensor")
+    if n > src.numel() or n > host_out.numel():
+        raise KernelError("publish: more entries than the buffers hold")
+    rc = library().qi_publish(_ptr(src), C.c_void_p(host_out.data_ptr()), n, _stream())
+    _check(rc, "publish")
+
+
 # --------------------------------------------------------------------------
 # tensor-core matrix product (bfloat16 operands, 32-bit accumulation)
 
