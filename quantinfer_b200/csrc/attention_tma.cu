@@ -211,15 +211,83 @@ attention_prefill_tma_kernel(const __grid_constant__ CUtensorMap map_q, const __
 constexpr int kDecodeThreads = 128;
 constexpr int kDecodeStages = 3;
 
+// What the decode kernel needs to make its own queries and the step's new key and value from the
+// q/k/v projection (FUSED): the projection's output [tokens, width] in bfloat16, or its K-split
+// partial sums [splits, tokens, width] in 32-bit (added here in split order); the q/k RMSNorm
+// gains (null: none); the rotation table [positions, D / 2] (null: none); the cache pages to
+// write the new key and value into (null: another layer wrote them, nothing is computed).
+struct DecodeRope {
+    const void* qkv;
+    long long split_stride;     // elements between two splits
+    const float* q_gain;
+    const float* k_gain;
+    const float* cos_t;
+    const float* sin_t;
+    qi::bf16* k_pages;
+    qi::bf16* v_pages;
+    float eps;
+    int splits, width;
+};
+
+template <typename TIn> __device__ __forceinline__ float2 load2(const TIn* p);
+template <> __device__ __forceinline__ float2 load2<float>(const float* p) { return *reinterpret_cast<const float2*>(p); }
+template <> __device__ __forceinline__ float2 load2<qi::bf16>(const qi::bf16* p) {
+    return __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(p));
+}
+
+// One warp, one head of D elements at `src` (plus the other splits): the sum of the splits, the
+// RMSNorm with `gain` (null: none) and the half-split rotation by `pos` (cos_t null: none), in
+// 32-bit, in the order of the stand-alone kernel (qknorm_rope_kv.cu). Lane l holds elements
+// 2l, 2l + 1 (lo) and D/2 + 2l, D/2 + 2l + 1 (hi); lanes with 2l >= D/2 hold nothing.
+template <int D, typename TIn>
+__device__ __forceinline__ void head_norm_rope(const TIn* src, int splits, long long stride, const float* gain, float eps,
+                                               const float* cos_t, const float* sin_t, int pos, int lane,
+                                               float2& lo, float2& hi) {
+    constexpr int kHalf = D / 2;
+    const int p = 2 * lane;
+    const bool has = p < kHalf;
+    float2 a = make_float2(0.f, 0.f), b = make_float2(0.f, 0.f);
+    if (has) {
+        a = load2<TIn>(src + p);
+        b = load2<TIn>(src + p + kHalf);
+        for (int k = 1; k < splits; ++k) {
+            const float2 x = load2<TIn>(src + k * stride + p), y = load2<TIn>(src + k * stride + p + kHalf);
+            a.x += x.x; a.y += x.y;
+            b.x += y.x; b.y += y.y;
+        }
+    }
+    if (gain) {
+        float ss = a.x * a.x + a.y * a.y;
+        ss += b.x * b.x + b.y * b.y;
+        ss = qi::warp_sum(ss);
+        const float inv = 1.0f / sqrtf(ss / (float)D + eps);
+        if (has) {
+            const float2 ga = *reinterpret_cast<const float2*>(gain + p), gb = *reinterpret_cast<const float2*>(gain + p + kHalf);
+            a.x = a.x * inv * ga.x; a.y = a.y * inv * ga.y;
+            b.x = b.x * inv * gb.x; b.y = b.y * inv * gb.y;
+        }
+    }
+    lo = a;
+    hi = b;
+    if (cos_t && has) {
+        const float2 c = *reinterpret_cast<const float2*>(cos_t + (size_t)pos * kHalf + p);
+        const float2 sn = *reinterpret_cast<const float2*>(sin_t + (size_t)pos * kHalf + p);
+        lo = make_float2(a.x * c.x - b.x * sn.x, a.y * c.y - b.y * sn.y);
+        hi = make_float2(a.x * sn.x + b.x * c.x, a.y * sn.y + b.y * c.y);
+    }
+}
+
 // DIRECT: the request's keys are one range, and the CTA writes the attention output itself.
-template <int D, bool DIRECT>
+// FUSED: the queries and the step's new key and value are made here from the q/k/v projection
+// (`rope`), not read from `q` and the cache; TIn is the projection's element type.
+template <int D, bool DIRECT, bool FUSED, typename TIn>
 __global__ void __launch_bounds__(kDecodeThreads)
 attention_decode_tma_kernel(const qi::bf16* __restrict__ q, qi::bf16* __restrict__ out, const __grid_constant__ CUtensorMap map_k,
                             const __grid_constant__ CUtensorMap map_v, const int* __restrict__ block_table,
                             int max_blocks, int page_size, int box_rows, int num_pages,
                             const int* __restrict__ kv_len, const int* __restrict__ q_start,
                             float* __restrict__ ws_o, float* __restrict__ ws_ml, int nq, int nkv, float scale_log2e,
-                            int window, int chunk, int* __restrict__ status) {
+                            int window, int chunk, int* __restrict__ status, const DecodeRope rope) {
     extern __shared__ uint8_t smem_raw[];
     constexpr int kTileBytes = kTileKeys * D * 2;
     constexpr int kQBytes = 16 * D * 2;
@@ -231,6 +299,7 @@ attention_decode_tma_kernel(const qi::bf16* __restrict__ q, qi::bf16* __restrict
     const uint32_t bars = q_s + kQBytes;
     auto full_bar = [&](int s) { return bars + 8u * s; };
     int* s_table = reinterpret_cast<int*>(aligned + kDecodeStages * 2 * kTileBytes + kQBytes + 64);
+    qi::bf16* new_kv = reinterpret_cast<qi::bf16*>(s_table + kMaxTableEntries);   // [2][D]: this step's key and value (FUSED)
 
     // Lengths and block tables were copied before the step began, and keys and values of earlier
     // positions were written by earlier steps: only the newest key (position S - 1) and the
@@ -285,11 +354,51 @@ attention_decode_tma_kernel(const qi::bf16* __restrict__ q, qi::bf16* __restrict
     }
     qi::pdl_wait();
     constexpr int kChunks = D / 8;
-    for (int idx = threadIdx.x; idx < 16 * kChunks; idx += kDecodeThreads) {
-        const int row = idx / kChunks, c = idx % kChunks;
-        uint4 v = make_uint4(0u, 0u, 0u, 0u);
-        if (row < G) v = *reinterpret_cast<const uint4*>(q + ((size_t)tok * nq + (size_t)hk * G + row) * D + c * 8);
-        *reinterpret_cast<uint4*>(q_tile + RowSwizzle<D>::off(row, c)) = v;
+    // this CTA's range holds the step's own position: it makes the new key and value, writes them to
+    // the cache and, since its copy of that cache row may be older than the write, into its tile
+    const bool owns_new = FUSED && rope.k_pages != nullptr && k1 == S;
+    if constexpr (FUSED) {
+        const int pos = S - 1;
+        const TIn* tok_row = reinterpret_cast<const TIn*>(rope.qkv) + (size_t)tok * rope.width;
+        for (int row = warp; row < 16; row += kDecodeThreads / 32) {
+            float2 lo = make_float2(0.f, 0.f), hi = lo;
+            if (row < G)
+                head_norm_rope<D, TIn>(tok_row + (size_t)(hk * G + row) * D, rope.splits, rope.split_stride, rope.q_gain, rope.eps,
+                                       rope.cos_t, rope.sin_t, pos, lane, lo, hi);
+            const int p = 2 * lane;
+            if (p < D / 2) {
+                *reinterpret_cast<uint32_t*>(q_tile + RowSwizzle<D>::off(row, p >> 3) + (p & 7) * 2) = pack_bf16(lo.x, lo.y);
+                const int ph = p + D / 2;
+                *reinterpret_cast<uint32_t*>(q_tile + RowSwizzle<D>::off(row, ph >> 3) + (ph & 7) * 2) = pack_bf16(hi.x, hi.y);
+            }
+        }
+        if (owns_new && warp < 2) {
+            // warp 0: the key (norm, rotation); warp 1: the value (as it is)
+            const TIn* src = tok_row + (size_t)(nq + (warp == 0 ? 0 : nkv) + hk) * D;
+            float2 lo, hi;
+            head_norm_rope<D, TIn>(src, rope.splits, rope.split_stride, warp == 0 ? rope.k_gain : nullptr, rope.eps,
+                                   warp == 0 ? rope.cos_t : nullptr, rope.sin_t, pos, lane, lo, hi);
+            const int page = block_table[(size_t)b * max_blocks + pos / page_size];
+            const int p = 2 * lane;
+            if (page < 0 || page >= num_pages) {
+                if (lane == 0 && status) atomicOr(status, qi::kStatusBadPage);
+            } else if (p < D / 2) {
+                qi::bf16* dst = (warp == 0 ? rope.k_pages : rope.v_pages) + (((size_t)page * nkv + hk) * page_size + (pos % page_size)) * (size_t)D;
+                *reinterpret_cast<uint32_t*>(dst + p) = pack_bf16(lo.x, lo.y);
+                *reinterpret_cast<uint32_t*>(dst + p + D / 2) = pack_bf16(hi.x, hi.y);
+            }
+            if (p < D / 2) {
+                *reinterpret_cast<uint32_t*>(new_kv + warp * D + p) = pack_bf16(lo.x, lo.y);
+                *reinterpret_cast<uint32_t*>(new_kv + warp * D + p + D / 2) = pack_bf16(hi.x, hi.y);
+            }
+        }
+    } else {
+        for (int idx = threadIdx.x; idx < 16 * kChunks; idx += kDecodeThreads) {
+            const int row = idx / kChunks, c = idx % kChunks;
+            uint4 v = make_uint4(0u, 0u, 0u, 0u);
+            if (row < G) v = *reinterpret_cast<const uint4*>(q + ((size_t)tok * nq + (size_t)hk * G + row) * D + c * 8);
+            *reinterpret_cast<uint4*>(q_tile + RowSwizzle<D>::off(row, c)) = v;
+        }
     }
     __syncthreads();
     if (threadIdx.x == 0) {
@@ -312,6 +421,16 @@ attention_decode_tma_kernel(const qi::bf16* __restrict__ q, qi::bf16* __restrict
         const int t0 = t_begin + i * kTileKeys;
         ok = mbar_wait(full_bar(stage), (uint32_t)(i / kDecodeStages) & 1u);
         if (!ok) break;
+        if (owns_new && i == n_tiles - 1) {
+            // the tile's row of position S - 1 is replaced by what this CTA computed
+            const int r = S - 1 - t0;
+            if (threadIdx.x < 2 * kChunks) {
+                const int which = threadIdx.x / kChunks, c = threadIdx.x % kChunks;
+                *reinterpret_cast<uint4*>(aligned + stage * 2 * kTileBytes + which * kTileBytes + TmaSwizzle<kTileKeys>::off(r, c)) =
+                    *reinterpret_cast<const uint4*>(new_kv + which * D + c * 8);
+            }
+            __syncthreads();
+        }
         const int wkey0 = t0 + warp * 16;   // each warp takes 16 of the tile's 64 keys
         if (wkey0 < k1 && wkey0 + 16 > k0) {
             const uint32_t k_s = kv_s + stage * 2 * kTileBytes, v_s = k_s + kTileBytes;
@@ -448,7 +567,7 @@ int make_map(CUtensorMap* map, const void* ptr, long long rows, int cols, int bo
 }
 
 template <int D> constexpr int prefill_smem() { return kPrefillRows * D * 2 + kPrefillStages * 2 * kTileKeys * D * 2 + 64 + 4 * kMaxTableEntries + 1024; }
-template <int D> constexpr int decode_smem() { return kDecodeStages * 2 * kTileKeys * D * 2 + 16 * D * 2 + 64 + 4 * kMaxTableEntries + 1024; }
+template <int D> constexpr int decode_smem() { return kDecodeStages * 2 * kTileKeys * D * 2 + 16 * D * 2 + 64 + 4 * kMaxTableEntries + 2 * D * 2 + 1024; }
 
 template <int D>
 int launch_prefill(const void* q, void* out, const void* k_pages, const void* v_pages, const int* block_table,
@@ -474,13 +593,13 @@ int launch_prefill(const void* q, void* out, const void* k_pages, const void* v_
     return qi::check_launch("attention_prefill_tma");
 }
 
-template <int D>
-int launch_decode(const void* q, void* out, const void* k_pages, const void* v_pages, const int* block_table,
-                  int max_blocks, int page_size, int num_pages, const int* kv_len, const int* q_start, int batch,
-                  int nq, int nkv, float scale, int window, int chunk, int n_splits, float* ws_o, float* ws_ml,
-                  int* status, cudaStream_t stream) {
-    auto kern = attention_decode_tma_kernel<D, false>;
-    auto kern_direct = attention_decode_tma_kernel<D, true>;
+template <int D, bool FUSED, typename TIn>
+int launch_decode_as(const void* q, void* out, const void* k_pages, const void* v_pages, const int* block_table,
+                     int max_blocks, int page_size, int num_pages, const int* kv_len, const int* q_start, int batch,
+                     int nq, int nkv, float scale, int window, int chunk, int n_splits, float* ws_o, float* ws_ml,
+                     int* status, cudaStream_t stream, const DecodeRope& rope) {
+    auto kern = attention_decode_tma_kernel<D, false, FUSED, TIn>;
+    auto kern_direct = attention_decode_tma_kernel<D, true, FUSED, TIn>;
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, decode_smem<D>());
@@ -496,16 +615,36 @@ int launch_decode(const void* q, void* out, const void* k_pages, const void* v_p
     if (n_splits == 1) {
         qi::launch(kern_direct, grid, dim3(kDecodeThreads), decode_smem<D>(), stream,
             (const qi::bf16*)q, (qi::bf16*)out, mk, mv, block_table, max_blocks, page_size, box_rows, num_pages, kv_len,
-            q_start, ws_o, ws_ml, nq, nkv, scale * 1.4426950408889634f, window, chunk, status);
+            q_start, ws_o, ws_ml, nq, nkv, scale * 1.4426950408889634f, window, chunk, status, rope);
         return qi::check_launch("attention_decode_tma");
     }
     qi::launch(kern, grid, dim3(kDecodeThreads), decode_smem<D>(), stream,
         (const qi::bf16*)q, (qi::bf16*)out, mk, mv, block_table, max_blocks, page_size, box_rows, num_pages, kv_len, q_start, ws_o,
-        ws_ml, nq, nkv, scale * 1.4426950408889634f, window, chunk, status);
+        ws_ml, nq, nkv, scale * 1.4426950408889634f, window, chunk, status, rope);
     if (int rc = qi::check_launch("attention_decode_tma")) return rc;
     qi::launch(attention_merge_kernel<D>, dim3(nq, batch), dim3(D >= 128 ? 128 : 64), 0, stream, (const float*)ws_o,
                (const float*)ws_ml, q_start, (qi::bf16*)out, nq, n_splits);
     return qi::check_launch("attention_merge");
+}
+
+// rope null: the queries are in `q` and the cache holds every key. Else the kernel makes them from
+// the projection (`rope_dtype` says whether that is bfloat16 or 32-bit partial sums).
+template <int D>
+int launch_decode(const void* q, void* out, const void* k_pages, const void* v_pages, const int* block_table,
+                  int max_blocks, int page_size, int num_pages, const int* kv_len, const int* q_start, int batch,
+                  int nq, int nkv, float scale, int window, int chunk, int n_splits, float* ws_o, float* ws_ml,
+                  int* status, cudaStream_t stream, const DecodeRope* rope = nullptr, int rope_dtype = qi::kF32) {
+    if (!rope)
+        return launch_decode_as<D, false, float>(q, out, k_pages, v_pages, block_table, max_blocks, page_size, num_pages, kv_len,
+                                                 q_start, batch, nq, nkv, scale, window, chunk, n_splits, ws_o, ws_ml, status,
+                                                 stream, DecodeRope{});
+    if (rope_dtype == qi::kF32)
+        return launch_decode_as<D, true, float>(q, out, k_pages, v_pages, block_table, max_blocks, page_size, num_pages, kv_len,
+                                                q_start, batch, nq, nkv, scale, window, chunk, n_splits, ws_o, ws_ml, status,
+                                                stream, *rope);
+    return launch_decode_as<D, true, qi::bf16>(q, out, k_pages, v_pages, block_table, max_blocks, page_size, num_pages, kv_len,
+                                               q_start, batch, nq, nkv, scale, window, chunk, n_splits, ws_o, ws_ml, status,
+                                               stream, *rope);
 }
 
 bool pow2(int v) { return v > 0 && (v & (v - 1)) == 0; }
@@ -562,6 +701,49 @@ extern "C" int qi_attention_decode_tma(const void* q, void* out, const void* k_p
                                  q_start, batch, nq, nkv, scale, window, chunk, n_splits, ws_o, ws_ml, status, stream);
     return launch_decode<128>(q, out, k_pages, v_pages, block_table, max_blocks, page_size, num_pages, kv_len,
                               q_start, batch, nq, nkv, scale, window, chunk, n_splits, ws_o, ws_ml, status, stream);
+}
+
+// The same for a decode step whose q/k/v projection has just run: the kernel sums the projection's
+// K-split partial sums (qkv_splits > 1: `qkv` is float32 [qkv_splits, tokens, (nq + 2 nkv) d]) or
+// reads its output (qkv_splits == 1, element type qkv_dtype, [tokens, (nq + 2 nkv) d]), applies the
+// q/k RMSNorm (gains null: none) and the rotation over the whole head (cos_t null: none), and writes
+// the step's key and value into the cache at position kv_len - 1 of each request (writes 0: another
+// layer has written them; nothing is computed). One launch does what qi_qk_norm_rope_kv followed by
+// qi_attention_decode_tma does. Request b's token is row q_start[b] of the projection.
+extern "C" int qi_attention_decode_rope_tma(const void* qkv, int qkv_dtype, int qkv_splits, int n_tokens, const float* q_gain,
+                                            const float* k_gain, float eps, const float* cos_t, const float* sin_t,
+                                            int table_positions, int writes, void* out, void* k_pages, void* v_pages,
+                                            const int* block_table, int max_blocks, int page_size, int num_pages,
+                                            const int* kv_len, const int* q_start, int batch, int nq, int nkv, int d,
+                                            float scale, int window, int chunk, int n_splits, float* ws_o, float* ws_ml,
+                                            int* status, cudaStream_t stream) {
+    QI_REQUIRE(qi_attention_tma_supported(nq, nkv, d, page_size, max_blocks),
+               "attention_decode_rope_tma: heads %d/%d of size %d with %d pages of %d per request are not covered", nq, nkv, d, max_blocks, page_size);
+    QI_REQUIRE(max_blocks > 0 && num_pages > 0 && window >= 0 && n_tokens >= batch, "attention_decode_rope_tma: bad sizes");
+    QI_REQUIRE(chunk > 0 && chunk % kTileKeys == 0, "attention_decode_rope_tma: the key range per CTA (%d) must be a positive multiple of %d", chunk, kTileKeys);
+    QI_REQUIRE(n_splits > 0 && n_splits <= 65535 && nkv <= 65535 && batch <= 65535, "attention_decode_rope_tma: grid too large");
+    QI_REQUIRE(ws_o && ws_ml && qkv && out, "attention_decode_rope_tma: a buffer is missing");
+    QI_REQUIRE(qkv_splits >= 1 && (qkv_splits == 1 || qkv_dtype == qi::kF32), "attention_decode_rope_tma: partial sums must be float32");
+    QI_REQUIRE(qkv_dtype == qi::kF32 || qkv_dtype == qi::kBF16, "attention_decode_rope_tma: unknown element type");
+    QI_REQUIRE((cos_t == nullptr) == (sin_t == nullptr) && (!cos_t || table_positions > 0), "attention_decode_rope_tma: incomplete rotation table");
+    QI_REQUIRE(((uintptr_t)qkv & 15) == 0 && ((uintptr_t)k_pages & 15) == 0 && ((uintptr_t)v_pages & 15) == 0 &&
+               ((uintptr_t)q_gain & 7) == 0 && ((uintptr_t)k_gain & 7) == 0 && ((uintptr_t)cos_t & 7) == 0 && ((uintptr_t)sin_t & 7) == 0,
+               "attention_decode_rope_tma: tensors must be aligned (16 bytes; gains and tables 8)");
+    QI_REQUIRE((long long)num_pages * nkv * page_size < 2147483647LL, "attention_decode_rope_tma: the page pool has too many rows");
+    if (batch == 0) return 0;
+    DecodeRope r;
+    r.qkv = qkv;
+    r.width = (nq + 2 * nkv) * d;
+    r.split_stride = (long long)n_tokens * r.width;
+    r.q_gain = q_gain; r.k_gain = k_gain; r.cos_t = cos_t; r.sin_t = sin_t;
+    r.k_pages = writes ? (qi::bf16*)k_pages : nullptr;
+    r.v_pages = writes ? (qi::bf16*)v_pages : nullptr;
+    r.eps = eps; r.splits = qkv_splits;
+    if (d == 64)
+        return launch_decode<64>(nullptr, out, k_pages, v_pages, block_table, max_blocks, page_size, num_pages, kv_len, q_start,
+                                 batch, nq, nkv, scale, window, chunk, n_splits, ws_o, ws_ml, status, stream, &r, qkv_dtype);
+    return launch_decode<128>(nullptr, out, k_pages, v_pages, block_table, max_blocks, page_size, num_pages, kv_len, q_start,
+                              batch, nq, nkv, scale, window, chunk, n_splits, ws_o, ws_ml, status, stream, &r, qkv_dtype);
 }
 
 // ------------------------------------------------------------------ the entry point that allocates nothing

@@ -410,6 +410,60 @@ def attention_decode(q, out, k_pages, v_pages, block_table, kv_len, q_start, nq,
     _check(rc, "attention_decode")
 
 
+def attention_decode_rope(qkv, out, q_gain, k_gain, eps, cos, sin, k_pages, v_pages, writes: bool, block_table, kv_len,
+                          q_start, nq, nkv, d, scale: float, window: int, chunk: int, n_splits: int, status,
+                          workspace=None) -> None:
+    """`qk_norm_rope_kv` and `attention_decode` in one launch, for a decode step: qkv is the
+    q/k/v projection's output, bfloat16 [tokens, (nq + 2 nkv) d], or its float32 K-split partial
+    sums [splits, tokens, (nq + 2 nkv) d]. The kernel makes each request's queries from it, and
+    its new key and value, which it writes to the cache at position kv_len - 1 (`writes` False:
+    another layer wrote them). Rotation over the whole head or none (cos None)."""
+    _req(qkv, "qkv")
+    if qkv.dim() == 3:
+        if qkv.dtype != torch.float32:
+            raise KernelError("attention_decode_rope: partial sums must be float32")
+        splits, n_tokens, width = qkv.shape
+    elif qkv.dim() == 2 and qkv.dtype in (torch.bfloat16, torch.float32):
+        splits, (n_tokens, width) = 1, qkv.shape
+    else:
+        raise KernelError(f"attention_decode_rope: qkv {tuple(qkv.shape)} {qkv.dtype} is neither an output nor partial sums")
+    _req(out, "out", torch.bfloat16, 2)
+    _req(k_pages, "k_pages", torch.bfloat16, 4)
+    _req(v_pages, "v_pages", torch.bfloat16, 4)
+    for t, name in ((block_table, "block_table"), (kv_len, "kv_len"), (q_start, "q_start")):
+        _req(t, name, torch.int32)
+    batch = kv_len.numel()
+    if width != (nq + 2 * nkv) * d or tuple(out.shape) != (n_tokens, nq * d) or n_tokens < batch:
+        raise KernelError(f"attention_decode_rope: qkv {tuple(qkv.shape)} / out {tuple(out.shape)} do not match {batch} requests, heads {nq}+2*{nkv} of {d}")
+    if k_pages.shape[1] != nkv or k_pages.shape[3] != d or k_pages.shape != v_pages.shape:
+        raise KernelError(f"attention_decode_rope: pages {tuple(k_pages.shape)} do not match {nkv} kv heads of {d}")
+    for g, name in ((q_gain, "q_gain"), (k_gain, "k_gain")):
+        if g is not None:
+            _req(g, name, torch.float32, 1)
+            if g.numel() != d:
+                raise KernelError(f"{name} has {g.numel()} elements, head_dim is {d}")
+    table_positions = 0
+    if cos is not None:
+        _req(cos, "cos", torch.float32, 2)
+        _req(sin, "sin", torch.float32, 2)
+        if cos.shape != sin.shape or cos.shape[1] * 2 != d:
+            raise KernelError("attention_decode_rope: rotation tables must cover the whole head")
+        table_positions = cos.shape[0]
+    need = batch * nq * n_splits * (d + 2)
+    if workspace is None:
+        workspace = torch.empty(need, dtype=torch.float32, device=out.device)
+    _req(workspace, "workspace", torch.float32, 1)
+    if workspace.numel() < need:
+        raise KernelError(f"attention_decode_rope: workspace has {workspace.numel()} floats, {need} are needed")
+    rc = library().qi_attention_decode_rope_tma(
+        _ptr(qkv), _code(qkv), splits, n_tokens, _ptr(q_gain), _ptr(k_gain), C.c_float(eps), _ptr(cos), _ptr(sin),
+        table_positions, int(bool(writes)), _ptr(out), _ptr(k_pages), _ptr(v_pages), _ptr(block_table),
+        block_table.shape[1], k_pages.shape[2], k_pages.shape[0], _ptr(kv_len), _ptr(q_start), batch, nq, nkv, d,
+        C.c_float(scale), int(window or 0), chunk, n_splits, _ptr(workspace), _ptr(workspace[batch * nq * n_splits * d:]),
+        _ptr(status), _stream())
+    _check(rc, "attention_decode_rope")
+
+
 # --------------------------------------------------------------------------
 # feed-forward
 

@@ -89,6 +89,17 @@ class Attention(Part):
             return self.o(out, keep_partials=True)
         # K-split partial sums of the projection are added by the next kernel where it can take them
         qkv = self.qkv(x, keep_partials=self.d % 4 == 0 and (pos is None or pos.rotary_dim == self.d))
+        if (batch.all_decode and qkv.dtype in (torch.bfloat16, torch.float32) and x.dtype == torch.bfloat16
+                and (pos is None or pos.rotary_dim == self.d) and (qkv.dim() == 3 or qkv.dtype == torch.bfloat16)
+                and kernels.attention_tma_supported(self.nq, self.nkv, self.d, cache.page_size, table.shape[1])):
+            # one token per request: the attention kernel makes its queries and the new key and value itself
+            out = torch.empty_like(q)
+            chunk, splits = kernels.attention_decode_plan(batch.n_requests, self.nkv, batch.max_kv_len)
+            kernels.attention_decode_rope(
+                qkv, out, self.q_gain, self.k_gain, self.spec.qk_norm_eps, pos.cos if pos else None,
+                pos.sin if pos else None, cache.k_pages, cache.v_pages, cache.writes, table, batch.kv_len,
+                batch.q_start, self.nq, self.nkv, self.d, self.scale, self.spec.window or 0, chunk, splits, rt.status)
+            return self.o(out, keep_partials=True)
         kernels.qk_norm_rope_kv(
             qkv, q, self.q_gain, self.k_gain, self.spec.qk_norm_eps,
             pos.cos if pos else None, pos.sin if pos else None, pos.rotary_dim if pos else 0,

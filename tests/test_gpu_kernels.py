@@ -361,6 +361,64 @@ def test_attention_decode_key_ranges(chunk, ctx, window):
     assert _attention_case(4, 1, 64, ctx[:2], [1, 1], 16, window, torch.bfloat16, "decode_tma", decode_chunk=chunk) < 1.2e-2
 
 
+@pytest.mark.parametrize("nq, nkv, d, lens, ps, window, chunk, partial, writes", [
+    (8, 2, 128, [1, 64, 65, 300, 513], 64, 0, 0, True, True),      # the new key opens a page, ends one, lies inside
+    (8, 2, 128, [1, 64, 65, 300, 513], 16, 0, 128, False, True),   # several ranges: only the last one holds the new key
+    (4, 4, 64, [33, 200], 8, 0, 64, True, True),
+    (6, 1, 64, [90, 7, 129], 32, 50, 0, False, True),              # a window
+    (8, 2, 128, [10, 140], 64, 0, 0, True, False),                 # the cache is another layer's: nothing is written
+    (32, 8, 128, [2049] * 3, 64, 0, 0, True, True),
+])
+def test_attention_decode_with_rope_equals_the_two_kernels(nq, nkv, d, lens, ps, window, chunk, partial, writes):
+    """One launch that makes the queries and the new key and value from the q/k/v projection against
+    qk_norm_rope_kv followed by attention_decode (each checked against its formulas above): the same
+    output, the same cache rows, nothing else touched."""
+    torch.manual_seed(len(lens) * 7 + d)
+    k = _k()
+    B, eps = len(lens), 1e-6
+    width = (nq + 2 * nkv) * d
+    y = torch.randn(B, width, device=DEV)
+    if partial:
+        parts = torch.randn(3, B, width, device=DEV)
+        parts[2] = y - parts[0] - parts[1]
+        qkv = parts.contiguous()
+    else:
+        qkv = y.bfloat16()
+    qg, kg = (1 + 0.1 * torch.randn(d)).to(DEV), (1 + 0.1 * torch.randn(d)).to(DEV)
+    inv_freq = torch.pow(torch.tensor(1e4), -(2.0 * torch.arange(d // 2)) / d)
+    cos, sin = k.rope_table(inv_freq.to(DEV), max(lens) + 1)
+    max_blocks = -(-max(lens) // ps) + 1
+    num_pages = B * max_blocks + 2
+    perm = torch.randperm(num_pages).tolist()
+    table = torch.tensor([[perm.pop() for _ in range(max_blocks)] for _ in range(B)], dtype=torch.int32, device=DEV)
+    pages = [(torch.randn(num_pages, nkv, ps, d, device=DEV) * 0.7).bfloat16() for _ in range(2)]
+    kv_len, q_start = I(lens), I(list(range(B + 1)))
+    positions, token_req = I([n - 1 for n in lens]), I(list(range(B)))
+    plan = k.attention_decode_plan(B, nkv, max(lens) + 40)
+    if chunk:
+        plan = (chunk, -(-(max(lens) + 40) // chunk))
+    # the two kernels
+    kp1, vp1 = pages[0].clone(), pages[1].clone()
+    q = torch.empty(B, nq * d, dtype=torch.bfloat16, device=DEV)
+    st = _status()
+    if writes:
+        k.qk_norm_rope_kv(qkv, q, qg, kg, eps, cos, sin, d, positions, token_req, table, ps, kp1, vp1, nq, nkv, d, st)
+    else:
+        k.qk_norm_rope_kv(qkv, q, qg, kg, eps, cos, sin, d, positions, token_req, table, ps, None, None, nq, nkv, d, st)
+    out1 = torch.empty_like(q)
+    k.attention_decode(q, out1, kp1, vp1, table, kv_len, q_start, nq, nkv, d, d ** -0.5, window, plan[0], plan[1], st, use_tma=True)
+    # the one kernel
+    kp2, vp2 = pages[0].clone(), pages[1].clone()
+    out2 = torch.empty_like(q)
+    k.attention_decode_rope(qkv, out2, qg, kg, eps, cos, sin, kp2, vp2, writes, table, kv_len, q_start, nq, nkv, d, d ** -0.5,
+                            window, plan[0], plan[1], st)
+    assert st.item() == 0
+    assert float((out1.float() - out2.float()).abs().max()) < 4e-3
+    assert float((kp1.float() - kp2.float()).abs().max()) < 2e-2 and float((vp1.float() - vp2.float()).abs().max()) < 2e-2
+    changed = int(((kp2 != pages[0]).sum(dim=3) > 0).sum())
+    assert changed == (B * nkv if writes else 0)
+
+
 def test_attention_kernels_refuse_what_they_do_not_cover():
     from quantinfer_b200.errors import KernelError
 
