@@ -6,22 +6,25 @@
 //     S = Q . K^T      (128 x 64,  K = head size)    -> tensor memory, 32-bit
 //     O_j = P . V      (128 x 128, K = 64 keys)      -> tensor memory, 32-bit
 // Two groups of 128 softmax threads (one thread per query row in each group) take the
-// tiles in turn: group b has the tiles of parity b, with an S buffer, a P buffer and an O_j
-// buffer of its own, so that one group's softmax overlaps the other group's products. A
-// softmax thread reads its row of S from tensor memory, updates its running maximum and
-// sum, writes the weights P as bfloat16 into shared memory in the layout the tensor core
-// reads (rows of 128 bytes, 128-byte swizzle), and adds the finished O_{j-2} to the row's
-// accumulator, which lives in registers:
-//     o = o * 2^(m_before - m_after) + O_j
-// so nothing in tensor memory ever has to be rescaled. At the end the two groups' partial
-// results (maximum, sum, accumulator over their own tiles) are merged through shared
-// memory like the ranges of a split-key attention.
+// tiles in turn: group b has the tiles of parity b, with an S buffer, a P buffer and an
+// accumulator O_b in tensor memory of its own, so that one group's softmax overlaps the
+// other group's products. A softmax thread reads its row of S from tensor memory, updates
+// its running maximum and sum, and writes the weights P as bfloat16 into shared memory in
+// the layout the tensor core reads (rows of 128 bytes, 128-byte swizzle); the tensor core
+// adds P . V to O_b. The exponent's reference m_ref is not the running maximum itself: it
+// follows the maximum only when that has grown by more than 8 (in the base-2 scale), and
+// only then is the row of O_b read back, scaled by 2^(m_ref_old - m_ref_new) and stored
+// again, after the group's last product has finished. Weights therefore reach 2^8 at most,
+// sum and accumulator share one reference, and their quotient is unchanged; after the
+// first few tiles of a row the accumulator is hardly ever touched. At the end the two
+// groups' partial results (reference, sum, accumulator over their own tiles) are merged
+// through shared memory like the ranges of a split-key attention.
 //
 // Roles (384 threads = three groups of four warps): warps 0-3 and 4-7 are the two softmax
 // groups; in the third group warp 8 issues TMA loads of Q and of the K/V tiles (page pieces
 // through the block table, as in attention_tma.cu), warp 9 allocates tensor memory and
 // issues the MMAs, warps 10-11 idle. The third group hands most of its registers to the
-// softmax groups (setmaxnreg), whose threads keep a whole output row in registers. K is read as a K-major
+// softmax groups (setmaxnreg). K is read as a K-major
 // operand, V as an MN-major operand (its rows are keys, the product contracts over keys),
 // P and Q as K-major operands.
 //
@@ -49,7 +52,8 @@ constexpr int kKVHalfBytes = BN * 128;            // K or V: 64 keys x 128 bytes
 constexpr int kKVBytes = 2 * kKVHalfBytes;        // 16 KB
 constexpr int kPBytes = BM * 128;                 // P: 128 rows x 64 keys (128 bytes): 16 KB
 constexpr int kMaxTableEntries = 2048;
-constexpr uint32_t kSpinLimit = 1u << 24;
+constexpr uint32_t kSpinLimit = 1u << 22;   // polls of a barrier before a role gives up (each poll may itself wait a little)
+constexpr float kRescaleStep = 8.f;   // the exponent's reference follows the maximum when that has grown by more (base 2)
 
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
@@ -65,6 +69,16 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
         "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+// The same without any waiting inside the instruction: for a thread that watches several barriers.
+__device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
         "selp.u32 %0, 1, 0, p;\n\t}"
         : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
     return ok != 0;
@@ -113,7 +127,36 @@ __device__ __forceinline__ void tmem_ld32(uint32_t addr, uint32_t (&r)[32]) {
           "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
         : "r"(addr));
 }
+__device__ __forceinline__ void tmem_st32(uint32_t addr, const uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+        "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+        ::"r"(addr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+          "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
+          "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]),
+          "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+        : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 using qi_attn::ex2;
+// 2^x without the special-function unit, which this kernel keeps busier than anything else: the
+// integer nearest to x comes from adding 1.5 * 2^23, the rest f = x - n lies in [-0.5, 0.5] where a
+// polynomial of degree 5 gives 2^f to 1e-7 (relative, the unit's own accuracy), and n goes into
+// the exponent bits. For x in [-126, 126].
+__device__ __forceinline__ float ex2_fma(float x) {
+    x = fmaxf(x, -126.f);
+    const float t = x + 12582912.f;
+    const float f = x - (t - 12582912.f);
+    float p = 0.0013400432653725147f;
+    p = fmaf(p, f, 0.009676037356257439f);
+    p = fmaf(p, f, 0.05550327152013779f);
+    p = fmaf(p, f, 0.2402210682630539f);
+    p = fmaf(p, f, 0.6931471824645996f);
+    p = fmaf(p, f, 1.0000001192092896f);
+    return __int_as_float(__float_as_int(p) + (__float_as_int(t) << 23));
+}
+constexpr int kFmaExpMask = 0x88;   // which of every 8 weights take ex2_fma instead of the unit (bit i: element i)
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
 // K-major operand tile (rows of 128 bytes, 128-byte swizzle): see gemm_tcgen05.cu.
@@ -151,8 +194,7 @@ struct Bars {   // byte offsets of the mbarriers from the barrier base
     static constexpr int s_full = kv_empty + 8 * kStages;  // [2]
     static constexpr int s_free = s_full + 16;             // [2]
     static constexpr int o_full = s_free + 16;             // [2]
-    static constexpr int o_free = o_full + 16;             // [2]
-    static constexpr int p_ready = o_free + 16;            // [2]
+    static constexpr int p_ready = o_full + 16;            // [2]
     static constexpr int p_free = p_ready + 16;            // [2]
     static constexpr int total = p_free + 16;
 };
@@ -210,7 +252,6 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
             mbar_init(bars + Bars::s_full + 8 * b, 1);
             mbar_init(bars + Bars::s_free + 8 * b, 4);    // one arrival per warp of the group
             mbar_init(bars + Bars::o_full + 8 * b, 1);
-            mbar_init(bars + Bars::o_free + 8 * b, 4);
             mbar_init(bars + Bars::p_ready + 8 * b, 4);
             mbar_init(bars + Bars::p_free + 8 * b, 1);
         }
@@ -226,7 +267,7 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
     const uint32_t tmem_s = tmem_base;            // S of group b: columns b * 64 .. b * 64 + 63
-    const uint32_t tmem_o = tmem_base + 128;      // O_j of group b: columns 128 + b * 128 ..
+    const uint32_t tmem_o = tmem_base + 128;      // accumulator of group b: columns 128 + b * 128 ..
 
     auto give_up = [&]() {
         if (!*abort_flag) {
@@ -281,11 +322,13 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
         if (lane == 0) {
             constexpr uint32_t idesc_qk = idesc(BN, false), idesc_pv = idesc(D, true);
             bool ok = mbar_wait(bars + Bars::q_full, 0, abort_flag);
-            auto issue_qk = [&](int j) -> bool {
+            // S = Q . K^T of tile j into the S buffer of group j & 1, once the tile's keys have landed and the
+            // group has taken its previous S into registers; false if one of the two is not there yet
+            auto try_qk = [&](int j) -> bool {
                 const int s = j % kStages, b = j & 1;
                 const uint32_t u = (uint32_t)j >> 1;                 // the group's own tile count
-                if (!mbar_wait(bars + Bars::kv_full + 8 * s, ((uint32_t)j / kStages) & 1u, abort_flag)) return false;
-                if (!mbar_wait(bars + Bars::s_free + 8 * b, (u & 1u) ^ 1u, abort_flag)) return false;
+                if (!mbar_test(bars + Bars::kv_full + 8 * s, ((uint32_t)j / kStages) & 1u)) return false;
+                if (!mbar_test(bars + Bars::s_free + 8 * b, (u & 1u) ^ 1u)) return false;
                 tc_fence_after();
                 const uint32_t k_addr = kv_s + s * 2 * kKVBytes;
 #pragma unroll
@@ -297,75 +340,58 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
                 umma_commit(bars + Bars::s_full + 8 * b);
                 return true;
             };
-            // S of the first two tiles, then for every tile: P.V as soon as its P is ready, and S two tiles on
-            for (int j = 0; j < 2 && j < n_tiles && ok; ++j) ok = issue_qk(j);
-            for (int j = 0; j < n_tiles && ok; ++j) {
+            // O_b += P . V of tile j, once the group's weights are ready (and with them its accumulator,
+            // rescaled if its reference moved)
+            auto try_pv = [&](int j) -> bool {
                 const int s = j % kStages, b = j & 1;
                 const uint32_t u = (uint32_t)j >> 1;
-                if (!mbar_wait(bars + Bars::p_ready + 8 * b, u & 1u, abort_flag) ||
-                    !mbar_wait(bars + Bars::o_free + 8 * b, (u & 1u) ^ 1u, abort_flag)) {
-                    ok = false;
-                    break;
-                }
+                if (!mbar_test(bars + Bars::p_ready + 8 * b, u & 1u)) return false;
                 tc_fence_after();
                 const uint32_t v_addr = kv_s + s * 2 * kKVBytes + kKVBytes;
 #pragma unroll
                 for (int kk = 0; kk < BN / 16; ++kk) {
                     const uint64_t adesc = desc_k_major(p_s + b * kPBytes) + 2u * kk;
                     const uint64_t bdesc = desc_mn_major(v_addr + kk * 16 * 128);
-                    umma_bf16(tmem_o + b * D, adesc, bdesc, idesc_pv, kk > 0 ? 1u : 0u);
+                    umma_bf16(tmem_o + b * D, adesc, bdesc, idesc_pv, (u > 0 || kk > 0) ? 1u : 0u);
                 }
-                umma_commit(bars + Bars::o_full + 8 * b);          // O_j is complete
+                umma_commit(bars + Bars::o_full + 8 * b);          // the accumulator holds the tiles up to this one
                 umma_commit(bars + Bars::kv_empty + 8 * s);        // K_j and V_j have been read
                 umma_commit(bars + Bars::p_free + 8 * b);          // the group's P may be overwritten
-                if (j + 2 < n_tiles) ok = issue_qk(j + 2);
+                return true;
+            };
+            // S of the first two tiles, then for every tile: P.V as soon as its weights are ready, and S two
+            // tiles on. (Issuing whatever is possible first, in no fixed order between the groups, and issuing
+            // a group's next S before this tile's P.V were both measured no faster.)
+            auto spin = [&](auto&& attempt) -> bool {
+                for (uint32_t i = 0; i < (kSpinLimit << 4); ++i) {
+                    if (attempt()) return true;
+                    if ((i & 4095u) == 4095u && *abort_flag) return false;
+                }
+                return false;
+            };
+            for (int j = 0; j < 2 && j < n_tiles && ok; ++j) ok = spin([&] { return try_qk(j); });
+            for (int j = 0; j < n_tiles && ok; ++j) {
+                ok = spin([&] { return try_pv(j); });
+                if (ok && j + 2 < n_tiles) ok = spin([&] { return try_qk(j + 2); });
             }
             if (!ok) give_up();
         }
       }
     } else {
         // ---------------- softmax threads: group b = warps 4 b .. 4 b + 3, one query row each ----------------
-        asm volatile("setmaxnreg.inc.sync.aligned.u32 232;" ::: "memory");     // a whole output row lives in registers
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 232;" ::: "memory");
         const int b = warp >> 2;
         const int quarter = warp & 3;                 // the 32 tensor-memory lanes this warp may read
         const int row = quarter * 32 + lane;
         const int pos = pos0 + row;
         const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
         uint8_t* p_tile = p_mem + b * kPBytes;
-        float m = -INFINITY, l = 0.f, corr_prev = 1.f;
-        float o[D];
-#pragma unroll
-        for (int i = 0; i < D; ++i) o[i] = 0.f;
+        float m = -INFINITY, l = 0.f;      // m: the exponent's reference (at most kRescaleStep below the row's maximum)
         bool ok = true;
-
-        // adds the group's finished O (its u-th tile) to the row's accumulator, scaled to the current maximum
-        auto drain = [&](uint32_t u, float corr) -> bool {
-            if (!mbar_wait(bars + Bars::o_full + 8 * b, u & 1u, abort_flag)) return false;
-            tc_fence_after();
-#pragma unroll
-            for (int c0 = 0; c0 < D; c0 += 64) {
-                uint32_t v[64];      // two loads in flight per wait
-                tmem_ld32(tmem_o + lane_addr + b * D + c0, *reinterpret_cast<uint32_t(*)[32]>(&v[0]));
-                tmem_ld32(tmem_o + lane_addr + b * D + c0 + 32, *reinterpret_cast<uint32_t(*)[32]>(&v[32]));
-                tmem_ld_wait();
-#pragma unroll
-                for (int i = 0; i < 64; ++i) o[c0 + i] = fmaf(o[c0 + i], corr, __uint_as_float(v[i]));
-            }
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(bars + Bars::o_free + 8 * b);
-            return true;
-        };
 
         uint32_t u = 0;
         for (int j = b; j < n_tiles && ok; j += 2, ++u) {
             const int t0 = t_begin + j * BN;
-            // the product of the group's previous tile has long finished: fold it in first, so that
-            // the tensor core can start P.V of this tile the moment P is ready
-            if (u > 0) {
-                ok = drain(u - 1, corr_prev);
-                if (!ok) break;
-            }
             if (!mbar_wait(bars + Bars::s_full + 8 * b, u & 1u, abort_flag)) { ok = false; break; }
             tc_fence_after();
             // keys this row may see in this tile: columns [c_lo, c_hi)
@@ -382,7 +408,8 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
             __syncwarp();
             if (lane == 0) mbar_arrive(bars + Bars::s_free + 8 * b);
             float mx = -INFINITY;
-            if (c_lo == 0 && c_hi == BN) {
+            const bool unmasked = c_lo == 0 && c_hi == BN;      // all but the tiles on the diagonal and at a window's edge
+            if (unmasked) {
                 float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};     // four chains instead of one
 #pragma unroll
                 for (int i = 0; i < BN; i += 4) {
@@ -395,21 +422,45 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
                 for (int i = 0; i < BN; ++i)
                     if (i >= c_lo && i < c_hi) mx = fmaxf(mx, __uint_as_float(sv[i]));
             }
-            const float m_new = fmaxf(m, mx * scale_log2e);
-            const float ms = (m_new == -INFINITY) ? 0.f : m_new;
-            const float corr = ex2(m - ms);                // m = -inf gives 0
-            m = m_new;
+            const float m_top = fmaxf(m, mx * scale_log2e);
+            // The reference moves only by large steps, and the rows of a warp are rescaled together (the
+            // tensor-memory accesses are the whole warp's). A row that has seen no key yet has nothing
+            // accumulated under another reference: it takes the maximum as it is.
+            const bool fresh = m == -INFINITY;
+            const bool moves = !fresh && m_top - m > kRescaleStep;
+            if (__any_sync(0xffffffffu, moves)) {
+                // the accumulator must be complete up to the group's previous tile
+                if (!mbar_wait(bars + Bars::o_full + 8 * b, (u - 1) & 1u, abort_flag)) { ok = false; break; }
+                tc_fence_after();
+                const float f = moves ? ex2(m - m_top) : 1.f;
+#pragma unroll 1
+                for (int c0 = 0; c0 < D; c0 += 32) {
+                    uint32_t v[32];
+                    tmem_ld32(tmem_o + lane_addr + b * D + c0, v);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * f);
+                    tmem_st32(tmem_o + lane_addr + b * D + c0, v);
+                }
+                tmem_st_wait();
+                tc_fence_before();
+                l *= f;
+            }
+            if (fresh || moves) m = m_top;
+            const float ms = (m == -INFINITY) ? 0.f : m;
             // the group's previous P must have been consumed before P is overwritten
             if (u > 0 && !mbar_wait(bars + Bars::p_free + 8 * b, (u - 1) & 1u, abort_flag)) { ok = false; break; }
             float sum = 0.f;
             uint8_t* prow = p_tile + row * 128;
-            const bool unmasked = c_lo == 0 && c_hi == BN;      // all but the tiles on the diagonal and at a window's edge
 #pragma unroll
             for (int q = 0; q < BN / 8; ++q) {
                 float p[8];
                 if (unmasked) {
 #pragma unroll
-                    for (int i = 0; i < 8; ++i) p[i] = ex2(fmaf(__uint_as_float(sv[8 * q + i]), scale_log2e, -ms));
+                    for (int i = 0; i < 8; ++i) {
+                        const float x = fmaf(__uint_as_float(sv[8 * q + i]), scale_log2e, -ms);
+                        p[i] = ((kFmaExpMask >> i) & 1) ? ex2_fma(x) : ex2(x);
+                    }
                 } else {
 #pragma unroll
                     for (int i = 0; i < 8; ++i) {
@@ -425,14 +476,27 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
                 w.w = qi_attn::pack_bf16(p[6], p[7]);
                 *reinterpret_cast<uint4*>(prow + ((q ^ (row & 7)) << 4)) = w;
             }
-            l = l * corr + sum;
+            l += sum;
             // P is written: make it visible to the tensor core, then signal
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             __syncwarp();
             if (lane == 0) mbar_arrive(bars + Bars::p_ready + 8 * b);
-            corr_prev = corr;
         }
-        if (ok && u > 0) ok = drain(u - 1, corr_prev);
+        // the group's accumulator, once its last product has finished
+        float o[D];
+#pragma unroll
+        for (int i = 0; i < D; ++i) o[i] = 0.f;
+        if (ok && u > 0) {
+            ok = mbar_wait(bars + Bars::o_full + 8 * b, (u - 1) & 1u, abort_flag);
+            if (ok) {
+                tc_fence_after();
+#pragma unroll
+                for (int c0 = 0; c0 < D; c0 += 32) {
+                    tmem_ld32(tmem_o + lane_addr + b * D + c0, *reinterpret_cast<uint32_t(*)[32]>(&o[c0]));
+                }
+                tmem_ld_wait();
+            }
+        }
         if (!ok && lane == 0) give_up();
 
         // merge the two groups: group 1 hands its partial result over through the K/V ring,
