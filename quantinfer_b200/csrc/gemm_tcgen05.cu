@@ -664,10 +664,11 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, TOut* out, int rows_a, 
     return qi::check_launch("gemm_bf16");
 }
 
-// Pipeline stages by tile width: 6 where two CTAs of 6 stages fit an SM (the first stages' weight
-// tiles are requested before the kernel waits for its predecessor, so deeper is better while
-// two CTAs stay resident), 4 for the widest tile.
-constexpr int stages_of(int bn) { return bn <= 32 ? 6 : bn == 128 ? 6 : 4; }
+// Pipeline stages by tile width: as many as let two CTAs stay resident on an SM for the narrow
+// tiles (6 of 18 KB, 5 of 20 KB, 4 of 24 KB: the first stages' weight tiles are requested before
+// the kernel waits for its predecessor, so deeper is better while two CTAs fit), 6 for the
+// 128-wide tile and 4 for the widest, one CTA an SM.
+constexpr int stages_of(int bn) { return bn <= 16 ? 6 : bn == 32 ? 5 : bn == 128 ? 6 : 4; }
 
 template <bool SWAP, typename TOut, int EPI = 0>
 int launch_bn(int bn, const CUtensorMap& ma, const CUtensorMap& mb, TOut* out, int rows_a, int rows_b, int K,
