@@ -24,7 +24,7 @@ namespace {
 using namespace qi_attn;
 
 constexpr int kTileKeys = 64;
-constexpr uint32_t kSpinLimit = 1u << 24;
+constexpr uint32_t kSpinLimit = 1u << 21;
 constexpr int kMaxTableEntries = 2048;   // block table entries one CTA keeps in shared memory
 
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {

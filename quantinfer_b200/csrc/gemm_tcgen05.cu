@@ -41,7 +41,7 @@ constexpr int BM = 128;       // rows of A per tile = MMA M
 constexpr int BK = 64;        // bf16 elements per k block = 128 bytes = one swizzle row
 constexpr int UMMA_K = 16;
 constexpr int kThreads = 192;
-constexpr uint32_t kSpinLimit = 1u << 24;   // polls of try_wait before giving up (a second or so)
+constexpr uint32_t kSpinLimit = 1u << 21;   // polls of try_wait before giving up (each poll may itself wait up to a few microseconds)
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
     return (uint32_t)__cvta_generic_to_shared(p);
@@ -426,6 +426,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     } else if (warp == 1) {
         // ---------------- MMA issuer ----------------
         if (lane == 0) {
+            qi::pdl_wait();   // its operands come after the producer's wait: the polls below start counting from there
             constexpr uint32_t idesc = make_idesc(BM, BN);
             uint32_t it = 0;
             int j = 0;                // tiles this CTA has started
