@@ -9,9 +9,9 @@
 // tiles in turn: group b has the tiles of parity b, with an S buffer, a P buffer and an
 // accumulator O_b in tensor memory of its own, so that one group's softmax overlaps the
 // other group's products. A softmax thread reads its row of S from tensor memory, updates
-// its running maximum and sum, and writes the weights P as bfloat16 into shared memory in
-// the layout the tensor core reads (rows of 128 bytes, 128-byte swizzle); the tensor core
-// adds P . V to O_b. The exponent's reference m_ref is not the running maximum itself: it
+// its running maximum and sum, and writes the weights P as bfloat16 back into tensor
+// memory (two to a 32-bit column), from where the tensor core takes them as the A operand
+// and adds P . V to O_b; P never passes through shared memory. The exponent's reference m_ref is not the running maximum itself: it
 // follows the maximum only when that has grown by more than 8 (in the base-2 scale), and
 // only then is the row of O_b read back, scaled by 2^(m_ref_old - m_ref_new) and stored
 // again, after the group's last product has finished. Weights therefore reach 2^8 at most,
@@ -26,7 +26,7 @@
 // issues the MMAs, warps 10-11 idle. The third group hands most of its registers to the
 // softmax groups (setmaxnreg). K is read as a K-major
 // operand, V as an MN-major operand (its rows are keys, the product contracts over keys),
-// P and Q as K-major operands.
+// Q as a K-major operand, P from tensor memory.
 //
 // Formulas: as attention_mma.cu (reference: crates/quantinfer-runtime/src/attention.rs:105-135).
 // No load uses cluster multicast. Every mbarrier wait is bounded; on expiry the kernel sets
@@ -44,13 +44,12 @@ using qi_attn::smem_u32;
 constexpr int BM = 128;          // query rows per CTA
 constexpr int BN = 64;           // keys per tile
 constexpr int D = 128;           // head size
-constexpr int kStages = 3;       // K/V ring
+constexpr int kStages = 4;       // K/V ring
 constexpr int kThreads = 384;    // two softmax groups of four warps, then a group with the producer and the MMA warp
 constexpr int kHalfBytes = 128 * 128;             // Q: 128 rows x 128 bytes, one 64-column half
 constexpr int kQBytes = 2 * kHalfBytes;           // 32 KB
 constexpr int kKVHalfBytes = BN * 128;            // K or V: 64 keys x 128 bytes, one 64-column half
 constexpr int kKVBytes = 2 * kKVHalfBytes;        // 16 KB
-constexpr int kPBytes = BM * 128;                 // P: 128 rows x 64 keys (128 bytes): 16 KB
 constexpr int kMaxTableEntries = 2048;
 constexpr uint32_t kSpinLimit = 1u << 22;   // polls of a barrier before a role gives up (each poll may itself wait a little)
 constexpr float kRescaleStep = 8.f;   // the exponent's reference follows the maximum when that has grown by more (base 2)
@@ -112,6 +111,14 @@ __device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t adesc, uint6
         "setp.ne.b32 p, %4, 0;\n\t"
         "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %6, %7, %8}, p;\n\t}"
         ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(0), "r"(0), "r"(0), "r"(0) : "memory");
+}
+// The same with the A operand in tensor memory (lane = row, two bfloat16 per 32-bit column, K ascending).
+__device__ __forceinline__ void umma_bf16_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, {%5, %6, %7, %8}, p;\n\t}"
+        ::"r"(tmem_d), "r"(tmem_a), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(0), "r"(0), "r"(0), "r"(0) : "memory");
 }
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
@@ -199,8 +206,7 @@ struct Bars {   // byte offsets of the mbarriers from the barrier base
     static constexpr int total = p_free + 16;
 };
 
-constexpr int kSmemBytes = kQBytes + kStages * 2 * kKVBytes + 2 * kPBytes + 256 /*barriers*/ + 4 * kMaxTableEntries +
-                           1024 /*alignment*/;
+constexpr int kSmemBytes = kQBytes + kStages * 2 * kKVBytes + 256 /*barriers*/ + 4 * kMaxTableEntries + 1024 /*alignment*/;
 static_assert(kStages * 2 * kKVBytes >= BM * (D + 2) * 4, "the K/V ring doubles as the merge buffer of the two softmax groups");
 
 __global__ void __launch_bounds__(kThreads, 1)
@@ -215,11 +221,9 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
     uint8_t* aligned = smem_raw + (base - smem_u32(smem_raw));
     const uint32_t q_s = base;
     const uint32_t kv_s = q_s + kQBytes;                          // stage s: K at kv_s + s * 2 * kKVBytes, V one tile further
-    const uint32_t p_s = kv_s + kStages * 2 * kKVBytes;           // P of group b at p_s + b * kPBytes
     uint8_t* kv_mem = aligned + kQBytes;
-    uint8_t* p_mem = kv_mem + kStages * 2 * kKVBytes;
-    const uint32_t bars = p_s + 2 * kPBytes;
-    uint8_t* bar_mem = p_mem + 2 * kPBytes;
+    const uint32_t bars = kv_s + kStages * 2 * kKVBytes;
+    uint8_t* bar_mem = kv_mem + kStages * 2 * kKVBytes;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_mem + Bars::total);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(bar_mem + Bars::total + 4);
     int* s_table = reinterpret_cast<int*>(bar_mem + 256);
@@ -268,6 +272,7 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
     const uint32_t tmem_base = *tmem_slot;
     const uint32_t tmem_s = tmem_base;            // S of group b: columns b * 64 .. b * 64 + 63
     const uint32_t tmem_o = tmem_base + 128;      // accumulator of group b: columns 128 + b * 128 ..
+    const uint32_t tmem_p = tmem_base + 384;      // weights P of group b, two bfloat16 a column: columns 384 + b * 32 ..
 
     auto give_up = [&]() {
         if (!*abort_flag) {
@@ -350,9 +355,8 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
                 const uint32_t v_addr = kv_s + s * 2 * kKVBytes + kKVBytes;
 #pragma unroll
                 for (int kk = 0; kk < BN / 16; ++kk) {
-                    const uint64_t adesc = desc_k_major(p_s + b * kPBytes) + 2u * kk;
                     const uint64_t bdesc = desc_mn_major(v_addr + kk * 16 * 128);
-                    umma_bf16(tmem_o + b * D, adesc, bdesc, idesc_pv, (u > 0 || kk > 0) ? 1u : 0u);
+                    umma_bf16_ts(tmem_o + b * D, tmem_p + b * (BN / 2) + kk * 8, bdesc, idesc_pv, (u > 0 || kk > 0) ? 1u : 0u);
                 }
                 umma_commit(bars + Bars::o_full + 8 * b);          // the accumulator holds the tiles up to this one
                 umma_commit(bars + Bars::kv_empty + 8 * s);        // K_j and V_j have been read
@@ -385,7 +389,6 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
         const int row = quarter * 32 + lane;
         const int pos = pos0 + row;
         const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
-        uint8_t* p_tile = p_mem + b * kPBytes;
         float m = -INFINITY, l = 0.f;      // m: the exponent's reference (at most kRescaleStep below the row's maximum)
         bool ok = true;
 
@@ -451,7 +454,7 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
             // the group's previous P must have been consumed before P is overwritten
             if (u > 0 && !mbar_wait(bars + Bars::p_free + 8 * b, (u - 1) & 1u, abort_flag)) { ok = false; break; }
             float sum = 0.f;
-            uint8_t* prow = p_tile + row * 128;
+            uint32_t pk[BN / 2];      // the row's weights, two bfloat16 a word
 #pragma unroll
             for (int q = 0; q < BN / 8; ++q) {
                 float p[8];
@@ -469,16 +472,16 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
                     }
                 }
                 sum += ((p[0] + p[1]) + (p[2] + p[3])) + ((p[4] + p[5]) + (p[6] + p[7]));
-                uint4 w;
-                w.x = qi_attn::pack_bf16(p[0], p[1]);
-                w.y = qi_attn::pack_bf16(p[2], p[3]);
-                w.z = qi_attn::pack_bf16(p[4], p[5]);
-                w.w = qi_attn::pack_bf16(p[6], p[7]);
-                *reinterpret_cast<uint4*>(prow + ((q ^ (row & 7)) << 4)) = w;
+                pk[4 * q] = qi_attn::pack_bf16(p[0], p[1]);
+                pk[4 * q + 1] = qi_attn::pack_bf16(p[2], p[3]);
+                pk[4 * q + 2] = qi_attn::pack_bf16(p[4], p[5]);
+                pk[4 * q + 3] = qi_attn::pack_bf16(p[6], p[7]);
             }
             l += sum;
-            // P is written: make it visible to the tensor core, then signal
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            // the weights go to tensor memory, where the tensor core reads them as the A operand of P . V
+            tmem_st32(tmem_p + lane_addr + b * (BN / 2), pk);
+            tmem_st_wait();
+            tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(bars + Bars::p_ready + 8 * b);
         }
