@@ -591,6 +591,291 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 }
 
 // Adds split-K partial sums in split order: out[i] = sum_s partial[s, i].
+// ------------------------------------------------------------------ two CTAs on one tile
+//
+// For many tokens the single-CTA kernel is bound by what its 128 x 256 tiles draw from L2 and
+// shared memory (48 KB per 64-wide k block for 512 cycles of tensor-core work) rather than
+// by the tensor core. Here a pair of CTAs on neighbouring SMs (a cluster of two) computes one
+// 256 x 256 tile with tcgen05.mma.cta_group::2: each CTA loads 128 rows of A and 128 rows of
+// B (32 KB per k block, six stages instead of four), the tensor cores of both SMs read B
+// from both CTAs' shared memory, and each CTA's tensor memory receives its 128 rows of the
+// result. Only the even CTA of the pair issues MMAs. Barriers:
+//   full[s]   in the even CTA: its producer announces the bytes of both CTAs' copies, and
+//             both CTAs' TMA copies report there (cta_group::2 form of the copy)
+//   empty[s]  in each CTA: the MMAs' commit arrives on both (multicast commit, not a load)
+//   acc_full  in each CTA: the same at the end of a tile
+//   acc_empty in the even CTA: the four epilogue warps of both CTAs arrive there
+// No load uses cluster multicast. All waits are bounded as in the kernel above; a CTA that
+// gave up is seen by its partner through the status word. Both CTAs pass a cluster barrier
+// before they leave, so that neither frees shared or tensor memory its partner still uses.
+
+constexpr int kPairStages = 6;
+constexpr int kPairHalfBytes = BM * BK * 2;              // 128 rows x 64 bf16 = 16 KB
+constexpr int kPairStageBytes = 2 * kPairHalfBytes;      // this CTA's rows of A, then its rows of B
+constexpr int kPairSmem = kPairStages * kPairStageBytes + 8 * (2 * kPairStages + 4) + 16 + 1024;
+
+__device__ __forceinline__ uint32_t cluster_rank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// The copy of a CTA of a pair; its bytes are reported to the barrier at the same address in the even CTA.
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(dst), "l"(map), "r"(bar & 0xFEFFFFFFu), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t dst_smem, uint32_t cols) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish_pair() {
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t addr, uint32_t cols) {
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void umma_bf16_pair(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, {%5, %6, %7, %8, %9, %10, %11, %12}, p;\n\t}"
+        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(0), "r"(0), "r"(0), "r"(0), "r"(0), "r"(0),
+          "r"(0), "r"(0) : "memory");
+}
+// Arrives on the barrier at this address in both CTAs of the pair when every MMA issued so far has completed.
+__device__ __forceinline__ void umma_commit_pair(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+                 ::"r"(bar), "h"((uint16_t)3) : "memory");
+}
+// Arrives on the barrier at this address in the even CTA of the pair.
+__device__ __forceinline__ void mbar_arrive_leader(uint32_t bar) {
+    asm volatile(
+        "{\n\t.reg .b32 ra;\n\t"
+        "mapa.shared::cluster.u32 ra, %0, 0;\n\t"
+        "mbarrier.arrive.release.cluster.shared::cluster.b64 _, [ra];\n\t}"
+        ::"r"(bar) : "memory");
+}
+
+// out[M, N] = A[M, K] . B[N, K]^T in tiles of 256 x 256, one per pair of CTAs at a time; A are the
+// tokens, B the weights. EPI as in the kernel above (0: the product, 1: silu(gate) * up of column
+// pairs, 2: the q/k/v projection's heads through `rope`).
+template <typename TOut, int EPI>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads)
+gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                         TOut* __restrict__ out, int rows_a, int rows_b, int K, long long ld_out, int* __restrict__ status,
+                         const RopeEpilogue rope) {
+    extern __shared__ uint8_t smem_raw[];
+    constexpr int STAGES = kPairStages;
+    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t* aligned = smem_raw + (base - smem_u32(smem_raw));
+    const uint32_t bars = base + STAGES * kPairStageBytes;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(aligned + STAGES * kPairStageBytes + 8 * (2 * STAGES + 4));
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    auto full_bar = [&](int s) { return bars + 8u * s; };
+    auto empty_bar = [&](int s) { return bars + 8u * (STAGES + s); };
+    auto acc_full_bar = [&](int a) { return bars + 8u * (2 * STAGES + a); };
+    auto acc_empty_bar = [&](int a) { return bars + 8u * (2 * STAGES + 2 + a); };
+
+    qi::pdl_launch_dependents();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_rank();
+    const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
+    constexpr int TM = 2 * BM, TN = 256;
+    const int tiles_m = (rows_a + TM - 1) / TM, tiles_n = (rows_b + TN - 1) / TN;
+    const int total_tiles = tiles_m * tiles_n;
+    const int n_kb = (K + BK - 1) / BK;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(full_bar(s), 1);
+            mbar_init(empty_bar(s), 1);
+        }
+        for (int a = 0; a < 2; ++a) {
+            mbar_init(acc_full_bar(a), 1);
+            mbar_init(acc_empty_bar(a), 8);     // four epilogue warps in each CTA of the pair
+        }
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        tmem_alloc_pair(smem_u32(tmem_slot), 512);
+        tmem_relinquish_pair();
+    }
+    tc_fence_before();
+    cluster_sync_all();       // both CTAs' barriers and tensor memory exist before anything crosses over
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    auto give_up = [&]() {
+        if (!*abort_flag) {
+            *abort_flag = 1;
+            if (status) atomicOr(status, qi::kStatusWaitTimeout);
+        }
+    };
+
+    if (warp == 0) {
+        // ---------------- TMA producer (in both CTAs) ----------------
+        if (lane == 0) {
+            // the first stages' weight rows are requested before the wait for the kernel before this one
+            uint32_t early = 0;
+            if (pair < total_tiles) {
+                const int tile_n = pair / tiles_m;
+                early = (uint32_t)min(n_kb, STAGES);
+                for (uint32_t i = 0; i < early; ++i) {
+                    if (rank == 0) mbar_expect_tx(full_bar(i), 2 * kPairStageBytes);
+                    tma_load_2d_pair(base + i * kPairStageBytes + kPairHalfBytes, &map_b, full_bar(i), (int)i * BK,
+                                     tile_n * TN + (int)rank * BM);
+                }
+            }
+            qi::pdl_wait();
+            uint32_t it = 0;
+            bool ok = true;
+            for (int tile = pair; tile < total_tiles && ok; tile += n_pairs) {
+                const int tile_m = tile % tiles_m, tile_n = tile / tiles_m;
+                for (int i = 0; i < n_kb; ++i, ++it) {
+                    const int s = it % STAGES;
+                    const uint32_t dst = base + s * kPairStageBytes;
+                    if (it < early) {
+                        tma_load_2d_pair(dst, &map_a, full_bar(s), i * BK, tile_m * TM + (int)rank * BM);
+                        continue;
+                    }
+                    if (!mbar_wait(empty_bar(s), ((it / STAGES) & 1u) ^ 1u, abort_flag, status)) {
+                        give_up();
+                        ok = false;
+                        break;
+                    }
+                    if (rank == 0) mbar_expect_tx(full_bar(s), 2 * kPairStageBytes);
+                    tma_load_2d_pair(dst, &map_a, full_bar(s), i * BK, tile_m * TM + (int)rank * BM);
+                    tma_load_2d_pair(dst + kPairHalfBytes, &map_b, full_bar(s), i * BK, tile_n * TN + (int)rank * BM);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer (the even CTA only) ----------------
+        if (lane == 0 && rank == 0) {
+            qi::pdl_wait();
+            constexpr uint32_t idesc = make_idesc(TM, TN);
+            uint32_t it = 0;
+            int j = 0;
+            bool ok = true;
+            for (int tile = pair; tile < total_tiles && ok; tile += n_pairs, ++j) {
+                const int acc = j & 1;
+                if (!mbar_wait(acc_empty_bar(acc), (((uint32_t)j >> 1) & 1u) ^ 1u, abort_flag, status)) {
+                    give_up();
+                    break;
+                }
+                tc_fence_after();
+                const uint32_t tmem_d = tmem_base + (uint32_t)acc * TN;
+                for (int i = 0; i < n_kb; ++i, ++it) {
+                    const int s = it % STAGES;
+                    if (!mbar_wait(full_bar(s), (it / STAGES) & 1u, abort_flag, status)) {
+                        give_up();
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after();
+                    const uint32_t a_addr = base + s * kPairStageBytes;
+                    const uint64_t adesc = make_smem_desc(a_addr);
+                    const uint64_t bdesc = make_smem_desc(a_addr + kPairHalfBytes);
+#pragma unroll
+                    for (int k = 0; k < BK / UMMA_K; ++k)
+                        umma_bf16_pair(tmem_d, adesc + 2u * k, bdesc + 2u * k, idesc, (i > 0 || k > 0) ? 1u : 0u);
+                    umma_commit_pair(empty_bar(s));
+                }
+                if (ok) umma_commit_pair(acc_full_bar(acc));
+            }
+        }
+    } else {
+        // ---------------- epilogue (warps 2..5 of both CTAs): this CTA's 128 rows of the tile ----------------
+        const int quarter = warp & 3;
+        qi::pdl_wait();
+        int j = 0;
+        for (int tile = pair; tile < total_tiles; tile += n_pairs, ++j) {
+            const int tile_m = tile % tiles_m, tile_n = tile / tiles_m;
+            const int acc = j & 1;
+            if (!mbar_wait(acc_full_bar(acc), ((uint32_t)j >> 1) & 1u, abort_flag, status)) {
+                if (lane == 0) give_up();
+                break;
+            }
+            tc_fence_after();
+            const int row = tile_m * TM + (int)rank * BM + quarter * 32 + lane;
+            const uint32_t tmem_tile = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)acc * TN;
+            if constexpr (EPI == 2) {
+                rope_epilogue<TN>(tmem_tile, tile_n * TN, row, row < rows_a, rows_b, rope, status);
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive_leader(acc_empty_bar(acc));
+                continue;
+            }
+#pragma unroll 1
+            for (int c0 = 0; c0 < TN; c0 += 32) {
+                uint32_t r[32];
+                tmem_ld32(tmem_tile + (uint32_t)c0, r);
+                tmem_ld_wait();
+                if (c0 + 32 >= TN) {
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive_leader(acc_empty_bar(acc));
+                }
+                const int b0 = tile_n * TN + c0;
+                if (row >= rows_a) continue;
+                const bool full = b0 + 32 <= rows_b;
+                if (EPI == 1) {
+                    // columns come in pairs (gate, up): half as many outputs
+                    TOut* orow = out + (size_t)row * ld_out + (b0 >> 1);
+                    if (full && ((reinterpret_cast<uintptr_t>(orow) & 15u) == 0) && sizeof(TOut) == 2) {
+#pragma unroll
+                        for (int q0 = 0; q0 < 32; q0 += 16) {
+                            uint4 v;
+                            v.x = pack2(silu_mul(__uint_as_float(r[q0 + 0]), __uint_as_float(r[q0 + 1])),
+                                        silu_mul(__uint_as_float(r[q0 + 2]), __uint_as_float(r[q0 + 3])));
+                            v.y = pack2(silu_mul(__uint_as_float(r[q0 + 4]), __uint_as_float(r[q0 + 5])),
+                                        silu_mul(__uint_as_float(r[q0 + 6]), __uint_as_float(r[q0 + 7])));
+                            v.z = pack2(silu_mul(__uint_as_float(r[q0 + 8]), __uint_as_float(r[q0 + 9])),
+                                        silu_mul(__uint_as_float(r[q0 + 10]), __uint_as_float(r[q0 + 11])));
+                            v.w = pack2(silu_mul(__uint_as_float(r[q0 + 12]), __uint_as_float(r[q0 + 13])),
+                                        silu_mul(__uint_as_float(r[q0 + 14]), __uint_as_float(r[q0 + 15])));
+                            *reinterpret_cast<uint4*>(reinterpret_cast<qi::bf16*>(orow) + (q0 >> 1)) = v;
+                        }
+                    } else {
+#pragma unroll
+                        for (int q = 0; q < 32; q += 2)
+                            if (b0 + q + 1 < rows_b)
+                                store1<TOut>(orow + (q >> 1), silu_mul(__uint_as_float(r[q]), __uint_as_float(r[q + 1])));
+                    }
+                } else {
+                    TOut* orow = out + (size_t)row * ld_out + b0;
+                    if (full && ((reinterpret_cast<uintptr_t>(orow) & 15u) == 0) && sizeof(TOut) == 2) {
+#pragma unroll
+                        for (int q = 0; q < 32; q += 8) {
+                            uint4 v;
+                            v.x = pack2(__uint_as_float(r[q + 0]), __uint_as_float(r[q + 1]));
+                            v.y = pack2(__uint_as_float(r[q + 2]), __uint_as_float(r[q + 3]));
+                            v.z = pack2(__uint_as_float(r[q + 4]), __uint_as_float(r[q + 5]));
+                            v.w = pack2(__uint_as_float(r[q + 6]), __uint_as_float(r[q + 7]));
+                            *reinterpret_cast<uint4*>(reinterpret_cast<qi::bf16*>(orow) + q) = v;
+                        }
+                    } else if (full && ((reinterpret_cast<uintptr_t>(orow) & 15u) == 0) && sizeof(TOut) == 4) {
+#pragma unroll
+                        for (int q = 0; q < 32; q += 4)
+                            *reinterpret_cast<uint4*>(reinterpret_cast<float*>(orow) + q) = make_uint4(r[q], r[q + 1], r[q + 2], r[q + 3]);
+                    } else {
+#pragma unroll
+                        for (int q = 0; q < 32; ++q)
+                            if (b0 + q < rows_b) store1<TOut>(orow + q, __uint_as_float(r[q]));
+                    }
+                }
+            }
+        }
+    }
+    tc_fence_before();
+    cluster_sync_all();       // neither CTA goes before its partner is done with what it holds
+    if (warp == 1) tmem_dealloc_pair(tmem_base, 512);
+}
+
 template <typename TOut>
 __global__ void splitk_reduce_kernel(const float* __restrict__ partial, TOut* __restrict__ out, size_t n, int splits) {
     qi::pdl_enter();
@@ -665,6 +950,23 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, TOut* out, int rows_a, 
     return qi::check_launch("gemm_bf16");
 }
 
+template <typename TOut, int EPI>
+int launch_pair(const CUtensorMap& ma, const CUtensorMap& mb, TOut* out, int M, int N, int K, long long ld, int* status,
+                cudaStream_t stream, const RopeEpilogue& rope = RopeEpilogue{}) {
+    auto kern = gemm_tcgen05_pair_kernel<TOut, EPI>;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kPairSmem);
+        if (e != cudaSuccess) return qi::fail("gemm_bf16: cannot reserve %d bytes of shared memory: %s", kPairSmem, cudaGetErrorString(e));
+        configured = true;
+    }
+    const long long tiles = (long long)((M + 2 * BM - 1) / (2 * BM)) * ((N + 255) / 256);
+    const long long pairs = sm_count() / 2;
+    const unsigned grid = 2u * (unsigned)(tiles < pairs ? tiles : pairs);
+    qi::launch(kern, dim3(grid), dim3(kThreads), kPairSmem, stream, ma, mb, out, M, N, K, ld, status, rope);
+    return qi::check_launch("gemm_bf16 (CTA pairs)");
+}
+
 // Pipeline stages by tile width: as many as let two CTAs stay resident on an SM for the narrow
 // tiles (6 of 18 KB, 5 of 20 KB, 4 of 24 KB: the first stages' weight tiles are requested before
 // the kernel waits for its predecessor, so deeper is better while two CTAs fit), 6 for the
@@ -686,7 +988,8 @@ int launch_bn(int bn, const CUtensorMap& ma, const CUtensorMap& mb, TOut* out, i
 
 }  // namespace
 
-// The orientation, tile width and K split `qi_gemm_bf16` uses when the caller does not say
+// The orientation (0: tokens on the 128 rows, 1: weights on the 128 rows, 2: tokens on the rows of
+// CTA pairs), tile width and K split `qi_gemm_bf16` uses when the caller does not say
 // (allow_split 0: the caller needs the whole sum in one CTA, as the fused activation does).
 //
 // Up to 64 tokens the product is a weight stream: the weights are the 128-row operand, the
@@ -735,6 +1038,15 @@ extern "C" int qi_gemm_bf16_plan(int M, int N, int K, int allow_split, int* swap
                 }
             }
         }
+        // pairs of CTAs on tiles of 256 x 256 (no K split): a k block of a pair's tile takes what a k block
+        // of a 128 x 256 tile takes on one SM, less the 13% the lighter load on L2 and shared memory gives
+        const long long pair_tiles = (long long)((M + 2 * BM - 1) / (2 * BM)) * ((N + 255) / 256);
+        const long long pair_waves = (pair_tiles + sms / 2 - 1) / (sms / 2);
+        if ((double)pair_waves * (kb_total + 12) * 0.87 < best * 0.999) {
+            sw = 2;
+            b = 256;
+            sp = 1;
+        }
     }
     *swap = sw; *bn = b; *splits = sp;
     return 0;
@@ -757,6 +1069,16 @@ extern "C" int qi_gemm_bf16(const void* x, const void* w, void* out, int out_dty
     const int kb_total = (K + BK - 1) / BK;
     const int kb_per_split = (kb_total + splits - 1) / splits;
     QI_REQUIRE((splits - 1) * kb_per_split < kb_total, "gemm_bf16: %d splits leave one without work (K=%d)", splits, K);
+    if (swap == 2) {
+        // pairs of CTAs: tokens on the rows, no K split
+        QI_REQUIRE(splits == 1, "gemm_bf16: the CTA-pair kernel does not split K");
+        CUtensorMap pa, pb;
+        if (make_map(&pa, x, M, K, BM)) return 1;
+        if (make_map(&pb, w, N, K, BM)) return 1;
+        if (epilogue == 1) return launch_pair<qi::bf16, 1>(pa, pb, (qi::bf16*)out, M, N, K, N / 2, status, stream);
+        if (out_dtype == qi::kF32) return launch_pair<float, 0>(pa, pb, (float*)out, M, N, K, N, status, stream);
+        return launch_pair<qi::bf16, 0>(pa, pb, (qi::bf16*)out, M, N, K, N, status, stream);
+    }
     const void* a = swap ? w : x;
     const void* b = swap ? x : w;
     const int rows_a = swap ? N : M, rows_b = swap ? M : N;
@@ -816,8 +1138,8 @@ extern "C" int qi_gemm_bf16_qkv_rope(const void* x, const void* w, int M, int K,
     const long long n_ll = (long long)(nq + 2 * nkv) * 128;
     QI_REQUIRE(n_ll < 2147483647LL, "gemm_bf16_qkv_rope: too many heads");
     const int N = (int)n_ll;
-    int plan_swap, bn, plan_splits;
-    qi_gemm_bf16_plan(M > 256 ? M : 257, N, K, 0, &plan_swap, &bn, &plan_splits);   // the width for operands that are not swapped
+    int plan_mode, bn, plan_splits;
+    qi_gemm_bf16_plan(M > 256 ? M : 257, N, K, 0, &plan_mode, &bn, &plan_splits);   // the width for operands that are not swapped
     if (bn < 128) bn = 128;                                                        // a tile holds whole heads
     const int kb_total = (K + BK - 1) / BK;
     QI_REQUIRE((long long)((M + BM - 1) / BM) * ((N + bn - 1) / bn) < 2147483647LL, "gemm_bf16_qkv_rope: too many tiles");
@@ -829,7 +1151,13 @@ extern "C" int qi_gemm_bf16_qkv_rope(const void* x, const void* w, int M, int K,
     e.positions = positions; e.token_req = token_req; e.block_table = block_table;
     e.k_pages = (qi::bf16*)k_pages; e.v_pages = (qi::bf16*)v_pages; e.eps = eps;
     e.max_blocks = max_blocks; e.page_size = page_size; e.num_pages = num_pages; e.nq = nq; e.nkv = nkv;
+    if (plan_mode == 2) {
+        CUtensorMap pb;
+        if (make_map(&pb, w, N, K, BM)) return 1;
+        return launch_pair<qi::bf16, 2>(ma, pb, (qi::bf16*)nullptr, M, N, K, N, status, stream, e);
+    }
     if (bn == 256)
         return launch<256, stages_of(256), false, qi::bf16, 2>(ma, mb, (qi::bf16*)nullptr, M, N, K, N, 1, kb_total, 0, status, stream, e);
     return launch<128, stages_of(128), false, qi::bf16, 2>(ma, mb, (qi::bf16*)nullptr, M, N, K, N, 1, kb_total, 0, status, stream, e);
 }
+

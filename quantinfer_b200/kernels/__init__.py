@@ -612,17 +612,19 @@ def gemm_bf16_supported(M: int, N: int, K: int, out_dtype) -> bool:
 
 
 def gemm_bf16_plan(M: int, N: int, K: int, allow_split: bool = True):
-    """(swap operands, tile width, K splits) the library would choose; allow_split=False for a
-    product whose epilogue needs the whole sum (the fused activation)."""
+    """(orientation, tile width, K splits) the library would choose; allow_split=False for a
+    product whose epilogue needs the whole sum (the fused activation). Orientation 0: the tokens
+    ride the 128 rows of the tensor-core tile; 1: the weights do (few tokens); 2: tokens on the rows
+    of tiles of 256 x 256 computed by pairs of CTAs (many tokens)."""
     swap, bn, splits = C.c_int(), C.c_int(), C.c_int()
     library().qi_gemm_bf16_plan(M, N, K, int(allow_split), C.byref(swap), C.byref(bn), C.byref(splits))
-    return bool(swap.value), bn.value, splits.value
+    return swap.value, bn.value, splits.value
 
 
 def gemm_bf16(x: torch.Tensor, w: torch.Tensor, out, plan=None, status=None, epilogue: str | None = None,
               keep_partials: bool = False):
     """out[M, N] = x[M, K] @ w[N, K]^T on the tcgen05 tensor cores; x, w bfloat16; out
-    bfloat16 or float32. `plan` = (swap, tile width, splits) overrides the choice.
+    bfloat16 or float32. `plan` = (orientation, tile width, splits) overrides the choice.
 
     epilogue="silu_mul": w's rows are (gate, up) pairs and out is [M, N / 2] =
     silu(gate) * up. keep_partials=True: when the plan splits K, the float32 partial sums

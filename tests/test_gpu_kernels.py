@@ -105,6 +105,8 @@ def test_gemm_simt(tx, tw, ty, M, N, K):
     (128, 128, 64, (False, 128, 1)), (100, 72, 136, (False, 64, 1)), (300, 520, 264, None),
     (4, 128, 64, (True, 16, 1)), (1, 384, 96, None), (33, 517, 168, (True, 64, 2)),
     (64, 1000, 2048, None), (200, 300, 4096, None), (700, 328, 168, (False, 256, 1)), (17, 264, 1032, (True, 32, 4)),
+    # pairs of CTAs on tiles of 256 x 256: one tile, ragged edges in both directions, many k blocks, more tiles than pairs
+    (256, 256, 64, (2, 256, 1)), (300, 400, 136, (2, 256, 1)), (129, 130, 1032, (2, 256, 1)), (2560, 2304, 320, (2, 256, 1)),
 ])
 @pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
 def test_gemm_tcgen05(M, N, K, plan, out_dtype):
@@ -133,6 +135,16 @@ def test_gemm_tcgen05_silu_epilogue_and_partials(M, N, K):
     parts = _k().gemm_bf16(x.to(DEV), w.to(DEV), None, plan=(True if M <= 256 else False, 16 if M <= 16 else 256 if M > 64 else 64, 2),
                            keep_partials=True)
     assert parts.shape == (2, M, N) and float((parts.double().sum(0).cpu() - y).abs().max()) < 2e-4
+    # the same activation from the kernel that runs on pairs of CTAs
+    act2 = torch.empty_like(act)
+    _k().gemm_bf16(x.to(DEV), w.to(DEV), act2, plan=(2, 256, 1), epilogue="silu_mul")
+    assert float((act2.double().cpu() - ref).abs().max()) < max(0.05, float(ref.abs().max()) * 2 ** -7)
+
+
+def test_gemm_plan_takes_cta_pairs_for_many_tokens():
+    k = _k()
+    assert k.gemm_bf16_plan(2048, 4096, 4096)[0] == 2 and k.gemm_bf16_plan(2048, 24576, 4096, allow_split=False)[0] == 2
+    assert k.gemm_bf16_plan(8, 4096, 4096)[0] == 1 and k.gemm_bf16_plan(64, 24576, 4096)[0] == 1
 
 
 # ------------------------------------------------------------------ q/k norm, rotation, cache write
@@ -143,12 +155,14 @@ def test_gemm_tcgen05_silu_epilogue_and_partials(M, N, K):
     (513, 256, 1, 1, 64, False, True, True),    # 3 heads: one tile of 256 and a half; no norm
     (384, 72, 1, 2, 32, True, False, True),     # no rotation
     (260, 64, 2, 1, 16, True, True, False),     # reads another layer's cache: queries only
+    (1300, 64, 12, 4, 16, True, True, True),    # 20 heads, many tokens: the kernel on pairs of CTAs
+    (1100, 136, 9, 3, 64, True, True, True),    # 15 heads: the pair's last tile holds one head only
 ])
 def test_gemm_qkv_rope(M, K, nq, nkv, ps, norm, rope, write):
     """The q/k/v projection with norm, rotation and cache write in its epilogue, against a 64-bit
     product followed by the formulas; heads that straddle tile borders, rows past the last token."""
     torch.manual_seed(M + K)
-    d, eps, theta, max_pos = 128, 1e-5, 1e4, 700
+    d, eps, theta, max_pos = 128, 1e-5, 1e4, 1400
     k = _k()
     assert k.gemm_qkv_rope_supported(M, K, d, d if rope else 0, torch.bfloat16, torch.bfloat16)
     assert not k.gemm_qkv_rope_supported(200, K, d, d, torch.bfloat16, torch.bfloat16)
