@@ -4,29 +4,32 @@
 // One CTA takes 128 query rows of one request and one query head and walks the keys in
 // tiles of 64. Per tile two products run on the tensor core:
 //     S = Q . K^T      (128 x 64,  K = head size)    -> tensor memory, 32-bit
-//     O_j = P . V      (128 x 128, K = 64 keys)      -> tensor memory, 32-bit
-// Two groups of 128 softmax threads (one thread per query row in each group) take the
-// tiles in turn: group b has the tiles of parity b, with an S buffer, a P buffer and an
-// accumulator O_b in tensor memory of its own, so that one group's softmax overlaps the
-// other group's products. A softmax thread reads its row of S from tensor memory, updates
-// its running maximum and sum, and writes the weights P as bfloat16 back into tensor
-// memory (two to a 32-bit column), from where the tensor core takes them as the A operand
-// and adds P . V to O_b; P never passes through shared memory. The exponent's reference m_ref is not the running maximum itself: it
-// follows the maximum only when that has grown by more than 8 (in the base-2 scale), and
-// only then is the row of O_b read back, scaled by 2^(m_ref_old - m_ref_new) and stored
-// again, after the group's last product has finished. Weights therefore reach 2^8 at most,
-// sum and accumulator share one reference, and their quotient is unchanged; after the
-// first few tiles of a row the accumulator is hardly ever touched. At the end the two
-// groups' partial results (reference, sum, accumulator over their own tiles) are merged
-// through shared memory like the ranges of a split-key attention.
+//     O += P . V       (128 x 128, K = 64 keys)      -> tensor memory, 32-bit
+// 128 softmax threads, one per query row, read their row of S from tensor memory, update the
+// row's running maximum and sum, and write the weights P as bfloat16 back into tensor memory
+// (two to a 32-bit column), from where the tensor core takes them as the A operand and adds
+// P . V to O; P never passes through shared memory. The exponent's reference m_ref is not the
+// running maximum itself: it follows the maximum only when that has grown by more than 8 (in
+// the base-2 scale), and only then is the row of O read back, scaled by
+// 2^(m_ref_old - m_ref_new) and stored again, after the last product has finished. Weights
+// therefore reach 2^8 at most, sum and accumulator share one reference, and their quotient is
+// unchanged; after the first few tiles of a row the accumulator is hardly ever touched.
 //
-// Roles (384 threads = three groups of four warps): warps 0-3 and 4-7 are the two softmax
-// groups; in the third group warp 8 issues TMA loads of Q and of the K/V tiles (page pieces
-// through the block table, as in attention_tma.cu), warp 9 allocates tensor memory and
-// issues the MMAs, warps 10-11 idle. The third group hands most of its registers to the
-// softmax groups (setmaxnreg). K is read as a K-major
-// operand, V as an MN-major operand (its rows are keys, the product contracts over keys),
-// Q as a K-major operand, P from tensor memory.
+// Two such CTAs share an SM (192 threads, 256 columns of tensor memory: S 64, O 128, P 32; Q
+// and two K/V stages in shared memory): the softmax of one overlaps the products of the
+// other, and so do one CTA's start (barriers, the copy of Q, the first tiles) and end (the
+// last product, the normalised store) with its neighbour's steady state, which at a few
+// thousand keys are as long as the work itself. (An earlier form had one CTA an SM with two
+// softmax groups on alternating key tiles of the same query rows, merged at the end: 322,
+// 626, 685 TFLOP/s at 2,048, 8,192 and 16,384 tokens against 403, 741, 773 now.)
+//
+// Roles: warps 0-3 are the softmax threads; warp 4 issues the TMA loads of Q and of the K/V
+// tiles (page pieces through the block table, as in attention_tma.cu); warp 5 allocates tensor
+// memory and issues the MMAs: S of tile j + 1 as soon as the softmax threads have taken S of
+// tile j into registers, then P.V of tile j when its weights are ready. K is read as a
+// K-major operand, V as an MN-major operand (its rows are keys, the product contracts over
+// keys), Q as a K-major operand, P from tensor memory. A quarter of the exponentials are
+// computed on the FMA pipe (the special-function unit is the busiest pipe of this kernel).
 //
 // Formulas: as attention_mma.cu (reference: crates/quantinfer-runtime/src/attention.rs:105-135).
 // No load uses cluster multicast. Every mbarrier wait is bounded; on expiry the kernel sets
@@ -44,8 +47,6 @@ using qi_attn::smem_u32;
 constexpr int BM = 128;          // query rows per CTA
 constexpr int BN = 64;           // keys per tile
 constexpr int D = 128;           // head size
-constexpr int kStages = 4;       // K/V ring
-constexpr int kThreads = 384;    // two softmax groups of four warps, then a group with the producer and the MMA warp
 constexpr int kHalfBytes = 128 * 128;             // Q: 128 rows x 128 bytes, one 64-column half
 constexpr int kQBytes = 2 * kHalfBytes;           // 32 KB
 constexpr int kKVHalfBytes = BN * 128;            // K or V: 64 keys x 128 bytes, one 64-column half
@@ -68,16 +69,6 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
         "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-    return ok != 0;
-}
-// The same without any waiting inside the instruction: for a thread that watches several barriers.
-__device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
         "selp.u32 %0, 1, 0, p;\n\t}"
         : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
     return ok != 0;
@@ -194,43 +185,41 @@ constexpr uint32_t idesc(int n, bool b_mn_major) {
            ((uint32_t)(BM >> 4) << 24);
 }
 
-struct Bars {   // byte offsets of the mbarriers from the barrier base
+constexpr int kStages = 2;       // K/V ring
+constexpr int kThreads = 192;    // four softmax warps, the TMA warp, the MMA warp
+struct Bars {
     static constexpr int q_full = 0;
-    static constexpr int kv_full = 8;                     // [kStages]
-    static constexpr int kv_empty = kv_full + 8 * kStages; // [kStages]
-    static constexpr int s_full = kv_empty + 8 * kStages;  // [2]
-    static constexpr int s_free = s_full + 16;             // [2]
-    static constexpr int o_full = s_free + 16;             // [2]
-    static constexpr int p_ready = o_full + 16;            // [2]
-    static constexpr int p_free = p_ready + 16;            // [2]
-    static constexpr int total = p_free + 16;
+    static constexpr int kv_full = 8;                            // [kStages]
+    static constexpr int kv_empty = kv_full + 8 * kStages;   // [kStages]
+    static constexpr int s_full = kv_empty + 8 * kStages;
+    static constexpr int s_free = s_full + 8;
+    static constexpr int o_full = s_free + 8;
+    static constexpr int p_ready = o_full + 8;
+    static constexpr int p_free = p_ready + 8;
+    static constexpr int total = p_free + 8;
 };
-
 constexpr int kSmemBytes = kQBytes + kStages * 2 * kKVBytes + 256 /*barriers*/ + 4 * kMaxTableEntries + 1024 /*alignment*/;
-static_assert(kStages * 2 * kKVBytes >= BM * (D + 2) * 4, "the K/V ring doubles as the merge buffer of the two softmax groups");
 
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__(kThreads, 2)
 attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
-                                 const __grid_constant__ CUtensorMap map_v, qi::bf16* __restrict__ out,
-                                 const int* __restrict__ block_table, int max_blocks, int page_size, int box_rows,
-                                 int num_pages, const int* __restrict__ q_start, const int* __restrict__ start_pos,
-                                 const int* __restrict__ tile_req, const int* __restrict__ tile_q0, int nq, int nkv,
-                                 float scale_log2e, int window, int* __restrict__ status) {
+                                      const __grid_constant__ CUtensorMap map_v, qi::bf16* __restrict__ out,
+                                      const int* __restrict__ block_table, int max_blocks, int page_size, int box_rows,
+                                      int num_pages, const int* __restrict__ q_start, const int* __restrict__ start_pos,
+                                      const int* __restrict__ tile_req, const int* __restrict__ tile_q0, int nq, int nkv,
+                                      float scale_log2e, int window, int* __restrict__ status) {
     extern __shared__ uint8_t smem_raw[];
+    using B = Bars;
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* aligned = smem_raw + (base - smem_u32(smem_raw));
     const uint32_t q_s = base;
-    const uint32_t kv_s = q_s + kQBytes;                          // stage s: K at kv_s + s * 2 * kKVBytes, V one tile further
-    uint8_t* kv_mem = aligned + kQBytes;
+    const uint32_t kv_s = q_s + kQBytes;
     const uint32_t bars = kv_s + kStages * 2 * kKVBytes;
-    uint8_t* bar_mem = kv_mem + kStages * 2 * kKVBytes;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_mem + Bars::total);
-    volatile int* abort_flag = reinterpret_cast<volatile int*>(bar_mem + Bars::total + 4);
+    uint8_t* bar_mem = aligned + kQBytes + kStages * 2 * kKVBytes;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_mem + B::total);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(bar_mem + B::total + 4);
     int* s_table = reinterpret_cast<int*>(bar_mem + 256);
 
     qi::pdl_enter();
-    // blockIdx.x is the head: CTAs that start together work on the same query rows of neighbouring heads
-    // (which share keys and values), and the tile list's order (most keys first) holds across all heads
     const int tile = blockIdx.y, h = blockIdx.x;
     const int hk = h / (nq / nkv);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -238,7 +227,7 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
     const int rows_valid = min(BM, q_start[r + 1] - q0);
     const int pos0 = start_pos[r] + (q0 - q_start[r]);
     const int* table = block_table + (size_t)r * max_blocks;
-    const int hi = pos0 + rows_valid;                                            // keys < hi
+    const int hi = pos0 + rows_valid;
     const int lo = (window > 0 && pos0 - window + 1 > 0) ? pos0 - window + 1 : 0;
     const int t_begin = (lo / BN) * BN;
     const int n_tiles = (hi - t_begin + BN - 1) / BN;
@@ -247,32 +236,28 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
     for (int i = threadIdx.x; i < n_blk; i += blockDim.x) s_table[i] = table[blk0 + i];
 
     if (threadIdx.x == 0) {
-        mbar_init(bars + Bars::q_full, 1);
+        mbar_init(bars + B::q_full, 1);
         for (int s = 0; s < kStages; ++s) {
-            mbar_init(bars + Bars::kv_full + 8 * s, 1);
-            mbar_init(bars + Bars::kv_empty + 8 * s, 1);
+            mbar_init(bars + B::kv_full + 8 * s, 1);
+            mbar_init(bars + B::kv_empty + 8 * s, 1);
         }
-        for (int b = 0; b < 2; ++b) {
-            mbar_init(bars + Bars::s_full + 8 * b, 1);
-            mbar_init(bars + Bars::s_free + 8 * b, 4);    // one arrival per warp of the group
-            mbar_init(bars + Bars::o_full + 8 * b, 1);
-            mbar_init(bars + Bars::p_ready + 8 * b, 4);
-            mbar_init(bars + Bars::p_free + 8 * b, 1);
-        }
+        mbar_init(bars + B::s_full, 1);
+        mbar_init(bars + B::s_free, 4);      // one arrival per softmax warp
+        mbar_init(bars + B::o_full, 1);
+        mbar_init(bars + B::p_ready, 4);
+        mbar_init(bars + B::p_free, 1);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == 9) {
-        tmem_alloc(smem_u32(tmem_slot), 512);
+    if (warp == 5) {
+        tmem_alloc(smem_u32(tmem_slot), 256);
         tmem_relinquish();
     }
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
-    const uint32_t tmem_s = tmem_base;            // S of group b: columns b * 64 .. b * 64 + 63
-    const uint32_t tmem_o = tmem_base + 128;      // accumulator of group b: columns 128 + b * 128 ..
-    const uint32_t tmem_p = tmem_base + 384;      // weights P of group b, two bfloat16 a column: columns 384 + b * 32 ..
+    const uint32_t tmem_s = tmem_base, tmem_o = tmem_base + 64, tmem_p = tmem_base + 192;
 
     auto give_up = [&]() {
         if (!*abort_flag) {
@@ -281,22 +266,20 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
         }
     };
 
-    if (warp >= 8) {
-      asm volatile("setmaxnreg.dec.sync.aligned.u32 40;" ::: "memory");    // the whole group gives registers back
-      if (warp == 8) {
+    if (warp == 4) {
         // ---------------- TMA producer ----------------
         if (lane == 0) {
-            mbar_expect_tx(bars + Bars::q_full, kQBytes);
-            tma_load_2d(q_s, &map_q, bars + Bars::q_full, h * D, q0);
-            tma_load_2d(q_s + kHalfBytes, &map_q, bars + Bars::q_full, h * D + 64, q0);
+            mbar_expect_tx(bars + B::q_full, kQBytes);
+            tma_load_2d(q_s, &map_q, bars + B::q_full, h * D, q0);
+            tma_load_2d(q_s + kHalfBytes, &map_q, bars + B::q_full, h * D + 64, q0);
             int issued = 0;
             for (int j = 0; j < n_tiles; ++j) {
                 const int s = j % kStages;
-                if (!mbar_wait(bars + Bars::kv_empty + 8 * s, (((uint32_t)j / kStages) & 1u) ^ 1u, abort_flag)) {
+                if (!mbar_wait(bars + B::kv_empty + 8 * s, (((uint32_t)j / kStages) & 1u) ^ 1u, abort_flag)) {
                     give_up();
                     break;
                 }
-                const uint32_t full = bars + Bars::kv_full + 8 * s;
+                const uint32_t full = bars + B::kv_full + 8 * s;
                 const uint32_t k_dst = kv_s + s * 2 * kKVBytes, v_dst = k_dst + kKVBytes;
                 mbar_expect_tx(full, 2 * kKVBytes);
                 const int t0 = t_begin + j * BN;
@@ -319,101 +302,81 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
             if (*abort_flag) {   // copies in flight write into this CTA's shared memory: wait (bounded) for them
                 for (int j = max(issued - kStages, 0); j < issued; ++j)
                     for (uint32_t t = 0; t < (1u << 20); ++t)
-                        if (mbar_try_wait(bars + Bars::kv_full + 8 * (j % kStages), ((uint32_t)j / kStages) & 1u)) break;
+                        if (mbar_try_wait(bars + B::kv_full + 8 * (j % kStages), ((uint32_t)j / kStages) & 1u)) break;
             }
         }
-      } else if (warp == 9) {
+    } else if (warp == 5) {
         // ---------------- MMA issuer ----------------
         if (lane == 0) {
             constexpr uint32_t idesc_qk = idesc(BN, false), idesc_pv = idesc(D, true);
-            bool ok = mbar_wait(bars + Bars::q_full, 0, abort_flag);
-            // S = Q . K^T of tile j into the S buffer of group j & 1, once the tile's keys have landed and the
-            // group has taken its previous S into registers; false if one of the two is not there yet
-            auto try_qk = [&](int j) -> bool {
-                const int s = j % kStages, b = j & 1;
-                const uint32_t u = (uint32_t)j >> 1;                 // the group's own tile count
-                if (!mbar_test(bars + Bars::kv_full + 8 * s, ((uint32_t)j / kStages) & 1u)) return false;
-                if (!mbar_test(bars + Bars::s_free + 8 * b, (u & 1u) ^ 1u)) return false;
+            bool ok = mbar_wait(bars + B::q_full, 0, abort_flag);
+            auto issue_qk = [&](int j) -> bool {
+                const int s = j % kStages;
+                if (!mbar_wait(bars + B::kv_full + 8 * s, ((uint32_t)j / kStages) & 1u, abort_flag)) return false;
+                if (!mbar_wait(bars + B::s_free, ((uint32_t)j & 1u) ^ 1u, abort_flag)) return false;   // the group holds S of tile j - 1
                 tc_fence_after();
                 const uint32_t k_addr = kv_s + s * 2 * kKVBytes;
 #pragma unroll
                 for (int ks = 0; ks < D / 16; ++ks) {
                     const uint64_t adesc = desc_k_major(q_s + (ks >> 2) * kHalfBytes) + 2u * (ks & 3);
                     const uint64_t bdesc = desc_k_major(k_addr + (ks >> 2) * kKVHalfBytes) + 2u * (ks & 3);
-                    umma_bf16(tmem_s + b * BN, adesc, bdesc, idesc_qk, ks > 0 ? 1u : 0u);
+                    umma_bf16(tmem_s, adesc, bdesc, idesc_qk, ks > 0 ? 1u : 0u);
                 }
-                umma_commit(bars + Bars::s_full + 8 * b);
+                umma_commit(bars + B::s_full);
                 return true;
             };
-            // O_b += P . V of tile j, once the group's weights are ready (and with them its accumulator,
-            // rescaled if its reference moved)
-            auto try_pv = [&](int j) -> bool {
-                const int s = j % kStages, b = j & 1;
-                const uint32_t u = (uint32_t)j >> 1;
-                if (!mbar_test(bars + Bars::p_ready + 8 * b, u & 1u)) return false;
+            if (ok && n_tiles > 0) ok = issue_qk(0);
+            for (int j = 0; j < n_tiles && ok; ++j) {
+                if (j + 1 < n_tiles && !issue_qk(j + 1)) {
+                    ok = false;
+                    break;
+                }
+                if (!mbar_wait(bars + B::p_ready, (uint32_t)j & 1u, abort_flag)) {
+                    ok = false;
+                    break;
+                }
                 tc_fence_after();
+                const int s = j % kStages;
                 const uint32_t v_addr = kv_s + s * 2 * kKVBytes + kKVBytes;
 #pragma unroll
                 for (int kk = 0; kk < BN / 16; ++kk) {
                     const uint64_t bdesc = desc_mn_major(v_addr + kk * 16 * 128);
-                    umma_bf16_ts(tmem_o + b * D, tmem_p + b * (BN / 2) + kk * 8, bdesc, idesc_pv, (u > 0 || kk > 0) ? 1u : 0u);
+                    umma_bf16_ts(tmem_o, tmem_p + kk * 8, bdesc, idesc_pv, (j > 0 || kk > 0) ? 1u : 0u);
                 }
-                umma_commit(bars + Bars::o_full + 8 * b);          // the accumulator holds the tiles up to this one
-                umma_commit(bars + Bars::kv_empty + 8 * s);        // K_j and V_j have been read
-                umma_commit(bars + Bars::p_free + 8 * b);          // the group's P may be overwritten
-                return true;
-            };
-            // S of the first two tiles, then for every tile: P.V as soon as its weights are ready, and S two
-            // tiles on. (Issuing whatever is possible first, in no fixed order between the groups, and issuing
-            // a group's next S before this tile's P.V were both measured no faster.)
-            auto spin = [&](auto&& attempt) -> bool {
-                for (uint32_t i = 0; i < (kSpinLimit << 4); ++i) {
-                    if (attempt()) return true;
-                    if ((i & 4095u) == 4095u && *abort_flag) return false;
-                }
-                return false;
-            };
-            for (int j = 0; j < 2 && j < n_tiles && ok; ++j) ok = spin([&] { return try_qk(j); });
-            for (int j = 0; j < n_tiles && ok; ++j) {
-                ok = spin([&] { return try_pv(j); });
-                if (ok && j + 2 < n_tiles) ok = spin([&] { return try_qk(j + 2); });
+                umma_commit(bars + B::o_full);
+                umma_commit(bars + B::kv_empty + 8 * s);
+                umma_commit(bars + B::p_free);
             }
             if (!ok) give_up();
         }
-      }
     } else {
-        // ---------------- softmax threads: group b = warps 4 b .. 4 b + 3, one query row each ----------------
-        asm volatile("setmaxnreg.inc.sync.aligned.u32 232;" ::: "memory");
-        const int b = warp >> 2;
-        const int quarter = warp & 3;                 // the 32 tensor-memory lanes this warp may read
+        // ---------------- softmax threads: one query row each ----------------
+        const int quarter = warp & 3;
         const int row = quarter * 32 + lane;
         const int pos = pos0 + row;
         const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
-        float m = -INFINITY, l = 0.f;      // m: the exponent's reference (at most kRescaleStep below the row's maximum)
+        float m = -INFINITY, l = 0.f;
         bool ok = true;
-
-        uint32_t u = 0;
-        for (int j = b; j < n_tiles && ok; j += 2, ++u) {
+        for (int j = 0; j < n_tiles && ok; ++j) {
+            const uint32_t u = (uint32_t)j;
             const int t0 = t_begin + j * BN;
-            if (!mbar_wait(bars + Bars::s_full + 8 * b, u & 1u, abort_flag)) { ok = false; break; }
+            if (!mbar_wait(bars + B::s_full, u & 1u, abort_flag)) { ok = false; break; }
             tc_fence_after();
-            // keys this row may see in this tile: columns [c_lo, c_hi)
             int c_hi = min(min(pos, hi - 1) - t0 + 1, BN);
             int c_lo = max(lo, window > 0 ? pos - window + 1 : 0) - t0;
             if (c_lo < 0) c_lo = 0;
             if (c_hi < 0) c_hi = 0;
             uint32_t sv[BN];
-            tmem_ld32(tmem_s + lane_addr + b * BN, *reinterpret_cast<uint32_t(*)[32]>(&sv[0]));
-            tmem_ld32(tmem_s + lane_addr + b * BN + 32, *reinterpret_cast<uint32_t(*)[32]>(&sv[32]));
+            tmem_ld32(tmem_s + lane_addr, *reinterpret_cast<uint32_t(*)[32]>(&sv[0]));
+            tmem_ld32(tmem_s + lane_addr + 32, *reinterpret_cast<uint32_t(*)[32]>(&sv[32]));
             tmem_ld_wait();
-            // S is in registers: the tensor core may write the group's next S
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(bars + Bars::s_free + 8 * b);
+            if (lane == 0) mbar_arrive(bars + B::s_free);
             float mx = -INFINITY;
-            const bool unmasked = c_lo == 0 && c_hi == BN;      // all but the tiles on the diagonal and at a window's edge
+            const bool unmasked = c_lo == 0 && c_hi == BN;
             if (unmasked) {
-                float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};     // four chains instead of one
+                float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
                 for (int i = 0; i < BN; i += 4) {
 #pragma unroll
@@ -426,24 +389,20 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
                     if (i >= c_lo && i < c_hi) mx = fmaxf(mx, __uint_as_float(sv[i]));
             }
             const float m_top = fmaxf(m, mx * scale_log2e);
-            // The reference moves only by large steps, and the rows of a warp are rescaled together (the
-            // tensor-memory accesses are the whole warp's). A row that has seen no key yet has nothing
-            // accumulated under another reference: it takes the maximum as it is.
             const bool fresh = m == -INFINITY;
             const bool moves = !fresh && m_top - m > kRescaleStep;
             if (__any_sync(0xffffffffu, moves)) {
-                // the accumulator must be complete up to the group's previous tile
-                if (!mbar_wait(bars + Bars::o_full + 8 * b, (u - 1) & 1u, abort_flag)) { ok = false; break; }
+                if (!mbar_wait(bars + B::o_full, (u - 1) & 1u, abort_flag)) { ok = false; break; }
                 tc_fence_after();
                 const float f = moves ? ex2(m - m_top) : 1.f;
 #pragma unroll 1
                 for (int c0 = 0; c0 < D; c0 += 32) {
                     uint32_t v[32];
-                    tmem_ld32(tmem_o + lane_addr + b * D + c0, v);
+                    tmem_ld32(tmem_o + lane_addr + c0, v);
                     tmem_ld_wait();
 #pragma unroll
                     for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * f);
-                    tmem_st32(tmem_o + lane_addr + b * D + c0, v);
+                    tmem_st32(tmem_o + lane_addr + c0, v);
                 }
                 tmem_st_wait();
                 tc_fence_before();
@@ -451,10 +410,9 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
             }
             if (fresh || moves) m = m_top;
             const float ms = (m == -INFINITY) ? 0.f : m;
-            // the group's previous P must have been consumed before P is overwritten
-            if (u > 0 && !mbar_wait(bars + Bars::p_free + 8 * b, (u - 1) & 1u, abort_flag)) { ok = false; break; }
+            if (u > 0 && !mbar_wait(bars + B::p_free, (u - 1) & 1u, abort_flag)) { ok = false; break; }
             float sum = 0.f;
-            uint32_t pk[BN / 2];      // the row's weights, two bfloat16 a word
+            uint32_t pk[BN / 2];
 #pragma unroll
             for (int q = 0; q < BN / 8; ++q) {
                 float p[8];
@@ -478,65 +436,41 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
                 pk[4 * q + 3] = qi_attn::pack_bf16(p[6], p[7]);
             }
             l += sum;
-            // the weights go to tensor memory, where the tensor core reads them as the A operand of P . V
-            tmem_st32(tmem_p + lane_addr + b * (BN / 2), pk);
+            tmem_st32(tmem_p + lane_addr, pk);
             tmem_st_wait();
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(bars + Bars::p_ready + 8 * b);
+            if (lane == 0) mbar_arrive(bars + B::p_ready);
         }
-        // the group's accumulator, once its last product has finished
-        float o[D];
-#pragma unroll
-        for (int i = 0; i < D; ++i) o[i] = 0.f;
-        if (ok && u > 0) {
-            ok = mbar_wait(bars + Bars::o_full + 8 * b, (u - 1) & 1u, abort_flag);
-            if (ok) {
-                tc_fence_after();
-#pragma unroll
-                for (int c0 = 0; c0 < D; c0 += 32) {
-                    tmem_ld32(tmem_o + lane_addr + b * D + c0, *reinterpret_cast<uint32_t(*)[32]>(&o[c0]));
-                }
-                tmem_ld_wait();
-            }
-        }
+        // the accumulator, once the last product has finished: normalise and store
+        if (ok && n_tiles > 0) ok = mbar_wait(bars + B::o_full, (uint32_t)(n_tiles - 1) & 1u, abort_flag);
         if (!ok && lane == 0) give_up();
-
-        // merge the two groups: group 1 hands its partial result over through the K/V ring,
-        // which nobody reads any more once both groups have drained their last product
-        asm volatile("bar.sync 1, 256;" ::: "memory");
-        float* mrg = reinterpret_cast<float*>(kv_mem) + (size_t)row * (D + 2);
-        if (b == 1) {
-            mrg[0] = m;
-            mrg[1] = l;
-#pragma unroll
-            for (int i = 0; i < D; ++i) mrg[2 + i] = o[i];
-        }
-        asm volatile("bar.sync 1, 256;" ::: "memory");
-        if (b == 0 && !*abort_flag && row < rows_valid) {
-            const float m1 = mrg[0], l1 = mrg[1];
-            const float M = fmaxf(m, m1);
-            const float f0 = (m == -INFINITY) ? 0.f : exp2f(m - M), f1 = (m1 == -INFINITY) ? 0.f : exp2f(m1 - M);
-            const float L = l * f0 + l1 * f1;
-            const float inv = L > 0.f ? 1.f / L : 0.f;
+        if (ok) {
+            tc_fence_after();
+            const float inv = l > 0.f ? 1.f / l : 0.f;
             qi::bf16* orow = out + ((size_t)(q0 + row) * nq + h) * D;
+#pragma unroll 1
+            for (int c0 = 0; c0 < D; c0 += 32) {
+                uint32_t v[32];
+                tmem_ld32(tmem_o + lane_addr + c0, v);
+                tmem_ld_wait();
+                if (row < rows_valid && n_tiles > 0) {
 #pragma unroll
-            for (int c0 = 0; c0 < D; c0 += 8) {
-                float y[8];
-#pragma unroll
-                for (int i = 0; i < 8; ++i) y[i] = (o[c0 + i] * f0 + mrg[2 + c0 + i] * f1) * inv;
-                uint4 w;
-                w.x = qi_attn::pack_bf16(y[0], y[1]);
-                w.y = qi_attn::pack_bf16(y[2], y[3]);
-                w.z = qi_attn::pack_bf16(y[4], y[5]);
-                w.w = qi_attn::pack_bf16(y[6], y[7]);
-                *reinterpret_cast<uint4*>(orow + c0) = w;
+                    for (int i = 0; i < 32; i += 8) {
+                        uint4 w;
+                        w.x = qi_attn::pack_bf16(__uint_as_float(v[i]) * inv, __uint_as_float(v[i + 1]) * inv);
+                        w.y = qi_attn::pack_bf16(__uint_as_float(v[i + 2]) * inv, __uint_as_float(v[i + 3]) * inv);
+                        w.z = qi_attn::pack_bf16(__uint_as_float(v[i + 4]) * inv, __uint_as_float(v[i + 5]) * inv);
+                        w.w = qi_attn::pack_bf16(__uint_as_float(v[i + 6]) * inv, __uint_as_float(v[i + 7]) * inv);
+                        *reinterpret_cast<uint4*>(orow + c0 + i) = w;
+                    }
+                }
             }
         }
     }
     tc_fence_before();
     __syncthreads();
-    if (warp == 9) tmem_dealloc(tmem_base, 512);
+    if (warp == 5) tmem_dealloc(tmem_base, 256);
 }
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
