@@ -21,15 +21,15 @@
 // last product, the normalised store) with its neighbour's steady state, which at a few
 // thousand keys are as long as the work itself. (An earlier form had one CTA an SM with two
 // softmax groups on alternating key tiles of the same query rows, merged at the end: 322,
-// 626, 685 TFLOP/s at 2,048, 8,192 and 16,384 tokens against 403, 741, 773 now.)
+// 626, 685 TFLOP/s at 2,048, 8,192 and 16,384 tokens against 412, 763, 795 now.)
 //
 // Roles: warps 0-3 are the softmax threads; warp 4 issues the TMA loads of Q and of the K/V
 // tiles (page pieces through the block table, as in attention_tma.cu); warp 5 allocates tensor
 // memory and issues the MMAs: S of tile j + 1 as soon as the softmax threads have taken S of
 // tile j into registers, then P.V of tile j when its weights are ready. K is read as a
 // K-major operand, V as an MN-major operand (its rows are keys, the product contracts over
-// keys), Q as a K-major operand, P from tensor memory. A quarter of the exponentials are
-// computed on the FMA pipe (the special-function unit is the busiest pipe of this kernel).
+// keys), Q as a K-major operand, P from tensor memory. (Computing part of the exponentials by a
+// polynomial on the FMA pipe, to relieve the special-function unit, was measured slower here.)
 //
 // Formulas: as attention_mma.cu (reference: crates/quantinfer-runtime/src/attention.rs:105-135).
 // No load uses cluster multicast. Every mbarrier wait is bounded; on expiry the kernel sets
@@ -138,25 +138,7 @@ __device__ __forceinline__ void tmem_st32(uint32_t addr, const uint32_t (&r)[32]
 }
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 using qi_attn::ex2;
-// 2^x without the special-function unit, which this kernel keeps busier than anything else: the
-// integer nearest to x comes from adding 1.5 * 2^23, the rest f = x - n lies in [-0.5, 0.5] where a
-// polynomial of degree 5 gives 2^f to 1e-7 (relative, the unit's own accuracy), and n goes into
-// the exponent bits. For x in [-126, 126].
-__device__ __forceinline__ float ex2_fma(float x) {
-    x = fmaxf(x, -126.f);
-    const float t = x + 12582912.f;
-    const float f = x - (t - 12582912.f);
-    float p = 0.0013400432653725147f;
-    p = fmaf(p, f, 0.009676037356257439f);
-    p = fmaf(p, f, 0.05550327152013779f);
-    p = fmaf(p, f, 0.2402210682630539f);
-    p = fmaf(p, f, 0.6931471824645996f);
-    p = fmaf(p, f, 1.0000001192092896f);
-    return __int_as_float(__float_as_int(p) + (__float_as_int(t) << 23));
-}
-constexpr int kFmaExpMask = 0x88;   // which of every 8 weights take ex2_fma instead of the unit (bit i: element i)
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
-
 // K-major operand tile (rows of 128 bytes, 128-byte swizzle): see gemm_tcgen05.cu.
 __device__ __forceinline__ uint64_t desc_k_major(uint32_t smem_addr) {
     uint64_t d = 0;
@@ -418,10 +400,7 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
                 float p[8];
                 if (unmasked) {
 #pragma unroll
-                    for (int i = 0; i < 8; ++i) {
-                        const float x = fmaf(__uint_as_float(sv[8 * q + i]), scale_log2e, -ms);
-                        p[i] = ((kFmaExpMask >> i) & 1) ? ex2_fma(x) : ex2(x);
-                    }
+                    for (int i = 0; i < 8; ++i) p[i] = ex2(fmaf(__uint_as_float(sv[8 * q + i]), scale_log2e, -ms));
                 } else {
 #pragma unroll
                     for (int i = 0; i < 8; ++i) {
