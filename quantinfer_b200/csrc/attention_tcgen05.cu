@@ -188,7 +188,8 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
                                       const int* __restrict__ block_table, int max_blocks, int page_size, int box_rows,
                                       int num_pages, const int* __restrict__ q_start, const int* __restrict__ start_pos,
                                       const int* __restrict__ tile_req, const int* __restrict__ tile_q0, int nq, int nkv,
-                                      float scale_log2e, int window, int* __restrict__ status) {
+                                      float scale_log2e, int window, int* __restrict__ status, int n_ranges,
+                                      float* __restrict__ ws_o, float* __restrict__ ws_ml) {
     extern __shared__ uint8_t smem_raw[];
     using B = Bars;
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -211,8 +212,27 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
     const int* table = block_table + (size_t)r * max_blocks;
     const int hi = pos0 + rows_valid;
     const int lo = (window > 0 && pos0 - window + 1 > 0) ? pos0 - window + 1 : 0;
-    const int t_begin = (lo / BN) * BN;
-    const int n_tiles = (hi - t_begin + BN - 1) / BN;
+    // With n_ranges > 1 the key tiles of these query rows are cut into that many ranges, one CTA each
+    // (blockIdx.z); every CTA leaves its rows' reference, sum and accumulator in the workspace and a
+    // second kernel merges them. A long context then gives enough CTAs to fill the GPU's last round.
+    int t_begin = (lo / BN) * BN;
+    int n_tiles = (hi - t_begin + BN - 1) / BN;
+    if (n_ranges > 1) {
+        const int per = (n_tiles + n_ranges - 1) / n_ranges;
+        const int first = (int)blockIdx.z * per;
+        const int count = max(min(n_tiles - first, per), 0);
+        t_begin += first * BN;
+        n_tiles = count;
+        if (count == 0) {    // nothing of the rows' keys falls into this range: an empty partial
+            const int row = threadIdx.x;
+            if (row < rows_valid) {
+                float* ml = ws_ml + (((size_t)(q0 + row) * nq + h) * n_ranges + blockIdx.z) * 2;
+                ml[0] = -INFINITY;
+                ml[1] = 0.f;
+            }
+            return;
+        }
+    }
     const int blk0 = t_begin / page_size;
     const int n_blk = min(min((t_begin + n_tiles * BN + page_size - 1) / page_size, max_blocks) - blk0, kMaxTableEntries);
     for (int i = threadIdx.x; i < n_blk; i += blockDim.x) s_table[i] = table[blk0 + i];
@@ -424,7 +444,25 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
         // the accumulator, once the last product has finished: normalise and store
         if (ok && n_tiles > 0) ok = mbar_wait(bars + B::o_full, (uint32_t)(n_tiles - 1) & 1u, abort_flag);
         if (!ok && lane == 0) give_up();
-        if (ok) {
+        if (ok && n_ranges > 1) {
+            tc_fence_after();
+            const size_t part = ((size_t)(q0 + row) * nq + h) * n_ranges + blockIdx.z;
+            if (row < rows_valid) {
+                ws_ml[part * 2] = m;
+                ws_ml[part * 2 + 1] = l;
+            }
+#pragma unroll 1
+            for (int c0 = 0; c0 < D; c0 += 32) {
+                uint32_t v[32];
+                tmem_ld32(tmem_o + lane_addr + c0, v);
+                tmem_ld_wait();
+                if (row < rows_valid) {
+#pragma unroll
+                    for (int i = 0; i < 32; i += 4)
+                        *reinterpret_cast<uint4*>(ws_o + part * D + c0 + i) = make_uint4(v[i], v[i + 1], v[i + 2], v[i + 3]);
+                }
+            }
+        } else if (ok) {
             tc_fence_after();
             const float inv = l > 0.f ? 1.f / l : 0.f;
             qi::bf16* orow = out + ((size_t)(q0 + row) * nq + h) * D;
@@ -450,6 +488,28 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
     tc_fence_before();
     __syncthreads();
     if (warp == 5) tmem_dealloc(tmem_base, 256);
+}
+
+// out[t, h, :] = sum_s o_s 2^(m_s - M) / sum_s l_s 2^(m_s - M) over the key ranges of a query row, in range order.
+__global__ void attention_prefill_merge_kernel(const float* __restrict__ ws_o, const float* __restrict__ ws_ml,
+                                               qi::bf16* __restrict__ out, int nq, int n_ranges) {
+    qi::pdl_enter();
+    const int h = blockIdx.x;
+    const size_t t = blockIdx.y;
+    const size_t base = (t * nq + h) * n_ranges;
+    float M = -INFINITY;
+    for (int s = 0; s < n_ranges; ++s) M = fmaxf(M, ws_ml[(base + s) * 2]);
+    for (int col = threadIdx.x; col < D; col += blockDim.x) {
+        float L = 0.f, O = 0.f;
+        for (int s = 0; s < n_ranges; ++s) {
+            const float ms = ws_ml[(base + s) * 2];
+            if (ms == -INFINITY) continue;          // an empty range's slot holds no data
+            const float f = exp2f(ms - M);
+            L += ws_ml[(base + s) * 2 + 1] * f;
+            O += ws_o[(base + s) * D + col] * f;
+        }
+        out[(t * nq + h) * D + col] = __float2bfloat16_rn(L > 0.f ? O / L : 0.f);
+    }
 }
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -492,12 +552,15 @@ extern "C" int qi_attention_prefill_tcgen05_supported(int nq, int nkv, int d, in
            max_blocks <= kMaxTableEntries;
 }
 
-// Same arguments as qi_attention_prefill_tma; the tile lists are cut to 128 query rows.
+// Arguments as qi_attention_prefill_tma (the tile lists are cut to 128 query rows), and: n_ranges > 1
+// cuts every query tile's keys into that many ranges over separate CTAs, merged by a second kernel;
+// `workspace` must then hold n_tokens * nq * n_ranges * (128 + 2) floats.
 extern "C" int qi_attention_prefill_tcgen05(const void* q, void* out, const void* k_pages, const void* v_pages,
                                             const int* block_table, int max_blocks, int page_size, int num_pages,
                                             const int* q_start, const int* start_pos, const int* tile_req,
                                             const int* tile_q0, int n_tiles, int n_tokens, int nq, int nkv, int d,
-                                            float scale, int window, int* status, cudaStream_t stream) {
+                                            float scale, int window, int n_ranges, float* workspace, int* status,
+                                            cudaStream_t stream) {
     QI_REQUIRE(qi_attention_prefill_tcgen05_supported(nq, nkv, d, page_size, max_blocks),
                "attention_prefill_tcgen05: heads %d/%d of size %d with %d pages of %d per request are not covered", nq, nkv,
                d, max_blocks, page_size);
@@ -506,6 +569,8 @@ extern "C" int qi_attention_prefill_tcgen05(const void* q, void* out, const void
                "attention_prefill_tcgen05: tensors must be 16-byte aligned");
     QI_REQUIRE((long long)num_pages * nkv * page_size < 2147483647LL, "attention_prefill_tcgen05: the page pool has too many rows");
     QI_REQUIRE(n_tiles >= 0 && n_tiles <= 65535, "attention_prefill_tcgen05: more than 65535 query tiles in one step");
+    QI_REQUIRE(n_ranges >= 1 && n_ranges <= 64 && (n_ranges == 1 || workspace), "attention_prefill_tcgen05: key ranges need a workspace (1 to 64 ranges)");
+    QI_REQUIRE(n_ranges == 1 || n_tokens <= 65535, "attention_prefill_tcgen05: key ranges take at most 65535 tokens a step");
     if (n_tiles == 0) return 0;
     static bool configured = false;
     if (!configured) {
@@ -518,8 +583,16 @@ extern "C" int qi_attention_prefill_tcgen05(const void* q, void* out, const void
     if (make_map(&mq, q, n_tokens, nq * D, BM)) return 1;
     if (make_map(&mk, k_pages, (long long)num_pages * nkv * page_size, D, box_rows)) return 1;
     if (make_map(&mv, v_pages, (long long)num_pages * nkv * page_size, D, box_rows)) return 1;
-    qi::launch(attention_prefill_tcgen05_kernel, dim3(nq, n_tiles), dim3(kThreads), kSmemBytes, stream, mq, mk, mv,
+    float* ws_o = workspace;
+    float* ws_ml = workspace ? workspace + (size_t)n_tokens * nq * n_ranges * D : nullptr;
+    qi::launch(attention_prefill_tcgen05_kernel, dim3(nq, n_tiles, n_ranges), dim3(kThreads), kSmemBytes, stream, mq, mk, mv,
                (qi::bf16*)out, block_table, max_blocks, page_size, box_rows, num_pages, q_start, start_pos, tile_req,
-               tile_q0, nq, nkv, scale * 1.4426950408889634f, window, status);
+               tile_q0, nq, nkv, scale * 1.4426950408889634f, window, status, n_ranges, ws_o, ws_ml);
+    if (n_ranges > 1) {
+        if (int rc = qi::check_launch("attention_prefill_tcgen05")) return rc;
+        qi::launch(attention_prefill_merge_kernel, dim3(nq, n_tokens), dim3(128), 0, stream, (const float*)ws_o,
+                   (const float*)ws_ml, (qi::bf16*)out, nq, n_ranges);
+        return qi::check_launch("attention_prefill_merge");
+    }
     return qi::check_launch("attention_prefill_tcgen05");
 }

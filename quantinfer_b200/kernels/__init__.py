@@ -308,9 +308,30 @@ def attention_prefill_tcgen05_supported(nq: int, nkv: int, d: int, page_size: in
     return bool(library().qi_attention_prefill_tcgen05_supported(nq, nkv, d, page_size, max_blocks))
 
 
+def attention_prefill_ranges(n_ctas: int, max_kv_len: int) -> int:
+    """Into how many key ranges the tcgen05 prefill attention cuts every query tile, given the CTAs
+    it would launch uncut (heads x query tiles) and the longest context of the step. 296 CTAs are
+    resident at once; a step of 2,048 tokens and 32 heads has 512, so its second round is 73% full,
+    and four ranges make 2,048 CTAs in seven rounds. Cutting costs the partial results' trip through
+    memory and a merge kernel, so it pays only for long contexts. Estimated times, fitted to
+    measurements at the 8B sizes (microseconds): rounds x keys of a CTA x 0.0247, plus
+    0.00034 for every (query row, head, range) when cut."""
+    best, best_time = 1, None
+    for ranges in (1, 2, 3, 4, 6, 8):
+        if ranges > 1 and max_kv_len < 2048 * ranges:
+            break
+        rounds = -(-n_ctas * ranges // 296)
+        time = rounds * (max_kv_len / ranges) * 0.0247
+        if ranges > 1:
+            time += n_ctas * 128 * ranges * 0.00034
+        if best_time is None or time < best_time * 0.97:
+            best, best_time = ranges, time
+    return best
+
+
 def attention_prefill(q, out, k_pages, v_pages, block_table, q_start, start_pos, tile_req, tile_q0,
                       nq, nkv, d, scale: float, window: int, status, use_tma: bool | None = None,
-                      impl: str | None = None) -> None:
+                      impl: str | None = None, max_kv_len: int = 0, key_ranges: int | None = None) -> None:
     """Causal paged GQA flash attention (bfloat16, head size 64 or 128) for spans of any
     length. `tile_req[i]`, `tile_q0[i]`: request index and first flat token of the i-th
     block of up to QUERY_TILE query rows.
@@ -319,7 +340,8 @@ def attention_prefill(q, out, k_pages, v_pages, block_table, q_start, start_pos,
     accumulators in tensor memory, TMA loads), "tma" (mma.sync with TMA loads, same page
     sizes, head size 64 or 128) and "cpasync" (mma.sync, any page size). `impl` forces one;
     the default is the first that takes the geometry. `use_tma` is the older switch between
-    the last two."""
+    the last two. `max_kv_len` (the longest context of the step) lets the tcgen05 kernel cut long
+    contexts into key ranges over more CTAs (`key_ranges` forces a number)."""
     if impl is None and use_tma is not None:
         impl = "tma" if use_tma else "cpasync"
     _req(q, "q", torch.bfloat16, 2)
@@ -343,10 +365,15 @@ def attention_prefill(q, out, k_pages, v_pages, block_table, q_start, start_pos,
         else:
             impl = "cpasync"
     if impl == "tcgen05":
+        ranges = key_ranges or attention_prefill_ranges(nq * tile_req.numel(), max_kv_len)
+        if q.shape[0] > 65535:
+            ranges = 1
+        ws = torch.empty(q.shape[0] * nq * ranges * (d + 2), dtype=torch.float32, device=q.device) if ranges > 1 else None
         rc = library().qi_attention_prefill_tcgen05(
             _ptr(q), _ptr(out), _ptr(k_pages), _ptr(v_pages), _ptr(block_table), block_table.shape[1],
             k_pages.shape[2], k_pages.shape[0], _ptr(q_start), _ptr(start_pos), _ptr(tile_req), _ptr(tile_q0),
-            tile_req.numel(), q.shape[0], nq, nkv, d, C.c_float(scale), int(window or 0), _ptr(status), _stream())
+            tile_req.numel(), q.shape[0], nq, nkv, d, C.c_float(scale), int(window or 0), ranges, _ptr(ws),
+            _ptr(status), _stream())
         _check(rc, "attention_prefill_tcgen05")
         return
     if impl not in ("tma", "cpasync"):

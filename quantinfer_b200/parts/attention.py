@@ -124,7 +124,8 @@ class Attention(Part):
             else:
                 kernels.attention_prefill(q, out, cache.k_pages, cache.v_pages, table, batch.q_start,
                                           batch.start_pos, batch.tile_req, batch.tile_q0, self.nq, self.nkv,
-                                          self.d, self.scale, self.spec.window or 0, rt.status)
+                                          self.d, self.scale, self.spec.window or 0, rt.status,
+                                          max_kv_len=batch.max_kv_len)
             return
         kernels.attention_generic(q, out, cache.k_pages, cache.v_pages, table, batch.positions,
                                   batch.token_req, self.nq, self.nkv, self.d, self.scale,

@@ -267,7 +267,7 @@ def test_qk_norm_rope_kv(dtype, nq, nkv, d, rot, ps):
 
 # ------------------------------------------------------------------ attention
 
-def _attention_case(nq, nkv, d, ctx, new, ps, window, dtype, mode, decode_chunk=0):
+def _attention_case(nq, nkv, d, ctx, new, ps, window, dtype, mode, decode_chunk=0, key_ranges=None):
     """ctx[r] cached positions and new[r] query tokens per request. One query per request
     has a far key that dominates its softmax, so a missed or misplaced key changes the result."""
     torch.manual_seed(7)
@@ -309,7 +309,7 @@ def _attention_case(nq, nkv, d, ctx, new, ps, window, dtype, mode, decode_chunk=
         tiles = [(r, q_start[r] + t0) for r in range(R) for t0 in range(0, new[r], k.QUERY_TILE)]
         impl = {"prefill": "cpasync", "prefill_tma": "tma", "prefill_tcgen05": "tcgen05"}[mode]
         k.attention_prefill(qd, out, kp, vp, table, I(q_start), I(ctx), I([t[0] for t in tiles]),
-                            I([t[1] for t in tiles]), nq, nkv, d, scale, window, st, impl=impl)
+                            I([t[1] for t in tiles]), nq, nkv, d, scale, window, st, impl=impl, key_ranges=key_ranges)
     assert st.item() == 0
     return float((out.double().cpu() - ref).abs().max())
 
@@ -344,6 +344,19 @@ def test_attention_prefill_tcgen05(nq, nkv, ctx, new, ps, window):
     pieces smaller and larger than a tile, a window, an odd number of key tiles (the two softmax groups
     then hold different numbers of tiles)."""
     assert _attention_case(nq, nkv, 128, ctx, new, ps, window, torch.bfloat16, "prefill_tcgen05") < 1.2e-2
+
+
+@pytest.mark.parametrize("ranges, ctx, new, ps, window", [
+    (2, [0], [300], 64, 0), (3, [1000, 0], [130, 257], 64, 0), (4, [40], [64], 16, 0),   # the last: more ranges than key tiles
+    (8, [2100], [200], 128, 0), (3, [700], [129], 32, 500), (2, [0, 37, 200], [130, 64, 1], 8, 0),
+])
+def test_attention_prefill_tcgen05_key_ranges(ranges, ctx, new, ps, window):
+    """The keys of every query tile cut into ranges over separate CTAs and merged by a second kernel:
+    ranges that are empty for short rows, a window that leaves the first ranges without keys."""
+    assert _attention_case(8, 2, 128, ctx, new, ps, window, torch.bfloat16, "prefill_tcgen05", key_ranges=ranges) < 1.2e-2
+    k = _k()
+    assert k.attention_prefill_ranges(512, 2048) == 1 and k.attention_prefill_ranges(512, 8192) == 1 and k.attention_prefill_ranges(512, 30000) == 4
+    assert k.attention_prefill_ranges(296, 30000) == 1
 
 
 def test_attention_prefill_without_tma_takes_any_page_size():
