@@ -665,8 +665,8 @@ __device__ __forceinline__ void mbar_arrive_leader(uint32_t bar) {
 template <typename TOut, int EPI>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads)
 gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-                         TOut* __restrict__ out, int rows_a, int rows_b, int K, long long ld_out, int* __restrict__ status,
-                         const RopeEpilogue rope) {
+                         TOut* __restrict__ out, int rows_a, int rows_b, int K, long long ld_out, int kb_per_split,
+                         int n_splits, long long split_stride, int* __restrict__ status, const RopeEpilogue rope) {
     extern __shared__ uint8_t smem_raw[];
     constexpr int STAGES = kPairStages;
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -685,8 +685,12 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
     const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
     constexpr int TM = 2 * BM, TN = 256;
     const int tiles_m = (rows_a + TM - 1) / TM, tiles_n = (rows_b + TN - 1) / TN;
-    const int total_tiles = tiles_m * tiles_n;
-    const int n_kb = (K + BK - 1) / BK;
+    const int total_tiles = tiles_m * tiles_n * n_splits;     // K splits slowest: split s writes out + s * split_stride
+    const int kb_total = (K + BK - 1) / BK;
+    auto kb_range = [&](int tile, int& kb_begin) {
+        kb_begin = (tile / (tiles_m * tiles_n)) * kb_per_split;
+        return max(min(kb_total, kb_begin + kb_per_split) - kb_begin, 0);
+    };
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
@@ -722,11 +726,13 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
             // the first stages' weight rows are requested before the wait for the kernel before this one
             uint32_t early = 0;
             if (pair < total_tiles) {
-                const int tile_n = pair / tiles_m;
+                const int tile_n = (pair / tiles_m) % tiles_n;
+                int kb_begin;
+                const int n_kb = kb_range(pair, kb_begin);
                 early = (uint32_t)min(n_kb, STAGES);
                 for (uint32_t i = 0; i < early; ++i) {
                     if (rank == 0) mbar_expect_tx(full_bar(i), 2 * kPairStageBytes);
-                    tma_load_2d_pair(base + i * kPairStageBytes + kPairHalfBytes, &map_b, full_bar(i), (int)i * BK,
+                    tma_load_2d_pair(base + i * kPairStageBytes + kPairHalfBytes, &map_b, full_bar(i), (kb_begin + (int)i) * BK,
                                      tile_n * TN + (int)rank * BM);
                 }
             }
@@ -734,12 +740,15 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
             uint32_t it = 0;
             bool ok = true;
             for (int tile = pair; tile < total_tiles && ok; tile += n_pairs) {
-                const int tile_m = tile % tiles_m, tile_n = tile / tiles_m;
+                const int tile_m = tile % tiles_m, tile_n = (tile / tiles_m) % tiles_n;
+                int kb_begin;
+                const int n_kb = kb_range(tile, kb_begin);
                 for (int i = 0; i < n_kb; ++i, ++it) {
                     const int s = it % STAGES;
                     const uint32_t dst = base + s * kPairStageBytes;
+                    const int k0 = (kb_begin + i) * BK;
                     if (it < early) {
-                        tma_load_2d_pair(dst, &map_a, full_bar(s), i * BK, tile_m * TM + (int)rank * BM);
+                        tma_load_2d_pair(dst, &map_a, full_bar(s), k0, tile_m * TM + (int)rank * BM);
                         continue;
                     }
                     if (!mbar_wait(empty_bar(s), ((it / STAGES) & 1u) ^ 1u, abort_flag, status)) {
@@ -748,8 +757,8 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
                         break;
                     }
                     if (rank == 0) mbar_expect_tx(full_bar(s), 2 * kPairStageBytes);
-                    tma_load_2d_pair(dst, &map_a, full_bar(s), i * BK, tile_m * TM + (int)rank * BM);
-                    tma_load_2d_pair(dst + kPairHalfBytes, &map_b, full_bar(s), i * BK, tile_n * TN + (int)rank * BM);
+                    tma_load_2d_pair(dst, &map_a, full_bar(s), k0, tile_m * TM + (int)rank * BM);
+                    tma_load_2d_pair(dst + kPairHalfBytes, &map_b, full_bar(s), k0, tile_n * TN + (int)rank * BM);
                 }
             }
         }
@@ -763,6 +772,8 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
             bool ok = true;
             for (int tile = pair; tile < total_tiles && ok; tile += n_pairs, ++j) {
                 const int acc = j & 1;
+                int kb_begin;
+                const int n_kb = kb_range(tile, kb_begin);
                 if (!mbar_wait(acc_empty_bar(acc), (((uint32_t)j >> 1) & 1u) ^ 1u, abort_flag, status)) {
                     give_up();
                     break;
@@ -794,7 +805,8 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
         qi::pdl_wait();
         int j = 0;
         for (int tile = pair; tile < total_tiles; tile += n_pairs, ++j) {
-            const int tile_m = tile % tiles_m, tile_n = tile / tiles_m;
+            const int tile_m = tile % tiles_m, tile_n = (tile / tiles_m) % tiles_n;
+            TOut* obase = out + (size_t)(tile / (tiles_m * tiles_n)) * split_stride;
             const int acc = j & 1;
             if (!mbar_wait(acc_full_bar(acc), ((uint32_t)j >> 1) & 1u, abort_flag, status)) {
                 if (lane == 0) give_up();
@@ -825,7 +837,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
                 const bool full = b0 + 32 <= rows_b;
                 if (EPI == 1) {
                     // columns come in pairs (gate, up): half as many outputs
-                    TOut* orow = out + (size_t)row * ld_out + (b0 >> 1);
+                    TOut* orow = obase + (size_t)row * ld_out + (b0 >> 1);
                     if (full && ((reinterpret_cast<uintptr_t>(orow) & 15u) == 0) && sizeof(TOut) == 2) {
 #pragma unroll
                         for (int q0 = 0; q0 < 32; q0 += 16) {
@@ -847,7 +859,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
                                 store1<TOut>(orow + (q >> 1), silu_mul(__uint_as_float(r[q]), __uint_as_float(r[q + 1])));
                     }
                 } else {
-                    TOut* orow = out + (size_t)row * ld_out + b0;
+                    TOut* orow = obase + (size_t)row * ld_out + b0;
                     if (full && ((reinterpret_cast<uintptr_t>(orow) & 15u) == 0) && sizeof(TOut) == 2) {
 #pragma unroll
                         for (int q = 0; q < 32; q += 8) {
@@ -952,7 +964,7 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, TOut* out, int rows_a, 
 
 template <typename TOut, int EPI>
 int launch_pair(const CUtensorMap& ma, const CUtensorMap& mb, TOut* out, int M, int N, int K, long long ld, int* status,
-                cudaStream_t stream, const RopeEpilogue& rope = RopeEpilogue{}) {
+                cudaStream_t stream, const RopeEpilogue& rope = RopeEpilogue{}, int splits = 1, long long split_stride = 0) {
     auto kern = gemm_tcgen05_pair_kernel<TOut, EPI>;
     static bool configured = false;
     if (!configured) {
@@ -960,10 +972,12 @@ int launch_pair(const CUtensorMap& ma, const CUtensorMap& mb, TOut* out, int M, 
         if (e != cudaSuccess) return qi::fail("gemm_bf16: cannot reserve %d bytes of shared memory: %s", kPairSmem, cudaGetErrorString(e));
         configured = true;
     }
-    const long long tiles = (long long)((M + 2 * BM - 1) / (2 * BM)) * ((N + 255) / 256);
+    const long long tiles = (long long)((M + 2 * BM - 1) / (2 * BM)) * ((N + 255) / 256) * splits;
     const long long pairs = sm_count() / 2;
     const unsigned grid = 2u * (unsigned)(tiles < pairs ? tiles : pairs);
-    qi::launch(kern, dim3(grid), dim3(kThreads), kPairSmem, stream, ma, mb, out, M, N, K, ld, status, rope);
+    const int kb_total = (K + BK - 1) / BK;
+    qi::launch(kern, dim3(grid), dim3(kThreads), kPairSmem, stream, ma, mb, out, M, N, K, ld, (kb_total + splits - 1) / splits,
+               splits, split_stride, status, rope);
     return qi::check_launch("gemm_bf16 (CTA pairs)");
 }
 
@@ -1038,14 +1052,22 @@ extern "C" int qi_gemm_bf16_plan(int M, int N, int K, int allow_split, int* swap
                 }
             }
         }
-        // pairs of CTAs on tiles of 256 x 256 (no K split): a k block of a pair's tile takes what a k block
+        // pairs of CTAs on tiles of 256 x 256: a k block of a pair's tile takes what a k block
         // of a 128 x 256 tile takes on one SM, less the 13% the lighter load on L2 and shared memory gives
         const long long pair_tiles = (long long)((M + 2 * BM - 1) / (2 * BM)) * ((N + 255) / 256);
-        const long long pair_waves = (pair_tiles + sms / 2 - 1) / (sms / 2);
-        if ((double)pair_waves * (kb_total + 12) * 0.87 < best * 0.999) {
-            sw = 2;
-            b = 256;
-            sp = 1;
+        for (int si = 0; si < (allow_split ? 8 : 1); ++si) {
+            const int s = split_choices[si];
+            const int kbs = (kb_total + s - 1) / s;
+            if (s > 1 && ((s - 1) * kbs >= kb_total || kbs < 8)) continue;
+            const long long waves = (pair_tiles * s + sms / 2 - 1) / (sms / 2);
+            double cost = (double)waves * (kbs + 12) * 0.87;
+            if (s > 1) cost += (double)s * M * N * 8.0 / 5.5e12 / 0.27e-6;
+            if (cost < best * 0.999) {
+                best = cost;
+                sw = 2;
+                b = 256;
+                sp = s;
+            }
         }
     }
     *swap = sw; *bn = b; *splits = sp;
@@ -1071,10 +1093,21 @@ extern "C" int qi_gemm_bf16(const void* x, const void* w, void* out, int out_dty
     QI_REQUIRE((splits - 1) * kb_per_split < kb_total, "gemm_bf16: %d splits leave one without work (K=%d)", splits, K);
     if (swap == 2) {
         // pairs of CTAs: tokens on the rows, no K split
-        QI_REQUIRE(splits == 1, "gemm_bf16: the CTA-pair kernel does not split K");
         CUtensorMap pa, pb;
         if (make_map(&pa, x, M, K, BM)) return 1;
         if (make_map(&pb, w, N, K, BM)) return 1;
+        if (splits > 1) {
+            float* ws = (float*)workspace;
+            if (int rc = launch_pair<float, 0>(pa, pb, ws, M, N, K, N, status, stream, RopeEpilogue{}, splits, (long long)M * N)) return rc;
+            if (out) {
+                const size_t n = (size_t)M * N;
+                unsigned blocks = (unsigned)((n + 255) / 256 < 148 * 8 ? (n + 255) / 256 : 148 * 8);
+                if (out_dtype == qi::kF32) qi::launch(splitk_reduce_kernel<float>, dim3(blocks), dim3(256), 0, stream, (const float*)ws, (float*)out, n, splits);
+                else qi::launch(splitk_reduce_kernel<qi::bf16>, dim3(blocks), dim3(256), 0, stream, (const float*)ws, (qi::bf16*)out, n, splits);
+                return qi::check_launch("splitk_reduce");
+            }
+            return 0;
+        }
         if (epilogue == 1) return launch_pair<qi::bf16, 1>(pa, pb, (qi::bf16*)out, M, N, K, N / 2, status, stream);
         if (out_dtype == qi::kF32) return launch_pair<float, 0>(pa, pb, (float*)out, M, N, K, N, status, stream);
         return launch_pair<qi::bf16, 0>(pa, pb, (qi::bf16*)out, M, N, K, N, status, stream);

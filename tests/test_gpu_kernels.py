@@ -107,6 +107,7 @@ def test_gemm_simt(tx, tw, ty, M, N, K):
     (64, 1000, 2048, None), (200, 300, 4096, None), (700, 328, 168, (False, 256, 1)), (17, 264, 1032, (True, 32, 4)),
     # pairs of CTAs on tiles of 256 x 256: one tile, ragged edges in both directions, many k blocks, more tiles than pairs
     (256, 256, 64, (2, 256, 1)), (300, 400, 136, (2, 256, 1)), (129, 130, 1032, (2, 256, 1)), (2560, 2304, 320, (2, 256, 1)),
+    (512, 300, 2048, (2, 256, 3)), (700, 1100, 1600, (2, 256, 2)),      # the same with K split: partial sums, then added
 ])
 @pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
 def test_gemm_tcgen05(M, N, K, plan, out_dtype):
@@ -134,6 +135,8 @@ def test_gemm_tcgen05_silu_epilogue_and_partials(M, N, K):
     assert float((act.double().cpu() - ref).abs().max()) < max(0.05, float(ref.abs().max()) * 2 ** -7)
     parts = _k().gemm_bf16(x.to(DEV), w.to(DEV), None, plan=(True if M <= 256 else False, 16 if M <= 16 else 256 if M > 64 else 64, 2),
                            keep_partials=True)
+    assert parts.shape == (2, M, N) and float((parts.double().sum(0).cpu() - y).abs().max()) < 2e-4
+    parts = _k().gemm_bf16(x.to(DEV), w.to(DEV), None, plan=(2, 256, 2), keep_partials=True)     # on pairs of CTAs
     assert parts.shape == (2, M, N) and float((parts.double().sum(0).cpu() - y).abs().max()) < 2e-4
     # the same activation from the kernel that runs on pairs of CTAs
     act2 = torch.empty_like(act)
