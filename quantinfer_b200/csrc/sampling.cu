@@ -17,6 +17,7 @@
 // sum of weights in 64-bit, warp by warp in index order.
 #include "common.cuh"
 
+#include <cooperative_groups.h>
 #include <math.h>
 
 namespace {
@@ -305,6 +306,354 @@ sample_kernel(const float* __restrict__ logits, int vocab, const float* __restri
     if (tid == 0) out_token[row] = result >= 0 ? result : max_i;
 }
 
+// ------------------------------------------------------------------ a row on a cluster of eight CTAs
+//
+// The kernel above passes over the whole row in global memory for every step of its two
+// threshold searches, on one SM: 1 to 2 ms for a vocabulary of 150,000. Here a row belongs to
+// a thread-block cluster of eight CTAs. Each keeps its eighth of the scaled logits y and of
+// the weights w = exp(y - max y) in shared memory, so a pass costs a few dozen
+// shared-memory reads a thread; sums and counts are added within the block and then over
+// the cluster through distributed shared memory, in rank order (the results are the same
+// numbers in every CTA). The rule is the one above, step for step: the top-k threshold is
+// the k-th largest key (found by four rounds of 256-bin counting instead of 32 bisection
+// passes: counts are integers, so the result is the same), the top-p threshold is found
+// by the same bisection over 64-bit sums, and the draw walks the kept candidates in index
+// order, CTA by CTA and warp by warp.
+
+namespace cg = cooperative_groups;
+constexpr int kClusterSize = 8;
+constexpr int kMaxSlice = 24576;      // elements of y (and of w) a CTA can keep: 2 x 96 KB
+
+struct ClusterScratch {
+    double d[2][2];            // [turn][which]: this CTA's block totals of a cluster sum
+    long long ll[2][2];
+    float best_v[2];
+    int best_i[2];
+    int hist[2][256];
+    int total_hist[256];
+    int pick[2];               // chosen bin, count above it
+};
+
+// Sum over the block (fixed order), then over the cluster's CTAs in rank order. Two values at a time; `turn`
+// alternates between calls so that one cluster barrier a call suffices (a slot is written again only
+// after every CTA has passed the barrier of the call in between).
+__device__ void cluster_sum_d2(cg::cluster_group& cluster, ClusterScratch* cs, int& turn, double a, double b, double* scratch,
+                               double& out_a, double& out_b) {
+    const double ta = block_sum_d(a, scratch), tb = block_sum_d(b, scratch);
+    if (threadIdx.x == 0) {
+        cs->d[turn][0] = ta;
+        cs->d[turn][1] = tb;
+    }
+    cluster.sync();
+    out_a = 0.0;
+    out_b = 0.0;
+    for (unsigned r = 0; r < kClusterSize; ++r) {
+        const ClusterScratch* o = cluster.map_shared_rank(cs, r);
+        out_a += o->d[turn][0];
+        out_b += o->d[turn][1];
+    }
+    turn ^= 1;
+}
+__device__ void cluster_sum_ll2(cg::cluster_group& cluster, ClusterScratch* cs, int& turn, long long a, long long b,
+                                long long* scratch, long long& out_a, long long& out_b) {
+    const long long ta = block_sum_ll(a, scratch), tb = block_sum_ll(b, scratch);
+    if (threadIdx.x == 0) {
+        cs->ll[turn][0] = ta;
+        cs->ll[turn][1] = tb;
+    }
+    cluster.sync();
+    out_a = 0;
+    out_b = 0;
+    for (unsigned r = 0; r < kClusterSize; ++r) {
+        const ClusterScratch* o = cluster.map_shared_rank(cs, r);
+        out_a += o->ll[turn][0];
+        out_b += o->ll[turn][1];
+    }
+    turn ^= 1;
+}
+
+__global__ void __cluster_dims__(kClusterSize, 1, 1) __launch_bounds__(kThreads, 1)
+sample_cluster_kernel(const float* __restrict__ logits, int vocab, int per, const float* __restrict__ temperature,
+                      const int* __restrict__ top_k, const float* __restrict__ top_p,
+                      const long long* __restrict__ seed, const int* __restrict__ counter,
+                      int* __restrict__ out_token, int* __restrict__ status) {
+    extern __shared__ float cache[];          // y[per], then w[per]
+    __shared__ ClusterScratch cs;
+    __shared__ double sd[kNumWarps];
+    __shared__ long long sl[kNumWarps];
+    __shared__ float sbest_v[kNumWarps];
+    __shared__ int sbest_i[kNumWarps];
+    __shared__ double warp_mass[kNumWarps];
+    __shared__ long long warp_eq[kNumWarps];
+
+    qi::pdl_enter();
+    cg::cluster_group cluster = cg::this_cluster();
+    const unsigned rank = cluster.block_rank();
+    const int row = blockIdx.x / kClusterSize;
+    const float* x = logits + (size_t)row * vocab;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int begin = min(vocab, (int)rank * per), end = min(vocab, begin + per), n = end - begin;
+    float* ys = cache;
+    float* ws = cache + per;
+    int turn = 0;
+
+    const float temp = temperature ? temperature[row] : 0.f;
+    const bool greedy = !(temp > 0.f);
+
+    // Pass 0: this CTA's first maximum, the finiteness check, and y into shared memory.
+    float bv = -INFINITY;
+    int bi = 0x7fffffff;
+    bool nonfinite = false;
+    for (int j = tid; j < n; j += kThreads) {
+        const float v = x[begin + j];
+        if (!isfinite(v)) nonfinite = true;
+        if (v > bv || bi == 0x7fffffff) { bv = v; bi = begin + j; }
+        ys[j] = greedy ? v : v / temp;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+    }
+    if (lane == 0) { sbest_v[warp] = bv; sbest_i[warp] = bi; }
+    if (nonfinite && status) atomicOr(status, qi::kStatusNonFinite);
+    __syncthreads();
+    if (tid == 0) {
+        float mv = sbest_v[0];
+        int mi = sbest_i[0];
+        for (int w = 1; w < kNumWarps; ++w)
+            if (sbest_v[w] > mv || (sbest_v[w] == mv && sbest_i[w] < mi)) { mv = sbest_v[w]; mi = sbest_i[w]; }
+        cs.best_v[0] = mv;
+        cs.best_i[0] = mi;
+    }
+    cluster.sync();
+    float max_v = -INFINITY;
+    int max_i = 0x7fffffff;
+    for (unsigned r = 0; r < kClusterSize; ++r) {
+        const ClusterScratch* o = cluster.map_shared_rank(&cs, r);
+        const float v = o->best_v[0];
+        const int i = o->best_i[0];
+        if (i != 0x7fffffff && (max_i == 0x7fffffff || v > max_v || (v == max_v && i < max_i))) { max_v = v; max_i = i; }
+    }
+    if (greedy) {
+        if (rank == 0 && tid == 0) out_token[row] = max_i;
+        cluster.sync();       // nobody leaves while a partner may still read its shared memory
+        return;
+    }
+
+    const float max_y = max_v / temp;
+    for (int j = tid; j < n; j += kThreads) ws[j] = expf(ys[j] - max_y);
+    __syncthreads();
+
+    int k = top_k ? top_k[row] : 0;
+    if (k <= 0 || k > vocab) k = 0;
+    float p_keep = top_p ? top_p[row] : 0.f;
+    if (!(p_keep > 0.f) || p_keep >= 1.f) p_keep = 0.f;
+
+    uint32_t thr_key = 0;
+    long long n_eq = (long long)vocab + 1;
+
+    if (k > 0) {
+        // the k-th largest key, eight bits a round: counts of the keys that share the bits found so far
+        uint32_t prefix = 0;
+        long long above = 0;          // keys greater than every key with this prefix
+        int hturn = 0;
+        for (int shift = 24; shift >= 0; shift -= 8) {
+            for (int b = tid; b < 256; b += kThreads) cs.hist[hturn][b] = 0;
+            __syncthreads();
+            for (int j = tid; j < n; j += kThreads) {
+                const uint32_t key = order_key(ys[j]);
+                if (shift == 24 || (key >> (shift + 8)) == (prefix >> (shift + 8))) atomicAdd(&cs.hist[hturn][(key >> shift) & 255u], 1);
+            }
+            __syncthreads();
+            cluster.sync();
+            if (tid < 256) {
+                int t = 0;
+                for (unsigned r = 0; r < kClusterSize; ++r) t += cluster.map_shared_rank(&cs, r)->hist[hturn][tid];
+                cs.total_hist[tid] = t;
+            }
+            __syncthreads();
+            if (tid == 0) {
+                long long cum = above;
+                int b = 255;
+                for (; b > 0; --b) {
+                    if (cum + cs.total_hist[b] >= k) break;
+                    cum += cs.total_hist[b];
+                }
+                cs.pick[0] = b;
+                cs.pick[1] = (int)(cum - above);
+            }
+            __syncthreads();
+            prefix |= (uint32_t)cs.pick[0] << shift;
+            above += cs.pick[1];
+            hturn ^= 1;
+            __syncthreads();
+        }
+        thr_key = prefix;
+        n_eq = k - above;
+    }
+
+    // Mass of the kept set after top-k.
+    double total, unused_d;
+    {
+        double s = 0.0;
+        for (int j = tid; j < n; j += kThreads)
+            if (order_key(ys[j]) > thr_key) s += (double)ws[j];
+        cluster_sum_d2(cluster, &cs, turn, s, 0.0, sd, total, unused_d);
+        if (thr_key != 0) total += (double)n_eq * (double)expf(key_value(thr_key) - max_y);
+    }
+
+    if (p_keep > 0.f) {
+        const double need = (double)p_keep * total;
+        const uint32_t max_key = order_key(max_y);
+        uint32_t t = 0;
+        for (int bit = 31; bit >= 0; --bit) {
+            const uint32_t cand = t | (1u << bit);
+            double mass;
+            if (cand <= thr_key) {
+                mass = total;
+            } else if (cand > max_key) {
+                mass = 0.0;              // no key reaches the candidate
+            } else {
+                double s = 0.0;
+                for (int j = tid; j < n; j += kThreads)
+                    if (order_key(ys[j]) >= cand) s += (double)ws[j];
+                cluster_sum_d2(cluster, &cs, turn, s, 0.0, sd, mass, unused_d);
+            }
+            if (mass >= need) t = cand;
+        }
+        double sgt = 0.0;
+        long long ceq = 0, unused_ll;
+        for (int j = tid; j < n; j += kThreads) {
+            const uint32_t key = order_key(ys[j]);
+            if (key > t) sgt += (double)ws[j];
+            ceq += key == t;
+        }
+        cluster_sum_d2(cluster, &cs, turn, sgt, 0.0, sd, sgt, unused_d);
+        cluster_sum_ll2(cluster, &cs, turn, ceq, 0, sl, ceq, unused_ll);
+        const long long avail = (t == thr_key) ? n_eq : ceq;
+        const double wt = (double)expf(key_value(t) - max_y);
+        long long want = 1;
+        if (wt > 0.0) {
+            const double rest = need - sgt;
+            want = (long long)ceil(rest / wt);
+            if (want < 1) want = 1;
+        }
+        if (want > avail) want = avail;
+        thr_key = t;
+        n_eq = want;
+        total = sgt + (double)want * wt;
+    }
+
+    // Draw.
+    const unsigned long long sd64 = seed ? (unsigned long long)seed[row] : 0ull;
+    const uint32_t ctr = counter ? (uint32_t)counter[row] : 0u;
+    const uint4 rnd = philox4x32_10(make_uint4(ctr, 0u, 0u, 0u), make_uint2((uint32_t)sd64, (uint32_t)(sd64 >> 32)));
+    const double target = (double)((float)(rnd.x >> 8) * (1.0f / 16777216.0f)) * total;
+
+    // Ordered passes: CTAs in rank order, inside a CTA each warp owns a contiguous range of indices.
+    int pw = (n + kNumWarps - 1) / kNumWarps;
+    pw = (pw + 31) / 32 * 32;
+    const int w_begin = min(n, warp * pw), w_end = min(n, w_begin + pw);
+
+    // (1) equals to the threshold: how many precede this CTA and this warp
+    {
+        long long c = 0;
+        for (int j = w_begin + lane; j < w_end; j += 32) c += order_key(ys[j]) == thr_key;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) c += __shfl_xor_sync(0xffffffffu, c, o);
+        if (lane == 0) warp_eq[warp] = c;
+    }
+    __syncthreads();
+    long long eq_cta = 0, eq_base = 0;
+    for (int w = 0; w < kNumWarps; ++w) {
+        if (w < warp) eq_base += warp_eq[w];
+        eq_cta += warp_eq[w];
+    }
+    if (tid == 0) cs.ll[turn][0] = eq_cta;
+    cluster.sync();
+    for (unsigned r = 0; r < rank; ++r) eq_base += cluster.map_shared_rank(&cs, r)->ll[turn][0];
+    turn ^= 1;
+
+    // (2) kept mass per warp, in index order
+    double my_mass = 0.0;
+    {
+        long long eq_seen = eq_base;
+        for (int base = w_begin; base < w_end; base += 32) {
+            const int j = base + lane;
+            const bool in = j < w_end;
+            const uint32_t key = in ? order_key(ys[j]) : 0u;
+            const bool is_eq = in && key == thr_key;
+            const unsigned eq_mask = __ballot_sync(0xffffffffu, is_eq);
+            const long long rk = eq_seen + __popc(eq_mask & ((1u << lane) - 1u));
+            const bool kept = in && (key > thr_key || (is_eq && rk < n_eq));
+            if (kept) my_mass += (double)ws[j];
+            eq_seen += __popc(eq_mask);
+        }
+        my_mass = warp_sum_d(my_mass);
+        if (lane == 0) warp_mass[warp] = my_mass;
+    }
+    __syncthreads();
+    double mass_cta = 0.0, mass_before = 0.0;
+    int last_warp = -1;
+    for (int w = 0; w < kNumWarps; ++w) {
+        if (w < warp) mass_before += warp_mass[w];
+        mass_cta += warp_mass[w];
+        if (warp_mass[w] > 0.0) last_warp = w;
+    }
+    if (tid == 0) cs.d[turn][0] = mass_cta;
+    if (rank == 0 && tid == 0) out_token[row] = 0x7fffffff;
+    cluster.sync();
+    int last_cta = -1;
+    for (unsigned r = 0; r < kClusterSize; ++r) {
+        const double mr = cluster.map_shared_rank(&cs, r)->d[turn][0];
+        if (r < rank) mass_before += mr;
+        if (mr > 0.0) last_cta = (int)r;
+    }
+    turn ^= 1;
+
+    // (3) the warp whose range holds the target walks it
+    const bool last_nonempty = (int)rank == last_cta && warp == last_warp;
+    const bool holds = (warp_mass[warp] > 0.0) &&
+                       ((target <= mass_before + warp_mass[warp] && target > mass_before) ||
+                        (target <= mass_before && mass_before == 0.0 && target == 0.0) ||
+                        (last_nonempty && target > mass_before));
+    if (holds) {
+        double cum = mass_before;
+        long long eq_seen = eq_base;
+        int found = -1, last_kept = -1;
+        for (int base = w_begin; base < w_end && found < 0; base += 32) {
+            const int j = base + lane;
+            const bool in = j < w_end;
+            const uint32_t key = in ? order_key(ys[j]) : 0u;
+            const bool is_eq = in && key == thr_key;
+            const unsigned eq_mask = __ballot_sync(0xffffffffu, is_eq);
+            const long long rk = eq_seen + __popc(eq_mask & ((1u << lane) - 1u));
+            const bool kept = in && (key > thr_key || (is_eq && rk < n_eq));
+            double inc = kept ? (double)ws[j] : 0.0;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const double nb = __shfl_up_sync(0xffffffffu, inc, o);
+                if (lane >= o) inc += nb;
+            }
+            const bool hit = kept && (cum + inc >= target);
+            const unsigned hit_mask = __ballot_sync(0xffffffffu, hit);
+            const unsigned kept_mask = __ballot_sync(0xffffffffu, kept);
+            if (kept_mask) last_kept = base + 31 - __clz(kept_mask);
+            if (hit_mask) found = base + __ffs(hit_mask) - 1;
+            cum += __shfl_sync(0xffffffffu, inc, 31);
+            eq_seen += __popc(eq_mask);
+        }
+        if (found < 0) found = last_kept;
+        // more than one warp can hold the target only through rounding: the lowest index wins
+        if (lane == 0 && found >= 0) atomicMin(&out_token[row], begin + found);
+    }
+    __threadfence();
+    cluster.sync();
+    if (rank == 0 && tid == 0 && out_token[row] == 0x7fffffff) out_token[row] = max_i;
+}
+
 // After a decode step that ran wholly on the device: the sampled tokens become the
 // next step's input, every request moves one position on, and its draw counter advances.
 __global__ void advance_decode_kernel(int* __restrict__ token_ids, int* __restrict__ positions,
@@ -339,6 +688,22 @@ extern "C" int qi_sample(const float* logits, int rows, int vocab, const float* 
                          const int* counter, int* out_token, int* status, cudaStream_t stream) {
     QI_REQUIRE(rows >= 0 && vocab > 0, "sample: bad sizes rows=%d vocab=%d", rows, vocab);
     if (rows == 0) return 0;
+    // rows that draw go to clusters of eight CTAs that keep the row in shared memory; all-greedy batches
+    // (temperature null) and vocabularies too large for that keep the one-block kernel
+    int per = (vocab + kClusterSize - 1) / kClusterSize;
+    per = (per + 31) / 32 * 32;
+    if (temperature && per <= kMaxSlice && rows <= 65535 / kClusterSize) {
+        const size_t smem = (size_t)per * 2 * sizeof(float);
+        static size_t configured = 0;
+        if (smem > configured) {
+            cudaError_t e = cudaFuncSetAttribute(sample_cluster_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(2 * kMaxSlice * sizeof(float)));
+            if (e != cudaSuccess) return qi::fail("sample: cannot reserve shared memory: %s", cudaGetErrorString(e));
+            configured = 2 * kMaxSlice * sizeof(float);
+        }
+        qi::launch(sample_cluster_kernel, dim3(rows * kClusterSize), dim3(kThreads), smem, stream, logits, vocab, per, temperature,
+                   top_k, top_p, seed, counter, out_token, status);
+        return qi::check_launch("sample (cluster)");
+    }
     qi::launch(sample_kernel, dim3(rows), dim3(kThreads), 0, stream, logits, vocab, temperature, top_k, top_p, seed, counter,
                out_token, status);
     return qi::check_launch("sample");
