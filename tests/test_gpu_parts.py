@@ -467,3 +467,23 @@ def test_toy_feed_forward_with_routing_and_another_position_encoding():
     ref = plain_linear(plain_rms_norm(h, w["final.weight"], spec.final_norm.eps), w["emb.weight"])
     assert len(used) > 1, "the router sent every token to one expert: the test shows nothing"
     assert float((got - ref).abs().max()) < 5e-5
+
+
+def test_shared_cache_and_window_through_the_tensor_core_kernels():
+    """The run order that shares a cache entry and a windowed layer, at head size 64 in bfloat16: the
+    attention kernels of the serving path (the decode kernel makes its own queries and, for the layer
+    that writes, the new key and value; the reading layer writes nothing), single tokens included."""
+    from quantinfer_b200.config import LayerCall
+
+    T = _SpecTools
+    ids = [int(x) for x in torch.randint(0, 97, (120,))]
+    layers = [T.layer(0, d=64), T.layer(1, d=64, inter=56), T.layer(2, d=64)]
+    order = (LayerCall(0, 0), LayerCall(1, 1), LayerCall(0, 2), LayerCall(2, 0, writes_cache=False))
+    spec = T.tiny_spec(layers, order)
+    eng, tensors = _engine(spec, dtype="bfloat16")
+    got = _run_in_portions(eng, ids, (33, 1, 1, 1, 30, 4) + (1,) * 50)
+    assert float((got - _plain_model(tensors, spec, ids)).abs().max()) < 3e-2
+    spec = T.tiny_spec([T.layer(0, d=64, window=24), T.layer(1, nkv=1, d=64, inter=56)])
+    eng, tensors = _engine(spec, dtype="bfloat16")
+    got = _run_in_portions(eng, ids, (40, 1, 1, 17, 2) + (1,) * 59)
+    assert float((got - _plain_model(tensors, spec, ids)).abs().max()) < 3e-2
