@@ -91,13 +91,15 @@ class Engine:
     # ---- construction ------------------------------------------------------
 
     @classmethod
-    def from_folder(cls, folder, **kw) -> "Engine":
+    def from_folder(cls, folder, *, check_finite: bool = False, strict_weights: bool = False, **kw) -> "Engine":
+        """The model of a folder (config.json and safetensors). `check_finite` refuses weights with
+        NaN or infinities by name; `strict_weights` refuses tensors the model does not use."""
         folder = Path(folder)
         config = load_config(folder)
         spec = config.to_model_spec()
         from .model import tensor_needs_of_spec
 
-        tensors = load_folder(folder, tensor_needs_of_spec(spec))
+        tensors = load_folder(folder, tensor_needs_of_spec(spec), strict=strict_weights, check_finite=check_finite)
         return cls(spec, tensors, config=config, **kw)
 
     # ---- requests ------------------------------------------------------------

@@ -7,6 +7,18 @@ returned in their stored element type: bfloat16 stays bfloat16, 32-bit stays
 32-bit, integer tables become int32. The model moves them to the device and
 converts what its compute type needs.
 
+Tensors that the model does not ask for (a buffer some exporter left in the
+file; `lm_head.weight` beside a tied configuration, whose head is the embedding
+table) do not stop a load: they are skipped and named once on stderr, as the
+reference's converter passes unknown names through
+(tools/quantinfer-convert/src/convert/gguf.rs:380-381) and builds a tied head
+from the table (crates/quantinfer-runtime/src/qwen3/loader.rs:59). They are
+still named in the error when something else is wrong, and `strict=True` makes
+them an error of their own. `check_finite=True` reads every needed tensor once
+more and refuses NaN and infinities by name, which the reference does at decode
+time for every element (crates/quantinfer-format/src/safetensors/decode.rs:8-53);
+it is off by default because it doubles the load time of a large checkpoint.
+
 The names are those of the checkpoint (`model.layers.N.self_attn.q_proj.weight`
 and so on), the same list the reference maps from
 (crates/quantinfer-format/src/dense.rs:9-46) and requires
@@ -19,6 +31,7 @@ operands are read along K, so no transpose is needed).
 
 from __future__ import annotations
 
+import sys
 from dataclasses import dataclass
 
 import torch
@@ -34,9 +47,11 @@ class TensorNeed:
     init: str = "normal"     # how random weights fill it: "normal" | "gain" | "zeros"
 
 
-def check_and_load(source, needs: dict) -> dict:
+def check_and_load(source, needs: dict, *, strict: bool = False, check_finite: bool = False, warn=None) -> dict:
     """Returns {name: CPU tensor} for every needed name, or raises one WeightError
-    listing missing tensors, unexpected tensors, wrong shapes and wrong element classes."""
+    listing missing tensors, unexpected tensors, wrong shapes and wrong element classes.
+    Unexpected tensors alone are skipped with one line through `warn` (stderr by default)
+    unless `strict`."""
     have = set(source.names())
     want = set(needs)
     missing = sorted(want - have)
@@ -51,7 +66,7 @@ def check_and_load(source, needs: dict) -> dict:
         is_float = dt in (torch.float32, torch.float16, torch.bfloat16)
         if (need.kind == "int") == is_float:
             wrong_type.append(f"{name}: stored as {dt}, expected {'an integer' if need.kind == 'int' else 'a floating-point'} type")
-    if missing or unexpected or wrong_shape or wrong_type:
+    if missing or wrong_shape or wrong_type or (strict and unexpected):
         lines = ["the weight files do not match the model:"]
         if missing:
             lines.append(f"  missing tensors ({len(missing)}): " + ", ".join(missing))
@@ -62,17 +77,31 @@ def check_and_load(source, needs: dict) -> dict:
         if wrong_type:
             lines.append(f"  wrong element types ({len(wrong_type)}): " + "; ".join(wrong_type))
         raise WeightError("\n".join(lines))
+    if unexpected:
+        shown = ", ".join(unexpected[:8]) + (f", ... ({len(unexpected) - 8} more)" if len(unexpected) > 8 else "")
+        note = ("the table serves as the head of this tied model; " if "lm_head.weight" in unexpected else "")
+        (warn or _warn)(f"warning: {note}{len(unexpected)} tensors that the model does not use were skipped: {shown}")
     out = {}
+    non_finite = []
     for name in needs:
         t = source.tensor(name)
+        if check_finite and t.is_floating_point() and not bool(torch.isfinite(t).all()):
+            bad = int((~torch.isfinite(t)).sum())
+            non_finite.append(f"{name} ({bad} of {t.numel()} values)")
         if needs[name].kind == "int":
             if t.dtype != torch.int32:
                 t = t.to(torch.int64).to(torch.int32)
         elif t.dtype == torch.float16:
             t = t.to(torch.float32)  # half is not a compute type here; widen exactly
         out[name] = t
+    if non_finite:
+        raise WeightError("the weight files hold values that are not finite: " + "; ".join(non_finite))
     return out
 
 
-def load_folder(folder, needs: dict) -> dict:
-    return check_and_load(SafeTensorsFolder(folder), needs)
+def _warn(line: str) -> None:
+    print(line, file=sys.stderr, flush=True)
+
+
+def load_folder(folder, needs: dict, *, strict: bool = False, check_finite: bool = False, warn=None) -> dict:
+    return check_and_load(SafeTensorsFolder(folder), needs, strict=strict, check_finite=check_finite, warn=warn)

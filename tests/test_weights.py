@@ -70,6 +70,57 @@ def test_one_error_lists_missing_unexpected_and_wrong_shapes(tmp_path):
     assert "wrong element types (1)" in msg and "model.norm.weight" in msg
 
 
+def test_tensors_the_model_does_not_use_are_skipped_with_one_line(tmp_path):
+    from safetensors.torch import load_file, save_file
+
+    folder = make_folder(tmp_path / "B", "B")
+    path = str(folder / "model.safetensors")
+    t = load_file(path)
+    t["model.layers.0.self_attn.rotary_emb.inv_freq"] = torch.ones(16)
+    t["something.else"] = torch.zeros(2, 2, dtype=torch.bfloat16)
+    save_file(t, path)
+    lines = []
+    got = load_folder(folder, _needs("B"), warn=lines.append)
+    assert set(got) == set(_needs("B"))
+    assert len(lines) == 1 and "2 tensors" in lines[0] and "something.else" in lines[0] and "inv_freq" in lines[0]
+    # asked to be strict, the same folder is refused, and the error names them
+    with pytest.raises(WeightError, match=r"unexpected tensors \(2\)"):
+        load_folder(folder, _needs("B"), strict=True)
+
+
+def test_a_tied_configuration_with_a_stored_head_uses_the_table(tmp_path):
+    from safetensors.torch import load_file, save_file
+
+    folder = make_folder(tmp_path / "A", "A")            # A ties its head to the embedding table
+    path = str(folder / "model.safetensors")
+    t = load_file(path)
+    t["lm_head.weight"] = torch.full_like(t["model.embed_tokens.weight"], 7.0)   # differs from the table
+    save_file(t, path)
+    lines = []
+    got = load_folder(folder, _needs("A"), warn=lines.append)
+    assert "lm_head.weight" not in got
+    assert len(lines) == 1 and "lm_head.weight" in lines[0] and "tied" in lines[0]
+
+
+def test_values_that_are_not_finite_are_refused_by_name_when_asked(tmp_path):
+    from safetensors.torch import load_file, save_file
+
+    folder = make_folder(tmp_path / "C", "C")
+    load_folder(folder, _needs("C"), check_finite=True)      # a clean folder passes the check
+    path = str(folder / "model.safetensors")
+    t = load_file(path)
+    t["model.layers.1.mlp.gate_proj.weight"][3, 5] = float("nan")
+    t["model.layers.0.post_attention_layernorm.weight"][2] = float("-inf")
+    t["model.layers.0.post_attention_layernorm.weight"][9] = float("inf")
+    save_file(t, path)
+    load_folder(folder, _needs("C"))                          # off by default
+    with pytest.raises(WeightError) as e:
+        load_folder(folder, _needs("C"), check_finite=True)
+    msg = str(e.value)
+    assert "model.layers.1.mlp.gate_proj.weight (1 of" in msg
+    assert "model.layers.0.post_attention_layernorm.weight (2 of 168" in msg
+
+
 def test_sharded_folder(tmp_path):
     folder = make_folder(tmp_path / "A", "A")
     from safetensors.torch import load_file

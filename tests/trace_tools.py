@@ -115,7 +115,7 @@ def collect(steps: list, outputs: dict) -> dict:
 def run_trace_engine(folder, dtype: str, steps: list, max_tokens: int, page_size: int) -> dict:
     from quantinfer_b200.engine import Engine, StepEntry
 
-    eng = Engine.from_folder(folder, dtype=dtype, page_size=page_size, max_tokens=max_tokens, max_requests=8)
+    eng = Engine.from_folder(folder, dtype=dtype, page_size=page_size, max_tokens=max_tokens, max_requests=8, check_finite=True)
     live, outputs = set(), {}
     for st in steps:
         entries = []
