@@ -20,82 +20,86 @@ from threading import RLock
 from .errors import QuantInferError
 from .sampling import GenerationConfig, Sampler
 
-EOS_AUTO = (1 << 32) - 1
+# The value that stands for "use the model's own end-of-sequence token" in `eos_token_id`; it is the
+# largest 32-bit unsigned number, as at the reference's C boundary, so that every real id stays usable.
+EOS_AUTO = 0xFFFFFFFF
 
 
-def _unsigned(value, maximum, name):
-    value = operator.index(value)
-    if not 0 <= value <= maximum:
-        raise ValueError(f"{name} is outside its unsigned integer range")
-    return value
+def _as_count(value, limit: int, what: str) -> int:
+    """`value` as a whole number in [0, limit]; anything else is a ValueError naming `what`."""
+    n = operator.index(value)
+    if n < 0 or n > limit:
+        raise ValueError(f"{what} must be a whole number between 0 and {limit}, got {n}")
+    return n
 
 
 class Model:
     """A model folder loaded onto one GPU."""
 
     def __init__(self, path, *, dtype="bfloat16", device="cuda:0", page_size=None, cache_tokens=None,
-                 max_requests=8, max_batch_tokens=2048, chunk_size=None, use_graphs=True, run_ahead=True):
+                 num_pages=None, max_requests=8, max_batch_tokens=2048, chunk_size=None, use_graphs=True,
+                 run_ahead=True, check_finite=False):
         """`run_ahead`: decode steps are launched before the host has read the tokens of the
-        step before (engine/pipeline.py); the tokens do not change, they arrive one step late."""
+        step before (engine/pipeline.py); the tokens do not change, they arrive one step late.
+        `cache_tokens` or `num_pages` size the page pool; `check_finite` refuses a folder whose
+        weights hold NaN or infinities."""
         from .engine import Engine
         from .engine.engine import DEFAULT_PAGE_SIZE
 
-        self._lock = RLock()
-        self._engine = Engine.from_folder(
-            path, dtype=dtype, device=device, page_size=page_size or DEFAULT_PAGE_SIZE,
-            max_tokens=cache_tokens, max_requests=max_requests, use_graphs=use_graphs)
-        self._sampler = Sampler.for_engine(self._engine)
-        self._max_batch_tokens = max_batch_tokens
-        self._chunk_size = chunk_size
-        self._run_ahead = run_ahead
-        self._open = True
+        engine = Engine.from_folder(
+            path, dtype=dtype, device=device, page_size=page_size or DEFAULT_PAGE_SIZE, max_tokens=cache_tokens,
+            num_pages=num_pages, max_requests=max_requests, use_graphs=use_graphs, check_finite=check_finite)
+        self._attach(engine, max_batch_tokens, chunk_size, run_ahead)
 
     @classmethod
     def from_engine(cls, engine, *, max_batch_tokens=2048, chunk_size=None, run_ahead=True) -> "Model":
         """A Model over an engine that already exists (random weights made on the device, tests)."""
         self = cls.__new__(cls)
+        self._attach(engine, max_batch_tokens, chunk_size, run_ahead)
+        return self
+
+    def _attach(self, engine, max_batch_tokens, chunk_size, run_ahead) -> None:
         self._lock = RLock()
         self._engine = engine
         self._sampler = Sampler.for_engine(engine)
         self._max_batch_tokens = max_batch_tokens
         self._chunk_size = chunk_size
         self._run_ahead = run_ahead
-        self._open = True
-        return self
+        self.last_scheduler = None
 
     # ---- lifetime -------------------------------------------------------------
 
     def close(self):
-        """Release the model once all calls on this handle finish."""
+        """Drops the engine (weights, cache, graphs). A call that is running on another thread
+        holds the lock and ends first; later calls raise."""
         with self._lock:
-            self._engine = None
-            self._sampler = None
-            self._open = False
+            self._engine = self._sampler = None
 
     def __enter__(self):
-        with self._lock:
-            self._require_open()
+        self._live()
         return self
 
-    def __exit__(self, exc_type, exc_value, traceback):
+    def __exit__(self, *exc_info):
         self.close()
+        return False
 
-    def _require_open(self):
-        if not self._open:
+    def _live(self):
+        engine = self._engine
+        if engine is None:
             raise QuantInferError("model is closed")
+        return engine
 
     @property
     def engine(self):
-        self._require_open()
-        return self._engine
+        return self._live()
 
     @property
     def vocab_size(self) -> int:
-        return self.engine.spec.vocab_size
+        return self._live().spec.vocab_size
 
     @property
     def max_position_embeddings(self) -> int:
-        return self.engine.spec.max_positions
+        return self._live().spec.max_positions
 
     # ---- no tokenizer ------------------------------------------------------------
 
@@ -111,27 +115,30 @@ class Model:
     # ---- generation ----------------------------------------------------------------
 
     def _config(self, n_prompt, max_new_tokens, context_length, temperature, top_k, top_p, eos_token_id, seed):
-        max_new_tokens = _unsigned(max_new_tokens, (1 << 63) - 1, "max_new_tokens")
-        if eos_token_id is None:
-            eos = None
-        else:
-            eos_token_id = _unsigned(eos_token_id, EOS_AUTO, "EOS token ID")
-            eos = self._engine.spec.eos_token_id if eos_token_id == EOS_AUTO else eos_token_id
+        engine = self._engine
+        max_new_tokens = _as_count(max_new_tokens, (1 << 63) - 1, "max_new_tokens")
+        eos = None
+        if eos_token_id is not None:
+            eos = _as_count(eos_token_id, EOS_AUTO, "eos_token_id")
+            if eos == EOS_AUTO:
+                eos = engine.spec.eos_token_id
         cfg = GenerationConfig(max_new_tokens=max_new_tokens, temperature=float(temperature),
-                               top_k=None if top_k is None else _unsigned(top_k, (1 << 63) - 1, "top_k"),
+                               top_k=None if top_k is None else _as_count(top_k, (1 << 63) - 1, "top_k"),
                                top_p=None if top_p is None else float(top_p), eos_token_id=eos,
-                               seed=_unsigned(seed, (1 << 64) - 1, "seed"))
-        cfg.validate(self._engine.spec.vocab_size)
-        context = n_prompt + max_new_tokens if context_length is None else _unsigned(context_length, (1 << 63) - 1, "context_length")
-        if context > self._engine.max_seq_len:
-            raise ValueError(f"context_length must be between 1 and {self._engine.max_seq_len}")
+                               seed=_as_count(seed, (1 << 64) - 1, "seed"))
+        cfg.validate(engine.spec.vocab_size)
+        context = n_prompt + max_new_tokens if context_length is None else _as_count(context_length, (1 << 63) - 1, "context_length")
+        if context > engine.max_seq_len:
+            raise ValueError(f"context_length must be between 1 and {engine.max_seq_len}")
         if n_prompt + max_new_tokens > context:
             raise ValueError("prompt and max_new_tokens exceed the context length")
         return cfg
 
     def generate_tokens(self, tokens, *, max_new_tokens=32, context_length=None, temperature=0.0,
                         top_k=None, top_p=None, eos_token_id=EOS_AUTO, seed=0):
-        """Generate token IDs. The default uses the model EOS and None disables it."""
+        """The ids generated after the prompt `tokens` (a list of ids on the host). `eos_token_id`:
+        EOS_AUTO stops at the end-of-sequence id that config.json names (if it names one), an id
+        stops at that id, None never stops early; the stopping token is part of the result."""
         return self.generate_batch([tokens], max_new_tokens=max_new_tokens, context_length=context_length,
                                    temperature=temperature, top_k=top_k, top_p=top_p,
                                    eos_token_id=eos_token_id, seed=seed)[0]
@@ -141,22 +148,12 @@ class Model:
         """Generates for every prompt (lists of token ids on the host); returns the
         lists of generated ids in the order of the prompts. Request i draws with
         seed + i."""
-        from .engine.pipeline import DecodePipeline
-        from .engine.scheduler import FailedEvent, Scheduler, TokenEvent
+        from .engine.generation import run_requests
 
         with self._lock:
-            self._require_open()
-            eng = self._engine
-            prompts = [[_unsigned(t, EOS_AUTO, "token ID") for t in p] for p in prompts]
-            # the sampler reads the step's status word together with the tokens: one wait per step
-            sched = Scheduler(eng.cache, lambda entries: eng.step(entries, check_status=False), self._sampler.sample,
-                              vocab_size=eng.spec.vocab_size,
-                              max_sequences=eng.cache.max_requests,
-                              max_tokens=max(self._max_batch_tokens, eng.cache.max_requests),
-                              chunk_size=self._chunk_size,
-                              pipeline=DecodePipeline(eng, self._sampler) if self._run_ahead and eng.use_graphs else None)
-            self.last_scheduler = sched
-            ids = []
+            engine = self._live()
+            prompts = [[_as_count(t, EOS_AUTO, "token id") for t in p] for p in prompts]
+            configs = []
             for i, p in enumerate(prompts):
                 if not p:
                     raise ValueError("a prompt must contain at least one token id")
@@ -164,16 +161,9 @@ class Model:
                                    eos_token_id, seed)
                 if i:
                     cfg = GenerationConfig(**{**cfg.__dict__, "seed": (cfg.seed + i) % (1 << 64)})
-                ids.append(sched.submit(p, cfg))
-            out = {rid: [] for rid in ids}
-            try:
-                for ev in sched.run(on_event):
-                    if isinstance(ev, TokenEvent):
-                        out[ev.request_id].append(ev.token_id)
-                    elif isinstance(ev, FailedEvent):
-                        raise QuantInferError(f"request {ev.request_id} failed: {ev.error}")
-            finally:
-                for rid in list(eng.cache.requests):
-                    if rid in out:
-                        eng.cache.close(rid)
-            return [out[rid] for rid in ids]
+                configs.append(cfg)
+            run = run_requests(engine, self._sampler, prompts, configs, max_batch_tokens=self._max_batch_tokens,
+                               chunk_size=self._chunk_size, run_ahead=self._run_ahead, on_event=on_event)
+            self.last_scheduler = run.scheduler
+            self.last_run = run
+            return [r.tokens for r in run.results]

@@ -18,6 +18,10 @@ group, cut into pages of `page_size` positions:
 * a *slot* is a request's index into per-request arrays of fixed size: mixer
   state (`StateNeed` entries, `[num_slots, *shape]`, zeroed at `open`) and
   whatever the engine keeps per request (sampler state).
+* state of fixed size is overwritten by a step, so a failed step cannot give it
+  back the way it gives pages back: `prepare` copies the request's state rows
+  aside (device to device, in stream order) and `rollback` copies them back.
+  A model without such state pays nothing for this.
 
 The bookkeeping is host-side and needs no device: `device=None` builds the
 manager without pools, which is how the scheduler tests drive it.
@@ -113,6 +117,7 @@ class CacheManager:
         self.groups: list[Group] = []
         self._entry_group: dict[int, tuple] = {}     # entry -> (group index, index in group)
         self.states: dict[int, torch.Tensor] = {}    # entry -> [num_slots, *shape]
+        self._state_saved: dict[int, torch.Tensor] = {}   # the rows as they were before the step in flight
         by_need: dict[PagedKVNeed, int] = {}
         for entry, need in enumerate(self.needs):
             if isinstance(need, PagedKVNeed):
@@ -126,6 +131,7 @@ class CacheManager:
                 if self.device is not None:
                     self.states[entry] = torch.zeros((max_requests, *need.shape), dtype=need.dtype or dtype,
                                                      device=self.device)
+                    self._state_saved[entry] = torch.zeros_like(self.states[entry])
             elif need is not None:
                 raise CacheError(f"cache entry {entry} asks for {need!r}, which the manager does not know")
         if self.device is not None:
@@ -210,6 +216,8 @@ class CacheManager:
             raise OutOfPages(
                 f"request {request_id!r} needs {need_blocks} pages per group for {end} positions; "
                 f"a pool of {self.num_pages} pages has none left") from None
+        for entry, st in self.states.items():
+            self._state_saved[entry][rc.slot].copy_(st[rc.slot])
         rc.pending = n_new
 
     def commit(self, request_id) -> None:
@@ -231,8 +239,12 @@ class CacheManager:
                     self.host_tables[gi][rc.slot, b] = -1
 
     def rollback(self, request_id) -> None:
-        """Undoes `prepare`: pages beyond the committed length go back."""
+        """Undoes `prepare`: pages beyond the committed length go back, and state of fixed
+        size is again what it was before the step."""
         rc = self.get(request_id)
+        if rc.pending:
+            for entry, st in self.states.items():
+                st[rc.slot].copy_(self._state_saved[entry][rc.slot])
         keep = -(-rc.length // self.page_size)
         for gi, g in enumerate(self.groups):
             table = rc.tables[gi]

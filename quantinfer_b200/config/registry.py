@@ -38,8 +38,11 @@ def config_class_for(name: str) -> type:
 
 
 def load_config(folder):
-    """Reads `folder/config.json` and returns the typed config its architecture names."""
-    path = Path(folder) / "config.json"
+    """Reads `folder/config.json` (or `folder` itself, if it is a file) and returns the typed
+    config its architecture names."""
+    path = Path(folder)
+    if not path.is_file():
+        path = path / "config.json"
     if not path.is_file():
         raise ConfigError(f"{path} does not exist")
     try:

@@ -29,14 +29,16 @@ class NormSpec:
 
 @dataclass(frozen=True)
 class PositionSpec:
-    """Rotary encoding over the first `rotary_dim` dimensions of each head,
-    pairs (p, p + rotary_dim / 2), angle = position * theta^(-2p / rotary_dim)."""
+    """Rotary encoding over the first `rotary_dim` dimensions of each head, angle of pair p =
+    position * theta^(-2p / rotary_dim). `pairing` says which two elements pair p is:
+    "half_split" (p, p + rotary_dim / 2) or "interleaved" (2p, 2p + 1)."""
 
     head_dim: int
     rotary_dim: int
     theta: float
     max_positions: int
     kind: str = "rope_half_split"
+    pairing: str = "half_split"
 
 
 @dataclass(frozen=True)

@@ -29,6 +29,17 @@
 //     instance on two streams, overwrite each other's partial results: serialise them.
 //
 // Arguments and return value are those of qi_attention_decode_tma without ws_o / ws_ml.
+// Two preconditions, the same for both entry points:
+//
+//   * kv_len, q_start and block_table must be complete in device memory when the kernel
+//     starts. The kernel reads them, and requests its first key/value tiles, before it
+//     waits for the kernel ahead of it in the stream. After a copy or an ordinary kernel
+//     launch that is always so. If you produce these arrays with a kernel launched under
+//     programmatic dependent launch, that kernel must not release its successors early
+//     (no cudaTriggerProgrammaticLaunchCompletion / griddepcontrol.launch_dependents).
+//   * n_splits * chunk must cover the longest kv_len. Keys beyond the last range are not
+//     read; the kernel then sets bit 16 of *status instead of returning a wrong result
+//     silently, and the caller must treat the output as invalid.
 #pragma once
 
 #include <cuda_runtime.h>

@@ -227,6 +227,7 @@ struct DecodeRope {
     qi::bf16* v_pages;
     float eps;
     int splits, width;
+    int table_positions;        // rows of cos_t / sin_t
 };
 
 template <typename TIn> __device__ __forceinline__ float2 load2(const TIn* p);
@@ -316,6 +317,9 @@ attention_decode_tma_kernel(const qi::bf16* __restrict__ q, qi::bf16* __restrict
     const int k0 = max(split * chunk, lo);
     const int k1 = min(S, (split + 1) * chunk);
     const size_t part = ((size_t)b * nq + (size_t)hk * G) * n_splits + split;
+    // the ranges of this launch must cover the request's keys; what lies beyond them is not read, so say so
+    if (split == n_splits - 1 && hk == 0 && threadIdx.x == 0 && (long long)n_splits * chunk < S && status)
+        atomicOr(status, qi::kStatusBadRange);
 
     const int tok = q_start[b];
     if (k0 >= k1) {   // nothing of this range belongs to the request: an empty partial
@@ -359,12 +363,17 @@ attention_decode_tma_kernel(const qi::bf16* __restrict__ q, qi::bf16* __restrict
     const bool owns_new = FUSED && rope.k_pages != nullptr && k1 == S;
     if constexpr (FUSED) {
         const int pos = S - 1;
+        int table_row = pos;
+        if (rope.cos_t && pos >= rope.table_positions) {   // beyond the rotation table: flagged, the last row stands in
+            if (threadIdx.x == 0 && status) atomicOr(status, qi::kStatusBadRange);
+            table_row = rope.table_positions - 1;
+        }
         const TIn* tok_row = reinterpret_cast<const TIn*>(rope.qkv) + (size_t)tok * rope.width;
         for (int row = warp; row < 16; row += kDecodeThreads / 32) {
             float2 lo = make_float2(0.f, 0.f), hi = lo;
             if (row < G)
                 head_norm_rope<D, TIn>(tok_row + (size_t)(hk * G + row) * D, rope.splits, rope.split_stride, rope.q_gain, rope.eps,
-                                       rope.cos_t, rope.sin_t, pos, lane, lo, hi);
+                                       rope.cos_t, rope.sin_t, table_row, lane, lo, hi);
             const int p = 2 * lane;
             if (p < D / 2) {
                 *reinterpret_cast<uint32_t*>(q_tile + RowSwizzle<D>::off(row, p >> 3) + (p & 7) * 2) = pack_bf16(lo.x, lo.y);
@@ -377,7 +386,7 @@ attention_decode_tma_kernel(const qi::bf16* __restrict__ q, qi::bf16* __restrict
             const TIn* src = tok_row + (size_t)(nq + (warp == 0 ? 0 : nkv) + hk) * D;
             float2 lo, hi;
             head_norm_rope<D, TIn>(src, rope.splits, rope.split_stride, warp == 0 ? rope.k_gain : nullptr, rope.eps,
-                                   warp == 0 ? rope.cos_t : nullptr, rope.sin_t, pos, lane, lo, hi);
+                                   warp == 0 ? rope.cos_t : nullptr, rope.sin_t, table_row, lane, lo, hi);
             const int page = block_table[(size_t)b * max_blocks + pos / page_size];
             const int p = 2 * lane;
             if (page < 0 || page >= num_pages) {
@@ -735,7 +744,7 @@ extern "C" int qi_attention_decode_rope_tma(const void* qkv, int qkv_dtype, int 
     r.qkv = qkv;
     r.width = (nq + 2 * nkv) * d;
     r.split_stride = (long long)n_tokens * r.width;
-    r.q_gain = q_gain; r.k_gain = k_gain; r.cos_t = cos_t; r.sin_t = sin_t;
+    r.q_gain = q_gain; r.k_gain = k_gain; r.cos_t = cos_t; r.sin_t = sin_t; r.table_positions = table_positions;
     r.k_pages = writes ? (qi::bf16*)k_pages : nullptr;
     r.v_pages = writes ? (qi::bf16*)v_pages : nullptr;
     r.eps = eps; r.splits = qkv_splits;

@@ -22,6 +22,7 @@ enum Status : int {
     kStatusBadPage = 2,      // block table entry < 0 or >= pool size where a page was needed
     kStatusNonFinite = 4,    // logits held NaN or Inf where a sampler read them
     kStatusWaitTimeout = 8,  // a bounded mbarrier wait ran out
+    kStatusBadRange = 16,    // a position beyond the rotation table, or keys beyond the ranges a launch covers
 };
 
 typedef __nv_bfloat16 bf16;

@@ -190,6 +190,7 @@ struct RopeEpilogue {
     qi::bf16* v_pages;
     float eps;
     int max_blocks, page_size, num_pages, nq, nkv;
+    int table_positions;     // rows of cos_t / sin_t
 };
 
 __device__ __forceinline__ uint32_t pack2(float a, float b) {
@@ -204,7 +205,17 @@ template <int BN>
 __device__ __forceinline__ void rope_epilogue(uint32_t tmem_tile, int col_base, int row, bool row_ok, int n_cols,
                                               const RopeEpilogue& e, int* __restrict__ status) {
     constexpr int D = 128, HALF = 64;
-    const int pos = row_ok ? e.positions[row] : 0;
+    int pos = row_ok ? e.positions[row] : 0;
+    if (pos < 0) {           // no such position: nothing of this token is written
+        if (status) atomicOr(status, qi::kStatusBadRange);
+        pos = 0;
+        row_ok = false;
+    }
+    int table_row = pos;     // a position beyond the rotation table is flagged and takes the table's last row
+    if (e.cos_t && pos >= e.table_positions) {
+        if (status) atomicOr(status, qi::kStatusBadRange);
+        table_row = e.table_positions - 1;
+    }
     int page = -2;           // -2: not looked up yet
 #pragma unroll 1
     for (int hh = 0; hh < BN / D; ++hh) {
@@ -271,8 +282,8 @@ __device__ __forceinline__ void rope_epilogue(uint32_t tmem_tile, int col_base, 
                 }
             }
             if (rotate) {
-                const float4* cs = reinterpret_cast<const float4*>(e.cos_t + (size_t)pos * HALF + 32 * c);
-                const float4* sn = reinterpret_cast<const float4*>(e.sin_t + (size_t)pos * HALF + 32 * c);
+                const float4* cs = reinterpret_cast<const float4*>(e.cos_t + (size_t)table_row * HALF + 32 * c);
+                const float4* sn = reinterpret_cast<const float4*>(e.sin_t + (size_t)table_row * HALF + 32 * c);
 #pragma unroll
                 for (int i = 0; i < 8; ++i) {
                     const float4 cc = cs[i], ss = sn[i];
@@ -1184,6 +1195,7 @@ extern "C" int qi_gemm_bf16_qkv_rope(const void* x, const void* w, int M, int K,
     e.positions = positions; e.token_req = token_req; e.block_table = block_table;
     e.k_pages = (qi::bf16*)k_pages; e.v_pages = (qi::bf16*)v_pages; e.eps = eps;
     e.max_blocks = max_blocks; e.page_size = page_size; e.num_pages = num_pages; e.nq = nq; e.nkv = nkv;
+    e.table_positions = table_positions;
     if (plan_mode == 2) {
         CUtensorMap pb;
         if (make_map(&pb, w, N, K, BM)) return 1;

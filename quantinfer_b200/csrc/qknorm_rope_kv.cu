@@ -6,6 +6,10 @@
 // shared by all heads (backends/cpu/src/backend.rs:195-203), then rotated
 // (half-split pairs (p, p + rot/2); backends/cpu/src/backend.rs:270-275), then k
 // (rotated) and v (raw) are appended to the cache (cache.rs:94-127).
+// The pairing rule is a parameter: `interleaved` rotates adjacent elements (2p, 2p + 1)
+// with the angle of pair p instead, the order the reference's converter produces for
+// architectures it stores that way (crates/quantinfer-format/src/gguf/layout.rs:52-55).
+// A position beyond the rotation table sets a status bit and uses the table's last row.
 // Norm sums, angles and the rotation are 32-bit. cos/sin come from a table
 // [max_positions, rot/2] built once by rope_table below from 32-bit inverse
 // frequencies (attention.rs:29-32: angle = position * theta^(-2p/d)).
@@ -24,7 +28,7 @@ template <typename T>
 __global__ void qk_norm_rope_kv_kernel(
     const T* __restrict__ qkv, T* __restrict__ q_out, const float* __restrict__ q_gain,
     const float* __restrict__ k_gain, float eps, const float* __restrict__ cos_t,
-    const float* __restrict__ sin_t, int rot, const int* __restrict__ positions,
+    const float* __restrict__ sin_t, int rot, int interleaved, int table_positions, const int* __restrict__ positions,
     const int* __restrict__ token_req, const int* __restrict__ block_table, int max_blocks,
     int page_size, int num_pages, T* __restrict__ k_pages, T* __restrict__ v_pages, int nq, int nkv,
     int d, int* __restrict__ status) {
@@ -37,6 +41,15 @@ __global__ void qk_norm_rope_kv_kernel(
     const int row_width = total_heads * d;
     const T* src = qkv + (size_t)t * row_width + (size_t)head * d;
     const int pos = positions[t];
+    if (pos < 0) {
+        if (lane == 0 && status) atomicOr(status, qi::kStatusBadRange);
+        return;
+    }
+    int table_row = pos;
+    if (cos_t && pos >= table_positions) {
+        if (lane == 0 && status) atomicOr(status, qi::kStatusBadRange);
+        table_row = table_positions - 1;
+    }
 
     // Destination row.
     T* dst = nullptr;
@@ -76,19 +89,20 @@ __global__ void qk_norm_rope_kv_kernel(
     const int half = rot / 2;
     // Rotated pairs.
     for (int p = lane; p < half; p += 32) {
-        float a = qi::to_f32<T>(src[p]);
-        float b = qi::to_f32<T>(src[p + half]);
+        const int ia = interleaved ? 2 * p : p, ib = interleaved ? 2 * p + 1 : p + half;
+        float a = qi::to_f32<T>(src[ia]);
+        float b = qi::to_f32<T>(src[ib]);
         if (gain) {
-            a = a * inv * gain[p];
-            b = b * inv * gain[p + half];  // stays 32-bit until after the rotation
+            a = a * inv * gain[ia];
+            b = b * inv * gain[ib];  // stays 32-bit until after the rotation
         }
         float c = 1.f, s = 0.f;
         if (cos_t) {
-            c = cos_t[(size_t)pos * half + p];
-            s = sin_t[(size_t)pos * half + p];
+            c = cos_t[(size_t)table_row * half + p];
+            s = sin_t[(size_t)table_row * half + p];
         }
-        dst[p] = qi::from_f32<T>(a * c - b * s);
-        dst[p + half] = qi::from_f32<T>(a * s + b * c);
+        dst[ia] = qi::from_f32<T>(a * c - b * s);
+        dst[ib] = qi::from_f32<T>(a * s + b * c);
     }
     // Dimensions beyond the rotary part pass through (normalised).
     for (int i = rot + lane; i < d; i += 32) {
@@ -132,7 +146,7 @@ template <typename TIn, typename T>
 __global__ void qk_norm_rope_kv_vec_kernel(
     const TIn* __restrict__ qkv, int splits, size_t split_stride, T* __restrict__ q_out, const float* __restrict__ q_gain,
     const float* __restrict__ k_gain, float eps, const float* __restrict__ cos_t,
-    const float* __restrict__ sin_t, const int* __restrict__ positions,
+    const float* __restrict__ sin_t, int table_positions, const int* __restrict__ positions,
     const int* __restrict__ token_req, const int* __restrict__ block_table, int max_blocks,
     int page_size, int num_pages, T* __restrict__ k_pages, T* __restrict__ v_pages, int nq, int nkv,
     int d, int* __restrict__ status) {
@@ -144,6 +158,15 @@ __global__ void qk_norm_rope_kv_vec_kernel(
     if (head >= total_heads) return;
     const TIn* src = qkv + (size_t)t * total_heads * d + (size_t)head * d;
     const int pos = positions[t];
+    if (pos < 0) {
+        if (lane == 0 && status) atomicOr(status, qi::kStatusBadRange);
+        return;
+    }
+    int table_row = pos;
+    if (cos_t && pos >= table_positions) {
+        if (lane == 0 && status) atomicOr(status, qi::kStatusBadRange);
+        table_row = table_positions - 1;
+    }
     const bool is_q = head < nq;
     const bool is_k = !is_q && head < nq + nkv;
     T* dst;
@@ -187,8 +210,8 @@ __global__ void qk_norm_rope_kv_vec_kernel(
         }
         float2 c = make_float2(1.f, 1.f), sn = make_float2(0.f, 0.f);
         if (cos_t) {
-            c = *reinterpret_cast<const float2*>(cos_t + (size_t)pos * half + p);
-            sn = *reinterpret_cast<const float2*>(sin_t + (size_t)pos * half + p);
+            c = *reinterpret_cast<const float2*>(cos_t + (size_t)table_row * half + p);
+            sn = *reinterpret_cast<const float2*>(sin_t + (size_t)table_row * half + p);
         }
         Pair<T>::store(dst + p, a.x * c.x - b.x * sn.x, a.y * c.y - b.y * sn.y);
         Pair<T>::store(dst + p + half, a.x * sn.x + b.x * c.x, a.y * sn.y + b.y * c.y);
@@ -217,10 +240,11 @@ extern "C" int qi_rope_table(const float* inv_freq, float* cos_t, float* sin_t, 
 }
 
 // q_gain/k_gain null: no norm. cos_t null: no rotation. k_pages null: no cache write.
+// interleaved: pairs (2p, 2p + 1) instead of (p, p + rot/2).
 // qkv_splits > 1: `qkv` holds float32 partial sums [qkv_splits, n_tokens, width] of the projection.
 extern "C" int qi_qk_norm_rope_kv(const void* qkv, int qkv_splits, void* q_out, int dtype, const float* q_gain,
                                   const float* k_gain, float eps, const float* cos_t,
-                                  const float* sin_t, int rot, int table_positions,
+                                  const float* sin_t, int rot, int interleaved, int table_positions,
                                   const int* positions, const int* token_req,
                                   const int* block_table, int max_blocks, int page_size,
                                   int num_pages, void* k_pages, void* v_pages, int n_tokens, int nq,
@@ -238,14 +262,14 @@ extern "C" int qi_qk_norm_rope_kv(const void* qkv, int qkv_splits, void* q_out, 
     QI_REQUIRE(grid.y <= 65535, "qk_norm_rope_kv: too many heads");
     if (!cos_t) rot = 0;
     QI_REQUIRE(qkv_splits >= 1, "qk_norm_rope_kv: qkv_splits must be >= 1");
-    const bool vec = d % 4 == 0 && (rot == d || rot == 0) && ((uintptr_t)qkv & 7) == 0 && ((uintptr_t)q_out & 7) == 0 &&
+    const bool vec = d % 4 == 0 && (rot == d || rot == 0) && (!interleaved || rot == 0) && ((uintptr_t)qkv & 7) == 0 && ((uintptr_t)q_out & 7) == 0 &&
                      ((uintptr_t)k_pages & 7) == 0 && ((uintptr_t)v_pages & 7) == 0;
     if (qkv_splits > 1) {
-        QI_REQUIRE(vec, "qk_norm_rope_kv: partial sums as input need head_dim %% 4 == 0 and rotation over the whole head");
+        QI_REQUIRE(vec, "qk_norm_rope_kv: partial sums as input need head_dim %% 4 == 0 and a half-split rotation over the whole head");
         const size_t stride = (size_t)n_tokens * heads * d;
         QI_DISPATCH_DTYPE(dtype, T, {
             qi::launch(qk_norm_rope_kv_vec_kernel<float, T>, grid, dim3(kWarpsPerBlock * 32), 0, stream,
-                (const float*)qkv, qkv_splits, stride, (T*)q_out, q_gain, k_gain, eps, cos_t, sin_t, positions, token_req,
+                (const float*)qkv, qkv_splits, stride, (T*)q_out, q_gain, k_gain, eps, cos_t, sin_t, table_positions, positions, token_req,
                 block_table, max_blocks, page_size, num_pages, (T*)k_pages, (T*)v_pages, nq, nkv, d, status);
         });
         return qi::check_launch("qk_norm_rope_kv");
@@ -253,14 +277,14 @@ extern "C" int qi_qk_norm_rope_kv(const void* qkv, int qkv_splits, void* q_out, 
     if (vec) {
         QI_DISPATCH_DTYPE(dtype, T, {
             qi::launch(qk_norm_rope_kv_vec_kernel<T, T>, grid, dim3(kWarpsPerBlock * 32), 0, stream,
-                (const T*)qkv, 1, (size_t)0, (T*)q_out, q_gain, k_gain, eps, cos_t, sin_t, positions, token_req,
+                (const T*)qkv, 1, (size_t)0, (T*)q_out, q_gain, k_gain, eps, cos_t, sin_t, table_positions, positions, token_req,
                 block_table, max_blocks, page_size, num_pages, (T*)k_pages, (T*)v_pages, nq, nkv, d, status);
         });
         return qi::check_launch("qk_norm_rope_kv");
     }
     QI_DISPATCH_DTYPE(dtype, T, {
         qi::launch(qk_norm_rope_kv_kernel<T>, grid, dim3(kWarpsPerBlock * 32), 0, stream,
-            (const T*)qkv, (T*)q_out, q_gain, k_gain, eps, cos_t, sin_t, rot, positions, token_req,
+            (const T*)qkv, (T*)q_out, q_gain, k_gain, eps, cos_t, sin_t, rot, interleaved, table_positions, positions, token_req,
             block_table, max_blocks, page_size, num_pages, (T*)k_pages, (T*)v_pages, nq, nkv, d,
             status);
     });

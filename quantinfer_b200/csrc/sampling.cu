@@ -656,11 +656,13 @@ sample_cluster_kernel(const float* __restrict__ logits, int vocab, int per, cons
 
 // After a decode step that ran wholly on the device: the sampled tokens become the
 // next step's input, every request moves one position on, and its draw counter advances.
+// It writes the lengths that the next step's kernels read before their own wait for their
+// predecessor, so it does not release its successor early (no launch_dependents).
 __global__ void advance_decode_kernel(int* __restrict__ token_ids, int* __restrict__ positions,
                                       int* __restrict__ start_pos, int* __restrict__ kv_len,
                                       int* __restrict__ counter, const int* __restrict__ sampled,
                                       int* __restrict__ history, int b) {
-    qi::pdl_enter();
+    qi::pdl_wait();
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= b) return;
     const int t = sampled[i];

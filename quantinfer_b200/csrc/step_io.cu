@@ -16,9 +16,12 @@
 
 namespace {
 
+// This kernel does not release its successor early (no launch_dependents): the kernels of the
+// step read lengths and block tables before their own wait for their predecessor, which is only
+// safe once these arrays are complete, so the step's first kernel starts when this one has ended.
 __global__ void stage_step_kernel(const int* __restrict__ host_meta, int* __restrict__ meta, int n,
                                   const int* __restrict__ device_tokens, int n_tokens) {
-    qi::pdl_enter();
+    qi::pdl_wait();
     for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x)
         meta[i] = (device_tokens && i < n_tokens) ? device_tokens[i] : host_meta[i];
 }

@@ -39,8 +39,35 @@ def _align(n: int, a: int = 4) -> int:
     return (n + a - 1) // a * a
 
 
+class _OnlyOnTheDevice:
+    """Stands where a batch's host-side lists would be when the step may be replayed from a
+    CUDA graph: the graph keeps the kernels and their device arrays, whose contents change from
+    step to step, while a host list would stay what it was at capture. Any use raises."""
+
+    def _refuse(self, *a, **k):
+        from ..errors import QuantInferError
+
+        raise QuantInferError(
+            "this step may be replayed from a CUDA graph, so its host-side lists (h_q_start, h_start_pos, h_kv_len, "
+            "h_slot_ids) do not exist: read q_start, start_pos, kv_len and slot_ids on the device, or build the "
+            "engine with use_graphs=False")
+
+    __getitem__ = __iter__ = __len__ = __bool__ = _refuse
+
+
+ONLY_ON_THE_DEVICE = _OnlyOnTheDevice()
+
+
 @dataclass
 class StepBatch:
+    """What a part may read of a step. The device arrays (int32) are the interface that holds in
+    every step, replayed from a graph or not: `token_ids`, `positions`, `token_req` per token;
+    `q_start`, `start_pos`, `kv_len`, `slot_ids` per entry; `logit_rows`; `block_tables[group]`.
+    The counts `n_tokens`, `n_requests`, `n_logit_rows` and `all_decode` are fixed for a captured
+    step and may be used on the host. The `h_*` lists are a convenience for choosing a kernel or a
+    grid in a step that runs once; in a step that may be replayed they raise on use. `max_kv_len`
+    is an upper bound there (the context bucket), not the longest context."""
+
     n_tokens: int
     n_requests: int
     n_logit_rows: int

@@ -27,7 +27,7 @@ from ..config.spec import ModelSpec
 from ..errors import CacheError, KernelError, QuantInferError
 from ..parts import Runtime
 from ..weights.loader import load_folder
-from .batch import StepBatch, StepEntry, batch_from_packed, pack_batch
+from .batch import ONLY_ON_THE_DEVICE, StepBatch, StepEntry, batch_from_packed, pack_batch
 from .model import Model
 
 _DTYPES = {"float32": torch.float32, "fp32": torch.float32, "bfloat16": torch.bfloat16, "bf16": torch.bfloat16,
@@ -194,6 +194,9 @@ class Engine:
                                       len(self.cache.groups), self.cache.max_blocks)
             batch.max_kv_len = bound
             batch.extra["graph"] = True
+            # a replay runs the captured kernels on whatever the device arrays then hold; host copies
+            # would stay those of the capturing step, so parts get none
+            batch.h_q_start = batch.h_start_pos = batch.h_kv_len = batch.h_slot_ids = ONLY_ON_THE_DEVICE
             logits = self.model.forward(batch, self._views)   # eager: warms up and gives this step's result
             torch.cuda.synchronize()
             graph = torch.cuda.CUDAGraph()

@@ -23,8 +23,9 @@ STATUS_BAD_TOKEN = 1
 STATUS_BAD_PAGE = 2
 STATUS_NON_FINITE = 4
 STATUS_WAIT_TIMEOUT = 8
+STATUS_BAD_RANGE = 16
 
-ABI_VERSION = 5
+ABI_VERSION = 6
 
 
 def status_names(code: int) -> list:
@@ -32,7 +33,8 @@ def status_names(code: int) -> list:
     return [name for bit, name in ((STATUS_BAD_TOKEN, "a token id outside the vocabulary"),
                                    (STATUS_BAD_PAGE, "a position without a cache page"),
                                    (STATUS_NON_FINITE, "non-finite logits"),
-                                   (STATUS_WAIT_TIMEOUT, "a bounded wait inside a kernel ran out")) if code & bit]
+                                   (STATUS_WAIT_TIMEOUT, "a bounded wait inside a kernel ran out"),
+                                   (STATUS_BAD_RANGE, "a position beyond the rotation table or the key ranges of a launch")) if code & bit]
 
 _lib = None
 _lib_lock = threading.Lock()
@@ -213,8 +215,9 @@ def rope_table(inv_freq: torch.Tensor, max_positions: int):
 
 
 def qk_norm_rope_kv(qkv, q_out, q_gain, k_gain, eps, cos, sin, rotary_dim, positions, token_req,
-                    block_table, page_size, k_pages, v_pages, nq, nkv, d, status) -> None:
-    """Per-head q/k RMSNorm, rotation, and the write of k and v into cache pages.
+                    block_table, page_size, k_pages, v_pages, nq, nkv, d, status, interleaved: bool = False) -> None:
+    """Per-head q/k RMSNorm, rotation, and the write of k and v into cache pages. Pairs of the
+    rotation are (p, p + rotary_dim / 2), or (2p, 2p + 1) when `interleaved`.
 
     qkv [n, (nq + 2 nkv) d], or float32 [splits, n, (nq + 2 nkv) d] partial sums of a
     K-split projection (added here); q_out [n, nq d]; gains float32 [d] or None; cos/sin
@@ -258,7 +261,7 @@ def qk_norm_rope_kv(qkv, q_out, q_gain, k_gain, eps, cos, sin, rotary_dim, posit
         num_pages, max_blocks = k_pages.shape[0], block_table.shape[1]
     rc = library().qi_qk_norm_rope_kv(
         _ptr(qkv), splits, _ptr(q_out), _code(q_out), _ptr(q_gain), _ptr(k_gain), C.c_float(eps), _ptr(cos),
-        _ptr(sin), rotary_dim, table_positions, _ptr(positions), _ptr(token_req), _ptr(block_table),
+        _ptr(sin), rotary_dim, int(bool(interleaved)), table_positions, _ptr(positions), _ptr(token_req), _ptr(block_table),
         max_blocks, page_size, num_pages, _ptr(k_pages), _ptr(v_pages), n, nq, nkv, d, _ptr(status),
         _stream())
     _check(rc, "qk_norm_rope_kv")

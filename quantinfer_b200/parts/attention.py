@@ -77,7 +77,9 @@ class Attention(Part):
         pos = self.position
         q = torch.empty((n, self.nq * self.d), dtype=x.dtype, device=x.device)
         table = batch.block_tables[cache.group]
-        if kernels.gemm_qkv_rope_supported(n, x.shape[1], self.d, pos.rotary_dim if pos else 0, x.dtype, self.qkv.weight.dtype):
+        # the two fused kernels rotate whole heads in half-split pairs; any other rule takes the stand-alone kernel
+        whole_head = pos is None or (pos.rotary_dim == self.d and getattr(pos, "pairing", "half_split") == "half_split")
+        if whole_head and kernels.gemm_qkv_rope_supported(n, x.shape[1], self.d, pos.rotary_dim if pos else 0, x.dtype, self.qkv.weight.dtype):
             # many tokens: norm, rotation and the cache write ride in the projection's epilogue
             kernels.gemm_qkv_rope(
                 x, self.qkv.weight, q, self.q_gain, self.k_gain, self.spec.qk_norm_eps,
@@ -88,9 +90,9 @@ class Attention(Part):
             self.attend(q, out, batch, cache, table)
             return self.o(out, keep_partials=True)
         # K-split partial sums of the projection are added by the next kernel where it can take them
-        qkv = self.qkv(x, keep_partials=self.d % 4 == 0 and (pos is None or pos.rotary_dim == self.d))
+        qkv = self.qkv(x, keep_partials=self.d % 4 == 0 and whole_head)
         if (batch.all_decode and qkv.dtype in (torch.bfloat16, torch.float32) and x.dtype == torch.bfloat16
-                and (pos is None or pos.rotary_dim == self.d) and (qkv.dim() == 3 or qkv.dtype == torch.bfloat16)
+                and whole_head and (qkv.dim() == 3 or qkv.dtype == torch.bfloat16)
                 and kernels.attention_tma_supported(self.nq, self.nkv, self.d, cache.page_size, table.shape[1])):
             # one token per request: the attention kernel makes its queries and the new key and value itself
             out = torch.empty_like(q)
@@ -105,7 +107,8 @@ class Attention(Part):
             pos.cos if pos else None, pos.sin if pos else None, pos.rotary_dim if pos else 0,
             batch.positions, batch.token_req, table, cache.page_size,
             cache.k_pages if cache.writes else None, cache.v_pages if cache.writes else None,
-            self.nq, self.nkv, self.d, rt.status)
+            self.nq, self.nkv, self.d, rt.status,
+            interleaved=pos is not None and getattr(pos, "pairing", "half_split") == "interleaved")
         out = torch.empty_like(q)
         self.attend(q, out, batch, cache, table)
         return self.o(out, keep_partials=True)

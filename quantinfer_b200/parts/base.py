@@ -19,6 +19,27 @@ model it sits in. The interfaces:
 
 Kinds are registered per category with :func:`register_part`; a spec's `kind`
 selects the class, so a new part needs no change to existing files.
+
+What a mixer reads of the step. The batch's device arrays are its interface:
+`q_start[i] .. q_start[i + 1]` are entry i's rows of `x`, `start_pos[i]` the
+position of its first token, `kv_len[i]` its context after the step,
+`slot_ids[i]` its slot (the row of a `StateNeed` tensor), `token_req[t]` and
+`positions[t]` the entry and position of row t, `block_tables[cache.group]`
+its pages. Decode steps are replayed from CUDA graphs and launched before the
+host has read the step before, so a mixer must work from these arrays alone,
+with kernels or torch operations whose shapes depend only on the batch's counts
+(`n_tokens`, `n_requests`); the batch's host-side lists raise in such a step.
+State of fixed size is saved by the cache manager before a step and restored
+if the step fails; a mixer only reads and writes `cache.state[slot]`.
+
+Partial sums. A projection whose product was cut along K may hand back the
+32-bit partial sums `[splits, tokens, width]` instead of their sum, when asked
+to (`Linear.forward(keep_partials=True)`); a part does that only for its own
+output `delta`, which the block passes to the next norm. So a norm's `delta` is
+either `[tokens, hidden]` in the activation type or `[splits, tokens, hidden]`
+in float32, to be added in split order; `parts.norm.sum_partials` turns the
+second into the first for a norm that has no kernel for it. A part that never
+asks for partial sums never sees any.
 """
 
 from __future__ import annotations

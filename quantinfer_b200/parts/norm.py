@@ -16,6 +16,18 @@ from ..weights.loader import TensorNeed
 from .base import Part, register_part
 
 
+def sum_partials(delta, dtype=None):
+    """`delta` as one [tokens, hidden] tensor: the K-split partial sums [splits, tokens, hidden]
+    of a projection added in split order (32-bit), or `delta` itself when it is already whole.
+    For norms that have no kernel that adds the partial sums itself."""
+    if delta is None or delta.dim() == 2:
+        return delta
+    total = delta[0].clone()
+    for k in range(1, delta.shape[0]):
+        total += delta[k]
+    return total if dtype is None else total.to(dtype)
+
+
 class RMSNorm(Part):
     def __init__(self, spec, runtime):
         super().__init__(spec, runtime)

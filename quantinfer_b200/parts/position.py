@@ -1,13 +1,17 @@
-"""Rotary position encoding, half-split pairing.
+"""Rotary position encoding.
 
 For pair p < rotary_dim / 2 of a head: angle = position * theta^(-2p / rotary_dim),
-all in 32-bit; (x[p], x[p + rotary_dim/2]) is rotated by it
+all in 32-bit; the pair's two elements are rotated by it
 (crates/quantinfer-runtime/src/attention.rs:7-36, the angle :29-32;
-backends/cpu/src/backend.rs:240-280, the rotation :270-275). The part owns the
-table: inverse frequencies are computed once in 32-bit, the cos/sin table
-[max_positions, rotary_dim / 2] is built on the device, and the mixer's fused
-kernel looks positions up in it. Tables are shared between layers with the
-same spec.
+backends/cpu/src/backend.rs:240-280, the rotation :270-275). Which two elements
+form pair p is the spec's `pairing`: "half_split" (x[p], x[p + rotary_dim/2]),
+the reference's rule for this architecture, or "interleaved" (x[2p], x[2p + 1]),
+the order its converter writes for others
+(crates/quantinfer-format/src/gguf/layout.rs:52-55). The part owns the table
+and the rule: inverse frequencies are computed once in 32-bit, the cos/sin
+table [max_positions, rotary_dim / 2] is built on the device, and the mixer's
+kernel looks positions up in it and pairs as `pairing` says. Tables are shared
+between layers with the same angles.
 """
 
 from __future__ import annotations
@@ -25,6 +29,9 @@ class RopeHalfSplit(Part):
         if spec.rotary_dim % 2 or not 0 < spec.rotary_dim <= spec.head_dim:
             raise ConfigError(f"rotary_dim {spec.rotary_dim} must be even and within head_dim {spec.head_dim}")
         self.rotary_dim = spec.rotary_dim
+        self.pairing = getattr(spec, "pairing", "half_split")
+        if self.pairing not in ("half_split", "interleaved"):
+            raise ConfigError(f"rotary pairing {self.pairing!r} is not known (half_split or interleaved)")
         key = ("rope_half_split", spec.rotary_dim, float(spec.theta), spec.max_positions)
         if key not in runtime.shared:
             half = spec.rotary_dim // 2

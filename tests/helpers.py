@@ -45,9 +45,29 @@ TINY_CONFIGS = {
         max_position_embeddings=384, rms_norm_eps=2e-6, rope_theta=100000.0,
         tie_word_embeddings=True,
     ),
+    # the serving geometry: heads of 128 in groups of four, pages of 64, contexts beyond a thousand positions.
+    # In bfloat16 this is the configuration that runs the kernels the large models run: the tcgen05 prefill
+    # attention, the projection with the rotation in its epilogue (prompts of more than 256 tokens), the
+    # decode attention that makes its own queries, decode graphs per bucket of 512 positions.
+    "E": dict(
+        architectures=["Qwen3ForCausalLM"], model_type="qwen3",
+        vocab_size=1000, hidden_size=256, intermediate_size=512, num_hidden_layers=2,
+        num_attention_heads=8, num_key_value_heads=2, head_dim=128,
+        max_position_embeddings=1536, rms_norm_eps=1e-6, rope_theta=1000000.0,
+        tie_word_embeddings=False,
+    ),
 }
-SEEDS = {"A": 0, "B": 1, "C": 2, "D": 3}
-PAGE_SIZES = {"A": 16, "B": 8, "C": 32, "D": 16}
+SEEDS = {"A": 0, "B": 1, "C": 2, "D": 3, "E": 4}
+PAGE_SIZES = {"A": 16, "B": 8, "C": 32, "D": 16, "E": 64}
+
+# Bounds on |engine logits - plain float32 logits|. float32: only the order of sums and the device's exp, sin
+# and cos differ. bfloat16: activations are rounded to 8 bits of mantissa between kernels; the bound of a
+# configuration is about three times the worst error the engine shows on it over all four ways of cutting
+# (measured: see TOL_BF16_MEASURED), so a key that is wrong, missing or stale (which moves these logits by
+# several times the bound, checked in test_gpu_replay.py) cannot pass.
+TOL_F32 = 2e-5
+TOL_BF16_MEASURED = {"A": 1e-2, "B": 1e-2, "C": 1e-2, "D": 1e-2, "E": 1e-2}
+TOL_BF16 = {k: 3.0 * v for k, v in TOL_BF16_MEASURED.items()}
 
 
 def make_folder(path, name: str, dtype=torch.bfloat16) -> Path:

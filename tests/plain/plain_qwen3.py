@@ -52,9 +52,23 @@ def plain_linear(x: torch.Tensor, w_out_in: torch.Tensor) -> torch.Tensor:
     return x @ w_out_in.t()
 
 
+_rope_rows = {}   # (theta, head_dim, dtype) -> {position: (cos row, sin row)}: a row depends on nothing else
+
+
 def plain_rope_tables(theta: float, head_dim: int, positions, dtype=torch.float32):
     """exponent = 2p / d; angle = position * theta^(-exponent); cos and sin; all in `dtype`.
-    crates/quantinfer-runtime/src/attention.rs:7-36 (the three lines :29-32)."""
+    crates/quantinfer-runtime/src/attention.rs:7-36 (the three lines :29-32). Rows are kept
+    between calls (every layer and every request asks for the same ones)."""
+    rows = _rope_rows.setdefault((float(theta), int(head_dim), dtype), {})
+    missing = [p for p in positions if p not in rows]
+    if missing:
+        cos, sin = _plain_rope_rows(theta, head_dim, missing, dtype)
+        for i, p in enumerate(missing):
+            rows[p] = (cos[i], sin[i])
+    return torch.stack([rows[p][0] for p in positions]), torch.stack([rows[p][1] for p in positions])
+
+
+def _plain_rope_rows(theta: float, head_dim: int, positions, dtype):
     pairs = head_dim // 2
     cos = torch.empty((len(positions), pairs), dtype=dtype)
     sin = torch.empty((len(positions), pairs), dtype=dtype)

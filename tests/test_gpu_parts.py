@@ -179,7 +179,7 @@ class _SpecTools:
                          FeedForwardSpec(hidden, inter, "silu", p + "mlp."))
 
 
-def _engine(spec, dtype="float32", seed=0, **kw):
+def _engine(spec, dtype="float32", seed=0, max_tokens=512, **kw):
     from quantinfer_b200.engine import Engine, tensor_needs_of_spec
     from quantinfer_b200.weights import random_tensors
 
@@ -187,7 +187,7 @@ def _engine(spec, dtype="float32", seed=0, **kw):
     for k in tensors:
         if k.endswith("q_norm.weight"):
             tensors[k] = tensors[k] * 3.0
-    return Engine(spec, tensors, dtype=dtype, page_size=8, max_tokens=512, max_requests=4, **kw), tensors
+    return Engine(spec, tensors, dtype=dtype, page_size=8, max_tokens=max_tokens, max_requests=4, **kw), tensors
 
 
 def _plain_model(tensors, spec, ids):
@@ -294,7 +294,9 @@ def _register_toy():
 
     class ToyRunningMean(Part):
         """y_t = W (s_t), s_t = decay * s_{t-1} + x_t: a recurrence over the sequence whose state s lives
-        in the request's slot. Written with torch operations: it is a test double, not a kernel."""
+        in the request's slot. Written with torch operations on the batch's device arrays only (no host
+        list, no synchronisation, shapes fixed by the batch's counts), so that it also runs inside a
+        captured step: it is a test double, not a kernel."""
 
         @classmethod
         def needs_of_spec(cls, spec):
@@ -307,27 +309,32 @@ def _register_toy():
             return StateNeed((self.spec.hidden_size,), torch.float32)
 
         def forward(self, x, batch, cache):
-            out = torch.empty_like(x, dtype=torch.float32)
-            for i in range(batch.n_requests):
-                a, z, slot = batch.h_q_start[i], batch.h_q_start[i + 1], batch.h_slot_ids[i]
-                s = cache.state[slot].clone()
-                for t in range(a, z):
-                    s = self.spec.decay * s + x[t].float()
-                    out[t] = s
-                cache.state[slot] = s
-            return (out @ self.w.t()).to(x.dtype)
+            n, decay = x.shape[0], self.spec.decay
+            xf = x.float()
+            req, q0, slots = batch.token_req.long(), batch.q_start.long(), batch.slot_ids.long()
+            local = torch.arange(n, device=x.device) - q0[req]            # place of a row within its entry
+            gap = local[:, None] - local[None, :]
+            earlier = (req[:, None] == req[None, :]) & (gap >= 0)
+            weights = torch.where(earlier, torch.pow(decay, gap.clamp(min=0).float()), torch.zeros((), device=x.device))
+            carried = torch.pow(decay, (local + 1).float())[:, None] * cache.state[slots[req]]
+            s = weights @ xf + carried                                     # s_t for every row
+            cache.state.index_copy_(0, slots, s[q0[1:] - 1])              # each entry's last row is its new state
+            return (s @ self.w.t()).to(x.dtype)
 
     register_part("mixer", "toy_running_mean", ToyRunningMean)
+
+
+def _toy_state_engine(**kw):
+    _register_toy()
+    T = _SpecTools
+    layers = [T.layer(0), T.layer(1, mixer=ToyStateSpec(48, 0.9, "l1.toy.")), T.layer(2)]
+    return _engine(T.tiny_spec(layers), **kw)
 
 
 def test_toy_mixer_with_state_is_registered_built_and_stepped():
     from quantinfer_b200.engine import StepEntry
 
-    _register_toy()
-    T = _SpecTools
-    layers = [T.layer(0), T.layer(1, mixer=ToyStateSpec(48, 0.9, "l1.toy.")), T.layer(2)]
-    spec = T.tiny_spec(layers)
-    eng, tensors = _engine(spec, use_graphs=False)
+    eng, tensors = _toy_state_engine(use_graphs=False)
     assert "l1.toy.mix.weight" in tensors and len(eng.cache.groups) == 1 and list(eng.cache.states) == [1]
     ids_a = [int(x) for x in torch.randint(0, 97, (40,))]
     ids_b = [int(x) for x in torch.randint(0, 97, (25,))]
@@ -339,6 +346,19 @@ def test_toy_mixer_with_state_is_registered_built_and_stepped():
         return out
 
     ref_a, ref_b = whole(ids_a), whole(ids_b)
+    # the recurrence, token by token on the host, against the part's one-pass form
+    x = torch.randn(7, 48)
+    s, rows = torch.zeros(48), []
+    for t in range(7):
+        s = 0.9 * s + x[t]
+        rows.append(s)
+    eng.open("p")
+    from quantinfer_b200.engine.batch import StepEntry as _E
+    batch = eng.make_batch([_E("p", [0] * 7, [])])
+    mixer = eng.model.blocks[1].mixer
+    got = mixer.forward(x.to(DEV), batch, eng._views[1]).cpu()
+    eng.close("p")
+    assert float((got - torch.stack(rows) @ tensors["l1.toy.mix.weight"].float().t()).abs().max()) < 1e-5
     # the same two requests interleaved in portions; slots are reused, so a state that
     # was not reset at open or that leaked between requests would show
     eng.open("a"), eng.open("b")
@@ -352,6 +372,87 @@ def test_toy_mixer_with_state_is_registered_built_and_stepped():
     assert float((torch.cat(got_a) - ref_a).abs().max()) < 2e-5
     assert float((torch.cat(got_b) - ref_b).abs().max()) < 2e-5
     assert not torch.allclose(ref_a[5], whole(ids_a[5:])[0])       # the recurrence does depend on its past
+
+
+def test_toy_mixer_with_state_in_captured_steps_and_steps_that_run_ahead():
+    """The stateful mixer under CUDA graphs: decode steps of one batch size are one captured graph,
+    replayed for other requests in other slots and in another order of slots; and through the scheduler
+    with steps launched ahead of the host. Both against the same engine without graphs."""
+    import quantinfer_b200
+    from quantinfer_b200.engine import StepEntry
+    from quantinfer_b200.errors import QuantInferError
+
+    prompts = {k: [int(x) for x in torch.randint(0, 97, (n,))] for k, n in (("a", 9), ("b", 21), ("c", 14), ("d", 5))}
+    feed = [int(x) for x in torch.randint(0, 97, (12,))]
+
+    def script(eng):
+        rows, slots = [], []
+        for pair in (("a", "b"), ("c", "d")):        # the second pair takes the first pair's slots, the other way round
+            for rid in pair:
+                eng.open(rid)
+                rows.append(eng.step([StepEntry(rid, prompts[rid], [len(prompts[rid]) - 1])]).cpu())
+            slots.append([eng.cache.get(rid).slot for rid in pair])
+            for t in feed:
+                rows.append(eng.step([StepEntry(rid, [t], [0]) for rid in pair]).cpu())
+            for rid in pair:
+                eng.close(rid)
+        return torch.cat(rows), slots
+
+    plain_eng, _ = _toy_state_engine(use_graphs=False)
+    graph_eng, _ = _toy_state_engine(use_graphs=True)
+    ref, _ = script(plain_eng)
+    got, slots = script(graph_eng)
+    assert slots[0] == slots[1][::-1]                                  # same slots, other order
+    assert len(graph_eng._graphs) == 1                                 # every decode step of both pairs replayed one graph
+    assert float((got - ref).abs().max()) < 1e-5
+    # a part that reads the host-side lists in such a step is told so
+    g = next(iter(graph_eng._graphs.values()))
+    with pytest.raises(QuantInferError, match="on the device"):
+        g["batch"].h_slot_ids[0]
+    # through the scheduler: four prompts on two sequence slots, steps that run ahead
+    outs = []
+    for eng, ahead in ((plain_eng, False), (graph_eng, True)):
+        m = quantinfer_b200.Model.from_engine(eng, max_batch_tokens=32, run_ahead=ahead)
+        outs.append(m.generate_batch(list(prompts.values()), max_new_tokens=20, eos_token_id=None))
+        if ahead:
+            assert m.last_scheduler.steps_ahead > 10
+        eng.cache.check_invariants()
+    assert outs[0] == outs[1]
+
+
+def test_state_of_fixed_size_is_rolled_back_when_a_step_fails():
+    """A step that fails gives a request's fixed-size state back as it was: once when a second request of
+    the step finds no page (nothing ran), once when a kernel flags a block table entry that holds no page
+    (the layers after it ran, and the stateful mixer overwrote its state). The request then goes on and
+    equals the run that never failed."""
+    from quantinfer_b200.engine import StepEntry
+    from quantinfer_b200.errors import OutOfPages, QuantInferError
+
+    eng, _ = _toy_state_engine(use_graphs=False, max_tokens=64)      # eight pages of eight positions
+    ids = [int(x) for x in torch.randint(0, 97, (30,))]
+    eng.open("w")
+    ref = eng.step([StepEntry("w", ids, list(range(30)))]).cpu()
+    eng.close("w")
+    eng.open("r"), eng.open("big")
+    rows = [eng.step([StepEntry("r", ids[:12], list(range(12)))]).cpu()]
+    state = eng.cache.states[1][eng.cache.get("r").slot].clone()
+    with pytest.raises(OutOfPages):          # r holds two pages and takes a third; the second entry wants eight
+        eng.step([StepEntry("r", ids[12:20], list(range(8))), StepEntry("big", [1] * 60, [])])
+    eng.cache.check_invariants()
+    assert eng.length("r") == 12 and torch.equal(eng.cache.states[1][eng.cache.get("r").slot], state)
+    # a block table entry without a page: the attention kernels set the status bit and skip the access
+    slot = eng.cache.get("r").slot
+    page = int(eng.cache.host_tables[0][slot, 0])
+    eng.cache.host_tables[0][slot, 0] = -1
+    with pytest.raises(QuantInferError, match="cache page"):
+        eng.step([StepEntry("r", ids[12:20], list(range(8)))])
+    eng.cache.host_tables[0][slot, 0] = page
+    assert eng.length("r") == 12 and torch.equal(eng.cache.states[1][slot], state)
+    rows.append(eng.step([StepEntry("r", ids[12:20], list(range(8)))]).cpu())
+    rows.append(eng.step([StepEntry("r", ids[20:], list(range(10)))]).cpu())
+    eng.close("r"), eng.close("big")
+    eng.cache.check_invariants()
+    assert float((torch.cat(rows) - ref).abs().max()) < 2e-5
 
 
 # ------------------------------------------------------------------ a toy feed-forward with routing, another position encoding
@@ -467,6 +568,138 @@ def test_toy_feed_forward_with_routing_and_another_position_encoding():
     ref = plain_linear(plain_rms_norm(h, w["final.weight"], spec.final_norm.eps), w["emb.weight"])
     assert len(used) > 1, "the router sent every token to one expert: the test shows nothing"
     assert float((got - ref).abs().max()) < 5e-5
+
+
+def _rotate_interleaved(x, cos, sin, rot):
+    """Pairs (2p, 2p + 1) of the first `rot` elements of each head turn by the angle of pair p; the rest
+    passes. x [tokens, heads, d]; cos, sin [tokens, rot / 2]."""
+    out = x.clone()
+    a, b = x[..., 0:rot:2], x[..., 1:rot:2]
+    c, s_ = cos[:, None, :], sin[:, None, :]
+    out[..., 0:rot:2] = a * c - b * s_
+    out[..., 1:rot:2] = a * s_ + b * c
+    return out
+
+
+@pytest.mark.parametrize("dtype, d, rot, n_tok", [("float32", 16, 16, 50), ("float32", 24, 12, 50), ("bfloat16", 128, 128, 300)])
+def test_interleaved_pairs_are_a_parameter_of_the_position_encoding(dtype, d, rot, n_tok):
+    """A position spec with pairing "interleaved" (and, in one case, a rotation over half the head): the
+    mixer's kernels pair (2p, 2p + 1). In bfloat16 at head size 128 with a prompt of 300 tokens the fused
+    projection and the fused decode attention, which only know the half-split rule, are passed over."""
+    from quantinfer_b200.config import AttentionSpec, PositionSpec
+
+    T = _SpecTools
+    hidden = 64
+    pos = PositionSpec(d, rot, 1e4, 512, pairing="interleaved")
+    layers = [T.layer(i, hidden=hidden, mixer=AttentionSpec(hidden, 2, 1, d, pos, qk_norm=True, prefix=f"l{i}.attn.")) for i in range(2)]
+    from quantinfer_b200.config import EmbeddingSpec, HeadSpec, LayerCall, ModelSpec, NormSpec
+    spec = ModelSpec("Test", 97, hidden, 512, EmbeddingSpec(97, hidden, "emb."), tuple(layers),
+                     (LayerCall(0, 0), LayerCall(1, 1)), NormSpec(hidden, 1e-6, "final."), HeadSpec(97, hidden, True, "head."))
+    eng, tensors = _engine(spec, dtype=dtype, max_tokens=1024)
+    ids = [int(x) for x in torch.randint(0, 97, (n_tok,))]
+    cuts = (n_tok - 9, 1, 1, 5, 2)
+    got = _run_in_portions(eng, ids, cuts)
+
+    w = {k: v.float() for k, v in tensors.items()}
+    h = plain_embedding(w["emb.weight"], ids)
+    cos, sin = plain_rope_tables(1e4, rot, list(range(n_tok)))
+    for L in spec.layers:
+        a, p = L.mixer, L.mixer.prefix
+        n = plain_rms_norm(h, w[L.mixer_norm.prefix + "weight"], L.mixer_norm.eps)
+        q = plain_rms_norm(plain_linear(n, w[p + "q_proj.weight"]).reshape(n_tok, a.num_heads, d), w[p + "q_norm.weight"], a.qk_norm_eps)
+        k = plain_rms_norm(plain_linear(n, w[p + "k_proj.weight"]).reshape(n_tok, a.num_kv_heads, d), w[p + "k_norm.weight"], a.qk_norm_eps)
+        v = plain_linear(n, w[p + "v_proj.weight"]).reshape(n_tok, a.num_kv_heads, d)
+        att = plain_gqa_attention(_rotate_interleaved(q, cos, sin, rot), _rotate_interleaved(k, cos, sin, rot), v, None)
+        h = h + plain_linear(att.reshape(n_tok, a.num_heads * d), w[p + "o_proj.weight"])
+        n = plain_rms_norm(h, w[L.ffn_norm.prefix + "weight"], L.ffn_norm.eps)
+        h = h + plain_feed_forward(n, w, L.ffn.prefix)
+    ref = plain_linear(plain_rms_norm(h, w["final.weight"], spec.final_norm.eps), w["emb.weight"])
+    assert float((got - ref).abs().max()) < (5e-5 if dtype == "float32" else 4e-2)
+    # the half-split rule on the same weights gives other logits: the parameter does reach the kernel
+    half = dataclasses.replace(pos, pairing="half_split")
+    spec_h = dataclasses.replace(spec, layers=tuple(dataclasses.replace(L, mixer=dataclasses.replace(L.mixer, position=half)) for L in layers))
+    eng_h, _ = _engine(spec_h, dtype=dtype, max_tokens=1024)
+    other = _run_in_portions(eng_h, ids, cuts)
+    assert float((other - ref).abs().max()) > 10 * (5e-5 if dtype == "float32" else 4e-2)
+
+
+@dataclasses.dataclass(frozen=True)
+class ToyCenteredNormSpec:
+    size: int
+    eps: float
+    prefix: str = ""
+    kind: str = "toy_centered_norm"
+
+
+def test_a_toy_norm_takes_partial_sums_through_the_documented_contract():
+    """Another norm kind (mean removed, then scaled), registered here, in a bfloat16 model whose
+    projections hand K-split partial sums to the norm that follows: the norm adds them with the
+    package's helper and needs no kernel of its own for them."""
+    from quantinfer_b200.config import LayerSpec
+    from quantinfer_b200.parts import Part, register_part
+    from quantinfer_b200.parts.norm import sum_partials
+    from quantinfer_b200.weights import TensorNeed
+
+    seen = {"partials": 0, "whole": 0}
+
+    class ToyCenteredNorm(Part):
+        @classmethod
+        def needs_of_spec(cls, spec):
+            return {spec.prefix + "weight": TensorNeed((spec.size,), "gain", "gain")}
+
+        def load(self, tensors):
+            self.gain = self._gain(tensors[self.spec.prefix + "weight"])
+
+        def forward(self, resid, delta, rows=None, write_resid=True):
+            if delta is not None:
+                seen["partials" if delta.dim() == 3 else "whole"] += 1
+                x = resid + sum_partials(delta).float()
+                if write_resid and rows is None:
+                    resid.copy_(x)
+            else:
+                x = resid
+            if rows is not None:
+                x = x[rows.long()]
+            x = x - x.mean(dim=-1, keepdim=True)
+            y = x * torch.rsqrt((x * x).mean(dim=-1, keepdim=True) + self.spec.eps) * self.gain
+            return y.to(self.runtime.dtype)
+
+        __call__ = forward
+
+    register_part("norm", "toy_centered_norm", ToyCenteredNorm)
+    T = _SpecTools
+    hidden = 256
+    base = [T.layer(i, hidden=hidden, nq=4, nkv=2, d=64, inter=512) for i in range(2)]
+    layers = [LayerSpec(base[0].mixer_norm, base[0].mixer, ToyCenteredNormSpec(hidden, 1e-5, "l0.n2."), base[0].ffn),
+              LayerSpec(ToyCenteredNormSpec(hidden, 1e-5, "l1.n1."), base[1].mixer, base[1].ffn_norm, base[1].ffn)]
+    spec = T.tiny_spec(layers, hidden=hidden)
+    eng, tensors = _engine(spec, dtype="bfloat16", use_graphs=False)
+    ids = [int(x) for x in torch.randint(0, 97, (40,))]
+    got = _run_in_portions(eng, ids, (30, 1, 1, 1, 7))
+    assert seen["partials"] > 0, "no projection of this model was cut along K: the test shows nothing"
+
+    w = {k: v.float() for k, v in tensors.items()}
+    h = plain_embedding(w["emb.weight"], ids)
+    n_tok, d = len(ids), 64
+
+    def norm(x, ns):
+        if ns.kind == "rmsnorm":
+            return plain_rms_norm(x, w[ns.prefix + "weight"], ns.eps)
+        x = x - x.mean(dim=-1, keepdim=True)
+        return x * torch.rsqrt((x * x).mean(dim=-1, keepdim=True) + ns.eps) * w[ns.prefix + "weight"]
+
+    cos, sin = plain_rope_tables(1e4, d, list(range(n_tok)))
+    for L in spec.layers:
+        a, p = L.mixer, L.mixer.prefix
+        n = norm(h, L.mixer_norm)
+        q = plain_rms_norm(plain_linear(n, w[p + "q_proj.weight"]).reshape(n_tok, a.num_heads, d), w[p + "q_norm.weight"], a.qk_norm_eps)
+        k = plain_rms_norm(plain_linear(n, w[p + "k_proj.weight"]).reshape(n_tok, a.num_kv_heads, d), w[p + "k_norm.weight"], a.qk_norm_eps)
+        v = plain_linear(n, w[p + "v_proj.weight"]).reshape(n_tok, a.num_kv_heads, d)
+        att = plain_gqa_attention(plain_apply_rope(q, cos, sin), plain_apply_rope(k, cos, sin), v, None)
+        h = h + plain_linear(att.reshape(n_tok, a.num_heads * d), w[p + "o_proj.weight"])
+        h = h + plain_feed_forward(norm(h, L.ffn_norm), w, L.ffn.prefix)
+    ref = plain_linear(plain_rms_norm(h, w["final.weight"], spec.final_norm.eps), w["emb.weight"])
+    assert float((got - ref).abs().max()) < 4e-2
 
 
 def test_shared_cache_and_window_through_the_tensor_core_kernels():

@@ -10,11 +10,14 @@ from pathlib import Path
 import pytest
 import torch
 
-from helpers import random_tokens
+from helpers import TOL_F32, random_tokens
 from trace_tools import (mixed_trace, plain_rows, portions_trace, round64, run_trace_engine, tail_trace, whole_trace,
                          worst_diff)
 
 pytestmark = pytest.mark.gpu
+
+# the bound of the fixed configurations, for logits of a few units (larger logits scale it, see below)
+TOL_BF16_RANDOM = 3e-2
 
 
 def _case(tmp_path, seed: int, long: bool):
@@ -36,13 +39,16 @@ def _case(tmp_path, seed: int, long: bool):
     folder = write_model_folder(Path(tmp_path) / "m", config_from_dict(cfg), seed, torch.bfloat16)
     lens = ([rng.randint(257, 900) for _ in range(rng.randint(1, 2))] if long
             else [rng.randint(2, 200) for _ in range(rng.randint(1, 5))])
+    if long:
+        lens += [rng.randint(2, 200) for _ in range(3)]      # so that the long ones share steps with others
     requests = {f"r{i}": random_tokens(n, cfg["vocab_size"], seed=seed * 10 + i) for i, n in enumerate(lens)}
     expect = plain_rows(folder, requests)
     # the tolerances of the fixed configurations hold for logits of a few units; larger logits scale them
     scale = max(1.0, max(float(abs(v).max()) for v in expect.values()) / 3.0)
     room = sum(round64(n) + page for n in lens) + 256
-    for dtype, tol in (("float32", 2e-5), ("bfloat16", 3e-2)):
-        mixed, peak = mixed_trace(requests, seed=seed)
+    sizes = (2, 3, 17, 64, 130, 300) if long else (2, 3, 5, 8, 13, 16, 17, 30)
+    for dtype, tol in (("float32", TOL_F32), ("bfloat16", TOL_BF16_RANDOM)):
+        mixed, peak = mixed_trace(requests, seed=seed, max_tokens=round64(max(lens)) + 256 if len(lens) > 2 else None, sizes=sizes)
         for kind, steps, max_tokens in (("whole", whole_trace(requests), room), ("tail", tail_trace(requests, 32), room),
                                         ("portions", portions_trace(requests, seed=seed), room),
                                         ("mixed", mixed, peak + 4 * page)):

@@ -55,7 +55,8 @@ def portions_trace(requests: dict, seed: int = 0, sizes=(7, 2, 16, 3, 2, 31, 5, 
     return steps
 
 
-def mixed_trace(requests: dict, seed: int = 0, max_live: int = 4, decode_tail: int = 6, max_tokens: int | None = None):
+def mixed_trace(requests: dict, seed: int = 0, max_live: int = 4, decode_tail: int = 6, max_tokens: int | None = None,
+                sizes=(2, 3, 5, 8, 13, 16, 17, 30)):
     """Up to `max_live` requests at a time, portions of some beside single tokens
     of others; a request may sit a step out. New requests start as earlier ones
     end, so that their pages are used again. Returns (steps, peak rounded tokens)."""
@@ -81,7 +82,7 @@ def mixed_trace(requests: dict, seed: int = 0, max_live: int = 4, decode_tail: i
             if left <= decode_tail:
                 n = 1
             else:
-                n = min(rng.choice([2, 3, 5, 8, 13, 16, 17, 30]), left - decode_tail)
+                n = min(rng.choice(list(sizes)), left - decode_tail)
             entries.append({"id": rid, "tokens": toks[pos[rid]:pos[rid] + n], "want": list(range(n))})
             pos[rid] += n
             if pos[rid] == len(toks):
@@ -112,7 +113,9 @@ def collect(steps: list, outputs: dict) -> dict:
     return rows
 
 
-def run_trace_engine(folder, dtype: str, steps: list, max_tokens: int, page_size: int) -> dict:
+def run_trace_engine(folder, dtype: str, steps: list, max_tokens: int, page_size: int, after_step=None) -> dict:
+    """Replays `steps` through an engine of this process. `after_step(engine)` runs between steps
+    (a test uses it to break the cache on purpose)."""
     from quantinfer_b200.engine import Engine, StepEntry
 
     eng = Engine.from_folder(folder, dtype=dtype, page_size=page_size, max_tokens=max_tokens, max_requests=8, check_finite=True)
@@ -131,6 +134,8 @@ def run_trace_engine(folder, dtype: str, steps: list, max_tokens: int, page_size
             eng.close(rid)
             live.discard(rid)
         eng.cache.check_invariants()
+        if after_step is not None:
+            after_step(eng)
     assert not eng.cache.requests
     return collect(steps, outputs)
 
