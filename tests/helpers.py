@@ -66,8 +66,13 @@ PAGE_SIZES = {"A": 16, "B": 8, "C": 32, "D": 16, "E": 64}
 # (measured: see TOL_BF16_MEASURED), so a key that is wrong, missing or stale (which moves these logits by
 # several times the bound, checked in test_gpu_replay.py) cannot pass.
 TOL_F32 = 2e-5
-TOL_BF16_MEASURED = {"A": 1e-2, "B": 1e-2, "C": 1e-2, "D": 1e-2, "E": 1e-2}
+TOL_BF16_MEASURED = {"A": 3.3e-3, "B": 4.8e-3, "C": 7.7e-3, "D": 6.9e-3, "E": 8.1e-3}
 TOL_BF16 = {k: 3.0 * v for k, v in TOL_BF16_MEASURED.items()}
+# The sharpened copies (q_norm gains tripled, test_gpu_replay.py) round worse, because their softmax turns a
+# score's rounding error into a larger change of weight; measured the same way. Two pages of a request's block
+# table swapped change these logits by 0.12 (A) to 2.0 (E), four to seventeen times the bound.
+TOL_BF16_SHARP_MEASURED = {"A": 6.8e-3, "B": 2.7e-2, "C": 2.9e-2, "D": 2.3e-2, "E": 4.0e-2}
+TOL_BF16_SHARP = {k: 3.0 * v for k, v in TOL_BF16_SHARP_MEASURED.items()}
 
 
 def make_folder(path, name: str, dtype=torch.bfloat16) -> Path:

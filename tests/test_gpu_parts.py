@@ -668,8 +668,8 @@ def test_a_toy_norm_takes_partial_sums_through_the_documented_contract():
 
     register_part("norm", "toy_centered_norm", ToyCenteredNorm)
     T = _SpecTools
-    hidden = 256
-    base = [T.layer(i, hidden=hidden, nq=4, nkv=2, d=64, inter=512) for i in range(2)]
+    hidden = 128     # a product is cut along K from 1,024 up: the output projection (8 heads of 128) and the down projection
+    base = [T.layer(i, hidden=hidden, nq=8, nkv=2, d=128, inter=1024) for i in range(2)]
     layers = [LayerSpec(base[0].mixer_norm, base[0].mixer, ToyCenteredNormSpec(hidden, 1e-5, "l0.n2."), base[0].ffn),
               LayerSpec(ToyCenteredNormSpec(hidden, 1e-5, "l1.n1."), base[1].mixer, base[1].ffn_norm, base[1].ffn)]
     spec = T.tiny_spec(layers, hidden=hidden)
@@ -680,7 +680,7 @@ def test_a_toy_norm_takes_partial_sums_through_the_documented_contract():
 
     w = {k: v.float() for k, v in tensors.items()}
     h = plain_embedding(w["emb.weight"], ids)
-    n_tok, d = len(ids), 64
+    n_tok, d = len(ids), 128
 
     def norm(x, ns):
         if ns.kind == "rmsnorm":

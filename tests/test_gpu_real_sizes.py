@@ -47,3 +47,117 @@ def test_one_layer_at_8b_sizes(folder, dtype):
     tol = 1e-4 if dtype == "float32" else 5e-2
     diff = (got - expect).abs().max(dim=1).values
     assert float(diff.max()) <= tol, (diff.tolist(), float(expect.abs().max()))
+
+
+# ---------------------------------------------------------------- the whole model, all 36 layers
+
+
+class _WidenedOnUse(dict):
+    """Weights kept as stored (bfloat16) on the host and widened to float32 when a plain function asks for
+    one: the 36-layer model is 16 GB as stored and would be 33 GB widened at once."""
+
+    def __getitem__(self, name):
+        return dict.__getitem__(self, name).float()
+
+
+@pytest.fixture(scope="module")
+def whole_8b():
+    """Qwen3-8B sizes at full depth with seed 8: the tensors on the device (bfloat16) and their host copies."""
+    from quantinfer_b200.config import config_from_dict
+    from quantinfer_b200.engine import tensor_needs_of_spec
+    from quantinfer_b200.weights import random_tensors
+
+    cfg_d = dict(CONFIG_8B_ONE_LAYER, num_hidden_layers=36)
+    config = config_from_dict(cfg_d)
+    spec = config.to_model_spec()
+    tensors = random_tensors(tensor_needs_of_spec(spec), 8, torch.bfloat16, device="cuda:0")
+    host = _WidenedOnUse({k: v.cpu() for k, v in tensors.items()})
+    plain_cfg = dict(cfg_d)
+    return config, spec, tensors, host, plain_cfg
+
+
+def _engine_8b(whole_8b, dtype):
+    from quantinfer_b200.engine import Engine
+
+    config, spec, tensors, _, _ = whole_8b
+    return Engine(spec, tensors, dtype=dtype, page_size=64, max_tokens=1024, max_requests=4, max_seq_len=4096, config=config)
+
+
+def _families_8b(requests):
+    from trace_tools import mixed_trace, portions_trace, tail_trace, whole_trace
+
+    mixed, peak = mixed_trace(requests, seed=5, max_live=3, sizes=(2, 3, 7, 16, 31, 64))
+    return {"whole": whole_trace(requests), "tail": tail_trace(requests, 32), "portions": portions_trace(requests),
+            "mixed": mixed}
+
+
+def _replay(eng, steps):
+    from quantinfer_b200.engine import StepEntry
+    from trace_tools import collect
+
+    live, outputs = set(), {}
+    for st in steps:
+        entries = []
+        for e in st["entries"]:
+            if e["id"] not in live:
+                eng.open(e["id"])
+                live.add(e["id"])
+            entries.append(StepEntry(e["id"], e["tokens"], e["want"]))
+        logits = eng.step(entries)
+        if logits.shape[0]:
+            outputs[st["step"]] = logits.cpu().numpy()
+        for rid in st["end"]:
+            eng.close(rid)
+            live.discard(rid)
+    eng.cache.check_invariants()
+    return collect(steps, outputs)
+
+
+def test_whole_model_at_8b_sizes_under_every_cut(whole_8b):
+    """The 36-layer model in float32 against the plain implementation (its 36 layers run on the host's
+    cores), for one request of 300 tokens and two shorter ones: whole, with the last 32 tokens one by one,
+    in portions down to two tokens, and mixed. The bound is the reference's own gate for its float32
+    logits against an independent implementation, max abs 1e-3
+    (crates/quantinfer-runtime/tests/qwen3_conformance.rs:60-66). Then the same traces in bfloat16 against
+    the float32 engine's rows, and greedy and sampled generation twice under one seed
+    (qwen3_conformance.rs:197-198)."""
+    import numpy as np
+
+    from trace_tools import worst_diff
+
+    config, spec, tensors, host, plain_cfg = whole_8b
+    requests = {"long": random_tokens(300, 151936, seed=31), "mid": random_tokens(70, 151936, seed=32),
+                "short": random_tokens(9, 151936, seed=33)}
+    expect = {}
+    for rid, toks in requests.items():
+        logits = plain_forward(host, plain_cfg, toks).numpy()
+        for pos in range(len(toks)):
+            expect[(rid, pos)] = logits[pos]
+    families = _families_8b(requests)
+    eng = _engine_8b(whole_8b, "float32")
+    rows32 = {}
+    for kind, steps in families.items():
+        rows32[kind] = _replay(eng, steps)
+        worst, where = worst_diff(rows32[kind], expect)
+        assert worst <= 1e-3, f"float32 {kind}: {worst} at {where}"
+    # the float32 path does not depend on the cut beyond rounding: far inside the bound above
+    for kind in ("tail", "portions", "mixed"):
+        worst, where = worst_diff(rows32[kind], rows32["whole"])
+        assert worst <= 2e-5, f"float32 {kind} against whole: {worst} at {where}"
+    del eng
+    torch.cuda.empty_cache()
+    eng = _engine_8b(whole_8b, "bfloat16")
+    spread = float(np.std(np.stack([expect[("long", p)] for p in range(0, 300, 50)])))
+    for kind, steps in families.items():
+        worst, where = worst_diff(_replay(eng, steps), rows32["whole"])
+        # logits here have a spread of about one; bfloat16 through 36 layers stays within a tenth of it
+        assert worst <= 0.1 * max(spread, 1.0), f"bfloat16 {kind}: {worst} at {where} (spread {spread})"
+    # generation twice under one seed
+    import quantinfer_b200
+
+    m = quantinfer_b200.Model.from_engine(eng, max_batch_tokens=256)
+    prompts = [requests["mid"], requests["short"]]
+    for kw in (dict(), dict(temperature=0.8, top_k=50, seed=3)):
+        a = m.generate_batch(prompts, max_new_tokens=12, eos_token_id=None, **kw)
+        b = m.generate_batch(prompts, max_new_tokens=12, eos_token_id=None, **kw)
+        assert a == b and all(len(t) == 12 for t in a)

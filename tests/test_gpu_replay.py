@@ -13,7 +13,7 @@ holds, and demands that the comparison then fails."""
 
 import pytest
 
-from helpers import PAGE_SIZES, TOL_BF16, TOL_F32, random_tokens, vocab_of
+from helpers import PAGE_SIZES, TOL_BF16, TOL_BF16_SHARP, TOL_F32, random_tokens, vocab_of
 from trace_tools import (mixed_trace, plain_rows, portions_trace, round64, run_trace_cli, run_trace_engine,
                          tail_trace, whole_trace, worst_diff)
 
@@ -29,8 +29,10 @@ _plain_cache = {}
 _sharp_folders = {}
 
 
-def tol(name, dtype):
-    return TOL_F32 if dtype == "float32" else TOL_BF16[name]
+def tol(name, dtype, sharp=False):
+    if dtype == "float32":
+        return TOL_F32
+    return TOL_BF16_SHARP[name] if sharp else TOL_BF16[name]
 
 
 def _requests(folder, name):
@@ -111,7 +113,7 @@ def test_replay_with_peaked_attention(tiny_folders, tmp_path_factory, name, dtyp
     steps, max_tokens = _family(name, _requests(folder, name), family, seed=11)
     got = run_trace_engine(folder, dtype, steps, max_tokens, PAGE_SIZES[name])
     worst, where = worst_diff(got, _expect(folder, name, key="sharp" + name))
-    assert worst <= tol(name, dtype), f"worst difference {worst} at (request, position) {where}"
+    assert worst <= tol(name, dtype, sharp=True), f"worst difference {worst} at (request, position) {where}"
 
 
 def _swap_two_pages(engine, state):
@@ -146,8 +148,8 @@ def test_a_wrong_page_in_a_block_table_shows(tiny_folders, tmp_path_factory, nam
     assert state.get("done") is not None, "no request ever held two pages with the last partly filled"
     expect = _expect(folder, name, key="sharp" + name)
     worst, where = worst_diff(got, expect)
-    assert worst > tol(name, "bfloat16"), f"two swapped pages of request {state['done']} changed the logits by only {worst}"
+    assert worst > tol(name, "bfloat16", sharp=True), f"two swapped pages of request {state['done']} changed the logits by only {worst}"
     # and only that request is touched: the others still match
     others = {k: v for k, v in got.items() if k[0] != state["done"]}
     worst_others, where = worst_diff(others, {k: expect[k] for k in others})
-    assert worst_others <= tol(name, "bfloat16"), f"{worst_others} at {where}"
+    assert worst_others <= tol(name, "bfloat16", sharp=True), f"{worst_others} at {where}"
