@@ -147,11 +147,19 @@ def test_whole_model_at_8b_sizes_under_every_cut(whole_8b):
     del eng
     torch.cuda.empty_cache()
     eng = _engine_8b(whole_8b, "bfloat16")
-    spread = float(np.std(np.stack([expect[("long", p)] for p in range(0, 300, 50)])))
+    # bfloat16 against the float32 engine. The logits of this model have a standard deviation of 1.28.
+    # Rounding activations to bfloat16 where kernels store them, layer after layer, gives an error that
+    # grows with depth like a random walk: measured root mean square 0.010 / 0.016 / 0.030 / 0.044 and largest
+    # 0.055 / 0.090 / 0.19 / 0.26 after 1 / 4 / 16 / 36 layers, and a float32 restatement of the model in
+    # torch that rounds at the same places gives 0.042 and 0.27 at 36 layers. The bounds are 1.4 times the
+    # measured figures; a wrong key, page or position does not hide under them at one layer (the test
+    # above) nor in the float32 run of this one.
     for kind, steps in families.items():
-        worst, where = worst_diff(_replay(eng, steps), rows32["whole"])
-        # logits here have a spread of about one; bfloat16 through 36 layers stays within a tenth of it
-        assert worst <= 0.1 * max(spread, 1.0), f"bfloat16 {kind}: {worst} at {where} (spread {spread})"
+        rows = _replay(eng, steps)
+        worst, where = worst_diff(rows, rows32["whole"])
+        sq = np.concatenate([(rows[k].astype(np.float64) - rows32["whole"][k]) ** 2 for k in rows])
+        rms = float(np.sqrt(sq.mean()))
+        assert worst <= 0.4 and rms <= 0.06, f"bfloat16 {kind}: largest {worst} at {where}, root mean square {rms}"
     # generation twice under one seed
     import quantinfer_b200
 
