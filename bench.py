@@ -1,20 +1,35 @@
 #!/usr/bin/env python3
-"""Decode and prefill throughput of the engine at the Qwen3-8B layer sizes, one GPU.
+"""Decode and prefill throughput of the engine at Qwen3 layer sizes, one GPU.
 
-    python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--layers L] [--impl reference]
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--model 8b|14b|32b] [--batch B] [--layers L]
+                    [--impl reference] [--skip-points] [--skip-classes] [--skip-mixed] [--only decode|prefill]
 
-Prints ONE JSON line. `value` is decoded tokens per second at the given batch
-(default 8) with 2,048-token prompts in a 4,096-token context, timed on the
-device with CUDA events around K decode steps that run without the host in the
-loop (CUDA-graph replay, sampling and feeding the token back on the device).
+Prints ONE JSON line. `value` is decoded tokens per second at the headline batch
+of the chosen model (8b: 8 requests with 2,048-token prompts in a 4,096-token
+context, the default; 14b: 32 requests; 32b: 16 requests with 8,192-token
+prompts in a 16,384-token context), timed on the device with CUDA events around
+K decode steps that run without the host in the loop (CUDA-graph replay,
+sampling and feeding the token back on the device).
+
 `e2e` is the same rate through the Python entry point (`Model.generate_batch`,
 host token lists in and out; every step copies its batch arrays from pinned
 host memory and reads the sampled tokens back), counted over the steps in which
 every request of the batch decodes: from the moment the last request has its
-first token until the first request ends (the scheduler starts requests one
-prompt after the other, so they also end one after the other). `prefill` is one 2,048-token
-prompt in one step; `points` are decode rates at batch 1 and 64; `roofline`
-relates the decode step to HBM bandwidth (weights once + the live cache).
+first token until the first request ends. It is taken at the headline batch and
+at the other batches of `points`.
+
+`prefill` is one prompt in one step (`frac` against the sustained matrix peak,
+`frac_burst` against the burst peak). `points` are decode rates at the other
+batches. `roofline` relates the decode step to HBM bandwidth (every weight once
+plus the live cache). `classes` splits the decode step and the prefill step by
+kernel class, by leaving one class out at a time and timing the rest: GEMMs,
+attention, and what remains; each with its share of the bytes (decode) or flops
+(prefill) and the fraction of the peak that gives. `mixed` is the scheduler
+workload of the 14B configuration (32 requests, prompt lengths uniform in
+[128, 4096], 128 new tokens each, temperature 0.7, context 8,192) at the chosen
+model's sizes through `Model.generate_batch`: all tokens per second of wall
+clock and the time to the first token.
+
 Weights are random (seeded) and token ids synthetic: there is no checkpoint or
 dataset here. Peaks come from MEASURED_PEAKS.json when the driver wrote it.
 """
@@ -27,7 +42,6 @@ import os
 import subprocess
 import sys
 import tempfile
-import threading
 import time
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
@@ -36,28 +50,35 @@ sys.path.insert(0, ROOT)
 FALLBACK_HBM_GBS = 6650.0
 FALLBACK_BF16_TFLOPS = 1590.0
 
-QWEN3_8B = dict(
-    architectures=["Qwen3ForCausalLM"], model_type="qwen3", vocab_size=151936, hidden_size=4096,
-    intermediate_size=12288, num_hidden_layers=36, num_attention_heads=32, num_key_value_heads=8,
-    head_dim=128, max_position_embeddings=40960, rms_norm_eps=1e-6, rope_theta=1000000.0,
-    tie_word_embeddings=False,
-)
-SEED = 8
-PROMPT_LEN = 2048
-CONTEXT = 4096
+_COMMON = dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3", vocab_size=151936, head_dim=128,
+               num_key_value_heads=8, max_position_embeddings=40960, rms_norm_eps=1e-6, rope_theta=1000000.0,
+               tie_word_embeddings=False)
+# layer sizes, the seed of the random weights, and the workload: (prompt length, context, headline batch, other batches)
+MODELS = {
+    "8b": dict(config=dict(_COMMON, hidden_size=4096, intermediate_size=12288, num_hidden_layers=36, num_attention_heads=32),
+               seed=8, prompt_len=2048, context=4096, batch=8, points=(1, 64), name="Qwen3-8B sizes"),
+    "14b": dict(config=dict(_COMMON, hidden_size=5120, intermediate_size=17408, num_hidden_layers=40, num_attention_heads=40),
+                seed=14, prompt_len=2048, context=8192, batch=32, points=(1,), name="Qwen3-14B sizes"),
+    "32b": dict(config=dict(_COMMON, hidden_size=5120, intermediate_size=25600, num_hidden_layers=64, num_attention_heads=64),
+                seed=32, prompt_len=8192, context=16384, batch=16, points=(1,), name="Qwen3-32B sizes"),
+}
+MIXED = dict(requests=32, prompt_lo=128, prompt_hi=4096, new_tokens=128, temperature=0.7, context=8192)
 
 
 def peaks():
+    """(HBM GB/s, sustained bf16 TFLOP/s, burst bf16 TFLOP/s, where they come from)."""
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
-    hbm, tf, src = FALLBACK_HBM_GBS, FALLBACK_BF16_TFLOPS, "fallback"
+    hbm, burst, src = FALLBACK_HBM_GBS, FALLBACK_BF16_TFLOPS, "fallback"
+    sustained = burst
     try:
         d = json.load(open(path))
         hbm = float(d.get("hbm_gbs", hbm))
-        tf = float(d.get("bf16_tflops_sustained", d.get("bf16_tflops", tf)))
+        burst = float(d.get("bf16_tflops", burst))
+        sustained = float(d.get("bf16_tflops_sustained", burst))
         src = "measured"
     except Exception:
         pass
-    return hbm, tf, src
+    return hbm, sustained, burst, src
 
 
 class ClockSampler:
@@ -110,16 +131,248 @@ class ClockSampler:
         return out
 
 
+def model_arithmetic(config, spec):
+    """Parameter counts, bytes and flops of the configuration (every matrix bf16)."""
+    L, H, I, V = len(spec.layers), spec.hidden_size, config.intermediate_size, spec.vocab_size
+    nq, nkv, d = config.num_attention_heads, config.num_key_value_heads, config.effective_head_dim
+    layer_params = H * (nq + 2 * nkv) * d + nq * d * H + 3 * H * I
+    a = dict(L=L, H=H, I=I, V=V, nq=nq, nkv=nkv, d=d, layer_params=layer_params)
+    a["weight_bytes"] = 2 * (L * layer_params + V * H)       # the head's matrix too; one embedding row is negligible
+    a["kv_bytes_per_token"] = 2 * L * nkv * d * 2
+    a["gemm_flops"] = lambda T, rows=1: 2.0 * T * L * layer_params + 2.0 * H * V * rows
+    a["attn_flops"] = lambda T: 4.0 * nq * d * (T * (T + 1) / 2) * L
+    return a
+
+
+def build_engine(args, entry, context, max_requests, pool_tokens):
+    import torch
+
+    from quantinfer_b200.config import config_from_dict
+    from quantinfer_b200.engine import Engine, tensor_needs_of_spec
+    from quantinfer_b200.weights import random_tensors
+
+    cfg_d = dict(entry["config"])
+    if args.layers:
+        cfg_d["num_hidden_layers"] = args.layers
+    config = config_from_dict(cfg_d)
+    spec = config.to_model_spec()
+    t0 = time.time()
+    tensors = random_tensors(tensor_needs_of_spec(spec), entry["seed"], torch.bfloat16, device="cuda:0")
+    engine = Engine(spec, tensors, dtype="bfloat16", device="cuda:0", page_size=64, max_tokens=pool_tokens,
+                    max_requests=max_requests, max_seq_len=context, config=config)
+    del tensors
+    torch.cuda.synchronize()
+    return engine, config, spec, time.time() - t0
+
+
+class Bench:
+    def __init__(self, args, entry):
+        import torch
+
+        from quantinfer_b200.sampling import Sampler
+
+        self.args, self.entry, self.torch = args, entry, torch
+        self.prompt_len, self.context = entry["prompt_len"], entry["context"]
+        self.batches = [args.batch] + ([] if args.skip_points else [b for b in entry["points"] if b != args.batch])
+        self.n_new = args.warmup + args.steps + 2
+        per_req = -(-(self.prompt_len + 2 * self.n_new + 64) // 64) * 64
+        max_b = max(self.batches)
+        self.engine, self.config, self.spec, self.load_s = build_engine(
+            args, entry, self.context, max_b, per_req * max_b + self.prompt_len + 2048)
+        self.sampler = Sampler(self.engine.device, self.engine.runtime.status)
+        self.gen = torch.Generator().manual_seed(1234)
+        self.arith = model_arithmetic(self.config, self.spec)
+
+    def prompt(self, n=None):
+        return self.torch.randint(0, self.spec.vocab_size, (n or self.prompt_len,), generator=self.gen).tolist()
+
+    # ---- prefill: one prompt in one step --------------------------------------------
+    def prefill_ms(self, runs=5, warm=2):
+        from quantinfer_b200.engine import StepEntry
+
+        torch, engine, times = self.torch, self.engine, []
+        for i in range(warm + runs):
+            engine.open("p")
+            toks = self.prompt()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            a.record()
+            engine.step([StepEntry("p", toks, [self.prompt_len - 1])], check_status=False)
+            b.record()
+            torch.cuda.synchronize()
+            engine.raise_on_status()
+            engine.close("p")
+            if i >= warm:
+                times.append(a.elapsed_time(b))
+        return sorted(times)[len(times) // 2]
+
+    # ---- decode on the device -----------------------------------------------------------
+    def fill(self, batch):
+        from quantinfer_b200.engine import StepEntry
+
+        ids = [f"d{i}" for i in range(batch)]
+        for rid in ids:
+            self.engine.open(rid)
+            self.engine.step([StepEntry(rid, self.prompt(), [])], check_status=False)
+        return ids
+
+    def decode_rate(self, batch, steps, warmup, sample_clocks=False):
+        from quantinfer_b200 import kernels
+        from quantinfer_b200.sampling import GenerationConfig
+
+        torch, engine = self.torch, self.engine
+        ids = self.fill(batch)
+        rows = [(GenerationConfig(max_new_tokens=1 << 20), 0)] * batch
+        first = [1 + i for i in range(batch)]
+        hist = engine.decode_on_device(ids, first, warmup, rows, self.sampler)
+        last = hist[-1].tolist()
+        torch.cuda.synchronize()
+        clocks = ClockSampler() if sample_clocks else None
+        before = kernels.launches
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        engine.decode_on_device(ids, last, steps, rows, self.sampler)
+        b.record()
+        torch.cuda.synchronize()
+        ms = a.elapsed_time(b)
+        launches = kernels.launches - before
+        ck = clocks.stop() if clocks else None
+        ctx = engine.length(ids[0])
+        for rid in ids:
+            engine.close(rid)
+        return dict(rate=batch * steps / ms * 1e3, ms=ms / steps, launches=launches, clocks=ck, ctx_mid=ctx - steps / 2.0)
+
+    # ---- end to end through the Python entry point ---------------------------------------
+    def e2e(self, model, batch):
+        """Rate over the steps in which the whole batch decodes, by the times at which tokens reach the host."""
+        engine, n_new = self.engine, self.n_new
+        prompts = [self.prompt() for _ in range(batch)]
+        # warm-up through the same entry point (W decode steps): graphs are captured, buffers pinned
+        model.generate_batch(prompts, max_new_tokens=self.args.warmup + 1, eos_token_id=None)
+        stamps = []
+        engine.h2d_bytes_max = 0
+        model.generate_batch(prompts, max_new_tokens=n_new, eos_token_id=None,
+                             on_event=lambda ev: stamps.append((time.perf_counter(), ev.request_id, getattr(ev, "stop_reason", None))))
+        # bytes a decode step of the full batch copies host -> device: its packed batch arrays (token ids,
+        # positions, lengths, slots, block tables)
+        h2d = max([g["meta"].numel() * 4 for (b, _), g in engine._graphs.items() if b == batch] or [engine.h2d_bytes_max])
+        # the window in which the whole batch decodes: after the last request's first token, up to the
+        # step in which the first request ends
+        seen, t_all_first, t_end, after = set(), None, None, 0
+        for t, rid, stop in stamps:
+            if t_all_first is None:
+                seen.add(rid)
+                if len(seen) == batch:
+                    t_all_first = t
+            elif t - t_all_first < 1e-4:                 # the events of one step arrive together:
+                continue                                 # the rest of the step that gave the last first token
+            elif t_end is None or t - t_end < 1e-4:
+                after += 1
+                if stop is not None and t_end is None:
+                    t_end = t
+        ok = t_all_first is not None and t_end is not None and after >= batch
+        return {"value": after / (t_end - t_all_first) if ok else None, "unit": "tokens/s", "h2d_bytes_per_step": h2d,
+                "d2h_bytes_per_step": 4 * batch + 4, "steps": after // max(batch, 1) if ok else 0,
+                "ms_per_step": (t_end - t_all_first) * 1e3 / (after / batch) if ok else None}
+
+    # ---- the step by kernel class ---------------------------------------------------------------
+    def classes(self, full_decode_ms, full_prefill_ms, ctx_mid, peaks_):
+        """Two timings for each class of kernels. `alone`: the step with every other class left out, so
+        that the class's kernels run back to back: the rate at which they stream their bytes (decode) or
+        do their flops (prefill). `left_out`: the full step's time less the step's without the class:
+        what the class costs where it stands, after what overlaps with its neighbours. The sum of the
+        `alone` times falls short of the step by what the hand-over from kernel to kernel costs."""
+        from quantinfer_b200 import kernels
+
+        hbm, sustained, burst, _ = peaks_
+        a, batch, T = self.arith, self.args.batch, self.prompt_len
+        steps = max(8, min(self.args.steps, 16))
+        every = ("gemm", "attention", "norm", "rope", "other")
+        work = {
+            "gemm": (a["weight_bytes"], a["gemm_flops"](T)),
+            "attention": (batch * ctx_mid * a["kv_bytes_per_token"], a["attn_flops"](T)),
+        }
+
+        def timed(knocked):
+            kernels.knock_out = frozenset(knocked)
+            self.engine._graphs.clear()
+            try:
+                return self.decode_rate(batch, steps, 3)["ms"], self.prefill_ms(runs=3, warm=1)
+            finally:
+                kernels.knock_out = frozenset()
+                self.engine._graphs.clear()
+
+        out = {"note": "alone: only this class runs; left_out: full step less the step without it"}
+        sum_alone = [0.0, 0.0]
+        for cls in ("gemm", "attention", "norm"):
+            d_alone, p_alone = timed([c for c in every if c != cls])
+            d_without, p_without = timed([cls])
+            row = {"decode_alone_ms": round(d_alone, 4), "decode_left_out_ms": round(full_decode_ms - d_without, 4),
+                   "prefill_alone_ms": round(p_alone, 4), "prefill_left_out_ms": round(full_prefill_ms - p_without, 4)}
+            sum_alone[0] += d_alone
+            sum_alone[1] += p_alone
+            if cls in work:
+                gbs, tf = work[cls][0] / (d_alone * 1e-3) / 1e9, work[cls][1] / (p_alone * 1e-3) / 1e12
+                row.update({"decode_gbs": round(gbs, 1), "decode_frac_hbm": round(gbs / hbm, 3), "prefill_tflops": round(tf, 1),
+                            "prefill_frac_burst": round(tf / burst, 3), "prefill_frac_sustained": round(tf / sustained, 3)})
+            out[cls] = row
+        out["rest"] = {"decode_ms": round(full_decode_ms - sum_alone[0], 4), "prefill_ms": round(full_prefill_ms - sum_alone[1], 4)}
+        return out
+
+
+def mixed_workload(args, entry):
+    """The scheduler workload: 32 requests with prompts of 128 to 4,096 tokens (seeded), 128 new tokens each at
+    temperature 0.7 in a context of 8,192, all submitted at once through Model.generate_batch. The first pass
+    captures the decode graphs; the second is timed by the wall clock, host in the loop."""
+    import torch
+
+    from quantinfer_b200 import Model
+
+    w = MIXED
+    g = torch.Generator().manual_seed(4321)
+    lens = torch.randint(w["prompt_lo"], w["prompt_hi"] + 1, (w["requests"],), generator=g).tolist()
+    pool = sum(-(-(n + w["new_tokens"]) // 64) * 64 for n in lens) + 4096
+    engine, config, spec, _ = build_engine(args, entry, w["context"], w["requests"], pool)
+    prompts = [torch.randint(0, spec.vocab_size, (n,), generator=g).tolist() for n in lens]
+    model = Model.from_engine(engine, max_batch_tokens=args.mixed_budget, chunk_size=args.mixed_chunk)
+    out = {}
+    for timed in (False, True):
+        clocks = ClockSampler() if timed else None
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        res = model.generate_batch(prompts, max_new_tokens=w["new_tokens"], eos_token_id=None, temperature=w["temperature"], seed=7)
+        torch.cuda.synchronize()
+        wall = time.perf_counter() - t0
+        if timed:
+            run = model.last_run
+            ttft = sorted((r.first_token_at - run.started_at) * 1e3 for r in run.results)
+            generated = sum(len(t) for t in res)
+            out = {"requests": w["requests"], "prompt_tokens": sum(lens), "generated_tokens": generated, "wall_s": round(wall, 4),
+                   "tokens_per_s": round((sum(lens) + generated) / wall, 1), "generated_per_s": round(generated / wall, 1),
+                   "ttft_ms_p50": round(ttft[len(ttft) // 2], 2), "ttft_ms_p90": round(ttft[int(len(ttft) * 0.9)], 2),
+                   "ttft_ms_max": round(ttft[-1], 2), "steps": run.scheduler.steps, "steps_ahead": run.scheduler.steps_ahead,
+                   "token_budget": args.mixed_budget, "chunk": args.mixed_chunk or args.mixed_budget,
+                   "context": w["context"], "temperature": w["temperature"], "clocks": clocks.stop()}
+    del model, engine
+    torch.cuda.empty_cache()
+    return out
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=64)
     ap.add_argument("--warmup", type=int, default=8)
-    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--model", default="8b", choices=sorted(MODELS))
+    ap.add_argument("--batch", type=int, default=None, help="headline batch (default: the model's)")
     ap.add_argument("--layers", type=int, default=None, help="run fewer layers than the configuration has (named in `config`)")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--skip-points", action="store_true", help="measure only the headline batch")
-    ap.add_argument("--only", choices=["decode", "prefill"], default=None,
+    ap.add_argument("--skip-classes", action="store_true", help="no split of the steps by kernel class")
+    ap.add_argument("--skip-mixed", action="store_true", help="no scheduler workload")
+    ap.add_argument("--mixed-budget", type=int, default=2048, help="token budget of a step of the scheduler workload")
+    ap.add_argument("--mixed-chunk", type=int, default=None, help="longest prompt portion of the scheduler workload")
+    ap.add_argument("--only", choices=["decode", "prefill", "mixed"], default=None,
                     help="run one part only (for profiler captures of a small case)")
     args = ap.parse_args()
 
@@ -130,171 +383,76 @@ def main() -> int:
     if args.gpus != 1:
         print("bench.py: this engine runs on one GPU; --gpus must be 1")
         return 2
-    if args.warmup < 3:
-        args.warmup = 3
+    args.warmup = max(args.warmup, 3)
+    entry = MODELS[args.model]
+    args.batch = args.batch or entry["batch"]
+    if args.only:
+        args.skip_points = args.skip_classes = True
 
     import torch
 
-    from quantinfer_b200 import Model, kernels
-    from quantinfer_b200.config import config_from_dict
-    from quantinfer_b200.engine import Engine, StepEntry, tensor_needs_of_spec
-    from quantinfer_b200.sampling import GenerationConfig, Sampler
-    from quantinfer_b200.weights import random_tensors
+    from quantinfer_b200 import Model
 
-    hbm_peak, tf_peak, peak_src = peaks()
-    cfg_d = dict(QWEN3_8B)
-    full_layers = cfg_d["num_hidden_layers"]
-    if args.layers:
-        cfg_d["num_hidden_layers"] = args.layers
-    config = config_from_dict(cfg_d)
-    spec = config.to_model_spec()
-    dev = "cuda:0"
     torch.cuda.set_device(0)
-    t0 = time.time()
-    tensors = random_tensors(tensor_needs_of_spec(spec), SEED, torch.bfloat16, device=dev)
-    max_b = 64 if not args.skip_points else max(args.batch, 1)
-    n_new = args.warmup + args.steps + 2
-    per_req = -(-(PROMPT_LEN + 2 * n_new + 64) // 64) * 64
-    engine = Engine(spec, tensors, dtype="bfloat16", device=dev, page_size=64,
-                    max_tokens=per_req * max(max_b, args.batch) + 4096, max_requests=max(max_b, args.batch),
-                    max_seq_len=CONTEXT, config=config)
-    del tensors
-    torch.cuda.synchronize()
-    load_s = time.time() - t0
-    sampler = Sampler(engine.device, engine.runtime.status)
-    g = torch.Generator().manual_seed(1234)
-    vocab = spec.vocab_size
+    if args.only == "mixed":
+        print(json.dumps({"only": "mixed", "mixed": mixed_workload(args, entry)}))
+        return 0
+    peaks_ = hbm_peak, tf_sustained, tf_burst, peak_src = peaks()
+    bench = Bench(args, entry)
+    a, T = bench.arith, bench.prompt_len
+    flops = a["gemm_flops"](T) + a["attn_flops"](T)
 
-    def prompt(n=PROMPT_LEN):
-        return torch.randint(0, vocab, (n,), generator=g).tolist()
-
-    # ---- model arithmetic -----------------------------------------------------
-    L, H, I = spec.layers and len(spec.layers), spec.hidden_size, config.intermediate_size
-    nq, nkv, d = config.num_attention_heads, config.num_key_value_heads, config.effective_head_dim
-    layer_params = H * (nq + 2 * nkv) * d + nq * d * H + 3 * H * I
-    weight_bytes = 2 * (L * layer_params + vocab * H)          # every matrix once, bf16 (head; one embedding row is negligible)
-    kv_bytes_per_token = 2 * L * nkv * d * 2
-
-    def prefill_flops(T):
-        return 2.0 * T * L * layer_params + 4.0 * nq * d * (T * (T + 1) / 2) * L + 2.0 * H * vocab
-
-    if args.only:
-        args.skip_points = True
-    # ---- prefill: one 2,048-token prompt in one step ---------------------------
-    times = []
-    for i in range(0 if args.only == "decode" else 2 + 5):
-        engine.open("p")
-        toks = prompt()
-        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        torch.cuda.synchronize()
-        a.record()
-        engine.step([StepEntry("p", toks, [PROMPT_LEN - 1])], check_status=False)
-        b.record()
-        torch.cuda.synchronize()
-        engine.raise_on_status()
-        engine.close("p")
-        if i >= 2:
-            times.append(a.elapsed_time(b))
-    pre_ms = sorted(times)[len(times) // 2] if times else float("nan")
-    prefill = {"value": PROMPT_LEN / pre_ms * 1e3, "tokens": PROMPT_LEN, "ms": pre_ms,
-               "frac": prefill_flops(PROMPT_LEN) / (pre_ms * 1e-3) / (tf_peak * 1e12)}
-
-    # ---- decode on the device ---------------------------------------------------
-    def fill(batch):
-        ids = [f"d{i}" for i in range(batch)]
-        for rid in ids:
-            engine.open(rid)
-            engine.step([StepEntry(rid, prompt(), [])], check_status=False)
-        engine.raise_on_status()
-        return ids
-
-    def decode_rate(batch, steps, warmup, sample_clocks=False):
-        ids = fill(batch)
-        rows = [(GenerationConfig(max_new_tokens=4096), 0)] * batch
-        first = [1 + i for i in range(batch)]
-        hist = engine.decode_on_device(ids, first, warmup, rows, sampler)
-        last = hist[-1].tolist()
-        torch.cuda.synchronize()
-        clocks = ClockSampler() if sample_clocks else None
-        before = kernels.launches
-        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        a.record()
-        engine.decode_on_device(ids, last, steps, rows, sampler)
-        b.record()
-        torch.cuda.synchronize()
-        ms = a.elapsed_time(b)
-        launches = kernels.launches - before
-        ck = clocks.stop() if clocks else None
-        ctx = engine.length(ids[0])
-        for rid in ids:
-            engine.close(rid)
-        return batch * steps / ms * 1e3, ms / steps, launches, ck, ctx
-
+    pre_ms = float("nan") if args.only == "decode" else bench.prefill_ms()
+    prefill = {"value": T / pre_ms * 1e3, "tokens": T, "ms": pre_ms, "frac": flops / (pre_ms * 1e-3) / (tf_sustained * 1e12),
+               "frac_burst": flops / (pre_ms * 1e-3) / (tf_burst * 1e12), "tflops": flops / (pre_ms * 1e-3) / 1e12}
     if args.only == "prefill":
         print(json.dumps({"only": "prefill", "prefill": prefill}))
         return 0
-    value, ms_per_step, launches, clocks, ctx_end = decode_rate(args.batch, args.steps, args.warmup, True)
-    ctx_mid = ctx_end - args.steps / 2.0
-    step_bytes = weight_bytes + args.batch * ctx_mid * kv_bytes_per_token
-    achieved = step_bytes / (ms_per_step * 1e-3) / 1e9
-    points = {}
-    if not args.skip_points:
-        for bsz in (1, 64):
-            r, _, _, _, _ = decode_rate(bsz, min(args.steps, 32), 3)
-            points[f"decode_b{bsz}"] = r
 
+    head = bench.decode_rate(args.batch, args.steps, args.warmup, sample_clocks=True)
+    step_bytes = a["weight_bytes"] + args.batch * head["ctx_mid"] * a["kv_bytes_per_token"]
+    achieved = step_bytes / (head["ms"] * 1e-3) / 1e9
     if args.only == "decode":
-        print(json.dumps({"only": "decode", "value": value, "ms_per_step": ms_per_step, "gpu_launches": launches}))
+        print(json.dumps({"only": "decode", "value": head["rate"], "ms_per_step": head["ms"], "gpu_launches": head["launches"]}))
         return 0
-    # ---- end to end through the Python entry point -----------------------------------
-    model = Model.from_engine(engine, max_batch_tokens=PROMPT_LEN)
-    prompts = [prompt() for _ in range(args.batch)]
-    # warm-up through the same entry point (W decode steps): graphs are captured, buffers pinned
-    model.generate_batch(prompts, max_new_tokens=args.warmup + 1, eos_token_id=None)
-    stamps = []
-    engine.h2d_bytes_max = 0
-    model.generate_batch(prompts, max_new_tokens=n_new, eos_token_id=None,
-                         on_event=lambda ev: stamps.append((time.perf_counter(), ev.request_id, getattr(ev, "stop_reason", None))))
-    # bytes a decode step of the full batch copies host -> device: its packed batch arrays (token ids,
-    # positions, lengths, slots, block tables)
-    h2d_max = max([g["meta"].numel() * 4 for (b, _), g in engine._graphs.items() if b == args.batch] or [engine.h2d_bytes_max])
-    # the window in which the whole batch decodes: after the last request's first token, up to the
-    # step in which the first request ends
-    seen, t_all_first, t_end, after = set(), None, None, 0
-    for t, rid, stop in stamps:
-        if t_all_first is None:
-            seen.add(rid)
-            if len(seen) == args.batch:
-                t_all_first = t
-        elif t - t_all_first < 1e-4:                 # the events of one step arrive together:
-            continue                                 # the rest of the step that gave the last first token
-        elif t_end is None or t - t_end < 1e-4:
-            after += 1
-            if stop is not None and t_end is None:
-                t_end = t
-    ok = t_all_first is not None and t_end is not None and after >= args.batch
-    e2e = {"value": after / (t_end - t_all_first) if ok else None, "unit": "tokens/s", "h2d_bytes_per_step": h2d_max,
-           "d2h_bytes_per_step": 4 * args.batch + 4, "steps": after // max(args.batch, 1) if ok else 0,
-           "ms_per_step": (t_end - t_all_first) * 1e3 / (after / args.batch) if ok else None}
+    points = {}
+    for bsz in bench.batches[1:]:
+        r = bench.decode_rate(bsz, min(args.steps, 32), 3)
+        points[f"decode_b{bsz}"] = r["rate"]
+        points[f"decode_b{bsz}_frac_hbm"] = round((a["weight_bytes"] + bsz * r["ctx_mid"] * a["kv_bytes_per_token"]) / (r["ms"] * 1e-3) / 1e9 / hbm_peak, 3)
+
+    model = Model.from_engine(bench.engine, max_batch_tokens=T)
+    e2e = bench.e2e(model, args.batch)
+    for bsz in bench.batches[1:]:
+        points[f"e2e_b{bsz}"] = bench.e2e(model, bsz)["value"]
+    del model
+    classes = None if args.skip_classes else bench.classes(head["ms"], pre_ms, head["ctx_mid"], peaks_)
+    engine = bench.engine
+    config = {
+        "model": entry["name"], "global_batch": args.batch, "seq_len": bench.context, "prompt_len": T,
+        "layers": a["L"], "layers_of_config": entry["config"]["num_hidden_layers"], "hidden": a["H"], "heads": a["nq"],
+        "kv_heads": a["nkv"], "head_dim": a["d"], "intermediate": a["I"], "vocab": a["V"], "page_size": engine.page_size,
+        "parallelism": "1 GPU", "l2": "inputs larger than L2 (weights %.1f GB per step)" % (a["weight_bytes"] / 1e9),
+        "peaks": peak_src, "load_s": round(bench.load_s, 1),
+    }
+    del bench, engine
+    torch.cuda.empty_cache()
+    mixed = None if args.skip_mixed else mixed_workload(args, entry)
 
     line = {
-        "metric": "decode tokens/s (Qwen3-8B sizes, random bf16 weights, 1 B200)",
-        "value": value, "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
-        "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "metric": "decode tokens/s (%s, random bf16 weights, 1 B200)" % entry["name"],
+        "value": head["rate"], "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": head["ms"], "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic token ids, seeded random weights", "impl": "ours",
-        "config": {
-            "model": "Qwen3-8B sizes", "global_batch": args.batch, "seq_len": CONTEXT, "prompt_len": PROMPT_LEN,
-            "layers": L, "layers_of_config": full_layers, "hidden": H, "heads": nq, "kv_heads": nkv, "head_dim": d,
-            "intermediate": I, "vocab": vocab, "page_size": engine.page_size, "parallelism": "1 GPU",
-            "l2": "inputs larger than L2 (weights %.1f GB per step)" % (weight_bytes / 1e9),
-            "peaks": peak_src, "load_s": round(load_s, 1),
-        },
+        "config": config,
         "prefill": prefill,
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": hbm_peak, "unit": "GB/s", "frac": achieved / hbm_peak},
         "points": points,
         "e2e": e2e,
-        "gpu_launches": launches,
-        "clocks": clocks,
+        "classes": classes,
+        "mixed": mixed,
+        "gpu_launches": head["launches"],
+        "clocks": head["clocks"],
     }
     print(json.dumps(line))
     return 0

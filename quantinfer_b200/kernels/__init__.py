@@ -87,6 +87,18 @@ def _check(rc: int, name: str) -> None:
         raise KernelError(f"{name}: {library().qi_last_error().decode()}")
 
 
+knock_out = frozenset()   # kernel classes ("gemm", "attention", "norm", "rope", "other") whose launches are left out
+
+
+def _call(cls, name: str, fn, *args) -> None:
+    """Calls an entry point and raises with the library's message if it refuses. A class named in
+    `knock_out` is not launched at all: a measurement leaves one class out at a time and times the
+    rest of the step (the results of such a step mean nothing)."""
+    if cls is not None and cls in knock_out:
+        return
+    _check(fn(*args), name)
+
+
 def _code(t: torch.Tensor) -> int:
     try:
         return _DTYPE_CODE[t.dtype]
@@ -122,9 +134,9 @@ def embedding(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor, status:
     n, hidden = out.shape
     if ids.numel() != n or table.shape[1] != hidden:
         raise KernelError(f"embedding: shapes do not agree: table {tuple(table.shape)}, ids {tuple(ids.shape)}, out {tuple(out.shape)}")
-    rc = library().qi_embedding(_ptr(table), _code(table), _ptr(ids), _ptr(out), n, hidden,
+    _call('other', "embedding", library().qi_embedding,
+          _ptr(table), _code(table), _ptr(ids), _ptr(out), n, hidden,
                                 table.shape[0], _ptr(status), _stream())
-    _check(rc, "embedding")
 
 
 # --------------------------------------------------------------------------
@@ -161,11 +173,10 @@ def add_rmsnorm(resid: torch.Tensor, delta, gain: torch.Tensor, eps: float, out:
         write_resid = False
     if tuple(out.shape) != (n_out, h):
         raise KernelError(f"add_rmsnorm: out is {tuple(out.shape)}, expected {(n_out, h)}")
-    rc = library().qi_add_rmsnorm(
-        _ptr(resid), _ptr(delta), _code(delta) if delta is not None else F32, splits,
+    _call('norm', "add_rmsnorm", library().qi_add_rmsnorm,
+          _ptr(resid), _ptr(delta), _code(delta) if delta is not None else F32, splits,
         C.c_longlong(stride), _ptr(gain), C.c_float(eps), _ptr(out), _code(out), _ptr(rows), n_out, h,
         int(bool(write_resid)), _stream())
-    _check(rc, "add_rmsnorm")
 
 
 def rmsnorm(x: torch.Tensor, gain: torch.Tensor, eps: float, out: torch.Tensor) -> None:
@@ -176,9 +187,9 @@ def rmsnorm(x: torch.Tensor, gain: torch.Tensor, eps: float, out: torch.Tensor) 
     width = x.shape[-1]
     if gain.numel() != width or out.shape != x.shape:
         raise KernelError("rmsnorm: shapes do not agree")
-    rc = library().qi_rmsnorm(_ptr(x), _ptr(gain), C.c_float(eps), _ptr(out), _code(x),
+    _call('norm', "rmsnorm", library().qi_rmsnorm,
+          _ptr(x), _ptr(gain), C.c_float(eps), _ptr(out), _code(x),
                               x.numel() // width, width, _stream())
-    _check(rc, "rmsnorm")
 
 
 # --------------------------------------------------------------------------
@@ -194,9 +205,9 @@ def gemm_simt(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
     N = w.shape[0]
     if w.shape[1] != K or tuple(out.shape) != (M, N):
         raise KernelError(f"gemm: shapes do not agree: x {tuple(x.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}")
-    rc = library().qi_gemm_simt(_ptr(x), _code(x), _ptr(w), _code(w), _ptr(out), _code(out), M, N, K,
+    _call('gemm', "gemm_simt", library().qi_gemm_simt,
+          _ptr(x), _code(x), _ptr(w), _code(w), _ptr(out), _code(out), M, N, K,
                                 C.c_longlong(K), C.c_longlong(K), C.c_longlong(N), _stream())
-    _check(rc, "gemm_simt")
 
 
 # --------------------------------------------------------------------------
@@ -209,8 +220,8 @@ def rope_table(inv_freq: torch.Tensor, max_positions: int):
     half = inv_freq.numel()
     cos = torch.empty((max_positions, half), dtype=torch.float32, device=inv_freq.device)
     sin = torch.empty_like(cos)
-    rc = library().qi_rope_table(_ptr(inv_freq), _ptr(cos), _ptr(sin), max_positions, half, _stream())
-    _check(rc, "rope_table")
+    _call(None, "rope_table", library().qi_rope_table,
+          _ptr(inv_freq), _ptr(cos), _ptr(sin), max_positions, half, _stream())
     return cos, sin
 
 
@@ -259,12 +270,11 @@ def qk_norm_rope_kv(qkv, q_out, q_gain, k_gain, eps, cos, sin, rotary_dim, posit
         if tuple(k_pages.shape[1:]) != (nkv, page_size, d) or k_pages.shape != v_pages.shape:
             raise KernelError(f"qk_norm_rope_kv: pages {tuple(k_pages.shape)} do not match (pages, {nkv}, {page_size}, {d})")
         num_pages, max_blocks = k_pages.shape[0], block_table.shape[1]
-    rc = library().qi_qk_norm_rope_kv(
-        _ptr(qkv), splits, _ptr(q_out), _code(q_out), _ptr(q_gain), _ptr(k_gain), C.c_float(eps), _ptr(cos),
+    _call('rope', "qk_norm_rope_kv", library().qi_qk_norm_rope_kv,
+          _ptr(qkv), splits, _ptr(q_out), _code(q_out), _ptr(q_gain), _ptr(k_gain), C.c_float(eps), _ptr(cos),
         _ptr(sin), rotary_dim, int(bool(interleaved)), table_positions, _ptr(positions), _ptr(token_req), _ptr(block_table),
         max_blocks, page_size, num_pages, _ptr(k_pages), _ptr(v_pages), n, nq, nkv, d, _ptr(status),
         _stream())
-    _check(rc, "qk_norm_rope_kv")
 
 
 # --------------------------------------------------------------------------
@@ -286,11 +296,10 @@ def attention_generic(q, out, k_pages, v_pages, block_table, positions, token_re
         raise KernelError(f"attention: q {tuple(q.shape)} does not match {nq} heads of {d}")
     if k_pages.shape[1] != nkv or k_pages.shape[3] != d or k_pages.shape != v_pages.shape:
         raise KernelError(f"attention: pages {tuple(k_pages.shape)} do not match {nkv} kv heads of {d}")
-    rc = library().qi_attention_generic(
-        _ptr(q), _ptr(out), _code(q), _ptr(k_pages), _ptr(v_pages), _ptr(block_table),
+    _call('attention', "attention_generic", library().qi_attention_generic,
+          _ptr(q), _ptr(out), _code(q), _ptr(k_pages), _ptr(v_pages), _ptr(block_table),
         block_table.shape[1], k_pages.shape[2], k_pages.shape[0], _ptr(positions), _ptr(token_req), n,
         nq, nkv, d, C.c_float(scale), int(window or 0), _ptr(status), _stream())
-    _check(rc, "attention_generic")
 
 
 def attention_mma_supported(nq: int, nkv: int, d: int) -> bool:
@@ -372,27 +381,24 @@ def attention_prefill(q, out, k_pages, v_pages, block_table, q_start, start_pos,
         if q.shape[0] > 65535:
             ranges = 1
         ws = torch.empty(q.shape[0] * nq * ranges * (d + 2), dtype=torch.float32, device=q.device) if ranges > 1 else None
-        rc = library().qi_attention_prefill_tcgen05(
-            _ptr(q), _ptr(out), _ptr(k_pages), _ptr(v_pages), _ptr(block_table), block_table.shape[1],
+        _call('attention', "attention_prefill_tcgen05", library().qi_attention_prefill_tcgen05,
+              _ptr(q), _ptr(out), _ptr(k_pages), _ptr(v_pages), _ptr(block_table), block_table.shape[1],
             k_pages.shape[2], k_pages.shape[0], _ptr(q_start), _ptr(start_pos), _ptr(tile_req), _ptr(tile_q0),
             tile_req.numel(), q.shape[0], nq, nkv, d, C.c_float(scale), int(window or 0), ranges, _ptr(ws),
             _ptr(status), _stream())
-        _check(rc, "attention_prefill_tcgen05")
         return
     if impl not in ("tma", "cpasync"):
         raise KernelError(f"attention_prefill: unknown kernel {impl!r}")
     if impl == "tma":
-        rc = library().qi_attention_prefill_tma(
-            _ptr(q), _ptr(out), _ptr(k_pages), _ptr(v_pages), _ptr(block_table), block_table.shape[1],
+        _call('attention', "attention_prefill_tma", library().qi_attention_prefill_tma,
+              _ptr(q), _ptr(out), _ptr(k_pages), _ptr(v_pages), _ptr(block_table), block_table.shape[1],
             k_pages.shape[2], k_pages.shape[0], _ptr(q_start), _ptr(start_pos), _ptr(tile_req), _ptr(tile_q0),
             tile_req.numel(), q.shape[0], nq, nkv, d, C.c_float(scale), int(window or 0), _ptr(status), _stream())
-        _check(rc, "attention_prefill_tma")
         return
-    rc = library().qi_attention_prefill(
-        _ptr(q), _ptr(out), _ptr(k_pages), _ptr(v_pages), _ptr(block_table), block_table.shape[1],
+    _call('attention', "attention_prefill", library().qi_attention_prefill,
+          _ptr(q), _ptr(out), _ptr(k_pages), _ptr(v_pages), _ptr(block_table), block_table.shape[1],
         k_pages.shape[2], k_pages.shape[0], _ptr(q_start), _ptr(start_pos), _ptr(tile_req), _ptr(tile_q0),
         tile_req.numel(), QUERY_TILE, nq, nkv, d, C.c_float(scale), int(window or 0), _ptr(status), _stream())
-    _check(rc, "attention_prefill")
 
 
 def attention_decode_plan(batch: int, nkv: int, max_kv_len: int):
@@ -433,11 +439,10 @@ def attention_decode(q, out, k_pages, v_pages, block_table, kv_len, q_start, nq,
     if use_tma is None:
         use_tma = attention_tma_supported(nq, nkv, d, k_pages.shape[2], block_table.shape[1])
     fn = library().qi_attention_decode_tma if use_tma else library().qi_attention_decode
-    rc = fn(
-        _ptr(q), _ptr(out), _ptr(k_pages), _ptr(v_pages), _ptr(block_table), block_table.shape[1],
+    _call('attention', "attention_decode", fn,
+          _ptr(q), _ptr(out), _ptr(k_pages), _ptr(v_pages), _ptr(block_table), block_table.shape[1],
         k_pages.shape[2], k_pages.shape[0], _ptr(kv_len), _ptr(q_start), batch, nq, nkv, d, C.c_float(scale),
         int(window or 0), chunk, n_splits, _ptr(ws_o), _ptr(ws_ml), _ptr(status), _stream())
-    _check(rc, "attention_decode")
 
 
 def attention_decode_rope(qkv, out, q_gain, k_gain, eps, cos, sin, k_pages, v_pages, writes: bool, block_table, kv_len,
@@ -485,13 +490,12 @@ def attention_decode_rope(qkv, out, q_gain, k_gain, eps, cos, sin, k_pages, v_pa
     _req(workspace, "workspace", torch.float32, 1)
     if workspace.numel() < need:
         raise KernelError(f"attention_decode_rope: workspace has {workspace.numel()} floats, {need} are needed")
-    rc = library().qi_attention_decode_rope_tma(
-        _ptr(qkv), _code(qkv), splits, n_tokens, _ptr(q_gain), _ptr(k_gain), C.c_float(eps), _ptr(cos), _ptr(sin),
+    _call('attention', "attention_decode_rope", library().qi_attention_decode_rope_tma,
+          _ptr(qkv), _code(qkv), splits, n_tokens, _ptr(q_gain), _ptr(k_gain), C.c_float(eps), _ptr(cos), _ptr(sin),
         table_positions, int(bool(writes)), _ptr(out), _ptr(k_pages), _ptr(v_pages), _ptr(block_table),
         block_table.shape[1], k_pages.shape[2], k_pages.shape[0], _ptr(kv_len), _ptr(q_start), batch, nq, nkv, d,
         C.c_float(scale), int(window or 0), chunk, n_splits, _ptr(workspace), _ptr(workspace[batch * nq * n_splits * d:]),
         _ptr(status), _stream())
-    _check(rc, "attention_decode_rope")
 
 
 # --------------------------------------------------------------------------
@@ -506,8 +510,8 @@ def silu_mul(gate_up: torch.Tensor, out: torch.Tensor, interleaved: bool = False
     n, two_i = gate_up.shape
     if two_i % 2 or tuple(out.shape) != (n, two_i // 2):
         raise KernelError(f"silu_mul: gate_up {tuple(gate_up.shape)} / out {tuple(out.shape)} do not agree")
-    rc = library().qi_silu_mul(_ptr(gate_up), _ptr(out), _code(out), n, two_i // 2, int(bool(interleaved)), _stream())
-    _check(rc, "silu_mul")
+    _call('other', "silu_mul", library().qi_silu_mul,
+          _ptr(gate_up), _ptr(out), _code(out), n, two_i // 2, int(bool(interleaved)), _stream())
 
 
 # --------------------------------------------------------------------------
@@ -532,9 +536,9 @@ def sample(logits, temperature, top_k, top_p, seed, counter, out_token, status) 
                 raise KernelError(f"sample: {name} has {t.numel()} entries for {rows} rows")
     if out_token.numel() < rows:
         raise KernelError("sample: out_token is too short")
-    rc = library().qi_sample(_ptr(logits), rows, vocab, _ptr(temperature), _ptr(top_k), _ptr(top_p),
+    _call('other', "sample", library().qi_sample,
+          _ptr(logits), rows, vocab, _ptr(temperature), _ptr(top_k), _ptr(top_p),
                              _ptr(seed), _ptr(counter), _ptr(out_token), _ptr(status), _stream())
-    _check(rc, "sample")
 
 
 def advance_decode(token_ids, positions, start_pos, kv_len, counter, sampled, history) -> None:
@@ -544,9 +548,9 @@ def advance_decode(token_ids, positions, start_pos, kv_len, counter, sampled, hi
                     (kv_len, "kv_len"), (sampled, "sampled")):
         _req(t, name, torch.int32, 1)
     b = token_ids.numel()
-    rc = library().qi_advance_decode(_ptr(token_ids), _ptr(positions), _ptr(start_pos), _ptr(kv_len),
+    _call(None, "advance_decode", library().qi_advance_decode,
+          _ptr(token_ids), _ptr(positions), _ptr(start_pos), _ptr(kv_len),
                                      _ptr(counter), _ptr(sampled), _ptr(history), b, _stream())
-    _check(rc, "advance_decode")
 
 
 def gemm_qkv_rope_supported(M: int, K: int, d: int, rotary_dim: int, dtype, weight_dtype) -> bool:
@@ -593,11 +597,10 @@ def gemm_qkv_rope(x, w, q_out, q_gain, k_gain, eps, cos, sin, positions, token_r
         if tuple(k_pages.shape[1:]) != (nkv, page_size, d) or k_pages.shape != v_pages.shape:
             raise KernelError(f"gemm_qkv_rope: pages {tuple(k_pages.shape)} do not match (pages, {nkv}, {page_size}, {d})")
         num_pages, max_blocks = k_pages.shape[0], block_table.shape[1]
-    rc = library().qi_gemm_bf16_qkv_rope(
-        _ptr(x), _ptr(w), M, K, _ptr(q_out), _ptr(q_gain), _ptr(k_gain), C.c_float(eps), _ptr(cos), _ptr(sin),
+    _call('gemm', "gemm_qkv_rope", library().qi_gemm_bf16_qkv_rope,
+          _ptr(x), _ptr(w), M, K, _ptr(q_out), _ptr(q_gain), _ptr(k_gain), C.c_float(eps), _ptr(cos), _ptr(sin),
         table_positions, _ptr(positions), _ptr(token_req), _ptr(block_table), max_blocks, page_size, num_pages,
         _ptr(k_pages), _ptr(v_pages), nq, nkv, _ptr(status), _stream())
-    _check(rc, "gemm_qkv_rope")
 
 
 def stage_step(host_meta: torch.Tensor, meta: torch.Tensor, device_tokens=None) -> None:
@@ -614,8 +617,8 @@ def stage_step(host_meta: torch.Tensor, meta: torch.Tensor, device_tokens=None) 
     if device_tokens is not None:
         _req(device_tokens, "device_tokens", torch.int32, 1)
         n_tok = device_tokens.numel()
-    rc = library().qi_stage_step(C.c_void_p(host_meta.data_ptr()), _ptr(meta), n, _ptr(device_tokens), n_tok, _stream())
-    _check(rc, "stage_step")
+    _call(None, "stage_step", library().qi_stage_step,
+          C.c_void_p(host_meta.data_ptr()), _ptr(meta), n, _ptr(device_tokens), n_tok, _stream())
 
 
 def publish(src: torch.Tensor, host_out: torch.Tensor, n: int) -> None:
@@ -626,8 +629,8 @@ def publish(src: torch.Tensor, host_out: torch.Tensor, n: int) -> None:
         raise KernelError("publish: host_out must be a pinned int32 host tensor")
     if n > src.numel() or n > host_out.numel():
         raise KernelError("publish: more entries than the buffers hold")
-    rc = library().qi_publish(_ptr(src), C.c_void_p(host_out.data_ptr()), n, _stream())
-    _check(rc, "publish")
+    _call(None, "publish", library().qi_publish,
+          _ptr(src), C.c_void_p(host_out.data_ptr()), n, _stream())
 
 
 # --------------------------------------------------------------------------
@@ -680,8 +683,8 @@ def gemm_bf16(x: torch.Tensor, w: torch.Tensor, out, plan=None, status=None, epi
         status = _gemm_status.get(x.device)
         if status is None:
             status = _gemm_status[x.device] = torch.zeros(1, dtype=torch.int32, device=x.device)
-    rc = library().qi_gemm_bf16(_ptr(x), _ptr(w), _ptr(None if partial_only else out),
+    _call('gemm', "gemm_bf16", library().qi_gemm_bf16,
+          _ptr(x), _ptr(w), _ptr(None if partial_only else out),
                                 BF16 if partial_only else _code(out), M, N, K, int(swap), bn, splits, epi,
                                 _ptr(ws), _ptr(status), _stream())
-    _check(rc, "gemm_bf16")
     return ws if partial_only else out
