@@ -78,10 +78,34 @@ __device__ long long block_sum_ll(long long v, long long* scratch) {
     return t;
 }
 
+// Where a row's options come from. Two forms:
+//  * arrays with one entry per row of the logits (slot_ids null, stride 1);
+//  * records of the per-request slots: the row's request is found through the step's own device
+//    arrays (logit_rows: flat token of the row; token_req: its entry; slot_ids: the entry's slot), the
+//    options lie `stride` 32-bit words apart (the record's size), and after the draw the kernel
+//    advances the slot's counter itself (`bump`), so that the host uploads nothing per step.
+struct SampleParams {
+    const float* temperature;
+    const int* top_k;
+    const float* top_p;
+    const long long* seed;
+    int* counter;
+    const int* logit_rows;
+    const int* token_req;
+    const int* slot_ids;
+    int stride;
+    int bump;
+};
+
+__device__ __forceinline__ size_t param_index(const SampleParams& sp, int row) {
+    const int r = sp.slot_ids ? sp.slot_ids[sp.token_req[sp.logit_rows[row]]] : row;
+    return (size_t)r * (size_t)sp.stride;
+}
+// seeds are 64-bit: in a record they lie stride / 2 of their own size apart
+__device__ __forceinline__ size_t seed_index(const SampleParams& sp, size_t pi) { return sp.stride == 1 ? pi : pi / 2; }
+
 __global__ void __launch_bounds__(kThreads)
-sample_kernel(const float* __restrict__ logits, int vocab, const float* __restrict__ temperature,
-              const int* __restrict__ top_k, const float* __restrict__ top_p,
-              const long long* __restrict__ seed, const int* __restrict__ counter,
+sample_kernel(const float* __restrict__ logits, int vocab, const SampleParams sp,
               int* __restrict__ out_token, int* __restrict__ status) {
     __shared__ double sd[kNumWarps];
     __shared__ long long sl[kNumWarps];
@@ -122,16 +146,20 @@ sample_kernel(const float* __restrict__ logits, int vocab, const float* __restri
             max_i = sbest_i[w];
         }
     }
-    const float temp = temperature ? temperature[row] : 0.f;
+    const size_t pi = param_index(sp, row);
+    const float temp = sp.temperature ? sp.temperature[pi] : 0.f;
     if (!(temp > 0.f)) {
-        if (tid == 0) out_token[row] = max_i;
+        if (tid == 0) {
+            out_token[row] = max_i;
+            if (sp.bump && sp.counter) sp.counter[pi] += 1;
+        }
         return;
     }
 
     const float max_y = max_v / temp;
-    int k = top_k ? top_k[row] : 0;
+    int k = sp.top_k ? sp.top_k[pi] : 0;
     if (k <= 0 || k > vocab) k = 0;  // 0: keep all
-    float p_keep = top_p ? top_p[row] : 0.f;
+    float p_keep = sp.top_p ? sp.top_p[pi] : 0.f;
     if (!(p_keep > 0.f) || p_keep >= 1.f) p_keep = 0.f;  // 0: keep all
 
     // Threshold of the kept set: every y > thr_key is kept, and the first
@@ -212,8 +240,8 @@ sample_kernel(const float* __restrict__ logits, int vocab, const float* __restri
     }
 
     // Draw.
-    const unsigned long long sd64 = seed ? (unsigned long long)seed[row] : 0ull;
-    const uint32_t ctr = counter ? (uint32_t)counter[row] : 0u;
+    const unsigned long long sd64 = sp.seed ? (unsigned long long)sp.seed[seed_index(sp, pi)] : 0ull;
+    const uint32_t ctr = sp.counter ? (uint32_t)sp.counter[pi] : 0u;
     const uint4 rnd = philox4x32_10(make_uint4(ctr, 0u, 0u, 0u),
                                     make_uint2((uint32_t)sd64, (uint32_t)(sd64 >> 32)));
     const double target = (double)((float)(rnd.x >> 8) * (1.0f / 16777216.0f)) * total;
@@ -303,7 +331,10 @@ sample_kernel(const float* __restrict__ logits, int vocab, const float* __restri
         if (lane == 0 && found >= 0) atomicCAS(&result, -1, found);
     }
     __syncthreads();
-    if (tid == 0) out_token[row] = result >= 0 ? result : max_i;
+    if (tid == 0) {
+        out_token[row] = result >= 0 ? result : max_i;
+        if (sp.bump && sp.counter) sp.counter[pi] += 1;      // every thread read the counter before the barrier above
+    }
 }
 
 // ------------------------------------------------------------------ a row on a cluster of eight CTAs
@@ -373,9 +404,7 @@ __device__ void cluster_sum_ll2(cg::cluster_group& cluster, ClusterScratch* cs, 
 }
 
 __global__ void __cluster_dims__(kClusterSize, 1, 1) __launch_bounds__(kThreads, 1)
-sample_cluster_kernel(const float* __restrict__ logits, int vocab, int per, const float* __restrict__ temperature,
-                      const int* __restrict__ top_k, const float* __restrict__ top_p,
-                      const long long* __restrict__ seed, const int* __restrict__ counter,
+sample_cluster_kernel(const float* __restrict__ logits, int vocab, int per, const SampleParams sp,
                       int* __restrict__ out_token, int* __restrict__ status) {
     extern __shared__ float cache[];          // y[per], then w[per]
     __shared__ ClusterScratch cs;
@@ -397,7 +426,8 @@ sample_cluster_kernel(const float* __restrict__ logits, int vocab, int per, cons
     float* ws = cache + per;
     int turn = 0;
 
-    const float temp = temperature ? temperature[row] : 0.f;
+    const size_t pi = param_index(sp, row);
+    const float temp = sp.temperature ? sp.temperature[pi] : 0.f;
     const bool greedy = !(temp > 0.f);
 
     // Pass 0: this CTA's first maximum, the finiteness check, and y into shared memory.
@@ -437,7 +467,10 @@ sample_cluster_kernel(const float* __restrict__ logits, int vocab, int per, cons
         if (i != 0x7fffffff && (max_i == 0x7fffffff || v > max_v || (v == max_v && i < max_i))) { max_v = v; max_i = i; }
     }
     if (greedy) {
-        if (rank == 0 && tid == 0) out_token[row] = max_i;
+        if (rank == 0 && tid == 0) {
+            out_token[row] = max_i;
+            if (sp.bump && sp.counter) sp.counter[pi] += 1;
+        }
         cluster.sync();       // nobody leaves while a partner may still read its shared memory
         return;
     }
@@ -446,9 +479,9 @@ sample_cluster_kernel(const float* __restrict__ logits, int vocab, int per, cons
     for (int j = tid; j < n; j += kThreads) ws[j] = expf(ys[j] - max_y);
     __syncthreads();
 
-    int k = top_k ? top_k[row] : 0;
+    int k = sp.top_k ? sp.top_k[pi] : 0;
     if (k <= 0 || k > vocab) k = 0;
-    float p_keep = top_p ? top_p[row] : 0.f;
+    float p_keep = sp.top_p ? sp.top_p[pi] : 0.f;
     if (!(p_keep > 0.f) || p_keep >= 1.f) p_keep = 0.f;
 
     uint32_t thr_key = 0;
@@ -547,8 +580,8 @@ sample_cluster_kernel(const float* __restrict__ logits, int vocab, int per, cons
     }
 
     // Draw.
-    const unsigned long long sd64 = seed ? (unsigned long long)seed[row] : 0ull;
-    const uint32_t ctr = counter ? (uint32_t)counter[row] : 0u;
+    const unsigned long long sd64 = sp.seed ? (unsigned long long)sp.seed[seed_index(sp, pi)] : 0ull;
+    const uint32_t ctr = sp.counter ? (uint32_t)sp.counter[pi] : 0u;
     const uint4 rnd = philox4x32_10(make_uint4(ctr, 0u, 0u, 0u), make_uint2((uint32_t)sd64, (uint32_t)(sd64 >> 32)));
     const double target = (double)((float)(rnd.x >> 8) * (1.0f / 16777216.0f)) * total;
 
@@ -651,7 +684,10 @@ sample_cluster_kernel(const float* __restrict__ logits, int vocab, int per, cons
     }
     __threadfence();
     cluster.sync();
-    if (rank == 0 && tid == 0 && out_token[row] == 0x7fffffff) out_token[row] = max_i;
+    if (rank == 0 && tid == 0) {
+        if (out_token[row] == 0x7fffffff) out_token[row] = max_i;
+        if (sp.bump && sp.counter) sp.counter[pi] += 1;      // every CTA of the cluster read the counter before the barrier above
+    }
 }
 
 // After a decode step that ran wholly on the device: the sampled tokens become the
@@ -685,16 +721,15 @@ extern "C" int qi_advance_decode(int* token_ids, int* positions, int* start_pos,
     return qi::check_launch("advance_decode");
 }
 
-extern "C" int qi_sample(const float* logits, int rows, int vocab, const float* temperature,
-                         const int* top_k, const float* top_p, const long long* seed,
-                         const int* counter, int* out_token, int* status, cudaStream_t stream) {
-    QI_REQUIRE(rows >= 0 && vocab > 0, "sample: bad sizes rows=%d vocab=%d", rows, vocab);
-    if (rows == 0) return 0;
+namespace {
+
+int launch_sample(const float* logits, int rows, int vocab, const SampleParams& sp, int* out_token, int* status,
+                  cudaStream_t stream) {
     // rows that draw go to clusters of eight CTAs that keep the row in shared memory; all-greedy batches
     // (temperature null) and vocabularies too large for that keep the one-block kernel
     int per = (vocab + kClusterSize - 1) / kClusterSize;
     per = (per + 31) / 32 * 32;
-    if (temperature && per <= kMaxSlice && rows <= 65535 / kClusterSize) {
+    if (sp.temperature && per <= kMaxSlice && rows <= 65535 / kClusterSize) {
         const size_t smem = (size_t)per * 2 * sizeof(float);
         static size_t configured = 0;
         if (smem > configured) {
@@ -702,11 +737,54 @@ extern "C" int qi_sample(const float* logits, int rows, int vocab, const float* 
             if (e != cudaSuccess) return qi::fail("sample: cannot reserve shared memory: %s", cudaGetErrorString(e));
             configured = 2 * kMaxSlice * sizeof(float);
         }
-        qi::launch(sample_cluster_kernel, dim3(rows * kClusterSize), dim3(kThreads), smem, stream, logits, vocab, per, temperature,
-                   top_k, top_p, seed, counter, out_token, status);
+        qi::launch(sample_cluster_kernel, dim3(rows * kClusterSize), dim3(kThreads), smem, stream, logits, vocab, per, sp,
+                   out_token, status);
         return qi::check_launch("sample (cluster)");
     }
-    qi::launch(sample_kernel, dim3(rows), dim3(kThreads), 0, stream, logits, vocab, temperature, top_k, top_p, seed, counter,
-               out_token, status);
+    qi::launch(sample_kernel, dim3(rows), dim3(kThreads), 0, stream, logits, vocab, sp, out_token, status);
     return qi::check_launch("sample");
+}
+
+}  // namespace
+
+// One token per row of float32 logits [rows, vocab]. The options are arrays with one entry per row; any
+// of them may be null (greedy / no truncation / seed 0 / counter 0).
+extern "C" int qi_sample(const float* logits, int rows, int vocab, const float* temperature,
+                         const int* top_k, const float* top_p, const long long* seed,
+                         const int* counter, int* out_token, int* status, cudaStream_t stream) {
+    QI_REQUIRE(rows >= 0 && vocab > 0, "sample: bad sizes rows=%d vocab=%d", rows, vocab);
+    if (rows == 0) return 0;
+    SampleParams sp = {};
+    sp.temperature = temperature; sp.top_k = top_k; sp.top_p = top_p; sp.seed = seed;
+    sp.counter = const_cast<int*>(counter);
+    sp.stride = 1;
+    return launch_sample(logits, rows, vocab, sp, out_token, status, stream);
+}
+
+// The same with the options taken from the per-request slot records: `slots` is int32
+// [num_slots, QI_SLOT_WORDS] on the device, one record a slot: temperature (float bits), top_k, top_p
+// (float bits), tokens emitted (the counter of the request's random stream), seed low and high word,
+// max_new_tokens, eos token id (-1: none). Row r of the logits belongs to the request in slot
+// slot_ids[token_req[logit_rows[r]]], the step's own arrays. After a row's token is chosen the kernel
+// adds one to the record's count of emitted tokens, so the host writes a record once, when the request
+// is admitted, and nothing per step.
+extern "C" int qi_sample_slots(const float* logits, int rows, int vocab, const int* logit_rows, const int* token_req,
+                               const int* slot_ids, int* slots, int slot_words, int all_greedy, int* out_token,
+                               int* status, cudaStream_t stream) {
+    QI_REQUIRE(rows >= 0 && vocab > 0, "sample_slots: bad sizes rows=%d vocab=%d", rows, vocab);
+    QI_REQUIRE(slot_words == 8, "sample_slots: a slot record has 8 words, got %d", slot_words);
+    QI_REQUIRE(logit_rows && token_req && slot_ids && slots, "sample_slots: a step array or the slot records are missing");
+    QI_REQUIRE(((uintptr_t)slots & 31) == 0, "sample_slots: the slot records must be 32-byte aligned");
+    if (rows == 0) return 0;
+    SampleParams sp = {};
+    // a step whose rows are all greedy takes the one-block kernel (temperature null), as with arrays
+    sp.temperature = all_greedy ? nullptr : reinterpret_cast<const float*>(slots);
+    sp.top_k = slots + 1;
+    sp.top_p = reinterpret_cast<const float*>(slots + 2);
+    sp.counter = slots + 3;
+    sp.seed = reinterpret_cast<const long long*>(slots + 4);
+    sp.logit_rows = logit_rows; sp.token_req = token_req; sp.slot_ids = slot_ids;
+    sp.stride = slot_words;
+    sp.bump = 1;
+    return launch_sample(logits, rows, vocab, sp, out_token, status, stream);
 }

@@ -77,6 +77,10 @@ class Engine:
         self.cache = CacheManager(self.model.cache_needs, page_size, num_pages, max_requests,
                                   self.max_seq_len, self.dtype, self.device)
         self._views = [self.cache.view(call.cache, call.writes_cache) for call in self.model.order]
+        from ..sampling.slots import RequestSlots
+
+        self.slots = RequestSlots(max_requests, self.device)   # the sampler's record of every slot, on the device
+        self.last_batch = None                                 # the device arrays of the step that ran last
         self._staging = [None, None]
         self._staging_event = [None, None]
         self._staging_turn = 0
@@ -109,6 +113,11 @@ class Engine:
 
     def close(self, request_id) -> None:
         self.cache.close(request_id)
+
+    def assign_sampling(self, request_id, config, emitted: int = 0) -> None:
+        """Writes the sampler's record of an open request's slot (its options and the tokens it has
+        emitted); `Sampler.sample_step` and the steps that run ahead draw by it."""
+        self.slots.assign(self.cache.get(request_id).slot, config, emitted)
 
     def length(self, request_id) -> int:
         return self.cache.get(request_id).length
@@ -197,6 +206,7 @@ class Engine:
             # a replay runs the captured kernels on whatever the device arrays then hold; host copies
             # would stay those of the capturing step, so parts get none
             batch.h_q_start = batch.h_start_pos = batch.h_kv_len = batch.h_slot_ids = ONLY_ON_THE_DEVICE
+            self.last_batch = batch
             logits = self.model.forward(batch, self._views)   # eager: warms up and gives this step's result
             torch.cuda.synchronize()
             graph = torch.cuda.CUDAGraph()
@@ -210,6 +220,7 @@ class Engine:
             return logits, g
         kernels.stage_step(host, g["meta"], device_tokens)
         event.record()
+        self.last_batch = g["batch"]
         g["graph"].replay()
         kernels.launches += g["launches"]
         return g["logits"], g
@@ -230,7 +241,7 @@ class Engine:
             if self._graph_eligible(entries):
                 logits, _ = self._graph_step(entries)
             else:
-                batch = self.make_batch(entries)
+                batch = self.last_batch = self.make_batch(entries)
                 logits = self.model.forward(batch, self._views)
             if check_status:
                 self.raise_on_status()
@@ -266,16 +277,22 @@ class Engine:
                 o, n = lay[name]
                 return g["meta"][o:o + n]
 
-            params = sampler.device_params(rows)
+            for rid, (cfg, emitted) in zip(request_ids, rows):
+                self.assign_sampling(rid, cfg, emitted)
+            greedy = all(cfg.temperature == 0.0 for cfg, _ in rows)
+            batch = g["batch"]
             history = torch.empty((n_steps, b), dtype=torch.int32, device=self.device)
+            tokens = torch.empty(b, dtype=torch.int32, device=self.device)
             for i in range(n_steps):
                 if i:
                     g["graph"].replay()
                     kernels.launches += g["launches"]
                     logits = g["logits"]
-                tokens = sampler.sample_with(logits, params)
+                # the kernel finds each row's record through the step's arrays and advances its counter
+                kernels.sample_slots(logits, batch.logit_rows, batch.token_req, batch.slot_ids, self.slots.table, greedy,
+                                     tokens, sampler.status)
                 kernels.advance_decode(part("token_ids"), part("positions"), part("start_pos"), part("kv_len"),
-                                       params["counter"], tokens, history[i])
+                                       None, tokens, history[i])
             self.raise_on_status()
         except Exception:
             for rid in prepared:

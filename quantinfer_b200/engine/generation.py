@@ -58,9 +58,12 @@ def run_requests(engine, sampler, prompts: Sequence[Sequence[int]], configs: Seq
     sequences = min(max_sequences or cache.max_requests, cache.max_requests)
     pipeline = DecodePipeline(engine, sampler) if run_ahead and engine.use_graphs else None
     # the sampler reads the step's status word together with the tokens: one wait per step
-    sched = Scheduler(cache, lambda entries: engine.step(entries, check_status=False), sampler.sample,
+    # a request's options go into its slot's record on the device when it is admitted (with the tokens it
+    # has emitted, if it comes back after a preemption); sampling then reads them there
+    sched = Scheduler(cache, lambda entries: engine.step(entries, check_status=False), sampler.sample_step,
                       vocab_size=engine.spec.vocab_size, max_sequences=sequences,
-                      max_tokens=max(max_batch_tokens, sequences), chunk_size=chunk_size, pipeline=pipeline)
+                      max_tokens=max(max_batch_tokens, sequences), chunk_size=chunk_size, pipeline=pipeline,
+                      admit_fn=lambda r: engine.assign_sampling(r.id, r.config, len(r.emitted)))
     started = time.perf_counter()
     ids = [sched.submit(list(p), cfg, timeout=timeout) for p, cfg in zip(prompts, configs)]
     results = {rid: RequestResult(list(p)) for rid, p in zip(ids, prompts)}

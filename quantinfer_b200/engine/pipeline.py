@@ -98,11 +98,13 @@ class DecodePipeline:
             for rid in request_ids:
                 eng.cache.prepare(rid, 1)
                 prepared.append(rid)
-            logits, _ = eng._graph_step(entries, device_tokens=None if prev is None else prev.device_tokens)
-            params = self.sampler.device_params(rows)
+            logits, g = eng._graph_step(entries, device_tokens=None if prev is None else prev.device_tokens)
             out = io[1:1 + b]
-            kernels.sample(logits, params["temperature"], params["top_k"], params["top_p"], params["seed"],
-                           params["counter"], out, self.sampler.status)
+            # the options and the draw counter come from the requests' slot records, which the device
+            # advances itself: a step that runs ahead needs nothing from the host for its draw
+            batch = g["batch"]
+            kernels.sample_slots(logits, batch.logit_rows, batch.token_req, batch.slot_ids, eng.slots.table,
+                                 all(cfg.temperature == 0.0 for cfg, _ in rows), out, self.sampler.status)
             turn = self._turn
             self._turn ^= 1
             if self._host[turn] is None:

@@ -98,7 +98,7 @@ class Request:
 class Scheduler:
     def __init__(self, cache, step_fn: Callable, sample_fn: Callable, *, vocab_size: int,
                  max_sequences: int = 8, max_tokens: int = 512, chunk_size: Optional[int] = None,
-                 clock: Callable[[], float] = time.monotonic, pipeline=None):
+                 clock: Callable[[], float] = time.monotonic, pipeline=None, admit_fn: Optional[Callable] = None):
         """Defaults 8 sequences and 512 tokens per step are those the reference's
         server drives its scheduler with (apps/quantinfer-server/src/config.rs:32-45)."""
         if max_sequences <= 0 or max_tokens <= 0:
@@ -121,6 +121,7 @@ class Scheduler:
         self.preemptions = 0
         self._hold_admission = False   # set by a preemption until some request gives pages back
         self.pipeline = pipeline
+        self.admit_fn = admit_fn       # called with a request when it has been given its slot and its pages' reservation
         self._inflight = None          # (requests, pending result) of a launched decode step
         self.steps_ahead = 0           # steps launched before the tokens of the step before were read
 
@@ -174,6 +175,8 @@ class Scheduler:
             r.reserved_pages = need
             self.reserved_pages += need
             self.cache.open(r.id)
+            if self.admit_fn is not None:
+                self.admit_fn(r)
             self.running.append(r)
 
     def plan(self) -> list:

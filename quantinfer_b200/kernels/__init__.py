@@ -541,6 +541,24 @@ def sample(logits, temperature, top_k, top_p, seed, counter, out_token, status) 
                              _ptr(seed), _ptr(counter), _ptr(out_token), _ptr(status), _stream())
 
 
+def sample_slots(logits, logit_rows, token_req, slot_ids, slots, all_greedy: bool, out_token, status) -> None:
+    """Token per row of float32 logits [rows, vocab] with the options of the row's request, read from
+    the slot records `slots` (int32 [num_slots, 8], sampling/slots.py). The request of row r is the one
+    in slot slot_ids[token_req[logit_rows[r]]] (the step's device arrays). The kernel adds one to the
+    record's count of emitted tokens after the draw. `all_greedy`: no row draws (the host knows)."""
+    _req(logits, "logits", torch.float32, 2)
+    _req(out_token, "out_token", torch.int32, 1)
+    _req(slots, "slots", torch.int32, 2)
+    rows, vocab = logits.shape
+    for t, name in ((logit_rows, "logit_rows"), (token_req, "token_req"), (slot_ids, "slot_ids")):
+        _req(t, name, torch.int32, 1)
+    if logit_rows.numel() < rows or out_token.numel() < rows:
+        raise KernelError(f"sample_slots: {rows} rows of logits, {logit_rows.numel()} wanted rows, {out_token.numel()} places for tokens")
+    _call("other", "sample_slots", library().qi_sample_slots,
+          _ptr(logits), rows, vocab, _ptr(logit_rows), _ptr(token_req), _ptr(slot_ids), _ptr(slots), slots.shape[1],
+          int(bool(all_greedy)), _ptr(out_token), _ptr(status), _stream())
+
+
 def advance_decode(token_ids, positions, start_pos, kv_len, counter, sampled, history) -> None:
     """In place, for a decode batch kept on the device: token_ids = sampled, positions,
     start_pos and kv_len + 1, counter + 1 (may be None), history = sampled (may be None)."""

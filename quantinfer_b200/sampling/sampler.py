@@ -36,7 +36,34 @@ class Sampler:
 
     @classmethod
     def for_engine(cls, engine) -> "Sampler":
-        return cls(engine.device, io=engine.runtime.io)
+        self = cls(engine.device, io=engine.runtime.io)
+        self.engine = engine
+        return self
+
+    def sample_step(self, logits: torch.Tensor, rows: Sequence[tuple]) -> list:
+        """As `sample`, for the logits of the engine's last step and requests whose slot records were
+        written (`Engine.assign_sampling`): the kernel reads each row's options from its request's record,
+        found through the step's device arrays, and advances the record's counter; nothing is uploaded.
+        `rows` only says how many rows there are and whether any of them draws."""
+        n = logits.shape[0]
+        if n != len(rows):
+            raise ValueError(f"{n} rows of logits for {len(rows)} requests")
+        if n == 0:
+            return []
+        engine = getattr(self, "engine", None)
+        batch = engine.last_batch if engine is not None else None
+        if batch is None or self.io is None or n + 1 > self.io.numel() or batch.n_logit_rows != n:
+            return self.sample(logits, rows)
+        out = self.io[1:1 + n]
+        greedy = all(cfg.temperature == 0.0 for cfg, _ in rows)
+        kernels.sample_slots(logits, batch.logit_rows, batch.token_req, batch.slot_ids, engine.slots.table, greedy,
+                             out, self.status)
+        host = self.io[:1 + n].cpu().tolist()          # waits for the step; status and tokens together
+        if host[0]:
+            self.status.zero_()
+            raise QuantInferError(f"the step failed on the device (status {host[0]}: "
+                                  + "; ".join(kernels.status_names(host[0])) + ")")
+        return host[1:]
 
     def sample(self, logits: torch.Tensor, rows: Sequence[tuple]) -> list:
         """`rows[i] = (GenerationConfig, emitted)` for row i of `logits`. Returns token ids."""

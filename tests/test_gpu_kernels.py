@@ -529,6 +529,43 @@ def test_sample_follows_the_distribution_and_the_counter():
     assert other != toks[:50]
 
 
+@pytest.mark.parametrize("vocab", [517, 4099])
+def test_sample_from_slot_records(vocab):
+    """The options of a row come from its request's slot record, found through the step's arrays
+    (row -> flat token -> entry -> slot), and the kernel advances the record's counter: three draws in a
+    row equal the plain sampler's with counters c, c + 1, c + 2, for requests that sit in other slots
+    than their place in the batch, greedy rows among them."""
+    from quantinfer_b200.sampling import GenerationConfig, RequestSlots
+
+    torch.manual_seed(3)
+    slots = RequestSlots(8, DEV)
+    cfgs = {5: GenerationConfig(temperature=0.8, seed=11), 2: GenerationConfig(temperature=1.2, top_k=20, seed=(1 << 40) + 5),
+            7: GenerationConfig(), 0: GenerationConfig(temperature=0.6, top_p=0.7, seed=3)}
+    start = {5: 0, 2: 9, 7: 4, 0: 100}
+    for slot, cfg in cfgs.items():
+        slots.assign(slot, cfg, start[slot])
+    # a step of four entries with 3, 1, 2 and 1 tokens; the rows wanted are the last token of each
+    slot_ids, token_req, logit_rows = I([5, 2, 7, 0]), I([0, 0, 0, 1, 2, 2, 3]), I([2, 3, 5, 6])
+    order = [5, 2, 7, 0]
+    st = torch.zeros(1, dtype=torch.int32, device=DEV)
+    for draw in range(3):
+        x = torch.randn(4, vocab) * 2
+        out = torch.empty(4, dtype=torch.int32, device=DEV)
+        _k().sample_slots(x.to(DEV), logit_rows, token_req, slot_ids, slots.table, False, out, st)
+        for r, slot in enumerate(order):
+            c = cfgs[slot]
+            assert int(out[r]) == plain_sample(x[r], c.temperature, c.top_k, c.top_p, c.seed, start[slot] + draw), (draw, slot)
+    assert int(st) == 0
+    assert slots.table[:, 3].tolist() == [103, 0, 12, 0, 0, 3, 0, 7]        # every record's counter moved by three
+    # a step that the host knows to be all greedy takes the other kernel; the counter still moves
+    slots.assign(1, GenerationConfig(), 0)
+    x = torch.randn(1, vocab)
+    out = torch.empty(1, dtype=torch.int32, device=DEV)
+    _k().sample_slots(x.to(DEV), I([0]), I([0]), I([1]), slots.table, True, out, st)
+    assert int(out[0]) == int(x[0].argmax()) and int(slots.table[1, 3]) == 1
+    assert slots.table[1].tolist()[6:] == [128, -1]                          # max_new_tokens, no eos
+
+
 def test_advance_decode():
     tok, pos, sp, kv, ctr = I([5, 6]), I([10, 20]), I([10, 20]), I([11, 21]), I([0, 3])
     hist = torch.zeros(2, dtype=torch.int32, device=DEV)
