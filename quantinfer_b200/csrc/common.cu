@@ -45,4 +45,4 @@ int check_launch(const char* what) {
 extern "C" const char* qi_last_error() { return qi::g_error; }
 
 // Bumped whenever an entry point's signature changes; the Python side checks it.
-extern "C" int qi_abi_version() { return 7; }
+extern "C" int qi_abi_version() { return 6; }

@@ -25,7 +25,7 @@ STATUS_NON_FINITE = 4
 STATUS_WAIT_TIMEOUT = 8
 STATUS_BAD_RANGE = 16
 
-ABI_VERSION = 7
+ABI_VERSION = 6
 
 
 def status_names(code: int) -> list:
@@ -706,86 +706,3 @@ def gemm_bf16(x: torch.Tensor, w: torch.Tensor, out, plan=None, status=None, epi
                                 BF16 if partial_only else _code(out), M, N, K, int(swap), bn, splits, epi,
                                 _ptr(ws), _ptr(status), _stream())
     return ws if partial_only else out
-
-
-# --------------------------------------------------------------------------
-# a chain of a decode step's products and norms in one persistent kernel
-
-
-class _ChainPhase(C.Structure):
-    _fields_ = [("kind", C.c_int), ("N", C.c_int), ("K", C.c_int), ("splits", C.c_int), ("epi", C.c_int),
-                ("w", C.c_void_p), ("x", C.c_void_p), ("out", C.c_void_p), ("resid", C.c_void_p), ("delta", C.c_void_p),
-                ("delta_splits", C.c_int), ("hidden", C.c_int), ("gain", C.c_void_p), ("eps", C.c_float),
-                ("x_out", C.c_void_p)]
-
-
-CHAIN_MAX_PHASES = 6
-CHAIN_MAX_TOKENS = 64
-
-
-def chain_splits(N: int, K: int, allow_split: bool = True) -> int:
-    """Into how many parts `gemm_chain` should cut K of a product with weights [N, K]."""
-    return int(library().qi_gemm_chain_splits(N, K, int(bool(allow_split))))
-
-
-def chain_product(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, splits: int = 1, epilogue: str | None = None):
-    """A product phase of `gemm_chain`: x[tokens, K] . w[N, K]^T, both bfloat16. `out` is float32
-    [splits, tokens, N] (partial sums, added by the consumer), or with epilogue="silu_mul" (w's rows in
-    (gate, up) pairs, splits 1) bfloat16 [tokens, N / 2]."""
-    _req(x, "x", torch.bfloat16, 2)
-    _req(w, "w", torch.bfloat16, 2)
-    tokens, K = x.shape
-    N = w.shape[0]
-    if w.shape[1] != K:
-        raise KernelError(f"chain_product: x {tuple(x.shape)} and w {tuple(w.shape)} do not agree")
-    if epilogue == "silu_mul":
-        _req(out, "out", torch.bfloat16, 2)
-        if splits != 1 or tuple(out.shape) != (tokens, N // 2):
-            raise KernelError(f"chain_product: the fused activation writes [tokens, N / 2] without a K split; out is {tuple(out.shape)}")
-    elif epilogue is None:
-        _req(out, "out", torch.float32, 3)
-        if tuple(out.shape) != (splits, tokens, N):
-            raise KernelError(f"chain_product: out is {tuple(out.shape)}, expected {(splits, tokens, N)}")
-    else:
-        raise KernelError(f"chain_product: unknown epilogue {epilogue!r}")
-    ph = _ChainPhase(kind=0, N=N, K=K, splits=splits, epi=1 if epilogue else 0, w=w.data_ptr(), x=x.data_ptr(), out=out.data_ptr())
-    ph._keep = (x, w, out)
-    return ph
-
-
-def chain_norm(resid: torch.Tensor, delta, gain: torch.Tensor, eps: float, x_out: torch.Tensor):
-    """A norm phase of `gemm_chain`: resid[tokens, hidden] (float32, in place) += the sum over delta's
-    first dimension (float32 [splits, tokens, hidden], or None); x_out = rmsnorm(resid) * gain as bfloat16."""
-    _req(resid, "resid", torch.float32, 2)
-    _req(gain, "gain", torch.float32, 1)
-    _req(x_out, "x_out", torch.bfloat16, 2)
-    tokens, hidden = resid.shape
-    if gain.numel() != hidden or tuple(x_out.shape) != (tokens, hidden):
-        raise KernelError(f"chain_norm: resid {tuple(resid.shape)}, gain {tuple(gain.shape)}, x_out {tuple(x_out.shape)} do not agree")
-    splits = 0
-    if delta is not None:
-        _req(delta, "delta", torch.float32, 3)
-        if tuple(delta.shape[1:]) != (tokens, hidden):
-            raise KernelError(f"chain_norm: delta {tuple(delta.shape)} does not match resid {tuple(resid.shape)}")
-        splits = delta.shape[0]
-    ph = _ChainPhase(kind=1, hidden=hidden, resid=resid.data_ptr(), delta=0 if delta is None else delta.data_ptr(),
-                     delta_splits=splits, gain=gain.data_ptr(), eps=float(eps), x_out=x_out.data_ptr())
-    ph._keep = (resid, delta, gain, x_out)
-    return ph
-
-
-def gemm_chain(phases, tokens: int, counters: torch.Tensor, status: torch.Tensor) -> None:
-    """Runs up to CHAIN_MAX_PHASES phases (`chain_product`, `chain_norm`), each reading what the ones
-    before it wrote, in one persistent kernel whose weight stream does not stop between them.
-    `counters`: int32, at least len(phases) entries, all zero (the kernel counts there)."""
-    n = len(phases)
-    if not 1 <= n <= CHAIN_MAX_PHASES:
-        raise KernelError(f"gemm_chain: {n} phases; one launch takes 1 to {CHAIN_MAX_PHASES}")
-    if not 1 <= tokens <= CHAIN_MAX_TOKENS:
-        raise KernelError(f"gemm_chain: {tokens} tokens; the chain takes 1 to {CHAIN_MAX_TOKENS}")
-    _req(counters, "counters", torch.int32, 1)
-    _req(status, "status", torch.int32)
-    if counters.numel() < n:
-        raise KernelError("gemm_chain: fewer counters than phases")
-    arr = (_ChainPhase * n)(*phases)
-    _call("gemm", "gemm_chain", library().qi_gemm_chain, arr, n, tokens, _ptr(counters), _ptr(status), _stream())

@@ -572,89 +572,3 @@ def test_advance_decode():
     _k().advance_decode(tok, pos, sp, kv, ctr, I([77, 88]), hist)
     assert tok.tolist() == [77, 88] and pos.tolist() == [11, 21] and sp.tolist() == [11, 21]
     assert kv.tolist() == [12, 22] and ctr.tolist() == [1, 4] and hist.tolist() == [77, 88]
-
-
-# ------------------------------------------------------------------ the chain of a decode step's products and norms
-
-
-def _bf(t):
-    return t.to(torch.bfloat16).float()
-
-
-@pytest.mark.parametrize("tokens, hidden, heads_width, inter, qkv_width, splits", [
-    (5, 136, 96, 200, 320, (1, 2, 1)),          # nothing a power of two, K tails that TMA fills with zeros
-    (1, 1024, 2048, 1536, 1280, (4, 2, 4)),     # one token, K cut into parts
-    (40, 256, 512, 640, 40000, (2, 1, 1)),      # 64-wide token tile; a last product with more tiles than CTAs
-    (17, 512, 1024, 768, 384, (16, 4, 8)),      # 32-wide token tile, many parts
-])
-def test_gemm_chain_against_the_formulas(tokens, hidden, heads_width, inter, qkv_width, splits):
-    """The stretch of a layer that one chain kernel runs: output projection, add + norm, gate_up with
-    silu(gate) * up, down projection, add + norm, the next layer's q/k/v projection. Every phase reads
-    what the phases before it wrote. Against float64 formulas with bfloat16 rounding where the kernel
-    stores bfloat16."""
-    k = _k()
-    torch.manual_seed(tokens + hidden)
-    s_o, s_d, s_q = splits
-    attn = torch.randn(tokens, heads_width).to(torch.bfloat16)
-    w_o = (torch.randn(hidden, heads_width) * 0.05).to(torch.bfloat16)
-    w_gu = (torch.randn(2 * inter, hidden) * 0.05).to(torch.bfloat16)       # rows in (gate, up) pairs
-    w_d = (torch.randn(hidden, inter) * 0.05).to(torch.bfloat16)
-    w_q = (torch.randn(qkv_width, hidden) * 0.05).to(torch.bfloat16)
-    g2, g1 = 1 + 0.1 * torch.randn(hidden), 1 + 0.1 * torch.randn(hidden)
-    resid0 = torch.randn(tokens, hidden)
-    eps = 1e-5
-    dev = lambda t: t.to(DEV).contiguous()
-    resid = dev(resid0)
-    p_o = torch.full((s_o, tokens, hidden), 7.0, device=DEV)            # stale values must be overwritten, not added to
-    x2 = torch.empty((tokens, hidden), dtype=torch.bfloat16, device=DEV)
-    act = torch.empty((tokens, inter), dtype=torch.bfloat16, device=DEV)
-    p_d = torch.full((s_d, tokens, hidden), -3.0, device=DEV)
-    x1 = torch.empty((tokens, hidden), dtype=torch.bfloat16, device=DEV)
-    p_q = torch.full((s_q, tokens, qkv_width), 5.0, device=DEV)
-    wo, wgu, wd, wq, a = dev(w_o), dev(w_gu), dev(w_d), dev(w_q), dev(attn)
-    phases = [k.chain_product(a, wo, p_o, s_o), k.chain_norm(resid, p_o, dev(g2), eps, x2),
-              k.chain_product(x2, wgu, act, 1, "silu_mul"), k.chain_product(act, wd, p_d, s_d),
-              k.chain_norm(resid, p_d, dev(g1), eps, x1), k.chain_product(x1, wq, p_q, s_q)]
-    counters = torch.zeros(8, dtype=torch.int32, device=DEV)
-    status = torch.zeros(1, dtype=torch.int32, device=DEV)
-    k.gemm_chain(phases, tokens, counters, status)
-    torch.cuda.synchronize()
-    assert int(status) == 0
-    assert counters[:6].tolist() == [counters[0].item()] * 6 and counters[0].item() >= 148     # every CTA counted every phase
-
-    def rms(x, g):
-        return x * torch.rsqrt((x * x).mean(dim=-1, keepdim=True) + eps) * g.double()
-
-    o = attn.double() @ w_o.double().t()
-    r1 = resid0.double() + o
-    e_x2 = _bf(rms(r1, g2)).double()
-    gu = e_x2 @ w_gu.double().t()
-    e_act = _bf(gu[:, 0::2] / (1 + torch.exp(-gu[:, 0::2])) * gu[:, 1::2]).double()
-    r2 = r1 + e_act @ w_d.double().t()
-    e_x1 = _bf(rms(r2, g1)).double()
-    e_q = e_x1 @ w_q.double().t()
-    close = lambda got, want, tol: float((got.double().cpu() - want).abs().max()) <= tol * max(1.0, float(want.abs().max()))
-    assert close(p_o.sum(0), o, 1e-4)
-    assert close(x2, e_x2, 1e-2)
-    assert close(act, e_act, 2e-2)
-    assert close(resid, r2, 2e-3)
-    assert close(x1, e_x1, 1.5e-2)
-    assert close(p_q.sum(0), e_q, 2e-2)
-    # and against the kernels that run the same phases one by one (the same roundings: close to the last bit)
-    y = k.gemm_bf16(x1, wq, torch.empty((tokens, qkv_width), dtype=torch.float32, device=DEV), plan=(1, 16 if tokens <= 16 else 32 if tokens <= 32 else 64, 1))
-    assert float((p_q.sum(0) - y).abs().max()) <= 1e-3 * max(1.0, float(y.abs().max()))
-
-
-def test_gemm_chain_refuses_what_it_does_not_cover():
-    k = _k()
-    x = torch.zeros((65, 64), dtype=torch.bfloat16, device=DEV)
-    w = torch.zeros((128, 64), dtype=torch.bfloat16, device=DEV)
-    out = torch.zeros((1, 65, 128), device=DEV)
-    ctr, st = torch.zeros(8, dtype=torch.int32, device=DEV), torch.zeros(1, dtype=torch.int32, device=DEV)
-    with pytest.raises(k.KernelError, match="1 to 64"):
-        k.gemm_chain([k.chain_product(x, w, out)], 65, ctr, st)
-    with pytest.raises(k.KernelError, match="phases"):
-        k.gemm_chain([k.chain_product(x[:4], w, out[:, :4].contiguous())] * 7, 4, ctr, st)
-    bad = torch.zeros((4, 60), dtype=torch.bfloat16, device=DEV)
-    with pytest.raises(k.KernelError, match="multiple of 8"):
-        k.gemm_chain([k.chain_product(bad, torch.zeros((128, 60), dtype=torch.bfloat16, device=DEV), torch.zeros((1, 4, 128), device=DEV))], 4, ctr, st)
