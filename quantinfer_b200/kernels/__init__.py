@@ -74,7 +74,20 @@ def library_file() -> str:
 
 
 def _stream() -> C.c_void_p:
-    return C.c_void_p(torch.cuda.current_stream().cuda_stream)
+    """The current CUDA stream of the current device, as the raw handle the entry points take. (Through
+    torch's C binding: `torch.cuda.current_stream()` builds a Python object and costs about as much as
+    a whole launch; a step of a few hundred launches asks this a few hundred times.)"""
+    return C.c_void_p(_raw_stream(_current_device()))
+
+
+try:
+    _raw_stream = torch._C._cuda_getCurrentRawStream
+    _current_device = torch._C._cuda_getDevice
+except AttributeError:      # another torch: the public, slower way
+    def _raw_stream(index):
+        return torch.cuda.current_stream(index).cuda_stream
+
+    _current_device = torch.cuda.current_device
 
 
 launches = 0   # entry points called so far (each launches at least one kernel)
@@ -667,9 +680,16 @@ def gemm_bf16_plan(M: int, N: int, K: int, allow_split: bool = True):
     product whose epilogue needs the whole sum (the fused activation). Orientation 0: the tokens
     ride the 128 rows of the tensor-core tile; 1: the weights do (few tokens); 2: tokens on the rows
     of tiles of 256 x 256 computed by pairs of CTAs (many tokens)."""
-    swap, bn, splits = C.c_int(), C.c_int(), C.c_int()
-    library().qi_gemm_bf16_plan(M, N, K, int(allow_split), C.byref(swap), C.byref(bn), C.byref(splits))
-    return swap.value, bn.value, splits.value
+    key = (M, N, K, bool(allow_split))
+    plan = _plans.get(key)
+    if plan is None:
+        swap, bn, splits = C.c_int(), C.c_int(), C.c_int()
+        library().qi_gemm_bf16_plan(M, N, K, int(allow_split), C.byref(swap), C.byref(bn), C.byref(splits))
+        plan = _plans[key] = (swap.value, bn.value, splits.value)
+    return plan
+
+
+_plans = {}
 
 
 def gemm_bf16(x: torch.Tensor, w: torch.Tensor, out, plan=None, status=None, epilogue: str | None = None,
