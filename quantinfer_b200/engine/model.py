@@ -12,6 +12,7 @@ from __future__ import annotations
 
 import torch
 
+from .. import kernels
 from ..config.spec import ModelSpec
 from ..errors import ConfigError
 from ..parts import Runtime, build_part, part_class
@@ -40,6 +41,8 @@ class Model:
         if spec.head.tied:
             self.head.tie(self.embedding)
         self.order = spec.order
+        self.native = None            # the C++ driver's description of this model (engine/native.py), once asked for
+        self.use_native = True
         # what each cache entry must hold comes from the layer that writes it
         self.cache_needs = [None] * spec.cache_entries()
         for call in self.order:
@@ -74,7 +77,16 @@ class Model:
         return total
 
     def forward(self, batch, cache_views) -> torch.Tensor:
-        """Runs the batch's tokens; returns float32 logits [len(batch.logit_rows), vocab]."""
+        """Runs the batch's tokens; returns float32 logits [len(batch.logit_rows), vocab]. A model whose
+        parts are all of the kinds the library's C++ driver knows runs through it (one call a step);
+        any other, and any step while kernels are being left out for a measurement, runs part by part."""
+        if self.use_native and not kernels.knock_out:
+            if self.native is None:
+                from .native import NativeProgram
+
+                self.native = NativeProgram.build(self, cache_views) or False
+            if self.native:
+                return self.native.forward(batch)
         resid = self.embedding(batch.token_ids)
         delta = None
         for call, view in zip(self.order, cache_views):
