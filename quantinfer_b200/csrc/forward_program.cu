@@ -123,6 +123,8 @@ constexpr int kMaxGroups = 8;
 
 struct QiStep {               // one step's batch (engine/batch.py): counts and device arrays
     int n_tokens, n_requests, n_logit_rows, all_decode, max_kv_len, n_tiles;
+    int n_lead_decode;        // mixed steps: entries of one token at the front, which the tile lists leave out
+    int reserved;
     const int* token_ids;
     const int* positions;
     const int* token_req;
@@ -275,6 +277,22 @@ void attend(Run& r, const QiBlock& B, const QiCall& c, const void* q, void* out)
             });
             return;
         }
+        // a mixed step: the entries of one token at its front go to the decode kernel (their rows of q and out
+        // are the first rows), the others, which the tile lists hold, to the flash kernel
+        if (b.n_lead_decode > 0) {
+            const int lead = b.n_lead_decode;
+            int chunk = 0, splits = 0;
+            decode_plan(lead, B.nkv, b.max_kv_len, &chunk, &splits);
+            const long long n_o = (long long)lead * B.nq * splits * B.d;
+            float* ws = (float*)r.arena.take((n_o + (long long)lead * B.nq * splits * 2) * 4);
+            const bool tma = qi_attention_tma_supported(B.nq, B.nkv, B.d, c.page_size, max_blocks);
+            r.call([&] {
+                return (tma ? qi_attention_decode_tma : qi_attention_decode)(
+                    q, out, c.k_pages, c.v_pages, table, max_blocks, c.page_size, c.num_pages, b.kv_len, b.q_start, lead, B.nq,
+                    B.nkv, B.d, B.scale, B.window, chunk, splits, ws, ws + n_o, m.status, r.stream);
+            });
+        }
+        if (b.n_tiles == 0) return;
         if (qi_attention_prefill_tcgen05_supported(B.nq, B.nkv, B.d, c.page_size, max_blocks)) {
             int ranges = prefill_ranges((long long)B.nq * b.n_tiles, b.max_kv_len);
             if (b.n_tokens > 65535) ranges = 1;

@@ -12,7 +12,10 @@ Device arrays (int32), all views of one buffer that crosses in one copy:
     token_ids[n]   positions[n]   token_req[n]      per token (token_req: index of its entry)
     q_start[b+1]   start_pos[b]   kv_len[b]   slot_ids[b]      per entry
     logit_rows[r]                                    rows of the flattened batch whose logits are wanted
-    tile_req[t]    tile_q0[t]                        blocks of up to 128 query rows of one entry (longest context first)
+    tile_req[t]    tile_q0[t]                        blocks of up to 128 query rows of one entry (longest context first);
+                                                     in a step that mixes decode tokens and prompt portions the entries
+                                                     of one token that stand first are left out (n_lead_decode of them):
+                                                     the split-key decode kernel takes those, the flash kernel the rest
     block_tables[g][b, max_blocks]                   per layer group
 """
 
@@ -90,6 +93,7 @@ class StepBatch:
     max_q_len: int = 0
     max_kv_len: int = 0
     all_decode: bool = False
+    n_lead_decode: int = 0      # mixed steps: entries of one token at the front, which the tile lists leave out
     extra: dict = field(default_factory=dict)   # what fast kernels derive once per step (work lists)
 
 
@@ -104,12 +108,21 @@ def pack_batch(entries: Sequence[StepEntry], starts: Sequence[int], slots: Seque
     n = sum(lens)
     r = sum(len(e.want) for e in entries)
     n_groups = len(tables)
+    # Entries of one token at the front of a step that also holds longer entries (the scheduler puts the
+    # decode tokens first): their attention is the decode kernel's work, where the query heads of a group
+    # share each key and the keys are split over CTAs; as query tiles of their own they would each read
+    # their whole context once per query head.
+    n_lead = 0
+    if any(ln > 1 for ln in lens):
+        while n_lead < b and lens[n_lead] == 1:
+            n_lead += 1
     # blocks of QUERY_TILE query rows; those that read the most keys go first
     tiles = []
     a = 0
     for i, ln in enumerate(lens):
         for t0 in range(0, ln, QUERY_TILE):
-            tiles.append((-(starts[i] + min(t0 + QUERY_TILE, ln)), i, a + t0))
+            if i >= n_lead:
+                tiles.append((-(starts[i] + min(t0 + QUERY_TILE, ln)), i, a + t0))
         a += ln
     tiles.sort()
     layout, off = {}, 0
@@ -147,6 +160,7 @@ def pack_batch(entries: Sequence[StepEntry], starts: Sequence[int], slots: Seque
             ri += 1
     for g in range(n_groups):
         part(f"table{g}").reshape(b, max_blocks)[:] = tables[g][list(slots)]
+    layout["n_lead_decode"] = n_lead
     return buf, layout, q_start, lens
 
 
@@ -158,6 +172,7 @@ def batch_from_packed(dev: torch.Tensor, layout: dict, entries, starts, slots, q
 
     b = len(entries)
     kv = [s + l for s, l in zip(starts, lens)]
+    n_lead = layout.get("n_lead_decode", 0)
     return StepBatch(
         n_tokens=int(q_start[-1]), n_requests=b, n_logit_rows=layout["logit_rows"][1],
         token_ids=part("token_ids"), positions=part("positions"), token_req=part("token_req"),
@@ -167,5 +182,5 @@ def batch_from_packed(dev: torch.Tensor, layout: dict, entries, starts, slots, q
         block_tables=[part(f"table{g}").view(b, max_blocks) for g in range(n_groups)],
         h_q_start=[int(x) for x in q_start], h_start_pos=list(starts), h_kv_len=kv,
         h_slot_ids=list(slots), max_q_len=max(lens) if lens else 0, max_kv_len=max(kv) if kv else 0,
-        all_decode=all(l == 1 for l in lens),
+        all_decode=all(l == 1 for l in lens), n_lead_decode=n_lead,
     )

@@ -52,7 +52,7 @@ class _ModelDesc(C.Structure):
 
 class _Step(C.Structure):
     _fields_ = [("n_tokens", C.c_int), ("n_requests", C.c_int), ("n_logit_rows", C.c_int), ("all_decode", C.c_int),
-                ("max_kv_len", C.c_int), ("n_tiles", C.c_int),
+                ("max_kv_len", C.c_int), ("n_tiles", C.c_int), ("n_lead_decode", C.c_int), ("reserved", C.c_int),
                 ("token_ids", C.c_void_p), ("positions", C.c_void_p), ("token_req", C.c_void_p), ("q_start", C.c_void_p),
                 ("start_pos", C.c_void_p), ("kv_len", C.c_void_p), ("logit_rows", C.c_void_p), ("tile_req", C.c_void_p),
                 ("tile_q0", C.c_void_p), ("block_tables", C.c_void_p * MAX_GROUPS), ("max_blocks", C.c_int * MAX_GROUPS)]
@@ -114,13 +114,13 @@ class NativeProgram:
         """Runs the batch; float32 logits [len(batch.logit_rows), vocab]."""
         lib = kernels.library()
         step = _Step(batch.n_tokens, batch.n_requests, batch.n_logit_rows, int(batch.all_decode), batch.max_kv_len,
-                     batch.tile_req.numel(), batch.token_ids.data_ptr(), batch.positions.data_ptr(), batch.token_req.data_ptr(),
+                     batch.tile_req.numel(), batch.n_lead_decode, 0, batch.token_ids.data_ptr(), batch.positions.data_ptr(), batch.token_req.data_ptr(),
                      batch.q_start.data_ptr(), batch.start_pos.data_ptr(), batch.kv_len.data_ptr(), batch.logit_rows.data_ptr(),
                      batch.tile_req.data_ptr(), batch.tile_q0.data_ptr())
         for g, table in enumerate(batch.block_tables):
             step.block_tables[g] = table.data_ptr()
             step.max_blocks[g] = table.shape[1]
-        key = (batch.n_tokens, batch.n_requests, batch.n_logit_rows, batch.all_decode, batch.max_kv_len, step.n_tiles,
+        key = (batch.n_tokens, batch.n_requests, batch.n_logit_rows, batch.all_decode, batch.max_kv_len, step.n_tiles, batch.n_lead_decode,
                tuple(t.shape[1] for t in batch.block_tables))
         need = self._sizes.get(key)
         if need is None:

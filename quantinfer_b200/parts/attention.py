@@ -125,10 +125,19 @@ class Attention(Part):
                                          self.nq, self.nkv, self.d, self.scale, self.spec.window or 0, chunk,
                                          splits, rt.status)
             else:
-                kernels.attention_prefill(q, out, cache.k_pages, cache.v_pages, table, batch.q_start,
-                                          batch.start_pos, batch.tile_req, batch.tile_q0, self.nq, self.nkv,
-                                          self.d, self.scale, self.spec.window or 0, rt.status,
-                                          max_kv_len=batch.max_kv_len)
+                # a mixed step: the entries of one token at its front go to the decode kernel (their rows of q
+                # and out are the first rows), the others, which the tile lists hold, to the flash kernel
+                lead = batch.n_lead_decode
+                if lead:
+                    chunk, splits = kernels.attention_decode_plan(lead, self.nkv, batch.max_kv_len)
+                    kernels.attention_decode(q, out, cache.k_pages, cache.v_pages, table[:lead], batch.kv_len[:lead],
+                                             batch.q_start[:lead], self.nq, self.nkv, self.d, self.scale,
+                                             self.spec.window or 0, chunk, splits, rt.status)
+                if batch.tile_req.numel():
+                    kernels.attention_prefill(q, out, cache.k_pages, cache.v_pages, table, batch.q_start,
+                                              batch.start_pos, batch.tile_req, batch.tile_q0, self.nq, self.nkv,
+                                              self.d, self.scale, self.spec.window or 0, rt.status,
+                                              max_kv_len=batch.max_kv_len)
             return
         kernels.attention_generic(q, out, cache.k_pages, cache.v_pages, table, batch.positions,
                                   batch.token_req, self.nq, self.nkv, self.d, self.scale,

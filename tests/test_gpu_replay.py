@@ -153,3 +153,46 @@ def test_a_wrong_page_in_a_block_table_shows(tiny_folders, tmp_path_factory, nam
     others = {k: v for k, v in got.items() if k[0] != state["done"]}
     worst_others, where = worst_diff(others, {k: expect[k] for k in others})
     assert worst_others <= tol(name, "bfloat16", sharp=True), f"{worst_others} at {where}"
+
+
+@pytest.mark.parametrize("name", ["B", "D", "E"])
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_decode_tokens_in_front_of_prompt_portions(tiny_folders, name, dtype):
+    """The steps a scheduler makes while it takes new prompts in: single decode tokens of running requests
+    first, then portions of prompts. In such a step the decode kernel serves the entries in front and the
+    flash kernel the portions (two launches over one batch); every row against the plain whole sequence."""
+    folder = tiny_folders[name]
+    reqs = _requests(folder, name)
+    long_enough = [r for r in reqs if len(reqs[r]) >= 30]
+    decoders, feeders = long_enough[:3], long_enough[3:5]
+    ids = decoders + feeders
+    assert len(ids) == 5
+    steps = []
+    pos = {r: 0 for r in ids}
+
+    def entry(r, n):
+        e = {"id": r, "tokens": reqs[r][pos[r]:pos[r] + n], "want": list(range(min(n, len(reqs[r]) - pos[r])))}
+        pos[r] += len(e["tokens"])
+        return e
+
+    def step(entries):
+        end = [e["id"] for e in entries if pos[e["id"]] == len(reqs[e["id"]])]
+        steps.append({"step": len(steps), "entries": entries, "end": end})
+
+    for r in decoders:                                   # all but the last 12 tokens of the three that will decode
+        step([entry(r, len(reqs[r]) - 12)])
+    sizes = [17, 2, 300, 64, 5, 130, 3, 40, 9, 31, 2, 200]
+    for i in range(12):
+        entries = [entry(r, 1) for r in decoders]
+        for f in feeders:
+            if pos[f] < len(reqs[f]):
+                entries.append(entry(f, sizes[(i + len(entries)) % len(sizes)]))
+        step(entries)
+    for f in feeders:                                    # what is left of the prompts
+        while pos[f] < len(reqs[f]):
+            step([entry(f, 50)])
+    assert sum(1 for s in steps if len(s["entries"]) >= 4 and len(s["entries"][0]["tokens"]) == 1 and len(s["entries"][-1]["tokens"]) > 1) >= 3
+    got = run_trace_engine(folder, dtype, steps, sum(round64(len(reqs[r])) for r in ids), PAGE_SIZES[name])
+    expect = {k: v for k, v in _expect(folder, name).items() if k[0] in ids}
+    worst, where = worst_diff(got, expect)
+    assert worst <= tol(name, dtype), f"worst difference {worst} at (request, position) {where}"
