@@ -306,21 +306,24 @@ class Bench:
                 kernels.knock_out = frozenset()
                 self.engine._graphs.clear()
 
-        out = {"note": "alone: only this class runs; left_out: full step less the step without it"}
-        sum_alone = [0.0, 0.0]
+        out = {"note": "alone: only this class runs; left_out: full step less the step without it. decode fractions "
+                       "from alone (graph replays, no host in it), prefill fractions from left_out (a class alone is "
+                       "too short a step for its host)"}
+        rest = [full_decode_ms, full_prefill_ms]
         for cls in ("gemm", "attention", "norm"):
             d_alone, p_alone = timed([c for c in every if c != cls])
             d_without, p_without = timed([cls])
+            p_cost = full_prefill_ms - p_without
             row = {"decode_alone_ms": round(d_alone, 4), "decode_left_out_ms": round(full_decode_ms - d_without, 4),
-                   "prefill_alone_ms": round(p_alone, 4), "prefill_left_out_ms": round(full_prefill_ms - p_without, 4)}
-            sum_alone[0] += d_alone
-            sum_alone[1] += p_alone
-            if cls in work:
-                gbs, tf = work[cls][0] / (d_alone * 1e-3) / 1e9, work[cls][1] / (p_alone * 1e-3) / 1e12
+                   "prefill_alone_ms": round(p_alone, 4), "prefill_left_out_ms": round(p_cost, 4)}
+            rest[0] -= d_alone
+            rest[1] -= p_cost
+            if cls in work and d_alone > 0 and p_cost > 0:
+                gbs, tf = work[cls][0] / (d_alone * 1e-3) / 1e9, work[cls][1] / (p_cost * 1e-3) / 1e12
                 row.update({"decode_gbs": round(gbs, 1), "decode_frac_hbm": round(gbs / hbm, 3), "prefill_tflops": round(tf, 1),
                             "prefill_frac_burst": round(tf / burst, 3), "prefill_frac_sustained": round(tf / sustained, 3)})
             out[cls] = row
-        out["rest"] = {"decode_ms": round(full_decode_ms - sum_alone[0], 4), "prefill_ms": round(full_prefill_ms - sum_alone[1], 4)}
+        out["rest"] = {"decode_ms": round(rest[0], 4), "prefill_ms": round(rest[1], 4)}
         return out
 
 
