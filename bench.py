@@ -227,7 +227,8 @@ class Bench:
         rows = [(GenerationConfig(max_new_tokens=1 << 20), 0)] * batch
         first = [1 + i for i in range(batch)]
         hist = engine.decode_on_device(ids, first, warmup, rows, self.sampler)
-        last = hist[-1].tolist()
+        vocab = self.spec.vocab_size
+        last = [t if 0 <= t < vocab else 1 for t in hist[-1].tolist()]      # (with kernels left out the tokens mean nothing)
         torch.cuda.synchronize()
         clocks = ClockSampler() if sample_clocks else None
         before = kernels.launches
