@@ -362,6 +362,9 @@ def mixed_workload(args, entry):
                    "token_budget": args.mixed_budget, "chunk": args.mixed_chunk or args.mixed_budget,
                    "context": w["context"], "temperature": w["temperature"], "clocks": clocks.stop()}
     del model, engine
+    import gc
+
+    gc.collect()
     torch.cuda.empty_cache()
     return out
 
@@ -444,6 +447,9 @@ def main() -> int:
         "peaks": peak_src, "load_s": round(bench.load_s, 1),
     }
     del bench, engine
+    import gc
+
+    gc.collect()
     torch.cuda.empty_cache()
     mixed = None if args.skip_mixed else mixed_workload(args, entry)
 

@@ -64,7 +64,7 @@ def _linear(lin) -> _Linear:
 
 class NativeProgram:
     def __init__(self, model, desc, keep):
-        self.model = model
+        self.vocab_size = model.spec.vocab_size      # (no reference to the model: it holds this object)
         self.desc = desc
         self._keep = keep          # the arrays the description points into
         self._sizes = {}           # step geometry -> workspace bytes
@@ -133,7 +133,7 @@ class NativeProgram:
             self._sizes[key] = need
         device = batch.token_ids.device
         workspace = torch.empty(need, dtype=torch.uint8, device=device)
-        logits = torch.empty((batch.n_logit_rows, self.model.spec.vocab_size), dtype=torch.float32, device=device)
+        logits = torch.empty((batch.n_logit_rows, self.vocab_size), dtype=torch.float32, device=device)
         launched = C.c_int(0)
         rc = lib.qi_forward(C.byref(self.desc), C.byref(step), C.c_void_p(workspace.data_ptr()), C.c_longlong(need),
                             C.c_void_p(logits.data_ptr() if batch.n_logit_rows else 0), C.byref(launched), kernels._stream())
