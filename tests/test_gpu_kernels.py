@@ -572,3 +572,40 @@ def test_advance_decode():
     _k().advance_decode(tok, pos, sp, kv, ctr, I([77, 88]), hist)
     assert tok.tolist() == [77, 88] and pos.tolist() == [11, 21] and sp.tolist() == [11, 21]
     assert kv.tolist() == [12, 22] and ctr.tolist() == [1, 4] and hist.tolist() == [77, 88]
+
+
+# ------------------------------------------------------------------ lengths that a launch does not cover are flagged
+
+
+def test_lengths_beyond_what_a_launch_covers_set_a_status_bit():
+    """A position beyond the rotation table, and keys beyond the key ranges of a decode launch: the
+    kernels read nothing out of range and drop nothing silently, they set STATUS_BAD_RANGE (the engine
+    never passes such lengths; an embedder of the C symbols might)."""
+    k = _k()
+    torch.manual_seed(1)
+    nq, nkv, d, ps = 4, 2, 64, 16
+    # (1) the rotation table has 32 rows, one token stands at position 40
+    inv_freq = torch.pow(torch.tensor(1e4), -(2.0 * torch.arange(d // 2)) / d)
+    cos, sin = k.rope_table(inv_freq.to(DEV), 32)
+    qkv = torch.randn(2, (nq + 2 * nkv) * d, device=DEV)
+    q_out = torch.empty(2, nq * d, device=DEV)
+    table = I([[0, 1, 2, 3]])
+    kp = torch.zeros(4, nkv, ps, d, device=DEV)
+    vp = torch.zeros_like(kp)
+    for positions, want in (([3, 31], 0), ([3, 40], k.STATUS_BAD_RANGE)):
+        st = _status()
+        k.qk_norm_rope_kv(qkv, q_out, None, None, 1e-6, cos, sin, d, I(positions), I([0, 0]), table, ps, kp, vp, nq, nkv, d, st)
+        assert st.item() == want, positions
+    assert torch.isfinite(q_out).all()
+    # (2) two key ranges of 64 keys cover 128 positions; one request holds 200
+    ctx = [100, 200]
+    max_blocks = -(-max(ctx) // ps)
+    pages = torch.randn(2 * max_blocks, nkv, ps, d, device=DEV).bfloat16()
+    tbl = torch.arange(2 * max_blocks, dtype=torch.int32, device=DEV).view(2, max_blocks)
+    q = torch.randn(2, nq * d, device=DEV).bfloat16()
+    out = torch.empty_like(q)
+    for n_splits, want in ((4, 0), (2, k.STATUS_BAD_RANGE)):
+        st = _status()
+        k.attention_decode(q, out, pages, pages, tbl, I(ctx), I([0, 1, 2]), nq, nkv, d, d ** -0.5, 0, 64, n_splits, st)
+        assert st.item() == want, n_splits
+    assert k.status_names(k.STATUS_BAD_RANGE) and "rotation table" in k.status_names(k.STATUS_BAD_RANGE)[0]
