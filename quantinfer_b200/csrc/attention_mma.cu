@@ -211,6 +211,9 @@ attention_decode_kernel(const qi::bf16* __restrict__ q, const qi::bf16* __restri
     const int k0 = max(split * chunk, lo);
     const int k1 = min(S, (split + 1) * chunk);
     const size_t part = ((size_t)b * nq + (size_t)hk * G) * n_splits + split;   // + g * n_splits per head
+    // the ranges of this launch must cover the request's keys; what lies beyond them is not read, so say so
+    if (split == n_splits - 1 && hk == 0 && threadIdx.x == 0 && (long long)n_splits * chunk < S && status)
+        atomicOr(status, qi::kStatusBadRange);
 
     if (k0 >= k1) {   // nothing of this range belongs to the request
         if (threadIdx.x < G) {

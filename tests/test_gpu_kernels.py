@@ -604,8 +604,10 @@ def test_lengths_beyond_what_a_launch_covers_set_a_status_bit():
     tbl = torch.arange(2 * max_blocks, dtype=torch.int32, device=DEV).view(2, max_blocks)
     q = torch.randn(2, nq * d, device=DEV).bfloat16()
     out = torch.empty_like(q)
-    for n_splits, want in ((4, 0), (2, k.STATUS_BAD_RANGE)):
-        st = _status()
-        k.attention_decode(q, out, pages, pages, tbl, I(ctx), I([0, 1, 2]), nq, nkv, d, d ** -0.5, 0, 64, n_splits, st)
-        assert st.item() == want, n_splits
+    for use_tma in (True, False):
+        for n_splits, want in ((4, 0), (2, k.STATUS_BAD_RANGE)):
+            st = _status()
+            k.attention_decode(q, out, pages, pages, tbl, I(ctx), I([0, 1, 2]), nq, nkv, d, d ** -0.5, 0, 64, n_splits, st,
+                               use_tma=use_tma)
+            assert st.item() == want, (use_tma, n_splits)
     assert k.status_names(k.STATUS_BAD_RANGE) and "rotation table" in k.status_names(k.STATUS_BAD_RANGE)[0]
