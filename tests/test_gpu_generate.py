@@ -339,3 +339,49 @@ def test_random_weights_command_and_engine_errors(tmp_path):
         eng.step([StepEntry("a", [1], [0]), StepEntry("b", list(range(40)), [])])
     assert eng.cache.free_pages() == free and eng.length("a") == 100 and eng.length("b") == 0   # nothing advanced
     eng.cache.check_invariants()
+
+
+@pytest.mark.parametrize("run_ahead", [False, True])
+def test_pages_taken_by_someone_else_preempt_the_newest_request(tiny_folders, run_ahead):
+    """The scheduler reserves a request's pages at admission, so it runs out only when someone outside it
+    takes pages from the same pool. Here a callback does, in the middle of a run: the step finds no page,
+    the newest request gives everything back and is taken up again later with what it had emitted, and
+    every request's tokens are still those of the plain implementation, drawn tokens included (the
+    request's draw counter is written into its slot's record again when it is admitted again)."""
+    import quantinfer_b200
+    from quantinfer_b200.engine import StepEntry
+    from quantinfer_b200.engine.scheduler import TokenEvent
+
+    folder = tiny_folders["B"]
+    cfg, w = plain_load(folder)
+    prompts = [random_tokens(n, 384, seed=n) for n in (30, 41, 22)]
+    with quantinfer_b200.Model(folder, dtype="float32", page_size=8, num_pages=30, max_requests=4, max_batch_tokens=64,
+                               run_ahead=run_ahead) as m:
+        eng = m.engine
+        seen = {"events": 0, "held": False}
+
+        def meddle(ev):
+            if not isinstance(ev, TokenEvent):
+                return
+            seen["events"] += 1
+            if seen["events"] == 6 and not seen["held"]:
+                # an outsider takes every page that is free now
+                eng.open("outsider")
+                free = eng.cache.free_pages()
+                eng.step([StepEntry("outsider", [1] * (free * 8), [])])
+                seen["held"] = True
+            elif seen["events"] == 30 and seen["held"]:
+                eng.close("outsider")
+                seen["held"] = False
+
+        for kw in (dict(), dict(temperature=0.9, top_k=30, seed=5)):
+            seen.update(events=0, held=False)
+            got = m.generate_batch(prompts, max_new_tokens=24, eos_token_id=None, on_event=meddle, **kw)
+            assert m.last_scheduler.preemptions >= 1
+            for i, (p, g) in enumerate(zip(prompts, got)):
+                want = plain_generate(w, cfg, p, 24, **{**kw, "seed": kw.get("seed", 0) + i})
+                assert g == want, (kw, i)
+            if seen["held"]:
+                eng.close("outsider")
+            eng.cache.check_invariants()
+            assert not eng.cache.requests
