@@ -39,7 +39,8 @@ int qi_qk_norm_rope_kv(const void* qkv, int qkv_splits, void* q_out, int dtype, 
                        const int* positions, const int* token_req, const int* block_table, int max_blocks, int page_size,
                        int num_pages, void* k_pages, void* v_pages, int n_tokens, int nq, int nkv, int d, int* status,
                        cudaStream_t stream);
-int qi_silu_mul(const void* gate_up, void* out, int dtype, int n_tokens, int inter, int interleaved, cudaStream_t stream);
+int qi_act_mul(const void* gate_up, void* out, int dtype, int n_tokens, int inter, int interleaved, int activation,
+               cudaStream_t stream);
 int qi_attention_generic(const void* q, void* out, int dtype, const void* k_pages, const void* v_pages,
                          const int* block_table, int max_blocks, int page_size, int num_pages, const int* positions,
                          const int* token_req, int n_tokens, int nq, int nkv, int d, float scale, int window, int* status,
@@ -94,6 +95,7 @@ struct QiBlock {
     const float* sin_t;
     float qk_eps, scale;
     int nq, nkv, d, window, rotary_dim, table_positions, interleaved;
+    int activation;                      // of the feed-forward's gate: 0 silu, 1 gelu, 2 gelu_tanh, 3 relu
 };
 
 struct QiCall {               // one entry of the run order
@@ -198,19 +200,19 @@ Tensor linear(Run& r, const QiLinear& L, const void* x, int x_dtype, int M, int 
     return Tensor{out, out_dtype, 1};
 }
 
-// silu(gate) * up of a projection whose weight rows are (gate, up) pairs: [tokens, out / 2] (parts/linear.py).
-void* linear_silu_mul(Run& r, const QiLinear& L, const void* x, int dtype, int M) {
+// act(gate) * up of a projection whose weight rows are (gate, up) pairs: [tokens, out / 2] (parts/linear.py):
+// silu in the tensor-core product's epilogue, anything else by the activation kernel over the product's output.
+void* linear_act_mul(Run& r, const QiLinear& L, const void* x, int dtype, int M, int activation) {
     const int N = L.out_features, K = L.in_features, half = N / 2;
     void* act = r.arena.take((long long)M * half * esize(dtype));
-    if (dtype == qi::kBF16 && L.w_dtype == qi::kBF16 && K % 8 == 0) {
+    if (activation == 0 && dtype == qi::kBF16 && L.w_dtype == qi::kBF16 && K % 8 == 0) {
         int swap = 0, bn = 0, splits = 1;
         qi_gemm_bf16_plan(M, N, K, 0, &swap, &bn, &splits);
         r.call([&] { return qi_gemm_bf16(x, L.w, act, qi::kBF16, M, N, K, swap, bn, 1, 1, nullptr, r.m->status, r.stream); });
         return act;
     }
-    void* gu = r.arena.take((long long)M * N * esize(dtype));
-    r.call([&] { return qi_gemm_simt(x, dtype, L.w, L.w_dtype, gu, dtype, M, N, K, K, K, N, r.stream); });
-    r.call([&] { return qi_silu_mul(gu, act, dtype, M, half, 1, r.stream); });
+    Tensor gu = linear(r, L, x, dtype, M, dtype, false);
+    r.call([&] { return qi_act_mul(gu.p, act, dtype, M, half, 1, activation, r.stream); });
     return act;
 }
 
@@ -400,7 +402,7 @@ void forward(Run& r, float* logits) {
         void* x = add_norm(r, resid, have_delta ? &delta : nullptr, B.norm1_gain, B.norm1_eps, nullptr, n, n);
         Tensor a = attention(r, B, c, x);
         void* x2 = add_norm(r, resid, &a, B.norm2_gain, B.norm2_eps, nullptr, n, n);
-        void* act = linear_silu_mul(r, B.gate_up, x2, dt, n);
+        void* act = linear_act_mul(r, B.gate_up, x2, dt, n, B.activation);
         // the down projection writes into this layer's place for what crosses to the next layer
         QiLinear down = B.down;
         const long long keep = r.arena.off;

@@ -35,7 +35,7 @@ class _Block(C.Structure):
                 ("q_gain", C.c_void_p), ("k_gain", C.c_void_p), ("cos_t", C.c_void_p), ("sin_t", C.c_void_p),
                 ("qk_eps", C.c_float), ("scale", C.c_float),
                 ("nq", C.c_int), ("nkv", C.c_int), ("d", C.c_int), ("window", C.c_int), ("rotary_dim", C.c_int),
-                ("table_positions", C.c_int), ("interleaved", C.c_int)]
+                ("table_positions", C.c_int), ("interleaved", C.c_int), ("activation", C.c_int)]
 
 
 class _Call(C.Structure):
@@ -96,7 +96,8 @@ class NativeProgram:
                 a.q_gain.data_ptr() if a.q_gain is not None else None, a.k_gain.data_ptr() if a.k_gain is not None else None,
                 pos.cos.data_ptr() if pos is not None else None, pos.sin.data_ptr() if pos is not None else None,
                 a.spec.qk_norm_eps, a.scale, a.nq, a.nkv, a.d, a.spec.window or 0, pos.rotary_dim if pos is not None else 0,
-                pos.cos.shape[0] if pos is not None else 0, int(pos is not None and pos.pairing == "interleaved"))
+                pos.cos.shape[0] if pos is not None else 0, int(pos is not None and pos.pairing == "interleaved"),
+                kernels.ACTIVATIONS[b.ffn.spec.activation])
         calls = (_Call * len(model.order))()
         for i, (call, view) in enumerate(zip(model.order, views)):
             if view.k_pages is None or view.group < 0 or view.group >= MAX_GROUPS:

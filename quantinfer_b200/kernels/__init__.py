@@ -515,16 +515,26 @@ def attention_decode_rope(qkv, out, q_gain, k_gain, eps, cos, sin, k_pages, v_pa
 # feed-forward
 
 
+ACTIVATIONS = {"silu": 0, "gelu": 1, "gelu_tanh": 2, "relu": 3}
+
+
 def silu_mul(gate_up: torch.Tensor, out: torch.Tensor, interleaved: bool = False) -> None:
-    """out[t, i] = silu(gate[t, i]) * up[t, i]; gate, up = gate_up[t, i], gate_up[t, I + i],
-    or gate_up[t, 2i], gate_up[t, 2i + 1] when `interleaved`."""
+    """`act_mul` with the activation silu."""
+    act_mul(gate_up, out, "silu", interleaved)
+
+
+def act_mul(gate_up: torch.Tensor, out: torch.Tensor, activation: str = "silu", interleaved: bool = False) -> None:
+    """out[t, i] = act(gate[t, i]) * up[t, i]; gate, up = gate_up[t, i], gate_up[t, I + i],
+    or gate_up[t, 2i], gate_up[t, 2i + 1] when `interleaved`. `activation`: one of ACTIVATIONS."""
+    if activation not in ACTIVATIONS:
+        raise KernelError(f"act_mul: activation {activation!r} has no kernel (one of {sorted(ACTIVATIONS)})")
     _req(gate_up, "gate_up", ndim=2)
     _req(out, "out", gate_up.dtype, 2)
     n, two_i = gate_up.shape
     if two_i % 2 or tuple(out.shape) != (n, two_i // 2):
-        raise KernelError(f"silu_mul: gate_up {tuple(gate_up.shape)} / out {tuple(out.shape)} do not agree")
-    _call('other', "silu_mul", library().qi_silu_mul,
-          _ptr(gate_up), _ptr(out), _code(out), n, two_i // 2, int(bool(interleaved)), _stream())
+        raise KernelError(f"act_mul: gate_up {tuple(gate_up.shape)} / out {tuple(out.shape)} do not agree")
+    _call("other", "act_mul", library().qi_act_mul,
+          _ptr(gate_up), _ptr(out), _code(out), n, two_i // 2, int(bool(interleaved)), ACTIVATIONS[activation], _stream())
 
 
 # --------------------------------------------------------------------------

@@ -1,4 +1,5 @@
-"""Gated feed-forward (SwiGLU): y = down(silu(gate(x)) * up(x)), no biases.
+"""Gated feed-forward: y = down(act(gate(x)) * up(x)), no biases; act is the spec's `activation`
+(silu for this architecture: SwiGLU; gelu, gelu_tanh and relu have kernels too).
 
 gate and up are interleaved row by row into one [2I, H] weight at load (row 2i
 gate, row 2i + 1 up), so that one product computes both and the thread that
@@ -21,8 +22,8 @@ from .linear import Linear
 class GatedMLP(Part):
     def __init__(self, spec, runtime):
         super().__init__(spec, runtime)
-        if spec.activation != "silu":
-            raise ConfigError(f"gated_mlp: activation {spec.activation!r} has no kernel (only 'silu')")
+        if spec.activation not in kernels.ACTIVATIONS:
+            raise ConfigError(f"gated_mlp: activation {spec.activation!r} has no kernel (one of {sorted(kernels.ACTIVATIONS)})")
         h, i = spec.hidden_size, spec.intermediate_size
         self.gate_up = Linear(runtime, 2 * i, h, spec.prefix + "gate_up_proj")
         self.down = Linear(runtime, h, i, spec.prefix + "down_proj")
@@ -45,7 +46,7 @@ class GatedMLP(Part):
         self.down.load(tensors[p + "down_proj.weight"])
 
     def forward(self, x):
-        return self.down(self.gate_up.forward_silu_mul(x), keep_partials=True)
+        return self.down(self.gate_up.forward_act_mul(x, self.spec.activation), keep_partials=True)
 
     __call__ = forward
 

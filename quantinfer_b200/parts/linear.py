@@ -56,18 +56,22 @@ class Linear:
         kernels.gemm_simt(x, self.weight, out)
         return out
 
-    def forward_silu_mul(self, x: torch.Tensor) -> torch.Tensor:
-        """silu(gate) * up of a projection whose weight rows are (gate, up) pairs: [tokens, out / 2]."""
+    def forward_act_mul(self, x: torch.Tensor, activation: str = "silu") -> torch.Tensor:
+        """act(gate) * up of a projection whose weight rows are (gate, up) pairs: [tokens, out / 2]. The
+        tensor-core product applies silu in its epilogue; any other activation, and any product that is
+        not on the tensor cores, writes gate and up and runs the activation kernel over them."""
         half = self.out_features // 2
         act = torch.empty((x.shape[0], half), dtype=x.dtype, device=x.device)
         if x.shape[0] == 0:
             return act
-        if self.tensor_core(x, x.dtype):
+        if activation == "silu" and self.tensor_core(x, x.dtype):
             kernels.gemm_bf16(x, self.weight, act, status=self.runtime.status, epilogue="silu_mul")
             return act
-        gu = torch.empty((x.shape[0], self.out_features), dtype=x.dtype, device=x.device)
-        kernels.gemm_simt(x, self.weight, gu)
-        kernels.silu_mul(gu, act, interleaved=True)
+        gu = self.forward(x)
+        kernels.act_mul(gu, act, activation, interleaved=True)
         return act
+
+    def forward_silu_mul(self, x: torch.Tensor) -> torch.Tensor:
+        return self.forward_act_mul(x, "silu")
 
     __call__ = forward

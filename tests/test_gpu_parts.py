@@ -73,6 +73,63 @@ def test_feed_forward_part(dtype):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("activation", ["gelu", "gelu_tanh", "relu"])
+def test_the_gate_activation_is_a_parameter_of_the_feed_forward(dtype, activation):
+    """The spec's `activation` reaches the kernel: the part alone against the formula, and a whole model
+    (which the C++ driver runs) whose layers gate differently, stepped in portions, against the plain parts."""
+    from quantinfer_b200.config import FeedForwardSpec, LayerSpec
+    from quantinfer_b200.errors import ConfigError
+    from quantinfer_b200.parts import build_part
+
+    acts = {"gelu": lambda g: torch.nn.functional.gelu(g), "gelu_tanh": lambda g: torch.nn.functional.gelu(g, approximate="tanh"),
+            "relu": torch.relu, "silu": lambda g: g / (1 + torch.exp(-g))}
+    torch.manual_seed(2)
+    spec = FeedForwardSpec(hidden_size=72, intermediate_size=136, activation=activation, prefix="m.")
+    part = build_part("ffn", spec, _runtime(dtype))
+    w = {"m.gate_proj.weight": (torch.randn(136, 72) * 0.3).to(dtype), "m.up_proj.weight": (torch.randn(136, 72) * 0.1).to(dtype),
+         "m.down_proj.weight": (torch.randn(72, 136) * 0.1).to(dtype)}
+    part.load(w)
+    x = torch.randn(9, 72).to(dtype)
+    y = part.forward(x.to(DEV))
+    if y.dim() == 3:
+        y = y.sum(0)
+    f = {k: v.float() for k, v in w.items()}
+    ref = (acts[activation](x.float() @ f["m.gate_proj.weight"].t()) * (x.float() @ f["m.up_proj.weight"].t())) @ f["m.down_proj.weight"].t()
+    assert float((y.float().cpu() - ref).abs().max()) < TOL[dtype]
+    with pytest.raises(ConfigError, match="no kernel"):
+        build_part("ffn", FeedForwardSpec(72, 136, activation="swish7", prefix="m."), _runtime(dtype))
+    if dtype != torch.float32:
+        return
+    # a model of two layers, the first gated by `activation`, the second by silu
+    T = _SpecTools
+    l0, l1 = T.layer(0), T.layer(1)
+    l0 = LayerSpec(l0.mixer_norm, l0.mixer, l0.ffn_norm, dataclasses.replace(l0.ffn, activation=activation))
+    spec = T.tiny_spec([l0, l1])
+    eng, tensors = _engine(spec)
+    assert eng.model.use_native
+    ids = [int(t) for t in torch.randint(0, 97, (40,))]
+    got = _run_in_portions(eng, ids, (25, 1, 1, 11, 2))
+    assert eng.model.native, "the C++ driver should run a model of built-in parts"
+    wf = {k: v.float() for k, v in tensors.items()}
+    h = plain_embedding(wf["emb.weight"], ids)
+    cos, sin = plain_rope_tables(1e4, 16, list(range(40)))
+    for L in spec.layers:
+        a, p = L.mixer, L.mixer.prefix
+        n = plain_rms_norm(h, wf[L.mixer_norm.prefix + "weight"], L.mixer_norm.eps)
+        q = plain_rms_norm(plain_linear(n, wf[p + "q_proj.weight"]).reshape(40, a.num_heads, 16), wf[p + "q_norm.weight"], a.qk_norm_eps)
+        k = plain_rms_norm(plain_linear(n, wf[p + "k_proj.weight"]).reshape(40, a.num_kv_heads, 16), wf[p + "k_norm.weight"], a.qk_norm_eps)
+        v = plain_linear(n, wf[p + "v_proj.weight"]).reshape(40, a.num_kv_heads, 16)
+        att = plain_gqa_attention(plain_apply_rope(q, cos, sin), plain_apply_rope(k, cos, sin), v, None)
+        h = h + plain_linear(att.reshape(40, a.num_heads * 16), wf[p + "o_proj.weight"])
+        n = plain_rms_norm(h, wf[L.ffn_norm.prefix + "weight"], L.ffn_norm.eps)
+        fp = L.ffn.prefix
+        gate = acts[L.ffn.activation](plain_linear(n, wf[fp + "gate_proj.weight"]))
+        h = h + plain_linear(gate * plain_linear(n, wf[fp + "up_proj.weight"]), wf[fp + "down_proj.weight"])
+    ref = plain_linear(plain_rms_norm(h, wf["final.weight"], spec.final_norm.eps), wf["emb.weight"])
+    assert float((got - ref).abs().max()) < 5e-5
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_embedding_and_head_parts(dtype):
     from quantinfer_b200.config import EmbeddingSpec, HeadSpec
     from quantinfer_b200.parts import build_part
