@@ -627,6 +627,85 @@ def test_toy_feed_forward_with_routing_and_another_position_encoding():
     assert float((got - ref).abs().max()) < 5e-5
 
 
+@dataclasses.dataclass(frozen=True)
+class ToyScaledEmbeddingSpec:
+    vocab_size: int
+    hidden_size: int
+    scale: float
+    prefix: str = ""
+    kind: str = "toy_scaled_embedding"
+
+
+@dataclasses.dataclass(frozen=True)
+class ToySoftcapHeadSpec:
+    vocab_size: int
+    hidden_size: int
+    cap: float
+    tied: bool = False
+    prefix: str = ""
+    kind: str = "toy_softcap_head"
+
+
+def test_a_scaled_embedding_and_a_capped_head_are_parts_too():
+    """What stands before the first block and after the last norm are parts of their own categories: an
+    embedding that scales its rows and a head that soft-caps its logits are registered here and named by
+    the model's spec; nothing in the model's forward pass changes. (Test doubles in torch.)"""
+    from quantinfer_b200.parts import Part, register_part
+    from quantinfer_b200.weights import TensorNeed
+
+    class ToyScaledEmbedding(Part):
+        @classmethod
+        def needs_of_spec(cls, spec):
+            return {spec.prefix + "weight": TensorNeed((spec.vocab_size, spec.hidden_size), "table")}
+
+        def load(self, tensors):
+            self.table = tensors[self.spec.prefix + "weight"].to(self.runtime.device, torch.float32)
+
+        def forward(self, token_ids):
+            return (self.table[token_ids.long()] * self.spec.scale).contiguous()
+
+        __call__ = forward
+
+    class ToySoftcapHead(Part):
+        @classmethod
+        def needs_of_spec(cls, spec):
+            return {spec.prefix + "weight": TensorNeed((spec.vocab_size, spec.hidden_size))}
+
+        def load(self, tensors):
+            self.w = tensors[self.spec.prefix + "weight"].to(self.runtime.device, torch.float32)
+
+        def forward(self, x):
+            return (self.spec.cap * torch.tanh((x.float() @ self.w.t()) / self.spec.cap)).contiguous()
+
+        __call__ = forward
+
+    register_part("embedding", "toy_scaled_embedding", ToyScaledEmbedding)
+    register_part("head", "toy_softcap_head", ToySoftcapHead)
+    T = _SpecTools
+    base = T.tiny_spec([T.layer(0), T.layer(1)])
+    spec = dataclasses.replace(base, embedding=ToyScaledEmbeddingSpec(97, 48, 6.9, "emb."), head=ToySoftcapHeadSpec(97, 48, 0.5, prefix="head."))
+    eng, tensors = _engine(spec)
+    assert "head.weight" in tensors
+    ids = [int(t) for t in torch.randint(0, 97, (30,))]
+    got = _run_in_portions(eng, ids, (19, 1, 1, 9))
+    assert not eng.model.native                       # a part from outside: the parts' own forward runs
+    w = {k: v.float() for k, v in tensors.items()}
+    h = w["emb.weight"][ids] * 6.9
+    cos, sin = plain_rope_tables(1e4, 16, list(range(30)))
+    for L in spec.layers:
+        a, p = L.mixer, L.mixer.prefix
+        n = plain_rms_norm(h, w[L.mixer_norm.prefix + "weight"], L.mixer_norm.eps)
+        q = plain_rms_norm(plain_linear(n, w[p + "q_proj.weight"]).reshape(30, a.num_heads, 16), w[p + "q_norm.weight"], a.qk_norm_eps)
+        k = plain_rms_norm(plain_linear(n, w[p + "k_proj.weight"]).reshape(30, a.num_kv_heads, 16), w[p + "k_norm.weight"], a.qk_norm_eps)
+        v = plain_linear(n, w[p + "v_proj.weight"]).reshape(30, a.num_kv_heads, 16)
+        att = plain_gqa_attention(plain_apply_rope(q, cos, sin), plain_apply_rope(k, cos, sin), v, None)
+        h = h + plain_linear(att.reshape(30, a.num_heads * 16), w[p + "o_proj.weight"])
+        h = h + plain_feed_forward(plain_rms_norm(h, w[L.ffn_norm.prefix + "weight"], L.ffn_norm.eps), w, L.ffn.prefix)
+    ref = 0.5 * torch.tanh(plain_linear(plain_rms_norm(h, w["final.weight"], spec.final_norm.eps), w["head.weight"]) / 0.5)
+    assert float((got - ref).abs().max()) < 5e-5
+    assert float(ref.abs().max()) > 0.25                # the cap does bend these logits
+
+
 def _rotate_interleaved(x, cos, sin, rot):
     """Pairs (2p, 2p + 1) of the first `rot` elements of each head turn by the angle of pair p; the rest
     passes. x [tokens, heads, d]; cos, sin [tokens, rot / 2]."""
