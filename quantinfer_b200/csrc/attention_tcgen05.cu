@@ -15,13 +15,26 @@
 // therefore reach 2^8 at most, sum and accumulator share one reference, and their quotient is
 // unchanged; after the first few tiles of a row the accumulator is hardly ever touched.
 //
-// Two such CTAs share an SM (192 threads, 256 columns of tensor memory: S 64, O 128, P 32; Q
-// and two K/V stages in shared memory): the softmax of one overlaps the products of the
-// other, and so do one CTA's start (barriers, the copy of Q, the first tiles) and end (the
-// last product, the normalised store) with its neighbour's steady state, which at a few
-// thousand keys are as long as the work itself. (An earlier form had one CTA an SM with two
-// softmax groups on alternating key tiles of the same query rows, merged at the end: 322,
-// 626, 685 TFLOP/s at 2,048, 8,192 and 16,384 tokens against 412, 763, 795 now.)
+// Two such CTAs share an SM (192 threads, 256 columns of tensor memory: S 64, O 128, P twice
+// 32; Q, two stages of K and two of V in shared memory): the softmax of one overlaps the
+// products of the other, and so do one CTA's start (barriers, the copy of Q, the first tiles)
+// and end (the last product, the normalised store) with its neighbour's steady state, which at
+// a few thousand keys are as long as the work itself. (An earlier form had one CTA an SM with
+// two softmax groups on alternating key tiles of the same query rows, merged at the end: 322,
+// 626, 685 TFLOP/s at 2,048, 8,192 and 16,384 tokens.)
+//
+// What the steady state waits for, measured with the cycle counter around each wait and each
+// piece of work, decided the rest. K and V have rings and barriers of their own: a K tile's
+// slot is free as soon as its S has been computed, one softmax before P.V frees the V slot,
+// so the load of K for tile j + 2 starts a whole tile earlier than it would behind a shared
+// barrier (the MMA thread waited 1,400 cycles a tile for K before). P has two buffers, so the
+// weights of tile j + 1 do not wait for P.V of tile j. The exponentials of a row's 64 columns
+// are one block of straight code (the choice between the masked and the unmasked form is made
+// once per tile and warp, outside it): with a branch inside the loop only eight exponentials
+// were in flight at a time and the loop took 1,580 cycles a tile, now 890. Together: 526, 756,
+// 777 TFLOP/s before, 672, 1,077, 1,087 now. What is left is bound by shared-memory traffic:
+// per tile 32 KB written by the copies, 48 KB read by S (Q again for every tile) and 16 KB by
+// P.V, 768 cycles at 128 bytes a cycle for 512 cycles of tensor-core work.
 //
 // Roles: warps 0-3 are the softmax threads; warp 4 issues the TMA loads of Q and of the K/V
 // tiles (page pieces through the block table, as in attention_tma.cu); warp 5 allocates tensor
@@ -79,6 +92,11 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
         if ((i & 1023u) == 1023u && *abort_flag) return false;
     }
     return false;
+}
+__device__ __forceinline__ float max3(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
 }
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
     asm volatile(
@@ -167,20 +185,63 @@ constexpr uint32_t idesc(int n, bool b_mn_major) {
            ((uint32_t)(BM >> 4) << 24);
 }
 
-constexpr int kStages = 2;       // K/V ring
+
+// The largest score of a row's 64 columns, of those in [c_lo, c_hi) with kMasked.
+template <bool kMasked>
+__device__ __forceinline__ float row_max(const uint32_t (&sv)[BN], int c_lo, int c_hi) {
+    float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+    for (int i = 0; i < BN; i += 8) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const int c = i + 2 * e;
+            float a = __uint_as_float(sv[c]), b = __uint_as_float(sv[c + 1]);
+            if (kMasked) {
+                a = (c >= c_lo && c < c_hi) ? a : -INFINITY;
+                b = (c + 1 >= c_lo && c + 1 < c_hi) ? b : -INFINITY;
+            }
+            mx4[e] = max3(mx4[e], a, b);
+        }
+    }
+    return fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+}
+// p = 2^(s * scale - ms) for a row's 64 columns (0 outside [c_lo, c_hi) with kMasked), packed as
+// bfloat16 pairs; returns their sum in 32-bit. One block of straight code, so that the
+// exponentials of all columns can be in flight together.
+template <bool kMasked>
+__device__ __forceinline__ float row_weights(const uint32_t (&sv)[BN], uint32_t (&pk)[BN / 2], float scale_log2e, float ms,
+                                             int c_lo, int c_hi) {
+    float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int c = 0; c < BN; c += 2) {
+        float p0 = ex2(fmaf(__uint_as_float(sv[c]), scale_log2e, -ms));
+        float p1 = ex2(fmaf(__uint_as_float(sv[c + 1]), scale_log2e, -ms));
+        if (kMasked) {
+            p0 = (c >= c_lo && c < c_hi) ? p0 : 0.f;
+            p1 = (c + 1 >= c_lo && c + 1 < c_hi) ? p1 : 0.f;
+        }
+        sum4[(c >> 1) & 3] += p0 + p1;
+        pk[c >> 1] = qi_attn::pack_bf16(p0, p1);
+    }
+    return (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
+}
+
+constexpr int kStages = 2;       // stages of the K ring and of the V ring (a K slot is free after S, a V slot after P.V)
 constexpr int kThreads = 192;    // four softmax warps, the TMA warp, the MMA warp
 struct Bars {
     static constexpr int q_full = 0;
-    static constexpr int kv_full = 8;                            // [kStages]
-    static constexpr int kv_empty = kv_full + 8 * kStages;   // [kStages]
-    static constexpr int s_full = kv_empty + 8 * kStages;
+    static constexpr int k_full = 8;                         // [kStages]
+    static constexpr int k_empty = k_full + 8 * kStages;     // [kStages]
+    static constexpr int v_full = k_empty + 8 * kStages;     // [kStages]
+    static constexpr int v_empty = v_full + 8 * kStages;     // [kStages]
+    static constexpr int s_full = v_empty + 8 * kStages;
     static constexpr int s_free = s_full + 8;
-    static constexpr int o_full = s_free + 8;
-    static constexpr int p_ready = o_full + 8;
-    static constexpr int p_free = p_ready + 8;
-    static constexpr int total = p_free + 8;
+    static constexpr int p_ready = s_free + 8;               // [2]: one per buffer of P
+    static constexpr int p_free = p_ready + 16;              // [2]
+    static constexpr int total = p_free + 16;
 };
 constexpr int kSmemBytes = kQBytes + kStages * 2 * kKVBytes + 256 /*barriers*/ + 4 * kMaxTableEntries + 1024 /*alignment*/;
+
 
 __global__ void __launch_bounds__(kThreads, 2)
 attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
@@ -240,14 +301,17 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
     if (threadIdx.x == 0) {
         mbar_init(bars + B::q_full, 1);
         for (int s = 0; s < kStages; ++s) {
-            mbar_init(bars + B::kv_full + 8 * s, 1);
-            mbar_init(bars + B::kv_empty + 8 * s, 1);
+            mbar_init(bars + B::k_full + 8 * s, 1);
+            mbar_init(bars + B::k_empty + 8 * s, 1);
+            mbar_init(bars + B::v_full + 8 * s, 1);
+            mbar_init(bars + B::v_empty + 8 * s, 1);
         }
         mbar_init(bars + B::s_full, 1);
         mbar_init(bars + B::s_free, 4);      // one arrival per softmax warp
-        mbar_init(bars + B::o_full, 1);
-        mbar_init(bars + B::p_ready, 4);
-        mbar_init(bars + B::p_free, 1);
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(bars + B::p_ready + 8 * b, 4);
+            mbar_init(bars + B::p_free + 8 * b, 1);
+        }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -259,7 +323,7 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
-    const uint32_t tmem_s = tmem_base, tmem_o = tmem_base + 64, tmem_p = tmem_base + 192;
+    const uint32_t tmem_s = tmem_base, tmem_o = tmem_base + 64, tmem_p = tmem_base + 192;   // P: two buffers of 32 columns
 
     auto give_up = [&]() {
         if (!*abort_flag) {
@@ -274,37 +338,51 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
             mbar_expect_tx(bars + B::q_full, kQBytes);
             tma_load_2d(q_s, &map_q, bars + B::q_full, h * D, q0);
             tma_load_2d(q_s + kHalfBytes, &map_q, bars + B::q_full, h * D + 64, q0);
-            int issued = 0;
-            for (int j = 0; j < n_tiles; ++j) {
+            // K of tile j + 1 goes out before V of tile j: a K slot is free as soon as its S has been
+            // computed, a V slot only after P.V, one softmax later.
+            int issued_k = 0, issued_v = 0;
+            auto load_tile = [&](int j, bool is_v) -> bool {
                 const int s = j % kStages;
-                if (!mbar_wait(bars + B::kv_empty + 8 * s, (((uint32_t)j / kStages) & 1u) ^ 1u, abort_flag)) {
-                    give_up();
-                    break;
-                }
-                const uint32_t full = bars + B::kv_full + 8 * s;
-                const uint32_t k_dst = kv_s + s * 2 * kKVBytes, v_dst = k_dst + kKVBytes;
-                mbar_expect_tx(full, 2 * kKVBytes);
+                const uint32_t empty = bars + (is_v ? B::v_empty : B::k_empty) + 8 * s;
+                const uint32_t full = bars + (is_v ? B::v_full : B::k_full) + 8 * s;
+                if (!mbar_wait(empty, (((uint32_t)j / kStages) & 1u) ^ 1u, abort_flag)) return false;
+                const uint32_t dst = kv_s + s * 2 * kKVBytes + (is_v ? kKVBytes : 0);
+                const CUtensorMap* map = is_v ? &map_v : &map_k;
+                mbar_expect_tx(full, kKVBytes);
                 const int t0 = t_begin + j * BN;
                 for (int r0 = 0; r0 < BN; r0 += box_rows) {
                     const int key = t0 + r0;
                     const int blk = key / page_size - blk0;
                     int page = blk < n_blk ? s_table[blk] : -1;
                     if (page < 0 || page >= num_pages) {
-                        if (key < hi && key + box_rows > lo && status) atomicOr(status, qi::kStatusBadPage);
+                        if (!is_v && key < hi && key + box_rows > lo && status) atomicOr(status, qi::kStatusBadPage);
                         page = 0;
                     }
                     const int row = (page * nkv + hk) * page_size + (key % page_size);
-                    tma_load_2d(k_dst + r0 * 128, &map_k, full, 0, row);
-                    tma_load_2d(k_dst + kKVHalfBytes + r0 * 128, &map_k, full, 64, row);
-                    tma_load_2d(v_dst + r0 * 128, &map_v, full, 0, row);
-                    tma_load_2d(v_dst + kKVHalfBytes + r0 * 128, &map_v, full, 64, row);
+                    tma_load_2d(dst + r0 * 128, map, full, 0, row);
+                    tma_load_2d(dst + kKVHalfBytes + r0 * 128, map, full, 64, row);
                 }
-                issued = j + 1;
+                return true;
+            };
+            bool ok = n_tiles == 0 || load_tile(0, false);
+            if (ok && n_tiles > 0) issued_k = 1;
+            for (int j = 0; j < n_tiles && ok; ++j) {
+                if (j + 1 < n_tiles) {
+                    ok = load_tile(j + 1, false);
+                    if (!ok) break;
+                    issued_k = j + 2;
+                }
+                ok = load_tile(j, true);
+                if (ok) issued_v = j + 1;
             }
+            if (!ok) give_up();
             if (*abort_flag) {   // copies in flight write into this CTA's shared memory: wait (bounded) for them
-                for (int j = max(issued - kStages, 0); j < issued; ++j)
+                for (int j = max(issued_k - kStages, 0); j < issued_k; ++j)
                     for (uint32_t t = 0; t < (1u << 20); ++t)
-                        if (mbar_try_wait(bars + B::kv_full + 8 * (j % kStages), ((uint32_t)j / kStages) & 1u)) break;
+                        if (mbar_try_wait(bars + B::k_full + 8 * (j % kStages), ((uint32_t)j / kStages) & 1u)) break;
+                for (int j = max(issued_v - kStages, 0); j < issued_v; ++j)
+                    for (uint32_t t = 0; t < (1u << 20); ++t)
+                        if (mbar_try_wait(bars + B::v_full + 8 * (j % kStages), ((uint32_t)j / kStages) & 1u)) break;
             }
         }
     } else if (warp == 5) {
@@ -314,7 +392,7 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
             bool ok = mbar_wait(bars + B::q_full, 0, abort_flag);
             auto issue_qk = [&](int j) -> bool {
                 const int s = j % kStages;
-                if (!mbar_wait(bars + B::kv_full + 8 * s, ((uint32_t)j / kStages) & 1u, abort_flag)) return false;
+                if (!mbar_wait(bars + B::k_full + 8 * s, ((uint32_t)j / kStages) & 1u, abort_flag)) return false;
                 if (!mbar_wait(bars + B::s_free, ((uint32_t)j & 1u) ^ 1u, abort_flag)) return false;   // the group holds S of tile j - 1
                 tc_fence_after();
                 const uint32_t k_addr = kv_s + s * 2 * kKVBytes;
@@ -325,6 +403,7 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
                     umma_bf16(tmem_s, adesc, bdesc, idesc_qk, ks > 0 ? 1u : 0u);
                 }
                 umma_commit(bars + B::s_full);
+                umma_commit(bars + B::k_empty + 8 * s);
                 return true;
             };
             if (ok && n_tiles > 0) ok = issue_qk(0);
@@ -333,21 +412,22 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
                     ok = false;
                     break;
                 }
-                if (!mbar_wait(bars + B::p_ready, (uint32_t)j & 1u, abort_flag)) {
+                const int pb = j & 1;
+                const int s = j % kStages;
+                if (!mbar_wait(bars + B::p_ready + 8 * pb, ((uint32_t)j >> 1) & 1u, abort_flag) ||
+                    !mbar_wait(bars + B::v_full + 8 * s, ((uint32_t)j / kStages) & 1u, abort_flag)) {
                     ok = false;
                     break;
                 }
                 tc_fence_after();
-                const int s = j % kStages;
                 const uint32_t v_addr = kv_s + s * 2 * kKVBytes + kKVBytes;
 #pragma unroll
                 for (int kk = 0; kk < BN / 16; ++kk) {
                     const uint64_t bdesc = desc_mn_major(v_addr + kk * 16 * 128);
-                    umma_bf16_ts(tmem_o, tmem_p + kk * 8, bdesc, idesc_pv, (j > 0 || kk > 0) ? 1u : 0u);
+                    umma_bf16_ts(tmem_o, tmem_p + pb * 32 + kk * 8, bdesc, idesc_pv, (j > 0 || kk > 0) ? 1u : 0u);
                 }
-                umma_commit(bars + B::o_full);
-                umma_commit(bars + B::kv_empty + 8 * s);
-                umma_commit(bars + B::p_free);
+                umma_commit(bars + B::v_empty + 8 * s);
+                umma_commit(bars + B::p_free + 8 * pb);
             }
             if (!ok) give_up();
         }
@@ -375,26 +455,15 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(bars + B::s_free);
-            float mx = -INFINITY;
-            const bool unmasked = c_lo == 0 && c_hi == BN;
-            if (unmasked) {
-                float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-#pragma unroll
-                for (int i = 0; i < BN; i += 4) {
-#pragma unroll
-                    for (int e = 0; e < 4; ++e) mx4[e] = fmaxf(mx4[e], __uint_as_float(sv[i + e]));
-                }
-                mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
-            } else {
-#pragma unroll
-                for (int i = 0; i < BN; ++i)
-                    if (i >= c_lo && i < c_hi) mx = fmaxf(mx, __uint_as_float(sv[i]));
-            }
+            // a tile that lies wholly inside every row's span takes the code without the comparisons
+            const bool interior = __all_sync(0xffffffffu, c_lo == 0 && c_hi == BN);
+            const float mx = interior ? row_max<false>(sv, 0, BN) : row_max<true>(sv, c_lo, c_hi);
             const float m_top = fmaxf(m, mx * scale_log2e);
             const bool fresh = m == -INFINITY;
             const bool moves = !fresh && m_top - m > kRescaleStep;
             if (__any_sync(0xffffffffu, moves)) {
-                if (!mbar_wait(bars + B::o_full, (u - 1) & 1u, abort_flag)) { ok = false; break; }
+                // every product into O so far has finished: the one of tile j - 1 arrives on its buffer's barrier
+                if (!mbar_wait(bars + B::p_free + 8 * ((u - 1) & 1u), ((u - 1) >> 1) & 1u, abort_flag)) { ok = false; break; }
                 tc_fence_after();
                 const float f = moves ? ex2(m - m_top) : 1.f;
 #pragma unroll 1
@@ -412,37 +481,22 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
             }
             if (fresh || moves) m = m_top;
             const float ms = (m == -INFINITY) ? 0.f : m;
-            if (u > 0 && !mbar_wait(bars + B::p_free, (u - 1) & 1u, abort_flag)) { ok = false; break; }
-            float sum = 0.f;
+            if (u > 1 && !mbar_wait(bars + B::p_free + 8 * (u & 1u), ((u >> 1) & 1u) ^ 1u, abort_flag)) { ok = false; break; }   // P.V of tile j - 2 has read this buffer
             uint32_t pk[BN / 2];
-#pragma unroll
-            for (int q = 0; q < BN / 8; ++q) {
-                float p[8];
-                if (unmasked) {
-#pragma unroll
-                    for (int i = 0; i < 8; ++i) p[i] = ex2(fmaf(__uint_as_float(sv[8 * q + i]), scale_log2e, -ms));
-                } else {
-#pragma unroll
-                    for (int i = 0; i < 8; ++i) {
-                        const int c = 8 * q + i;
-                        p[i] = (c >= c_lo && c < c_hi) ? ex2(fmaf(__uint_as_float(sv[c]), scale_log2e, -ms)) : 0.f;
-                    }
-                }
-                sum += ((p[0] + p[1]) + (p[2] + p[3])) + ((p[4] + p[5]) + (p[6] + p[7]));
-                pk[4 * q] = qi_attn::pack_bf16(p[0], p[1]);
-                pk[4 * q + 1] = qi_attn::pack_bf16(p[2], p[3]);
-                pk[4 * q + 2] = qi_attn::pack_bf16(p[4], p[5]);
-                pk[4 * q + 3] = qi_attn::pack_bf16(p[6], p[7]);
-            }
+            const float sum = interior ? row_weights<false>(sv, pk, scale_log2e, ms, 0, BN)
+                                       : row_weights<true>(sv, pk, scale_log2e, ms, c_lo, c_hi);
             l += sum;
-            tmem_st32(tmem_p + lane_addr, pk);
+            tmem_st32(tmem_p + (u & 1u) * 32 + lane_addr, pk);
             tmem_st_wait();
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(bars + B::p_ready);
+            if (lane == 0) mbar_arrive(bars + B::p_ready + 8 * (u & 1u));
         }
         // the accumulator, once the last product has finished: normalise and store
-        if (ok && n_tiles > 0) ok = mbar_wait(bars + B::o_full, (uint32_t)(n_tiles - 1) & 1u, abort_flag);
+        if (ok && n_tiles > 0) {
+            const uint32_t last = (uint32_t)(n_tiles - 1);
+            ok = mbar_wait(bars + B::p_free + 8 * (last & 1u), (last >> 1) & 1u, abort_flag);
+        }
         if (!ok && lane == 0) give_up();
         if (ok && n_ranges > 1) {
             tc_fence_after();
