@@ -32,9 +32,19 @@
 // are one block of straight code (the choice between the masked and the unmasked form is made
 // once per tile and warp, outside it): with a branch inside the loop only eight exponentials
 // were in flight at a time and the loop took 1,580 cycles a tile, now 890. Together: 526, 756,
-// 777 TFLOP/s before, 672, 1,077, 1,087 now. What is left is bound by shared-memory traffic:
-// per tile 32 KB written by the copies, 48 KB read by S (Q again for every tile) and 16 KB by
-// P.V, 768 cycles at 128 bytes a cycle for 512 cycles of tensor-core work.
+// 777 TFLOP/s before, 736, 1,116, 1,171 now (2,048, 8,192 and 16,384 tokens).
+//
+// What bounds it now is the tensor pipe itself: a tcgen05.mma of M = 128, K = 16 takes about 70
+// cycles whether N is 32, 64 or 128 (one thread issuing 4,096 of them back to back: 74, 74, 70
+// cycles with A in shared memory, 67 with A in tensor memory; N = 256 takes 128). S = Q.K^T
+// over 64 keys is eight such instructions at half the pipe's rate, P.V four at the full rate:
+// 835 cycles a tile, and the two CTAs of an SM finish a tile every 830 to 930 cycles. Key
+// tiles of 128 (S at the full rate) need 128 columns for S, so with O the weights must go
+// over S and a CTA's products and its softmax take turns; that was built (one softmax thread a
+// row, and two), was right, and ran at 1,105 and 1,030 TFLOP/s at 16,384 tokens: the two CTAs
+// of an SM fall into step instead of filling each other's gaps, their softmax phases share
+// the special-function unit and their products queue. Two heads of a KV group in one CTA of
+// 352 threads, so that one copy of K and V serves both: 1,042 TFLOP/s.
 //
 // Roles: warps 0-3 are the softmax threads; warp 4 issues the TMA loads of Q and of the K/V
 // tiles (page pieces through the block table, as in attention_tma.cu); warp 5 allocates tensor
