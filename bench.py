@@ -325,7 +325,50 @@ class Bench:
                             "prefill_frac_burst": round(tf / burst, 3), "prefill_frac_sustained": round(tf / sustained, 3)})
             out[cls] = row
         out["rest"] = {"decode_ms": round(rest[0], 4), "prefill_ms": round(rest[1], 4)}
+        kernel = self.prefill_attention_kernel(burst)
+        if kernel:      # the attention's prefill rate from its kernel alone, not from a difference of two capped steps
+            out["attention"].update(kernel)
+            out["attention"].update({"prefill_tflops": kernel["prefill_kernel_tflops"], "prefill_frac_burst": kernel["prefill_kernel_frac_burst"],
+                                     "prefill_frac_sustained": round(kernel["prefill_kernel_tflops"] / sustained, 3)})
         return out
+
+    def prefill_attention_kernel(self, burst):
+        """The prefill attention kernel by itself, the prompt's shape, 20 launches back to back between two
+        events (each takes longer than the host needs to issue it): in the step's `left_out` figure the clock
+        under the power cap moves with what the neighbours multiply, here it does not."""
+        from quantinfer_b200 import kernels
+
+        torch, spec, T = self.torch, self.spec, self.prompt_len
+        att = spec.layers[0].mixer
+        nq, nkv, d, ps = att.num_heads, att.num_kv_heads, att.head_dim, 64
+        if not kernels.attention_prefill_tcgen05_supported(nq, nkv, d, ps, T // ps + 2):
+            return None
+        dev = "cuda:0"
+        as_int = lambda v: torch.tensor(v, dtype=torch.int32, device=dev)
+        n_pages = T // ps + 2
+        kp = torch.randn(n_pages, nkv, ps, d, device=dev).to(torch.bfloat16)
+        vp = torch.randn_like(kp)
+        table = torch.arange(n_pages, dtype=torch.int32, device=dev).view(1, -1)
+        q = torch.randn(T, nq * d, device=dev).to(torch.bfloat16)
+        o = torch.zeros_like(q)
+        tiles = [(0, t0) for t0 in range(0, T, kernels.QUERY_TILE)][::-1]
+        status = torch.zeros(1, dtype=torch.int32, device=dev)
+        args = (q, o, kp, vp, table, as_int([0, T]), as_int([0]), as_int([t[0] for t in tiles]), as_int([t[1] for t in tiles]),
+                nq, nkv, d, d ** -0.5, 0, status)
+        call = lambda: kernels.attention_prefill(*args, impl="tcgen05", max_kv_len=T, key_ranges=1)
+        for _ in range(3):
+            call()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        n = 20
+        a.record()
+        for _ in range(n):
+            call()
+        b.record()
+        torch.cuda.synchronize()
+        us = a.elapsed_time(b) / n * 1e3
+        tf = 4.0 * nq * d * T * (T + 1) / 2 / us / 1e6
+        return {"prefill_kernel_us": round(us, 1), "prefill_kernel_tflops": round(tf, 1), "prefill_kernel_frac_burst": round(tf / burst, 3)}
 
 
 def mixed_workload(args, entry):
