@@ -175,10 +175,13 @@ class Bench:
         self.prompt_len, self.context = entry["prompt_len"], entry["context"]
         self.batches = [args.batch] + ([] if args.skip_points else [b for b in entry["points"] if b != args.batch])
         self.n_new = args.warmup + args.steps + 2
+        # the end-to-end window is at least 64 steps long, however few steps the device-timed run takes:
+        # the first steps after the prompts still run at the clock the prefill left behind
+        self.n_e2e = max(self.n_new, 64 + args.warmup)
         max_b = max(self.batches)
         # a request decodes warm-up + timed steps on the device, or (end to end) as many steps as it takes until
         # the last request of its batch has joined plus the timed ones: room for the longer of the two
-        per_req = -(-(self.prompt_len + 2 * self.n_new + max_b + 64) // 64) * 64
+        per_req = -(-(self.prompt_len + self.n_new + self.n_e2e + max_b + 64) // 64) * 64
         self.engine, self.config, self.spec, self.load_s = build_engine(
             args, entry, self.context, max_b, per_req * max_b + self.prompt_len + 2048)
         self.sampler = Sampler(self.engine.device, self.engine.runtime.status)
@@ -250,7 +253,7 @@ class Bench:
         """Rate over the steps in which the whole batch decodes, by the times at which tokens reach the host."""
         # requests join one prompt after the other: each decodes `batch` steps more than the timed ones, so that
         # the window in which all of them decode is as long as the device-timed run
-        engine, n_new = self.engine, min(self.n_new + batch, self.context - self.prompt_len)
+        engine, n_new = self.engine, min(self.n_e2e + batch, self.context - self.prompt_len)
         prompts = [self.prompt() for _ in range(batch)]
         # warm-up through the same entry point (W decode steps): graphs are captured, buffers pinned
         model.generate_batch(prompts, max_new_tokens=self.args.warmup + 1, eos_token_id=None)
