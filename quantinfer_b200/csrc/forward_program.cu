@@ -237,9 +237,10 @@ int prefill_ranges(long long n_ctas, int max_kv_len) {
     for (int i = 0; i < 6; ++i) {
         const int ranges = choices[i];
         if (ranges > 1 && max_kv_len < 2048 * ranges) break;
-        const long long rounds = (n_ctas * ranges + 295) / 296;
-        double time = (double)rounds * ((double)max_kv_len / ranges) * 0.0247;
-        if (ranges > 1) time += (double)n_ctas * 128 * ranges * 0.00034;
+        const long long units = n_ctas * ranges;
+        const long long rounds = (units + 295) / 296;
+        double time = (double)rounds * ((double)max_kv_len / ranges) * (units <= 148 ? 0.0132 : 0.0154);
+        if (ranges > 1) time += (double)n_ctas * 128 * ranges * 0.0009;
         if (best_time < 0 || time < best_time * 0.97) {
             best = ranges;
             best_time = time;

@@ -336,19 +336,22 @@ def attention_prefill_tcgen05_supported(nq: int, nkv: int, d: int, page_size: in
 def attention_prefill_ranges(n_ctas: int, max_kv_len: int) -> int:
     """Into how many key ranges the tcgen05 prefill attention cuts every query tile, given the CTAs
     it would launch uncut (heads x query tiles) and the longest context of the step. 296 CTAs are
-    resident at once; a step of 2,048 tokens and 32 heads has 512, so its second round is 73% full,
-    and four ranges make 2,048 CTAs in seven rounds. Cutting costs the partial results' trip through
-    memory and a merge kernel, so it pays only for long contexts. Estimated times, fitted to
-    measurements at the 8B sizes (microseconds): rounds x keys of a CTA x 0.0247, plus
-    0.00034 for every (query row, head, range) when cut."""
+    resident at once; cutting makes more and shorter ones, which fills the GPU when a step has few
+    query tiles (a portion of 512 tokens of 32 heads is 128 CTAs: after 30,000 tokens 402 us uncut,
+    268 in two ranges), and costs the partial results' trip through memory and a merge kernel, so
+    it does not pay where the uncut launch already fills its rounds (2,048 tokens after 30,000:
+    1,007 us uncut, 1,120 in four ranges). Estimated times, fitted to measurements at the 8B sizes
+    (microseconds): rounds x keys of a CTA x 0.0154 (0.0132 while every CTA has an SM to itself),
+    plus 0.0009 for every (query row, head, range) when cut."""
     best, best_time = 1, None
     for ranges in (1, 2, 3, 4, 6, 8):
         if ranges > 1 and max_kv_len < 2048 * ranges:
             break
-        rounds = -(-n_ctas * ranges // 296)
-        time = rounds * (max_kv_len / ranges) * 0.0247
+        units = n_ctas * ranges
+        rounds = -(-units // 296)
+        time = rounds * (max_kv_len / ranges) * (0.0132 if units <= 148 else 0.0154)
         if ranges > 1:
-            time += n_ctas * 128 * ranges * 0.00034
+            time += n_ctas * 128 * ranges * 0.0009
         if best_time is None or time < best_time * 0.97:
             best, best_time = ranges, time
     return best

@@ -358,8 +358,11 @@ def test_attention_prefill_tcgen05_key_ranges(ranges, ctx, new, ps, window):
     ranges that are empty for short rows, a window that leaves the first ranges without keys."""
     assert _attention_case(8, 2, 128, ctx, new, ps, window, torch.bfloat16, "prefill_tcgen05", key_ranges=ranges) < 1.2e-2
     k = _k()
-    assert k.attention_prefill_ranges(512, 2048) == 1 and k.attention_prefill_ranges(512, 8192) == 1 and k.attention_prefill_ranges(512, 30000) == 4
+    # a launch that fills its rounds stays whole; one of few CTAs and many keys is cut
+    assert k.attention_prefill_ranges(512, 2048) == 1 and k.attention_prefill_ranges(512, 8192) == 1 and k.attention_prefill_ranges(512, 32768) == 1
     assert k.attention_prefill_ranges(296, 30000) == 1
+    assert k.attention_prefill_ranges(128, 2560) == 1 and k.attention_prefill_ranges(128, 6656) == 2 and k.attention_prefill_ranges(128, 31232) == 2
+    assert k.attention_prefill_ranges(32, 32768) == 8
 
 
 def test_attention_prefill_without_tma_takes_any_page_size():
