@@ -273,7 +273,10 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
     volatile int* abort_flag = reinterpret_cast<volatile int*>(bar_mem + B::total + 4);
     int* s_table = reinterpret_cast<int*>(bar_mem + 256);
 
-    qi::pdl_enter();
+    // The lists of the step (requests, query tiles, block tables) were copied before the step's first
+    // kernel began: the CTA reads them, sets up its barriers and its tensor memory while the kernel
+    // before this one still runs, and waits for it only before it touches Q, the cache or the output.
+    qi::pdl_launch_dependents();
     const int tile = blockIdx.y, h = blockIdx.x;
     const int hk = h / (nq / nkv);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -296,6 +299,7 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
         n_tiles = count;
         if (count == 0) {    // nothing of the rows' keys falls into this range: an empty partial
             const int row = threadIdx.x;
+            qi::pdl_wait();
             if (row < rows_valid) {
                 float* ml = ws_ml + (((size_t)(q0 + row) * nq + h) * n_ranges + blockIdx.z) * 2;
                 ml[0] = -INFINITY;
@@ -334,6 +338,7 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
     const uint32_t tmem_s = tmem_base, tmem_o = tmem_base + 64, tmem_p = tmem_base + 192;   // P: two buffers of 32 columns
+    qi::pdl_wait();
 
     auto give_up = [&]() {
         if (!*abort_flag) {
@@ -530,14 +535,16 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
             tc_fence_after();
             const float inv = l > 0.f ? 1.f / l : 0.f;
             qi::bf16* orow = out + ((size_t)(q0 + row) * nq + h) * D;
+            // the row's 128 columns in two halves, each half's loads in flight together
 #pragma unroll 1
-            for (int c0 = 0; c0 < D; c0 += 32) {
-                uint32_t v[32];
-                tmem_ld32(tmem_o + lane_addr + c0, v);
+            for (int c0 = 0; c0 < D; c0 += 64) {
+                uint32_t v[64];
+                tmem_ld32(tmem_o + lane_addr + c0, *reinterpret_cast<uint32_t(*)[32]>(&v[0]));
+                tmem_ld32(tmem_o + lane_addr + c0 + 32, *reinterpret_cast<uint32_t(*)[32]>(&v[32]));
                 tmem_ld_wait();
                 if (row < rows_valid && n_tiles > 0) {
 #pragma unroll
-                    for (int i = 0; i < 32; i += 8) {
+                    for (int i = 0; i < 64; i += 8) {
                         uint4 w;
                         w.x = qi_attn::pack_bf16(__uint_as_float(v[i]) * inv, __uint_as_float(v[i + 1]) * inv);
                         w.y = qi_attn::pack_bf16(__uint_as_float(v[i + 2]) * inv, __uint_as_float(v[i + 3]) * inv);
@@ -616,6 +623,9 @@ extern "C" int qi_attention_prefill_tcgen05_supported(int nq, int nkv, int d, in
            max_blocks <= kMaxTableEntries;
 }
 
+// The kernel reads q_start, start_pos, the tile lists and the block table before it waits for the
+// kernel launched before it: they must be complete when this call is made (copied, or written by a
+// kernel that has ended), not still being written by a kernel under programmatic dependent launch.
 // Arguments as qi_attention_prefill_tma (the tile lists are cut to 128 query rows), and: n_ranges > 1
 // cuts every query tile's keys into that many ranges over separate CTAs, merged by a second kernel;
 // `workspace` must then hold n_tokens * nq * n_ranges * (128 + 2) floats.
