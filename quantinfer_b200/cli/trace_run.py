@@ -19,8 +19,6 @@ def main(argv=None) -> int:
     ap.add_argument("--device", default="cuda:0")
     args = ap.parse_args(argv)
 
-    import numpy as np
-
     from quantinfer_b200.engine import Engine, StepEntry
     from quantinfer_b200.engine.engine import DEFAULT_PAGE_SIZE
 

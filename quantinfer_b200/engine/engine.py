@@ -24,7 +24,7 @@ from .. import kernels
 from ..cache import CacheManager
 from ..config import load_config
 from ..config.spec import ModelSpec
-from ..errors import CacheError, KernelError, QuantInferError
+from ..errors import KernelError, QuantInferError
 from ..parts import Runtime
 from ..weights.loader import load_folder
 from .batch import ONLY_ON_THE_DEVICE, StepBatch, StepEntry, batch_from_packed, pack_batch

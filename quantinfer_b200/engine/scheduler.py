@@ -48,7 +48,7 @@ from collections import deque
 from dataclasses import dataclass, field
 from typing import Callable, Optional
 
-from ..errors import OutOfPages, QuantInferError
+from ..errors import OutOfPages
 from ..sampling.params import GenerationConfig
 from .batch import StepEntry
 

@@ -17,7 +17,6 @@ import torch
 
 from .. import kernels
 from ..errors import QuantInferError
-from .params import GenerationConfig
 
 
 class Sampler:
