@@ -208,8 +208,13 @@ attention_decode_kernel(const qi::bf16* __restrict__ q, const qi::bf16* __restri
     const int g = lane >> 2, t4 = lane & 3;
     const int S = kv_len[b];
     const int lo = (window > 0 && S - window > 0) ? S - window : 0;
-    const int k0 = max(split * chunk, lo);
-    const int k1 = min(S, (split + 1) * chunk);
+    // The request's visible key tiles are dealt out evenly over the ranges (`chunk` is only the most a
+    // range may hold, for which the launch was sized): a request that is shorter than the longest one the
+    // launch allows for still keeps every CTA of its ranges equally busy.
+    const int t_lo = lo / kTileKeys, t_hi = (S + kTileKeys - 1) / kTileKeys;
+    const int per = (t_hi - t_lo + n_splits - 1) / n_splits;
+    const int k0 = max((t_lo + split * per) * kTileKeys, lo);
+    const int k1 = min(S, (t_lo + (split + 1) * per) * kTileKeys);
     const size_t part = ((size_t)b * nq + (size_t)hk * G) * n_splits + split;   // + g * n_splits per head
     // the ranges of this launch must cover the request's keys; what lies beyond them is not read, so say so
     if (split == n_splits - 1 && hk == 0 && threadIdx.x == 0 && (long long)n_splits * chunk < S && status)

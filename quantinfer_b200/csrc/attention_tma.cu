@@ -53,9 +53,20 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
         ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y) : "memory");
 }
 
+// The same with a hint for the L2: in a decode step a key/value tile is read once, so it is the first
+// to go when the L2 needs room (what the step's small kernels pass on stays there meanwhile).
+__device__ __forceinline__ void tma_load_2d_once(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
+    uint64_t policy;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(policy));
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1, {%3, %4}], [%2], %5;"
+        ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y), "l"(policy) : "memory");
+}
+
 // Issues the copies of keys [t0, t0 + 64) of kv head hk for K and V into one stage.
 // `needed` = [lo, hi): a missing page inside it is an error; outside it any page will do.
-template <int D>
+// ONCE: the tile is read once in the step (decode), not by many CTAs (prefill).
+template <int D, bool ONCE = false>
 __device__ __forceinline__ void issue_kv_tile(uint32_t stage_smem, uint32_t bar, const CUtensorMap* map_k,
                                               const CUtensorMap* map_v, const int* table, int blk0,
                                               int n_blk, int page_size, int box_rows, int num_pages, int nkv,
@@ -74,8 +85,13 @@ __device__ __forceinline__ void issue_kv_tile(uint32_t stage_smem, uint32_t bar,
         const int row = (page * nkv + hk) * page_size + (key % page_size);
 #pragma unroll
         for (int h = 0; h < D / 64; ++h) {
-            tma_load_2d(stage_smem + h * kHalfBytes + r0 * 128, map_k, bar, h * 64, row);
-            tma_load_2d(stage_smem + kTileBytes + h * kHalfBytes + r0 * 128, map_v, bar, h * 64, row);
+            if (ONCE) {
+                tma_load_2d_once(stage_smem + h * kHalfBytes + r0 * 128, map_k, bar, h * 64, row);
+                tma_load_2d_once(stage_smem + kTileBytes + h * kHalfBytes + r0 * 128, map_v, bar, h * 64, row);
+            } else {
+                tma_load_2d(stage_smem + h * kHalfBytes + r0 * 128, map_k, bar, h * 64, row);
+                tma_load_2d(stage_smem + kTileBytes + h * kHalfBytes + r0 * 128, map_v, bar, h * 64, row);
+            }
         }
     }
 }
@@ -314,8 +330,13 @@ attention_decode_tma_kernel(const qi::bf16* __restrict__ q, qi::bf16* __restrict
     const int g = lane >> 2, t4 = lane & 3;
     const int S = kv_len[b];
     const int lo = (window > 0 && S - window > 0) ? S - window : 0;
-    const int k0 = max(split * chunk, lo);
-    const int k1 = min(S, (split + 1) * chunk);
+    // The request's visible key tiles are dealt out evenly over the ranges (`chunk` is only the most a
+    // range may hold, for which the launch was sized): a request that is shorter than the longest one the
+    // launch allows for still keeps every CTA of its ranges equally busy.
+    const int t_lo = lo / kTileKeys, t_hi = (S + kTileKeys - 1) / kTileKeys;
+    const int per = (t_hi - t_lo + n_splits - 1) / n_splits;
+    const int k0 = max((t_lo + split * per) * kTileKeys, lo);
+    const int k1 = min(S, (t_lo + (split + 1) * per) * kTileKeys);
     const size_t part = ((size_t)b * nq + (size_t)hk * G) * n_splits + split;
     // the ranges of this launch must cover the request's keys; what lies beyond them is not read, so say so
     if (split == n_splits - 1 && hk == 0 && threadIdx.x == 0 && (long long)n_splits * chunk < S && status)
@@ -352,7 +373,7 @@ attention_decode_tma_kernel(const qi::bf16* __restrict__ q, qi::bf16* __restrict
     if (threadIdx.x == 0) {
         for (; issued < kDecodeStages && issued < n_tiles; ++issued) {
             if (t_begin + (issued + 1) * kTileKeys >= S) break;      // holds the newest key
-            issue_kv_tile<D>(kv_s + issued * 2 * kTileBytes, full_bar(issued), &map_k, &map_v, s_table, blk0, n_blk, page_size,
+            issue_kv_tile<D, true>(kv_s + issued * 2 * kTileBytes, full_bar(issued), &map_k, &map_v, s_table, blk0, n_blk, page_size,
                              box_rows, num_pages, nkv, hk, t_begin + issued * kTileKeys, k0, k1, status);
         }
     }
@@ -412,7 +433,7 @@ attention_decode_tma_kernel(const qi::bf16* __restrict__ q, qi::bf16* __restrict
     __syncthreads();
     if (threadIdx.x == 0) {
         for (int i = issued; i < kDecodeStages && i < n_tiles; ++i)
-            issue_kv_tile<D>(kv_s + i * 2 * kTileBytes, full_bar(i), &map_k, &map_v, s_table, blk0, n_blk, page_size, box_rows,
+            issue_kv_tile<D, true>(kv_s + i * 2 * kTileBytes, full_bar(i), &map_k, &map_v, s_table, blk0, n_blk, page_size, box_rows,
                              num_pages, nkv, hk, t_begin + i * kTileKeys, k0, k1, status);
     }
     float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
@@ -458,7 +479,7 @@ attention_decode_tma_kernel(const qi::bf16* __restrict__ q, qi::bf16* __restrict
         }
         __syncthreads();
         if (threadIdx.x == 0 && i + kDecodeStages < n_tiles)
-            issue_kv_tile<D>(kv_s + stage * 2 * kTileBytes, full_bar(stage), &map_k, &map_v, s_table, blk0, n_blk, page_size,
+            issue_kv_tile<D, true>(kv_s + stage * 2 * kTileBytes, full_bar(stage), &map_k, &map_v, s_table, blk0, n_blk, page_size,
                              box_rows, num_pages, nkv, hk, t0 + kDecodeStages * kTileKeys, k0, k1, status);
     }
     if (!ok) {
@@ -526,10 +547,39 @@ __global__ void attention_merge_kernel(const float* __restrict__ ws_o, const flo
     qi::pdl_enter();
     const int h = blockIdx.x, b = blockIdx.y;
     const size_t base = ((size_t)b * nq + h) * n_splits;
+    const int tok = q_start[b];
+    if (n_splits <= 8 && (int)threadIdx.x < D && (int)blockDim.x >= D) {
+        // few ranges: everything a column needs is requested at once (one round trip), then merged in range order
+        const int col = threadIdx.x;
+        float ms[8], ls[8], ov[8];
+#pragma unroll
+        for (int s = 0; s < 8; ++s) {
+            if (s < n_splits) {
+                ms[s] = ws_ml[(base + s) * 2];
+                ls[s] = ws_ml[(base + s) * 2 + 1];
+                ov[s] = ws_o[(base + s) * D + col];
+            }
+        }
+        float M = -INFINITY;
+#pragma unroll
+        for (int s = 0; s < 8; ++s)
+            if (s < n_splits) M = fmaxf(M, ms[s]);
+        float L = 0.f, O = 0.f;
+#pragma unroll
+        for (int s = 0; s < 8; ++s) {
+            if (s < n_splits) {
+                const float f = (ms[s] == -INFINITY) ? 0.f : exp2f(ms[s] - M);
+                L += ls[s] * f;
+                O += (ms[s] == -INFINITY) ? 0.f : ov[s] * f;      // an empty range's slot holds no data
+            }
+        }
+        out[((size_t)tok * nq + h) * D + col] = __float2bfloat16_rn(L > 0.f ? O / L : 0.f);
+        return;
+    }
+    if (n_splits <= 8 && (int)blockDim.x >= D) return;      // the threads beyond the head's columns
     float M = -INFINITY;
 #pragma unroll 4
     for (int s = 0; s < n_splits; ++s) M = fmaxf(M, ws_ml[(base + s) * 2]);
-    const int tok = q_start[b];
     for (int col = threadIdx.x; col < D; col += blockDim.x) {
         float L = 0.f, O = 0.f;
 #pragma unroll 4

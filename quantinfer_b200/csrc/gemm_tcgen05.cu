@@ -88,6 +88,20 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
         ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y) : "memory");
 }
 
+// The same with a hint for the L2: a weight tile of a product of few tokens is read once in a step,
+// so it is the first to go when the L2 needs room, and what the step's small kernels pass on
+// (partial sums, the residual stream, the attention's operands) stays there meanwhile.
+__device__ __forceinline__ uint64_t l2_evict_first_policy() {
+    uint64_t policy;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(policy));
+    return policy;
+}
+__device__ __forceinline__ void tma_load_2d_hint(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y, uint64_t policy) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1, {%3, %4}], [%2], %5;"
+        ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y), "l"(policy) : "memory");
+}
+
 __device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t cols) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(cols) : "memory");
 }
@@ -383,6 +397,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             // The weights are the operand with the many rows: A when the operands are swapped
             // (few tokens), else B. They are never written on the device, so the first stages'
             // weight tiles of this CTA's first tile are requested before the wait.
+            const uint64_t stream_once = l2_evict_first_policy();
             uint32_t early = 0;
             if (blockIdx.x < total_tiles) {
                 const int tile = blockIdx.x;
@@ -394,7 +409,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     mbar_expect_tx(full_bar(i), L::kStageBytes);
                     const uint32_t a_dst = base + i * L::kStageBytes;
                     const int k0 = (kb_begin + (int)i) * BK;
-                    if (SWAP) tma_load_2d(a_dst, &map_a, full_bar(i), k0, tile_a * BM);
+                    if (SWAP) tma_load_2d_hint(a_dst, &map_a, full_bar(i), k0, tile_a * BM, stream_once);
                     else tma_load_2d(a_dst + L::kABytes, &map_b, full_bar(i), k0, tile_b * BN);
                 }
             }
@@ -421,7 +436,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                         break;
                     }
                     mbar_expect_tx(full_bar(s), L::kStageBytes);
-                    tma_load_2d(a_dst, &map_a, full_bar(s), k0, tile_a * BM);
+                    if (SWAP) tma_load_2d_hint(a_dst, &map_a, full_bar(s), k0, tile_a * BM, stream_once);
+                    else tma_load_2d(a_dst, &map_a, full_bar(s), k0, tile_a * BM);
                     tma_load_2d(a_dst + L::kABytes, &map_b, full_bar(s), k0, tile_b * BN);
                 }
             }

@@ -101,7 +101,19 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ resid, const TD* __re
         if (active) {
             Vec8<float>::load(xr + i, x);
             Vec8<float>::load(gain + i, g);
-            if (dr) {
+            if (dr && delta_splits <= 8) {
+                // all partial sums are requested at once (one round trip), then added in their order
+                float d8[8][8];
+#pragma unroll
+                for (int k = 0; k < 8; ++k)
+                    if (k < delta_splits) Vec8<TD>::load(dr + k * delta_split_stride + i, d8[k]);
+#pragma unroll
+                for (int k = 0; k < 8; ++k)
+                    if (k < delta_splits) {
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) x[j] += d8[k][j];
+                    }
+            } else if (dr) {
 #pragma unroll 4
                 for (int k = 0; k < delta_splits; ++k) {
                     Vec8<TD>::load(dr + k * delta_split_stride + i, d);
