@@ -11,6 +11,8 @@
 // inverse :187, scale :189; the residual add is crates/quantinfer-runtime/src/linear.rs:129-142).
 #include "common.cuh"
 
+#include <cooperative_groups.h>
+
 namespace {
 
 template <typename TD, typename TO>
@@ -171,6 +173,95 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ resid, const TD* __re
     }
 }
 
+// The same for few rows (a decode step): a row is spread over a thread-block cluster of kRowCtas
+// CTAs, so that as many SMs pull the row's partial sums as the row has parts (eight rows of
+// eight partial sums are 1 MB: on eight SMs the loads alone took 1.9 us). Each CTA adds its part of
+// the row, the sums of squares meet in distributed shared memory and are added in the order of
+// the CTAs' ranks.
+constexpr int kRowCtas = 4;
+
+template <typename TD, typename TO>
+__global__ void add_rmsnorm_cluster_kernel(float* __restrict__ resid, const TD* __restrict__ delta,
+                                           int delta_splits, size_t delta_split_stride,
+                                           const float* __restrict__ gain, float eps, TO* __restrict__ out,
+                                           const int* __restrict__ rows, int hidden, int write_resid) {
+    namespace cg = cooperative_groups;
+    __shared__ float scratch[32];
+    __shared__ float part_sum;
+    cg::cluster_group cluster = cg::this_cluster();
+    qi::pdl_enter();
+    const int r = blockIdx.x / kRowCtas, part = (int)cluster.block_rank();
+    const int cols = hidden / kRowCtas;                 // of this CTA (the launch checked that it divides)
+    const int s = rows ? rows[r] : r;
+    float* xr = resid + (size_t)s * hidden + (size_t)part * cols;
+    const TD* dr = delta ? delta + (size_t)s * hidden + (size_t)part * cols : nullptr;
+    const float* gr = gain + (size_t)part * cols;
+    TO* orow = out + (size_t)r * hidden + (size_t)part * cols;
+    const int i = threadIdx.x * 8;
+    const bool active = i < cols;
+    float x[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f}, d[8], g[8];
+    if (active) {
+        Vec8<float>::load(xr + i, x);
+        Vec8<float>::load(gr + i, g);
+        if (dr && delta_splits <= 8) {
+            float d8[8][8];
+#pragma unroll
+            for (int k = 0; k < 8; ++k)
+                if (k < delta_splits) Vec8<TD>::load(dr + k * delta_split_stride + i, d8[k]);
+#pragma unroll
+            for (int k = 0; k < 8; ++k)
+                if (k < delta_splits) {
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) x[j] += d8[k][j];
+                }
+        } else if (dr) {
+#pragma unroll 4
+            for (int k = 0; k < delta_splits; ++k) {
+                Vec8<TD>::load(dr + k * delta_split_stride + i, d);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) x[j] += d[j];
+            }
+        }
+        if (write_resid) Vec8<float>::store(xr + i, x);
+    }
+    float sumsq = 0.f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) sumsq += x[j] * x[j];
+    const float mine = qi::block_sum(sumsq, scratch);
+    if (threadIdx.x == 0) part_sum = mine;
+    cluster.sync();
+    float total = 0.f;
+#pragma unroll
+    for (int c = 0; c < kRowCtas; ++c) total += *cluster.map_shared_rank(&part_sum, c);      // rank order
+    cluster.sync();                                      // nobody leaves while its sum may still be read
+    const float inv = 1.0f / sqrtf(total / (float)hidden + eps);
+    if (active) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) x[j] = x[j] * inv * g[j];
+        Vec8<TO>::store(orow + i, x);
+    }
+}
+
+// Launch with a cluster of kRowCtas CTAs along x (and the programmatic-serialization attribute, as qi::launch).
+template <typename... KArgs, typename... Args>
+cudaError_t launch_cluster(void (*kern)(KArgs...), dim3 grid, dim3 block, cudaStream_t stream, Args&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = 0;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = kRowCtas;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = qi::pdl_enabled() ? 2 : 1;
+    return cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
+}
+
 // Plain RMSNorm over the last dimension of a [rows, width] matrix of type T,
 // used by tests of the norm alone and by parts that normalise activations.
 template <typename T>
@@ -209,6 +300,18 @@ extern "C" int qi_add_rmsnorm(float* resid, const void* delta, int delta_dtype, 
     const int dd = delta ? delta_dtype : qi::kF32;
     const bool vec = hidden % 8 == 0 && ((uintptr_t)resid & 31) == 0 && ((uintptr_t)delta & 15) == 0 &&
                      ((uintptr_t)out & 15) == 0 && ((uintptr_t)gain & 15) == 0 && delta_split_stride % 8 == 0;
+    // few rows (a decode step): a row over a cluster of CTAs, so that more SMs pull its partial sums
+    if (vec && n_rows <= 64 && delta && delta_splits > 1 && hidden % (8 * kRowCtas) == 0 && hidden / (8 * kRowCtas) <= 1024 &&
+        hidden / kRowCtas >= 256) {
+        const int threads = (hidden / kRowCtas / 8 + 31) / 32 * 32;
+        QI_DISPATCH_DTYPE(dd, TD, {
+            QI_DISPATCH_DTYPE(out_dtype, TO, {
+                launch_cluster(add_rmsnorm_cluster_kernel<TD, TO>, dim3(n_rows * kRowCtas), dim3(threads), stream, resid, (const TD*)delta,
+                               delta_splits, (size_t)delta_split_stride, gain, eps, (TO*)out, rows, hidden, write_resid);
+            });
+        });
+        return qi::check_launch("add_rmsnorm (clusters)");
+    }
     if (vec) {
         int threads = (hidden / 8 + 31) / 32 * 32;
         if (threads > 512) threads = 512;
