@@ -264,10 +264,36 @@ __device__ __forceinline__ void head_norm_rope(const TIn* src, int splits, long 
     const int p = 2 * lane;
     const bool has = p < kHalf;
     float2 a = make_float2(0.f, 0.f), b = make_float2(0.f, 0.f);
+    // everything the head needs is requested at once (one round trip): its parts of up to eight
+    // splits, the gain, the row of the rotation table
+    float2 ga = make_float2(1.f, 1.f), gb = ga, c = make_float2(1.f, 1.f), sn = make_float2(0.f, 0.f);
     if (has) {
-        a = load2<TIn>(src + p);
-        b = load2<TIn>(src + p + kHalf);
-        for (int k = 1; k < splits; ++k) {
+        float2 xs[8], ys[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            if (k < splits) {
+                xs[k] = load2<TIn>(src + k * stride + p);
+                ys[k] = load2<TIn>(src + k * stride + p + kHalf);
+            }
+        }
+        if (gain) {
+            ga = *reinterpret_cast<const float2*>(gain + p);
+            gb = *reinterpret_cast<const float2*>(gain + p + kHalf);
+        }
+        if (cos_t) {
+            c = *reinterpret_cast<const float2*>(cos_t + (size_t)pos * kHalf + p);
+            sn = *reinterpret_cast<const float2*>(sin_t + (size_t)pos * kHalf + p);
+        }
+        a = xs[0];
+        b = ys[0];
+#pragma unroll
+        for (int k = 1; k < 8; ++k) {
+            if (k < splits) {
+                a.x += xs[k].x; a.y += xs[k].y;
+                b.x += ys[k].x; b.y += ys[k].y;
+            }
+        }
+        for (int k = 8; k < splits; ++k) {
             const float2 x = load2<TIn>(src + k * stride + p), y = load2<TIn>(src + k * stride + p + kHalf);
             a.x += x.x; a.y += x.y;
             b.x += y.x; b.y += y.y;
@@ -279,7 +305,6 @@ __device__ __forceinline__ void head_norm_rope(const TIn* src, int splits, long 
         ss = qi::warp_sum(ss);
         const float inv = 1.0f / sqrtf(ss / (float)D + eps);
         if (has) {
-            const float2 ga = *reinterpret_cast<const float2*>(gain + p), gb = *reinterpret_cast<const float2*>(gain + p + kHalf);
             a.x = a.x * inv * ga.x; a.y = a.y * inv * ga.y;
             b.x = b.x * inv * gb.x; b.y = b.y * inv * gb.y;
         }
@@ -287,8 +312,6 @@ __device__ __forceinline__ void head_norm_rope(const TIn* src, int splits, long 
     lo = a;
     hi = b;
     if (cos_t && has) {
-        const float2 c = *reinterpret_cast<const float2*>(cos_t + (size_t)pos * kHalf + p);
-        const float2 sn = *reinterpret_cast<const float2*>(sin_t + (size_t)pos * kHalf + p);
         lo = make_float2(a.x * c.x - b.x * sn.x, a.y * c.y - b.y * sn.y);
         hi = make_float2(a.x * sn.x + b.x * c.x, a.y * sn.y + b.y * c.y);
     }
