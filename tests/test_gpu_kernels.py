@@ -73,16 +73,29 @@ def test_add_rmsnorm(dtype, rows, hidden):
     assert float((out2.double().cpu() - ref2).abs().max()) < tol and torch.equal(r2.cpu(), resid)
 
 
-def test_add_rmsnorm_takes_split_partials():
+@pytest.mark.parametrize("rows, hidden, splits", [
+    (6, 264, 3),          # one CTA a row
+    (8, 4096, 8),         # few rows of a wide model: a row over a cluster of four CTAs, all partial sums at once
+    (64, 1024, 2),        # the most rows and the narrowest rows that take the clusters
+    (3, 5120, 16),        # more partial sums than are requested at once
+    (65, 4096, 4),        # one row too many for the clusters
+])
+def test_add_rmsnorm_takes_split_partials(rows, hidden, splits):
     torch.manual_seed(2)
-    resid, parts = torch.randn(6, 264), torch.randn(3, 6, 264)
-    gain = torch.ones(264)
+    resid, parts = torch.randn(rows, hidden), torch.randn(splits, rows, hidden)
+    gain = 1 + 0.1 * torch.randn(hidden)
     x = resid.double() + parts.double().sum(0)
-    ref = x * torch.rsqrt((x * x).mean(-1, keepdim=True) + 1e-6)
-    out = torch.empty(6, 264, dtype=torch.bfloat16, device=DEV)
+    ref = x * torch.rsqrt((x * x).mean(-1, keepdim=True) + 1e-6) * gain.double()
+    out = torch.empty(rows, hidden, dtype=torch.bfloat16, device=DEV)
     r = resid.to(DEV)
     _k().add_rmsnorm(r, parts.to(DEV), gain.to(DEV), 1e-6, out)
-    assert float((out.double().cpu() - ref).abs().max()) < 2e-2 and float((r.double().cpu() - x).abs().max()) < 1e-5
+    assert float((out.double().cpu() - ref).abs().max()) < 3e-2 and float((r.double().cpu() - x).abs().max()) < 1e-5
+    # the same sums for picked rows only (what the head's norm does): the residual stays as it was
+    r2 = resid.to(DEV)
+    pick = [rows - 1, 0]
+    out2 = torch.empty(2, hidden, dtype=torch.float32, device=DEV)
+    _k().add_rmsnorm(r2, parts.to(DEV), gain.to(DEV), 1e-6, out2, rows=I(pick))
+    assert float((out2.double().cpu() - ref[pick]).abs().max()) < 2e-5 and torch.equal(r2.cpu(), resid)
 
 
 # ------------------------------------------------------------------ matrix products
