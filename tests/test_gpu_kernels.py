@@ -420,14 +420,15 @@ def test_attention_decode_kernels(mode, nq, nkv, d, ctx, ps, window):
 @pytest.mark.parametrize("chunk, ctx, window", [
     (2048, [2047, 100, 513, 0], 0),     # one range: the CTA writes the result itself
     (2048, [2047, 100, 513, 0], 300),   # the same with a window
-    (1024, [1500, 100, 1023, 1024], 0), # two ranges, the second empty for the short requests
+    (1024, [1500, 100, 1023, 1024], 0), # two ranges; a request of two key tiles has one in each
     (512, [1999, 64, 700, 0], 0),       # five ranges
-    (256, [1700, 300, 255, 256], 200),  # a window: leading ranges are empty
+    (256, [1700, 300, 255, 256], 200),  # a window: its tiles are dealt out over the ranges, the rest are empty
     (192, [1700, 300, 255, 256], 0),    # ten ranges
 ])
 def test_attention_decode_key_ranges(chunk, ctx, window):
     """One key range per request (the kernel writes the output itself) and several (partial results,
-    merged by a second kernel), with ranges that are empty for the shorter requests."""
+    merged by a second kernel). A request's key tiles are dealt out evenly over the ranges, so a request
+    with fewer tiles than ranges leaves the last ranges empty."""
     assert _attention_case(8, 2, 128, ctx, [1] * len(ctx), 64, window, torch.bfloat16, "decode_tma", decode_chunk=chunk) < 1.2e-2
     assert _attention_case(4, 1, 64, ctx[:2], [1, 1], 16, window, torch.bfloat16, "decode_tma", decode_chunk=chunk) < 1.2e-2
 
