@@ -37,9 +37,10 @@
 //     launch that is always so. If you produce these arrays with a kernel launched under
 //     programmatic dependent launch, that kernel must not release its successors early
 //     (no cudaTriggerProgrammaticLaunchCompletion / griddepcontrol.launch_dependents).
-//   * n_splits * chunk must cover the longest kv_len. Keys beyond the last range are not
-//     read; the kernel then sets bit 16 of *status instead of returning a wrong result
-//     silently, and the caller must treat the output as invalid.
+//   * n_splits * chunk must cover the longest kv_len: `chunk` is the most keys a range may
+//     hold, which the launch's staging is sized for (a request's key tiles are dealt out
+//     evenly over the ranges, whatever its length). For a longer request the kernel sets
+//     bit 16 of *status, and the caller must treat the output as invalid.
 #pragma once
 
 #include <cuda_runtime.h>

@@ -431,7 +431,8 @@ def attention_decode(q, out, k_pages, v_pages, block_table, kv_len, q_start, nq,
                      window: int, chunk: int, n_splits: int, status, workspace=None,
                      use_tma: bool | None = None) -> None:
     """Paged GQA attention for one query token per request (bfloat16, head size 64 or
-    128), keys split into `n_splits` ranges of `chunk` positions. `workspace`: float32,
+    128), a request's key tiles dealt out evenly over `n_splits` ranges of at most `chunk` positions
+    (`n_splits * chunk` must cover the longest request). `workspace`: float32,
     at least batch * nq * n_splits * (d + 2) elements (allocated when None)."""
     _req(q, "q", torch.bfloat16, 2)
     _req(out, "out", torch.bfloat16, 2)
