@@ -415,6 +415,101 @@ def mixed_workload(args, entry):
     return out
 
 
+TIMELINE_KINDS = {10: "add + norm", 11: "add + norm (clusters)", 20: "product", 21: "product + SiLU", 30: "decode attention",
+                  31: "range merge"}
+
+
+def timeline_stamps(lib):
+    """The records the instrumented kernels left since the last call (csrc/common.cuh, QI_TIMELINE)."""
+    import ctypes as C
+
+    class Stamp(C.Structure):
+        _fields_ = [("t0", C.c_ulonglong), ("tw", C.c_ulonglong), ("td", C.c_ulonglong), ("t1", C.c_ulonglong),
+                    ("kind", C.c_int), ("grid", C.c_int), ("cta", C.c_int), ("sm", C.c_int)]
+
+    cap, out = 1 << 17, []
+    for name in ("qi_timeline_norm", "qi_timeline_gemm", "qi_timeline_attention"):
+        n, buf = C.c_uint(0), (Stamp * cap)()
+        getattr(lib, name)(buf, C.byref(n), 1)
+        out += [(s.t0, s.tw, s.td, s.t1, s.kind, s.grid) for s in buf[:min(n.value, cap)]]
+    return out
+
+
+def timeline_launches(stamps):
+    """Sorts CTA records into launches: records of one kind and grid size, in the order of their starts, as
+    many as the grid has CTAs. Per launch: first start, first wake (the wait for the kernel before it ended),
+    first data, first and last end."""
+    launches, open_ = [], {}
+    for s in sorted(stamps):
+        key = (s[4], s[5])
+        cur = open_.get(key)
+        if cur is None or len(cur) >= s[5]:
+            cur = open_[key] = []
+            launches.append((key, cur))
+        cur.append(s)
+    rows = []
+    for (kind, grid), recs in launches:
+        if len(recs) != grid:
+            continue
+        wakes, datas = [r[1] for r in recs if r[1]], [r[2] for r in recs if r[2]]
+        rows.append(dict(kind=kind, grid=grid, start=min(r[0] for r in recs), wake=min(wakes) if wakes else min(r[0] for r in recs),
+                         data=min(datas) if datas else 0, first_end=min(r[3] for r in recs), end=max(r[3] for r in recs)))
+    return sorted(rows, key=lambda r: r["wake"])
+
+
+def timeline_report(bench, batch):
+    """Markdown: the kernels of one layer of a decode step as they ran in their place (microseconds from the
+    first listed kernel's wake), and the means over two steps by kind and grid. Needs the kernels built with
+    their time stamps (QUANTINFER_B200_TIMELINE=1, which `--timeline` sets before the library is loaded)."""
+    import collections
+
+    from quantinfer_b200 import kernels
+    from quantinfer_b200.sampling import GenerationConfig
+
+    torch, engine, lib = bench.torch, bench.engine, kernels.library()
+    ids = bench.fill(batch)
+    rows = [(GenerationConfig(max_new_tokens=1 << 20), 0)] * batch
+    hist = engine.decode_on_device(ids, [1 + i for i in range(batch)], 12, rows, bench.sampler)
+    torch.cuda.synchronize()
+    timeline_stamps(lib)                                   # forget the warm-up
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    engine.decode_on_device(ids, hist[-1].tolist(), 2, rows, bench.sampler)
+    b.record()
+    torch.cuda.synchronize()
+    launches = timeline_launches(timeline_stamps(lib))
+    name = lambda r: f"{TIMELINE_KINDS.get(r['kind'], r['kind'])}, {r['grid']} CTAs"
+    out = [f"Two decode steps, batch {batch}: {a.elapsed_time(b) / 2:.3f} ms a step with the stamps in; {len(launches)} launches sorted.", "",
+           "One layer from the middle of the second step (us from the first row's wake):", "",
+           "| kernel | first CTA starts | wake | first data | first CTA ends | last CTA ends | wake after the kernel before ended | wake to end |",
+           "|---|---|---|---|---|---|---|---|"]
+    mid = len(launches) // 2 + len(launches) // 8
+    first = next((i for i in range(mid, len(launches)) if launches[i]["kind"] in (10, 11)), mid)
+    t00, prev_end = launches[first]["wake"], launches[first - 1]["end"] if first else None
+    rel = lambda t: f"{(t - t00) / 1e3:.2f}" if t else "-"
+    for r in launches[first:first + 9]:
+        gap = f"{(r['wake'] - prev_end) / 1e3:.2f}" if prev_end else "-"
+        out.append(f"| {name(r)} | {rel(r['start'])} | {rel(r['wake'])} | {rel(r['data'])} | {rel(r['first_end'])} | {rel(r['end'])} | {gap} | {(r['end'] - r['wake']) / 1e3:.2f} |")
+        prev_end = r["end"]
+    agg, prev_end = collections.OrderedDict(), None
+    for r in launches:
+        if prev_end is not None:
+            g = agg.setdefault(name(r), [0, 0.0, 0.0, 0.0, 0.0])
+            g[0] += 1
+            g[1] += (r["wake"] - prev_end) / 1e3
+            g[2] += (r["end"] - r["wake"]) / 1e3
+            g[3] += (r["data"] - r["wake"]) / 1e3 if r["data"] else 0.0
+            g[4] += (r["end"] - r["first_end"]) / 1e3
+        prev_end = r["end"]
+    out += ["", "Means over both steps (us):", "", "| kernel | launches | wake after the kernel before ended | wake to last end | wake to first data | first end to last end |",
+            "|---|---|---|---|---|---|"]
+    for k, g in agg.items():
+        out.append(f"| {k} | {g[0]} | {g[1] / g[0]:.2f} | {g[2] / g[0]:.2f} | {g[3] / g[0]:.2f} | {g[4] / g[0]:.2f} |")
+    for rid in ids:
+        engine.close(rid)
+    return "\n".join(out)
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -431,7 +526,12 @@ def main() -> int:
     ap.add_argument("--mixed-chunk", type=int, default=None, help="longest prompt portion of the scheduler workload")
     ap.add_argument("--only", choices=["decode", "prefill", "mixed"], default=None,
                     help="run one part only (for profiler captures of a small case)")
+    ap.add_argument("--timeline", action="store_true",
+                    help="build the kernels with their time stamps and print where a decode step's time goes, kernel by kernel")
     args = ap.parse_args()
+    if args.timeline:
+        os.environ["QUANTINFER_B200_TIMELINE"] = "1"      # before the library is built and loaded
+        args.only = "decode"
 
     if args.impl == "reference":
         print(json.dumps({"impl": "reference",
@@ -459,6 +559,9 @@ def main() -> int:
     a, T = bench.arith, bench.prompt_len
     flops = a["gemm_flops"](T) + a["attn_flops"](T)
 
+    if args.timeline:
+        print(timeline_report(bench, args.batch))
+        return 0
     # the headline first: the K timed decode steps, before anything else has heated the device
     if args.only != "prefill":
         head = bench.decode_rate(args.batch, args.steps, args.warmup, sample_clocks=True)

@@ -317,6 +317,8 @@ __device__ __forceinline__ void head_norm_rope(const TIn* src, int splits, long 
     }
 }
 
+QI_TL_DEFINE(qi_timeline_attention)
+
 // DIRECT: the request's keys are one range, and the CTA writes the attention output itself.
 // FUSED: the queries and the step's new key and value are made here from the q/k/v projection
 // (`rope`), not read from `q` and the cache; TIn is the projection's element type.
@@ -345,6 +347,7 @@ attention_decode_tma_kernel(const qi::bf16* __restrict__ q, qi::bf16* __restrict
     // positions were written by earlier steps: only the newest key (position S - 1) and the
     // queries come from the kernel before this one. So the first tiles are requested before the
     // wait for that kernel, unless they hold the newest key.
+    QI_TL_BEGIN();
     qi::pdl_launch_dependents();
     const int split = blockIdx.x, hk = blockIdx.y, b = blockIdx.z;
     const int n_splits = gridDim.x;
@@ -368,6 +371,8 @@ attention_decode_tma_kernel(const qi::bf16* __restrict__ q, qi::bf16* __restrict
     const int tok = q_start[b];
     if (k0 >= k1) {   // nothing of this range belongs to the request: an empty partial
         qi::pdl_wait();
+        QI_TL_WAKE();
+        QI_TL_END(30);
         if (DIRECT) {
             for (int idx = threadIdx.x; idx < G * D; idx += kDecodeThreads)
                 out[((size_t)tok * nq + (size_t)hk * G) * D + idx] = __float2bfloat16_rn(0.f);
@@ -401,6 +406,7 @@ attention_decode_tma_kernel(const qi::bf16* __restrict__ q, qi::bf16* __restrict
         }
     }
     qi::pdl_wait();
+    QI_TL_WAKE();
     constexpr int kChunks = D / 8;
     // this CTA's range holds the step's own position: it makes the new key and value, writes them to
     // the cache and, since its copy of that cache row may be older than the write, into its tile
@@ -474,6 +480,7 @@ attention_decode_tma_kernel(const qi::bf16* __restrict__ q, qi::bf16* __restrict
         const int t0 = t_begin + i * kTileKeys;
         ok = mbar_wait(full_bar(stage), (uint32_t)(i / kDecodeStages) & 1u);
         if (!ok) break;
+        if (i == 0) QI_TL_DATA();
         if (owns_new && i == n_tiles - 1) {
             // the tile's row of position S - 1 is replaced by what this CTA computed
             const int r = S - 1 - t0;
@@ -556,6 +563,7 @@ attention_decode_tma_kernel(const qi::bf16* __restrict__ q, qi::bf16* __restrict
             }
         }
     }
+    QI_TL_END(30);
 }
 
 // out[b, h, :] = sum_s o_s 2^(m_s - M) / sum_s l_s 2^(m_s - M), key ranges in order. A separate
@@ -567,7 +575,9 @@ template <int D>
 __global__ void attention_merge_kernel(const float* __restrict__ ws_o, const float* __restrict__ ws_ml,
                                        const int* __restrict__ q_start, qi::bf16* __restrict__ out, int nq,
                                        int n_splits) {
+    QI_TL_BEGIN();
     qi::pdl_enter();
+    QI_TL_WAKE();
     const int h = blockIdx.x, b = blockIdx.y;
     const size_t base = ((size_t)b * nq + h) * n_splits;
     const int tok = q_start[b];
@@ -597,6 +607,7 @@ __global__ void attention_merge_kernel(const float* __restrict__ ws_o, const flo
             }
         }
         out[((size_t)tok * nq + h) * D + col] = __float2bfloat16_rn(L > 0.f ? O / L : 0.f);
+        QI_TL_END(31);
         return;
     }
     if (n_splits <= 8 && (int)blockDim.x >= D) return;      // the threads beyond the head's columns
@@ -615,6 +626,7 @@ __global__ void attention_merge_kernel(const float* __restrict__ ws_o, const flo
         }
         out[((size_t)tok * nq + h) * D + col] = __float2bfloat16_rn(L > 0.f ? O / L : 0.f);
     }
+    QI_TL_END(31);
 }
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -879,3 +891,5 @@ extern "C" int qi_attention_decode_tma_static(const void* q, void* out, const vo
     return qi_attention_decode_tma(q, out, k_pages, v_pages, block_table, max_blocks, page_size, num_pages, kv_len,
                                    q_start, batch, nq, nkv, d, scale, window, chunk, n_splits, ws_o, ws_ml, status, stream);
 }
+
+QI_TL_EXPORT(qi_timeline_attention)

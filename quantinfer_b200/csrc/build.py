@@ -32,6 +32,16 @@ NVCC_FLAGS = [
 ]
 
 
+def timeline() -> bool:
+    """QUANTINFER_B200_TIMELINE=1: the kernels are built with their time stamps (-DQI_TIMELINE), into a
+    folder of their own beside the ordinary build."""
+    return os.environ.get("QUANTINFER_B200_TIMELINE") == "1"
+
+
+def _flags() -> list[str]:
+    return NVCC_FLAGS + (["-DQI_TIMELINE"] if timeline() else [])
+
+
 def _say(msg: str) -> None:
     print(f"[quantinfer_b200] {msg}", file=sys.stderr, flush=True)
 
@@ -60,7 +70,7 @@ def find_nvcc() -> str:
 
 def _stamp() -> str:
     h = hashlib.sha256()
-    h.update(" ".join(NVCC_FLAGS).encode())
+    h.update(" ".join(_flags()).encode())
     for p in sorted(list(CSRC.glob("*.cu")) + list(CSRC.glob("*.cuh")) + list(CSRC.glob("*.h"))):
         h.update(p.name.encode())
         h.update(p.read_bytes())
@@ -73,15 +83,15 @@ def _build_dir() -> Path:
         d = Path(override)
         d.mkdir(parents=True, exist_ok=True)
         return d
-    d = CSRC / "_build"
+    d = CSRC / "_build" / "timeline" if timeline() else CSRC / "_build"
     try:
-        d.mkdir(exist_ok=True)
+        d.mkdir(parents=True, exist_ok=True)
         probe = d / f".write_probe_{os.getpid()}"
         probe.write_text("x")
         probe.unlink()
         return d
     except OSError:
-        d = Path(tempfile.gettempdir()) / f"quantinfer_b200_build_{os.getuid()}"
+        d = Path(tempfile.gettempdir()) / (f"quantinfer_b200_build_{os.getuid()}" + ("_timeline" if timeline() else ""))
         d.mkdir(parents=True, exist_ok=True)
         return d
 
@@ -124,7 +134,7 @@ def _compile(d: Path, lib: Path) -> None:
 
     def one(pair):
         src, obj = pair
-        cmd = [nvcc, *NVCC_FLAGS, "-I", str(CSRC), "-c", str(src), "-o", str(obj)]
+        cmd = [nvcc, *_flags(), "-I", str(CSRC), "-c", str(src), "-o", str(obj)]
         r = subprocess.run(cmd, capture_output=True, text=True)
         if r.returncode != 0:
             raise RuntimeError(f"nvcc failed on {src.name}:\n{r.stdout}\n{r.stderr}")

@@ -99,6 +99,56 @@ int check_launch(const char* what);  // cudaGetLastError -> message
 
 }  // namespace qi
 
+// ---- a timeline of a step in its place (built only with -DQI_TIMELINE) -------------------------
+// Thread 0 of every CTA of the instrumented kernels leaves a record: the global timer at the
+// CTA's start, when its wait for the kernel before it ended, when its first data had arrived, and
+// at its end. Each source file keeps its own log (qi_timeline_<file>), the host sorts the
+// records of a step into launches afterwards. Without the flag the macros are empty.
+#ifdef QI_TIMELINE
+struct QiStamp { unsigned long long t0, tw, td, t1; int kind, grid, cta, sm; };
+#define QI_TL_CAP (1 << 17)
+__device__ __forceinline__ unsigned long long qi_now() { unsigned long long t; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t)); return t; }
+#define QI_TL_DEFINE(NAME)                                                                                       \
+    __device__ QiStamp qi_tl_log[QI_TL_CAP];                                                                     \
+    __device__ unsigned qi_tl_n;                                                                                 \
+    __device__ __forceinline__ void qi_tl_put(int kind, unsigned long long t0, unsigned long long tw, unsigned long long td) { \
+        const unsigned i = atomicAdd(&qi_tl_n, 1u);                                                              \
+        if (i < QI_TL_CAP) {                                                                                     \
+            unsigned sm; asm volatile("mov.u32 %0, %smid;" : "=r"(sm));                                          \
+            QiStamp s; s.t0 = t0; s.tw = tw; s.td = td; s.t1 = qi_now(); s.kind = kind;                          \
+            s.grid = gridDim.x * gridDim.y * gridDim.z; s.cta = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z); \
+            s.sm = (int)sm; qi_tl_log[i] = s;                                                                    \
+        }                                                                                                        \
+    }                                                                                                            \
+    int NAME##_impl(QiStamp* host, unsigned* n, int reset) {                                                     \
+        cudaDeviceSynchronize();                                                                                 \
+        cudaMemcpyFromSymbol(n, qi_tl_n, 4);                                                                     \
+        if (host) cudaMemcpyFromSymbol(host, qi_tl_log, sizeof(QiStamp) * (*n < QI_TL_CAP ? *n : QI_TL_CAP));    \
+        if (reset) { unsigned z = 0; cudaMemcpyToSymbol(qi_tl_n, &z, 4); }                                       \
+        return 0;                                                                                                \
+    }
+#define QI_TL_EXPORT(NAME) extern "C" int NAME(QiStamp* host, unsigned* n, int reset) { return NAME##_impl(host, n, reset); }
+#define QI_TL_BEGIN() const unsigned long long qi_tl_t0 = qi_now(); unsigned long long qi_tl_tw = 0, qi_tl_td = 0; (void)qi_tl_tw; (void)qi_tl_td
+#define QI_TL_WAKE() qi_tl_tw = qi_now()
+#define QI_TL_DATA() qi_tl_td = qi_now()
+#define QI_TL_SHARED() __shared__ unsigned long long qi_tl_sh[2]
+#define QI_TL_SHARED_WAKE() do { qi_tl_sh[0] = qi_now(); qi_tl_sh[1] = 0; } while (0)
+#define QI_TL_SHARED_DATA() qi_tl_sh[1] = qi_now()
+#define QI_TL_END(kind) do { if (threadIdx.x == 0) qi_tl_put(kind, qi_tl_t0, qi_tl_tw, qi_tl_td); } while (0)
+#define QI_TL_END_SHARED(kind) do { if (threadIdx.x == 0) qi_tl_put(kind, qi_tl_t0, qi_tl_sh[0], qi_tl_sh[1]); } while (0)
+#else
+#define QI_TL_DEFINE(NAME)
+#define QI_TL_EXPORT(NAME)
+#define QI_TL_BEGIN() do { } while (0)
+#define QI_TL_WAKE() do { } while (0)
+#define QI_TL_DATA() do { } while (0)
+#define QI_TL_SHARED() do { } while (0)
+#define QI_TL_SHARED_WAKE() do { } while (0)
+#define QI_TL_SHARED_DATA() do { } while (0)
+#define QI_TL_END(kind) do { } while (0)
+#define QI_TL_END_SHARED(kind) do { } while (0)
+#endif
+
 #define QI_REQUIRE(cond, ...)                    \
     do {                                         \
         if (!(cond)) return qi::fail(__VA_ARGS__); \

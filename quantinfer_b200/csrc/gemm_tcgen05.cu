@@ -333,6 +333,8 @@ __device__ __forceinline__ void rope_epilogue(uint32_t tmem_tile, int col_base, 
 // B tile in L2). The accumulator in tensor memory is double-buffered: while the
 // epilogue warps drain one buffer, the MMA warp already fills the other with the next
 // tile, and the TMA ring runs on across tile borders.
+QI_TL_DEFINE(qi_timeline_gemm)
+
 template <int BN, int STAGES, bool SWAP, typename TOut, int EPI>
 __global__ void __launch_bounds__(kThreads)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
@@ -352,6 +354,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     auto acc_full_bar = [&](int a) { return bars + 8u * (2 * STAGES + a); };
     auto acc_empty_bar = [&](int a) { return bars + 8u * (2 * STAGES + 2 + a); };
 
+    QI_TL_BEGIN();
+    QI_TL_SHARED();
     qi::pdl_launch_dependents();   // the next kernel may be scheduled while this one runs
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int tiles_a = (rows_a + BM - 1) / BM, tiles_b = (rows_b + BN - 1) / BN;
@@ -454,6 +458,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         // ---------------- MMA issuer ----------------
         if (lane == 0) {
             qi::pdl_wait();   // its operands come after the producer's wait: the polls below start counting from there
+            QI_TL_SHARED_WAKE();
             constexpr uint32_t idesc = make_idesc(BM, BN);
             uint32_t it = 0;
             int j = 0;                // tiles this CTA has started
@@ -478,6 +483,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                         break;
                     }
                     tc_fence_after();
+                    if (it == 0) QI_TL_SHARED_DATA();
                     const uint32_t a_addr = base + s * L::kStageBytes;
                     const uint64_t adesc = make_smem_desc(a_addr);
                     const uint64_t bdesc = make_smem_desc(a_addr + L::kABytes);
@@ -614,6 +620,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     }
     tc_fence_before();
     __syncthreads();
+    QI_TL_END_SHARED(20 + EPI + (SWAP ? 0 : 5));
     if (warp == 1) tmem_dealloc(tmem_base, kTmemCols);
 }
 
@@ -1222,3 +1229,5 @@ extern "C" int qi_gemm_bf16_qkv_rope(const void* x, const void* w, int M, int K,
     return launch<128, stages_of(128), false, qi::bf16, 2>(ma, mb, (qi::bf16*)nullptr, M, N, K, N, 1, kb_total, 0, status, stream, e);
 }
 
+
+QI_TL_EXPORT(qi_timeline_gemm)

@@ -82,13 +82,17 @@ template <> struct Vec8<qi::bf16> {
     }
 };
 
+QI_TL_DEFINE(qi_timeline_norm)
+
 template <typename TD, typename TO>
 __global__ void add_rmsnorm_vec_kernel(float* __restrict__ resid, const TD* __restrict__ delta,
                                        int delta_splits, size_t delta_split_stride,
                                        const float* __restrict__ gain, float eps, TO* __restrict__ out,
                                        const int* __restrict__ rows, int hidden, int write_resid) {
     __shared__ float scratch[32];
+    QI_TL_BEGIN();
     qi::pdl_enter();
+    QI_TL_WAKE();
     const int r = blockIdx.x;
     const int s = rows ? rows[r] : r;
     float* xr = resid + (size_t)s * hidden;
@@ -135,6 +139,7 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ resid, const TD* __re
             for (int j = 0; j < 8; ++j) x[j] = x[j] * inv * g[j];
             Vec8<TO>::store(orow + i, x);
         }
+        QI_TL_END(10);
         return;
     }
     float sumsq = 0.f;
@@ -189,7 +194,9 @@ __global__ void add_rmsnorm_cluster_kernel(float* __restrict__ resid, const TD* 
     __shared__ float scratch[32];
     __shared__ float part_sum;
     cg::cluster_group cluster = cg::this_cluster();
+    QI_TL_BEGIN();
     qi::pdl_enter();
+    QI_TL_WAKE();
     const int r = blockIdx.x / kRowCtas, part = (int)cluster.block_rank();
     const int cols = hidden / kRowCtas;                 // of this CTA (the launch checked that it divides)
     const int s = rows ? rows[r] : r;
@@ -240,6 +247,7 @@ __global__ void add_rmsnorm_cluster_kernel(float* __restrict__ resid, const TD* 
         for (int j = 0; j < 8; ++j) x[j] = x[j] * inv * g[j];
         Vec8<TO>::store(orow + i, x);
     }
+    QI_TL_END(11);
 }
 
 // Launch with a cluster of kRowCtas CTAs along x (and the programmatic-serialization attribute, as qi::launch).
@@ -344,3 +352,5 @@ extern "C" int qi_rmsnorm(const void* x, const float* gain, float eps, void* out
     });
     return qi::check_launch("rmsnorm");
 }
+
+QI_TL_EXPORT(qi_timeline_norm)
