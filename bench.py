@@ -2,7 +2,8 @@
 """Decode and prefill throughput of the engine at Qwen3 layer sizes, one GPU.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--model 8b|14b|32b] [--batch B] [--layers L]
-                    [--impl reference] [--skip-points] [--skip-classes] [--skip-mixed] [--only decode|prefill]
+                    [--impl reference] [--skip-points] [--skip-classes] [--skip-mixed] [--only decode|prefill|mixed]
+    python bench.py --timeline [--batch B]      a decode step kernel by kernel (markdown, not the JSON line)
 
 Prints ONE JSON line. `value` is decoded tokens per second at the headline batch
 of the chosen model (8b: 8 requests with 2,048-token prompts in a 4,096-token
@@ -578,7 +579,7 @@ def main() -> int:
         return 0
     points = {}
     for bsz in bench.batches[1:]:
-        r = bench.decode_rate(bsz, min(args.steps, 32), 3)
+        r = bench.decode_rate(bsz, 64, 8)      # their own length: the first steps after the prompts run at the clock the prefill left
         points[f"decode_b{bsz}"] = r["rate"]
         points[f"decode_b{bsz}_frac_hbm"] = round((a["weight_bytes"] + bsz * r["ctx_mid"] * a["kv_bytes_per_token"]) / (r["ms"] * 1e-3) / 1e9 / hbm_peak, 3)
 
