@@ -428,7 +428,7 @@ def timeline_stamps(lib):
         _fields_ = [("t0", C.c_ulonglong), ("tw", C.c_ulonglong), ("td", C.c_ulonglong), ("t1", C.c_ulonglong),
                     ("kind", C.c_int), ("grid", C.c_int), ("cta", C.c_int), ("sm", C.c_int)]
 
-    cap, out = 1 << 17, []
+    cap, out = 1 << 19, []
     for name in ("qi_timeline_norm", "qi_timeline_gemm", "qi_timeline_attention"):
         n, buf = C.c_uint(0), (Stamp * cap)()
         getattr(lib, name)(buf, C.byref(n), 1)

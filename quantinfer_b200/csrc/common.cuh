@@ -106,7 +106,7 @@ int check_launch(const char* what);  // cudaGetLastError -> message
 // records of a step into launches afterwards. Without the flag the macros are empty.
 #ifdef QI_TIMELINE
 struct QiStamp { unsigned long long t0, tw, td, t1; int kind, grid, cta, sm; };
-#define QI_TL_CAP (1 << 17)
+#define QI_TL_CAP (1 << 19)
 __device__ __forceinline__ unsigned long long qi_now() { unsigned long long t; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t)); return t; }
 #define QI_TL_DEFINE(NAME)                                                                                       \
     __device__ QiStamp qi_tl_log[QI_TL_CAP];                                                                     \
