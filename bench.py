@@ -3,7 +3,7 @@
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--model 8b|14b|32b] [--batch B] [--layers L]
                     [--impl reference] [--skip-points] [--skip-classes] [--skip-mixed] [--only decode|prefill|mixed]
-    python bench.py --timeline [--batch B]      a decode step kernel by kernel (markdown, not the JSON line)
+    python bench.py --timeline [--batch B] [--only prefill]     a decode step (or a prefill) kernel by kernel (markdown, not the JSON line)
 
 Prints ONE JSON line. `value` is decoded tokens per second at the headline batch
 of the chosen model (8b: 8 requests with 2,048-token prompts in a 4,096-token
@@ -416,8 +416,9 @@ def mixed_workload(args, entry):
     return out
 
 
-TIMELINE_KINDS = {10: "add + norm", 11: "add + norm (clusters)", 20: "product", 21: "product + SiLU", 30: "decode attention",
-                  31: "range merge"}
+TIMELINE_KINDS = {10: "add + norm", 11: "add + norm (clusters)", 20: "product", 21: "product + SiLU", 25: "product on CTA pairs",
+                  26: "product on CTA pairs + SiLU", 27: "product on CTA pairs + q/k norm, RoPE, cache write", 30: "decode attention",
+                  31: "range merge", 32: "prefill attention"}
 
 
 def timeline_stamps(lib):
@@ -429,7 +430,7 @@ def timeline_stamps(lib):
                     ("kind", C.c_int), ("grid", C.c_int), ("cta", C.c_int), ("sm", C.c_int)]
 
     cap, out = 1 << 19, []
-    for name in ("qi_timeline_norm", "qi_timeline_gemm", "qi_timeline_attention"):
+    for name in ("qi_timeline_norm", "qi_timeline_gemm", "qi_timeline_attention", "qi_timeline_prefill_attention"):
         n, buf = C.c_uint(0), (Stamp * cap)()
         getattr(lib, name)(buf, C.byref(n), 1)
         out += [(s.t0, s.tw, s.td, s.t1, s.kind, s.grid) for s in buf[:min(n.value, cap)]]
@@ -458,29 +459,38 @@ def timeline_launches(stamps):
     return sorted(rows, key=lambda r: r["wake"])
 
 
-def timeline_report(bench, batch):
-    """Markdown: the kernels of one layer of a decode step as they ran in their place (microseconds from the
-    first listed kernel's wake), and the means over two steps by kind and grid. Needs the kernels built with
-    their time stamps (QUANTINFER_B200_TIMELINE=1, which `--timeline` sets before the library is loaded)."""
+def timeline_report(bench, batch, prefill=False):
+    """Markdown: the kernels of one layer of a decode step (or, `prefill`, of the prefill of one prompt) as they
+    ran in their place (microseconds from the first listed kernel's wake), and the means over two steps by kind
+    and grid. Needs the kernels built with their time stamps (QUANTINFER_B200_TIMELINE=1, which `--timeline`
+    sets before the library is loaded)."""
     import collections
 
     from quantinfer_b200 import kernels
     from quantinfer_b200.sampling import GenerationConfig
 
     torch, engine, lib = bench.torch, bench.engine, kernels.library()
-    ids = bench.fill(batch)
-    rows = [(GenerationConfig(max_new_tokens=1 << 20), 0)] * batch
-    hist = engine.decode_on_device(ids, [1 + i for i in range(batch)], 12, rows, bench.sampler)
-    torch.cuda.synchronize()
-    timeline_stamps(lib)                                   # forget the warm-up
-    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    a.record()
-    engine.decode_on_device(ids, hist[-1].tolist(), 2, rows, bench.sampler)
-    b.record()
-    torch.cuda.synchronize()
+    ids = []
+    if prefill:
+        bench.prefill_ms(runs=1, warm=2)
+        timeline_stamps(lib)                               # forget the warm-up
+        ms = bench.prefill_ms(runs=1, warm=1)
+        what = f"Two prefills of one prompt of {bench.prompt_len} tokens: {ms:.3f} ms each with the stamps in"
+    else:
+        ids = bench.fill(batch)
+        rows = [(GenerationConfig(max_new_tokens=1 << 20), 0)] * batch
+        hist = engine.decode_on_device(ids, [1 + i for i in range(batch)], 12, rows, bench.sampler)
+        torch.cuda.synchronize()
+        timeline_stamps(lib)                               # forget the warm-up
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        engine.decode_on_device(ids, hist[-1].tolist(), 2, rows, bench.sampler)
+        b.record()
+        torch.cuda.synchronize()
+        what = f"Two decode steps, batch {batch}: {a.elapsed_time(b) / 2:.3f} ms a step with the stamps in"
     launches = timeline_launches(timeline_stamps(lib))
     name = lambda r: f"{TIMELINE_KINDS.get(r['kind'], r['kind'])}, {r['grid']} CTAs"
-    out = [f"Two decode steps, batch {batch}: {a.elapsed_time(b) / 2:.3f} ms a step with the stamps in; {len(launches)} launches sorted.", "",
+    out = [f"{what}; {len(launches)} launches sorted.", "",
            "One layer from the middle of the second step (us from the first row's wake):", "",
            "| kernel | first CTA starts | wake | first data | first CTA ends | last CTA ends | wake after the kernel before ended | wake to end |",
            "|---|---|---|---|---|---|---|---|"]
@@ -532,7 +542,7 @@ def main() -> int:
     args = ap.parse_args()
     if args.timeline:
         os.environ["QUANTINFER_B200_TIMELINE"] = "1"      # before the library is built and loaded
-        args.only = "decode"
+        args.only = args.only if args.only == "prefill" else "decode"
 
     if args.impl == "reference":
         print(json.dumps({"impl": "reference",
@@ -561,7 +571,7 @@ def main() -> int:
     flops = a["gemm_flops"](T) + a["attn_flops"](T)
 
     if args.timeline:
-        print(timeline_report(bench, args.batch))
+        print(timeline_report(bench, args.batch, prefill=args.only == "prefill"))
         return 0
     # the headline first: the K timed decode steps, before anything else has heated the device
     if args.only != "prefill":

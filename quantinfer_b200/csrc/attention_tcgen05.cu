@@ -253,6 +253,8 @@ struct Bars {
 constexpr int kSmemBytes = kQBytes + kStages * 2 * kKVBytes + 256 /*barriers*/ + 4 * kMaxTableEntries + 1024 /*alignment*/;
 
 
+QI_TL_DEFINE(qi_timeline_prefill_attention)
+
 __global__ void __launch_bounds__(kThreads, 2)
 attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                                       const __grid_constant__ CUtensorMap map_v, qi::bf16* __restrict__ out,
@@ -276,6 +278,7 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
     // The lists of the step (requests, query tiles, block tables) were copied before the step's first
     // kernel began: the CTA reads them, sets up its barriers and its tensor memory while the kernel
     // before this one still runs, and waits for it only before it touches Q, the cache or the output.
+    QI_TL_BEGIN();
     qi::pdl_launch_dependents();
     const int tile = blockIdx.y, h = blockIdx.x;
     const int hk = h / (nq / nkv);
@@ -300,6 +303,8 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
         if (count == 0) {    // nothing of the rows' keys falls into this range: an empty partial
             const int row = threadIdx.x;
             qi::pdl_wait();
+            QI_TL_WAKE();
+            QI_TL_END(32);
             if (row < rows_valid) {
                 float* ml = ws_ml + (((size_t)(q0 + row) * nq + h) * n_ranges + blockIdx.z) * 2;
                 ml[0] = -INFINITY;
@@ -339,6 +344,7 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
     const uint32_t tmem_base = *tmem_slot;
     const uint32_t tmem_s = tmem_base, tmem_o = tmem_base + 64, tmem_p = tmem_base + 192;   // P: two buffers of 32 columns
     qi::pdl_wait();
+    QI_TL_WAKE();
 
     auto give_up = [&]() {
         if (!*abort_flag) {
@@ -558,6 +564,7 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
     }
     tc_fence_before();
     __syncthreads();
+    QI_TL_END(32);
     if (warp == 5) tmem_dealloc(tmem_base, 256);
 }
 
@@ -670,3 +677,5 @@ extern "C" int qi_attention_prefill_tcgen05(const void* q, void* out, const void
     }
     return qi::check_launch("attention_prefill_tcgen05");
 }
+
+QI_TL_EXPORT(qi_timeline_prefill_attention)

@@ -713,6 +713,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
     auto acc_full_bar = [&](int a) { return bars + 8u * (2 * STAGES + a); };
     auto acc_empty_bar = [&](int a) { return bars + 8u * (2 * STAGES + 2 + a); };
 
+    QI_TL_BEGIN();
     qi::pdl_launch_dependents();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t rank = cluster_rank();
@@ -771,6 +772,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
                 }
             }
             qi::pdl_wait();
+            QI_TL_WAKE();
             uint32_t it = 0;
             bool ok = true;
             for (int tile = pair; tile < total_tiles && ok; tile += n_pairs) {
@@ -919,6 +921,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
     }
     tc_fence_before();
     cluster_sync_all();       // neither CTA goes before its partner is done with what it holds
+    QI_TL_END(25 + EPI);
     if (warp == 1) tmem_dealloc_pair(tmem_base, 512);
 }
 

@@ -85,15 +85,19 @@ template <> struct Vec8<qi::bf16> {
 QI_TL_DEFINE(qi_timeline_norm)
 
 template <typename TD, typename TO>
-__global__ void add_rmsnorm_vec_kernel(float* __restrict__ resid, const TD* __restrict__ delta,
+__global__ void __launch_bounds__(512, 3) add_rmsnorm_vec_kernel(float* __restrict__ resid, const TD* __restrict__ delta,
                                        int delta_splits, size_t delta_split_stride,
                                        const float* __restrict__ gain, float eps, TO* __restrict__ out,
-                                       const int* __restrict__ rows, int hidden, int write_resid) {
+                                       const int* __restrict__ rows, int hidden, int write_resid, int n_rows) {
     __shared__ float scratch[32];
     QI_TL_BEGIN();
     qi::pdl_enter();
     QI_TL_WAKE();
-    const int r = blockIdx.x;
+    // A CTA takes rows blockIdx.x, blockIdx.x + gridDim.x, ...: the grid is what is resident at once, three
+    // CTAs of 512 threads an SM (the register bound above). A timeline of the prefill step showed this kernel
+    // at 40 us for a prompt of 2,048 tokens where it moves 100 MB: one CTA a row, and so many registers (all
+    // partial sums of a row held at once) that one CTA filled an SM. Now 24 us; four CTAs an SM spill and take 26.
+    for (int r = blockIdx.x; r < n_rows; r += gridDim.x) {
     const int s = rows ? rows[r] : r;
     float* xr = resid + (size_t)s * hidden;
     const TD* dr = delta ? delta + (size_t)s * hidden : nullptr;
@@ -107,19 +111,9 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ resid, const TD* __re
         if (active) {
             Vec8<float>::load(xr + i, x);
             Vec8<float>::load(gain + i, g);
-            if (dr && delta_splits <= 8) {
-                // all partial sums are requested at once (one round trip), then added in their order
-                float d8[8][8];
-#pragma unroll
-                for (int k = 0; k < 8; ++k)
-                    if (k < delta_splits) Vec8<TD>::load(dr + k * delta_split_stride + i, d8[k]);
-#pragma unroll
-                for (int k = 0; k < 8; ++k)
-                    if (k < delta_splits) {
-#pragma unroll
-                        for (int j = 0; j < 8; ++j) x[j] += d8[k][j];
-                    }
-            } else if (dr) {
+            if (dr) {
+                // (few registers, so that four CTAs of 512 threads share an SM; the cluster kernel below, for few
+                // rows, requests all partial sums at once instead)
 #pragma unroll 4
                 for (int k = 0; k < delta_splits; ++k) {
                     Vec8<TD>::load(dr + k * delta_split_stride + i, d);
@@ -139,8 +133,7 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ resid, const TD* __re
             for (int j = 0; j < 8; ++j) x[j] = x[j] * inv * g[j];
             Vec8<TO>::store(orow + i, x);
         }
-        QI_TL_END(10);
-        return;
+        continue;
     }
     float sumsq = 0.f;
     for (int i = threadIdx.x * 8; i < hidden; i += blockDim.x * 8) {
@@ -176,6 +169,8 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ resid, const TD* __re
         for (int j = 0; j < 8; ++j) x[j] = x[j] * inv * g[j];
         Vec8<TO>::store(orow + i, x);
     }
+    }
+    QI_TL_END(10);
 }
 
 // The same for few rows (a decode step): a row is spread over a thread-block cluster of kRowCtas
@@ -323,10 +318,18 @@ extern "C" int qi_add_rmsnorm(float* resid, const void* delta, int delta_dtype, 
     if (vec) {
         int threads = (hidden / 8 + 31) / 32 * 32;
         if (threads > 512) threads = 512;
+        static int sms = 0;
+        if (!sms) {
+            int dev = 0;
+            cudaGetDevice(&dev);
+            if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
+        }
+        const int resident = sms * (2048 / threads < 3 ? 2048 / threads : 3) * (threads < 512 ? 512 / threads : 1);
+        const int grid = n_rows < resident ? n_rows : resident;
         QI_DISPATCH_DTYPE(dd, TD, {
             QI_DISPATCH_DTYPE(out_dtype, TO, {
-                qi::launch(add_rmsnorm_vec_kernel<TD, TO>, dim3(n_rows), dim3(threads), 0, stream, resid, (const TD*)delta,
-                           delta_splits, (size_t)delta_split_stride, gain, eps, (TO*)out, rows, hidden, write_resid);
+                qi::launch(add_rmsnorm_vec_kernel<TD, TO>, dim3(grid), dim3(threads), 0, stream, resid, (const TD*)delta,
+                           delta_splits, (size_t)delta_split_stride, gain, eps, (TO*)out, rows, hidden, write_resid, n_rows);
             });
         });
         return qi::check_launch("add_rmsnorm");
