@@ -79,6 +79,7 @@ def test_add_rmsnorm(dtype, rows, hidden):
     (64, 1024, 2),        # the most rows and the narrowest rows that take the clusters
     (3, 5120, 16),        # more partial sums than are requested at once
     (65, 4096, 4),        # one row too many for the clusters
+    (1500, 2048, 2),      # more rows than CTAs that stay: each walks several rows
 ])
 def test_add_rmsnorm_takes_split_partials(rows, hidden, splits):
     torch.manual_seed(2)
