@@ -3,7 +3,6 @@ helpers that lay test data out the way the kernels read it (pages, block tables)
 
 from __future__ import annotations
 
-import math
 
 import torch
 

@@ -3,7 +3,6 @@ implementation, the command line's output, long decoding, the first tokens of a
 sequence, batches through the scheduler, and decoding that stays on the device."""
 
 import json
-import os
 import subprocess
 import sys
 from pathlib import Path

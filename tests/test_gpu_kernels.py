@@ -4,7 +4,6 @@ sizes in steps of 16, several page sizes. Inputs are built so that faults show: 
 key that dominates a softmax, a window's edge, values in unused pages that would
 poison a result if read."""
 
-import math
 
 import pytest
 import torch

@@ -1,7 +1,6 @@
 """The engine against the plain implementation: each request alone and whole."""
 
 import pytest
-import torch
 
 from helpers import PAGE_SIZES, TOL_BF16, TOL_F32, max_abs_diff, random_tokens, vocab_of
 from plain.plain_qwen3 import plain_forward, plain_load

@@ -5,7 +5,7 @@ import math
 
 import torch
 
-from helpers import TINY_CONFIGS, make_folder, random_tokens
+from helpers import make_folder, random_tokens
 from plain.plain_qwen3 import (plain_apply_rope, plain_argmax, plain_forward, plain_generate,
                                plain_gqa_attention, plain_linear, plain_load, plain_philox4x32_10,
                                plain_rms_norm, plain_rope_tables, plain_sample, plain_silu_mul, plain_uniform)

@@ -5,7 +5,7 @@ what happens when pages run out."""
 import pytest
 
 from quantinfer_b200.cache import CacheManager, PagedKVNeed
-from quantinfer_b200.engine.scheduler import (CANCELLED, EOS, FAILED, MAX_TOKENS, TIMED_OUT, FailedEvent,
+from quantinfer_b200.engine.scheduler import (CANCELLED, EOS, MAX_TOKENS, TIMED_OUT, FailedEvent,
                                               Scheduler, StoppedEvent, TokenEvent)
 from quantinfer_b200.errors import OutOfPages
 from quantinfer_b200.sampling import GenerationConfig

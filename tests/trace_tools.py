@@ -4,7 +4,6 @@ either through the engine in this process or through bin/trace_run."""
 from __future__ import annotations
 
 import json
-import os
 import random
 import subprocess
 import sys
@@ -12,7 +11,6 @@ import tempfile
 from pathlib import Path
 
 import numpy as np
-import torch
 
 ROOT = Path(__file__).resolve().parent.parent
 
