@@ -176,9 +176,12 @@ class Bench:
         self.prompt_len, self.context = entry["prompt_len"], entry["context"]
         self.batches = [args.batch] + ([] if args.skip_points else [b for b in entry["points"] if b != args.batch])
         self.n_new = args.warmup + args.steps + 2
-        # the end-to-end window is at least 64 steps long, however few steps the device-timed run takes:
-        # the first steps after the prompts still run at the clock the prefill left behind
-        self.n_e2e = max(self.n_new, 64 + args.warmup)
+        # End to end, the first W steps in which the whole batch decodes are warm-up, as they are on the device, and
+        # the window after them is at least 128 steps long, however few steps the device-timed run takes: for some
+        # 70 ms after the prompts the chip stays at the clock the prefill left it at under the power cap (at
+        # Qwen3-8B sizes 7 steps of 4.1 ms, then 11 of 3.8, then 3.53), which the device-timed run does not see,
+        # because the capture of its graph lies between its prompts and its steps
+        self.n_e2e = max(self.n_new, 128) + args.warmup
         max_b = max(self.batches)
         # a request decodes warm-up + timed steps on the device, or (end to end) as many steps as it takes until
         # the last request of its batch has joined plus the timed ones: room for the longer of the two
@@ -251,9 +254,10 @@ class Bench:
 
     # ---- end to end through the Python entry point ---------------------------------------
     def e2e(self, model, batch):
-        """Rate over the steps in which the whole batch decodes, by the times at which tokens reach the host."""
-        # requests join one prompt after the other: each decodes `batch` steps more than the timed ones, so that
-        # the window in which all of them decode is as long as the device-timed run
+        """Rate over the steps in which the whole batch decodes, after W such steps of warm-up, by the times at
+        which tokens reach the host."""
+        # requests join one prompt after the other: each decodes `batch` steps more than the warm-up and the timed
+        # ones, so that the window in which all of them decode is that long
         engine, n_new = self.engine, min(self.n_e2e + batch, self.context - self.prompt_len)
         prompts = [self.prompt() for _ in range(batch)]
         # warm-up through the same entry point (W decode steps): graphs are captured, buffers pinned
@@ -265,24 +269,30 @@ class Bench:
         # bytes a decode step of the full batch copies host -> device: its packed batch arrays (token ids,
         # positions, lengths, slots, block tables)
         h2d = max([g["meta"].numel() * 4 for (b, _), g in engine._graphs.items() if b == batch] or [engine.h2d_bytes_max])
-        # the window in which the whole batch decodes: after the last request's first token, up to the
-        # step in which the first request ends
-        seen, t_all_first, t_end, after = set(), None, None, 0
+        # the events of one step arrive together: steps = [time, events, one of them a stop]
+        steps = []
         for t, rid, stop in stamps:
-            if t_all_first is None:
-                seen.add(rid)
+            if not steps or t - steps[-1][0] > 1e-4:
+                steps.append([t, 0, False, set()])
+            steps[-1][1] += 1
+            steps[-1][2] |= stop is not None
+            steps[-1][3].add(rid)
+        # the window in which the whole batch decodes: from the step that gave the last request's first token and
+        # the W warm-up steps after it, up to the step in which the first request ends
+        seen, first, last = set(), None, None
+        for i, (_, _, stopped, rids) in enumerate(steps):
+            if first is None:
+                seen |= rids
                 if len(seen) == batch:
-                    t_all_first = t
-            elif t - t_all_first < 1e-4:                 # the events of one step arrive together:
-                continue                                 # the rest of the step that gave the last first token
-            elif t_end is None or t - t_end < 1e-4:
-                after += 1
-                if stop is not None and t_end is None:
-                    t_end = t
-        ok = t_all_first is not None and t_end is not None and after >= batch
-        return {"value": after / (t_end - t_all_first) if ok else None, "unit": "tokens/s", "h2d_bytes_per_step": h2d,
-                "d2h_bytes_per_step": 4 * batch + 4, "steps": after // max(batch, 1) if ok else 0,
-                "ms_per_step": (t_end - t_all_first) * 1e3 / (after / batch) if ok else None}
+                    first = i + self.args.warmup
+            elif stopped and last is None:
+                last = i
+        ok = first is not None and last is not None and last - first >= 8
+        tokens = sum(n for _, n, _, _ in steps[first + 1:last + 1]) if ok else 0
+        span = steps[last][0] - steps[first][0] if ok else None
+        return {"value": tokens / span if ok else None, "unit": "tokens/s", "h2d_bytes_per_step": h2d,
+                "d2h_bytes_per_step": 4 * batch + 4, "steps": last - first if ok else 0, "warmup": self.args.warmup,
+                "ms_per_step": span * 1e3 / (last - first) if ok else None}
 
     # ---- the step by kernel class ---------------------------------------------------------------
     def classes(self, full_decode_ms, full_prefill_ms, ctx_mid, peaks_):
